@@ -1,0 +1,426 @@
+// CPU oracle for the epsilon self-join (TEST INFRASTRUCTURE, not product code).
+//
+// This file restates, on the CPU, the algorithm that the FaSTED reference runs
+// on the GPU for its FP16-in / FP32-accumulate self-join, plus an FP64
+// brute-force join used as ground truth and as the timed CPU baseline.
+// Only tests, the smoke check and the benchmark's cpu_baseline / reference
+// arm may load this library; the product library never links or calls it.
+//
+// Every function names the reference source lines it follows (paths are
+// relative to the reference project's root).
+//
+// Build: see oracle/Makefile (g++ -O2 -fopenmp -frounding-math).
+
+#include <cfenv>
+#include <cmath>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <fstream>
+#include <random>
+#include <sstream>
+#include <string>
+#include <vector>
+
+#include <omp.h>
+
+#if defined(__x86_64__)
+#define ORACLE_CLONES __attribute__((target_clones("default", "avx2,fma", "avx512f")))
+#else
+#define ORACLE_CLONES
+#endif
+
+namespace {
+
+// IEEE binary16 -> binary32, exact (every half is representable as a float).
+inline float half_bits_to_float(uint16_t h) {
+    const uint32_t sign = (uint32_t)(h & 0x8000u) << 16;
+    uint32_t exp = (h >> 10) & 0x1fu;
+    uint32_t man = h & 0x3ffu;
+    uint32_t bits;
+    if (exp == 0) {
+        if (man == 0) {
+            bits = sign;
+        } else {  // subnormal half: normalise
+            int e = -1;
+            do {
+                man <<= 1;
+                ++e;
+            } while ((man & 0x400u) == 0);
+            man &= 0x3ffu;
+            bits = sign | ((uint32_t)(127 - 15 - e) << 23) | (man << 13);
+        }
+    } else if (exp == 31) {
+        bits = sign | 0x7f800000u | (man << 13);
+    } else {
+        bits = sign | ((exp + 127 - 15) << 23) | (man << 13);
+    }
+    float f;
+    std::memcpy(&f, &bits, 4);
+    return f;
+}
+
+// binary32 -> binary16, round-to-nearest-even. The reference converts
+// double -> float -> half with the default (nearest) rounding of its
+// half_float library: source/DataLoader/PointListBuilder.hpp:57-66.
+inline uint16_t float_to_half_bits_rn(float f) {
+    uint32_t x;
+    std::memcpy(&x, &f, 4);
+    const uint16_t sign = (uint16_t)((x >> 16) & 0x8000u);
+    x &= 0x7fffffffu;
+    if (x >= 0x7f800000u) {  // inf / nan
+        return (uint16_t)(sign | 0x7c00u | ((x > 0x7f800000u) ? 0x200u : 0u));
+    }
+    if (x >= 0x477ff000u) {  // rounds to >= 65520 -> inf
+        return (uint16_t)(sign | 0x7c00u);
+    }
+    if (x < 0x33000001u) {  // rounds to zero (<= 2^-25)
+        return sign;
+    }
+    int exp = (int)(x >> 23) - 127;
+    uint32_t man = (x & 0x7fffffu) | 0x800000u;
+    int shift;
+    uint32_t hexp;
+    if (exp < -14) {  // subnormal half
+        shift = 13 + (-14 - exp);
+        hexp = 0;
+    } else {
+        shift = 13;
+        hexp = (uint32_t)(exp + 15);
+    }
+    uint32_t q = man >> shift;
+    const uint32_t rem = man & ((1u << shift) - 1u);
+    const uint32_t halfway = 1u << (shift - 1);
+    if (rem > halfway || (rem == halfway && (q & 1u))) {
+        ++q;
+    }
+    uint32_t out;
+    if (hexp == 0) {
+        out = q;  // may carry into the exponent field, which is correct
+    } else {
+        out = ((hexp - 1) << 10) + q;  // q carries the implicit bit (0x400)
+    }
+    return (uint16_t)(sign | out);
+}
+
+struct RoundTowardZero {
+    int saved;
+    RoundTowardZero() : saved(fegetround()) { fesetround(FE_TOWARDZERO); }
+    ~RoundTowardZero() { fesetround(saved); }
+};
+
+}  // namespace
+
+extern "C" {
+
+// ---------------------------------------------------------------------------
+// Dataset construction
+// ---------------------------------------------------------------------------
+
+// Seeded synthetic generator. Follows
+// source/DataLoader/ExponentialPointGenerator.hpp:11 (seed 2137834274),
+// :22-31 (std::mt19937 + std::exponential_distribution<double>(lambda)),
+// :42-52 (row-major draw order, rejection of values outside [0, maxValue]),
+// and the double -> float -> half rounding of PointListBuilder.hpp:57-66.
+// `out` receives n rows of `ld` halfs; columns d..ld-1 are +0
+// (PointListBuilder.hpp:34-39, 175).
+void oracle_gen_exponential(int64_t n, int64_t d, double lambda, double max_value, uint16_t* out,
+                            int64_t ld) {
+    std::mt19937 gen(2137834274u);
+    std::exponential_distribution<double> dis(lambda);
+    for (int64_t i = 0; i < n; ++i) {
+        uint16_t* row = out + i * ld;
+        for (int64_t j = 0; j < d; ++j) {
+            double v;
+            do {
+                v = dis(gen);
+            } while (v < 0.0 || v > max_value);
+            row[j] = float_to_half_bits_rn(static_cast<float>(v));
+        }
+        for (int64_t j = d; j < ld; ++j) row[j] = 0;
+    }
+}
+
+// double[] -> half bits with the reference's two-step rounding
+// (PointListBuilder.hpp:63-65).
+void oracle_double_to_half(const double* in, int64_t count, uint16_t* out) {
+    for (int64_t i = 0; i < count; ++i) out[i] = float_to_half_bits_rn(static_cast<float>(in[i]));
+}
+
+void oracle_half_to_float(const uint16_t* in, int64_t count, float* out) {
+    for (int64_t i = 0; i < count; ++i) out[i] = half_bits_to_float(in[i]);
+}
+
+// CSV reader with the semantics of source/DataLoader/FilePointGenerator.hpp:33-56
+// (getline per row, split on ',', std::stod per token) and the shape rule of
+// PointListBuilder.hpp:154-163 (first row fixes D; a different length is an
+// error). Two-call protocol: with out == nullptr only *n and *d are filled.
+// Returns 0 on success, 1 cannot open, 2 parse error, 3 ragged row, 4 empty.
+int oracle_read_csv(const char* path, int64_t* n, int64_t* d, uint16_t* out, int64_t ld) {
+    std::ifstream f(path);
+    if (!f.is_open()) return 1;
+    std::string line;
+    int64_t rows = 0, dims = -1;
+    while (std::getline(f, line)) {
+        std::stringstream ss(line);
+        std::string tok;
+        int64_t c = 0;
+        while (std::getline(ss, tok, ',')) {
+            double v;
+            try {
+                v = std::stod(tok);
+            } catch (...) {
+                return 2;
+            }
+            if (out) {
+                if (dims >= 0 && c >= dims) return 3;
+                out[rows * ld + c] = float_to_half_bits_rn(static_cast<float>(v));
+            }
+            ++c;
+        }
+        if (dims < 0) {
+            dims = c;
+        } else if (c != dims) {
+            return 3;
+        }
+        if (out) {
+            for (int64_t j = c; j < ld; ++j) out[rows * ld + j] = 0;
+        }
+        ++rows;
+    }
+    if (rows == 0) return 4;
+    *n = rows;
+    *d = dims;
+    return 0;
+}
+
+// FNV-1a (64-bit) over 16-bit words, each word xored whole into the hash
+// before the multiply. Used only to pin generator output against a hash
+// obtained from the reference's own loader headers.
+uint64_t oracle_fnv1a64_u16(const uint16_t* data, int64_t count, uint64_t seed) {
+    uint64_t h = seed ? seed : 1469598103934665603ull;
+    for (int64_t i = 0; i < count; ++i) {
+        h ^= (uint64_t)data[i];
+        h *= 1099511628211ull;
+    }
+    return h;
+}
+
+// ---------------------------------------------------------------------------
+// Row norms
+// ---------------------------------------------------------------------------
+
+// s_i = sequential round-toward-zero sum over column pairs of RZ(x^2 + y^2),
+// squares exact in FP32. Follows source/sumSquared.cuh:34-40 (SumSquareHalf2:
+// half2 -> float2, square, __fadd_rz) and :59-72 (running __fadd_rz in
+// ascending k, one accumulator per point).
+void oracle_row_norms(const uint16_t* pts, int64_t n, int64_t d, int64_t ld, float* out) {
+#pragma omp parallel
+    {
+        RoundTowardZero rz;
+#pragma omp for schedule(static)
+        for (int64_t i = 0; i < n; ++i) {
+            const uint16_t* row = pts + i * ld;
+            volatile float acc = 0.0f;
+            for (int64_t k = 0; k < d; k += 2) {
+                const float x = half_bits_to_float(row[k]);
+                const float y = (k + 1 < d) ? half_bits_to_float(row[k + 1]) : 0.0f;
+                volatile float xx = x * x;  // exact: 11-bit x 11-bit significands
+                volatile float yy = y * y;
+                volatile float p = xx + yy;  // RZ
+                acc = acc + p;               // RZ
+            }
+            out[i] = acc;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// The reference's FP16 -> FP32 join, restated
+// ---------------------------------------------------------------------------
+
+// Gram entry model: exact FP16 x FP16 products, summed per ascending 16-wide
+// k-slice and added to a single FP32 accumulator with truncation. Follows
+// source/ptxMma.cuh:173-191 (one mma.m16n8k16 f16 x f16 -> f32 per slice) and
+// source/findPairs.cuh:276-284, 489 (slices consumed in ascending k). The
+// rounding inside a tensor-core instruction is hardware-defined; truncation
+// is what the reference's paper states for its GPU, and any other choice
+// moves d^2 by a few FP32 ulps of |p|^2, which the comparison band absorbs.
+static inline float gram_entry(const float* a, const float* b, int64_t d) {
+    float acc = 0.0f;
+    for (int64_t k0 = 0; k0 < d; k0 += 16) {
+        const int64_t k1 = (k0 + 16 < d) ? k0 + 16 : d;
+        double s = 0.0;
+        for (int64_t k = k0; k < k1; ++k) s += (double)a[k] * (double)b[k];
+        volatile double t = (double)acc + s;  // RZ in double
+        volatile float r = (float)t;          // RZ to float (truncations compose)
+        acc = r;
+    }
+    return acc;
+}
+
+// Epilogue and output rule. Follows source/warpMma.cuh:239-242
+// (d2 = (s_q + s_c) - 2*a in FP32, round-to-nearest), :257 (hit iff
+// d2 <= eps2, inclusive), :259 (only real, un-padded indices),
+// source/findPairs.cuh:678 (eps2 = float(eps*eps), product formed in double)
+// and source/pair.cuh:39-45 (row-major order). Self pairs and both
+// orientations are produced, like the reference.
+//
+// Query rows [q_begin, q_end) are joined against all n candidates. `norms` are
+// the n row norms from oracle_row_norms. pairs_out (2 ints per pair) and
+// d2_out may be null; at most `capacity` pairs are stored; the return value
+// is the number found.
+uint64_t oracle_join_fp16_fp32(const uint16_t* pts, int64_t n, int64_t d, int64_t ld,
+                               const float* norms, double eps, int64_t q_begin, int64_t q_end,
+                               int32_t* pairs_out, float* d2_out, uint64_t capacity) {
+    const float eps2 = (float)(eps * eps);
+    std::vector<float> f((size_t)n * (size_t)d);
+    for (int64_t i = 0; i < n; ++i)
+        for (int64_t k = 0; k < d; ++k) f[(size_t)i * d + k] = half_bits_to_float(pts[i * ld + k]);
+
+    const int64_t rows = q_end - q_begin;
+    std::vector<std::vector<int32_t>> hit_c((size_t)rows);
+    std::vector<std::vector<float>> hit_d((size_t)rows);
+#pragma omp parallel
+    {
+        std::vector<float> g((size_t)n);
+#pragma omp for schedule(dynamic, 8)
+        for (int64_t r = 0; r < rows; ++r) {
+            const int64_t i = q_begin + r;
+            const float* a = &f[(size_t)i * d];
+            {
+                // The Gram model accumulates with truncation ...
+                RoundTowardZero rz;
+                for (int64_t j = 0; j < n; ++j) g[(size_t)j] = gram_entry(a, &f[(size_t)j * d], d);
+            }
+            // ... the epilogue rounds to nearest.
+            for (int64_t j = 0; j < n; ++j) {
+                volatile float t = norms[i] + norms[j];
+                volatile float d2 = t - 2.0f * g[(size_t)j];
+                if (d2 <= eps2) {
+                    hit_c[(size_t)r].push_back((int32_t)j);
+                    hit_d[(size_t)r].push_back((float)d2);
+                }
+            }
+        }
+    }
+    uint64_t found = 0;
+    for (int64_t r = 0; r < rows; ++r) {
+        for (size_t h = 0; h < hit_c[(size_t)r].size(); ++h) {
+            if (found < capacity) {
+                if (pairs_out) {
+                    pairs_out[2 * found] = (int32_t)(q_begin + r);
+                    pairs_out[2 * found + 1] = hit_c[(size_t)r][h];
+                }
+                if (d2_out) d2_out[found] = hit_d[(size_t)r][h];
+            }
+            ++found;
+        }
+    }
+    return found;
+}
+
+// ---------------------------------------------------------------------------
+// FP64 brute force (ground truth and timed CPU baseline)
+// ---------------------------------------------------------------------------
+
+ORACLE_CLONES
+static void f64_block(const float* q, const float* c, int64_t d, int64_t nq, int64_t nc,
+                      double* out /* nq x nc */) {
+    for (int64_t a = 0; a < nq; ++a) {
+        const float* x = q + a * d;
+        for (int64_t b = 0; b < nc; ++b) {
+            const float* y = c + b * d;
+            double s = 0.0;
+#pragma omp simd reduction(+ : s)
+            for (int64_t k = 0; k < d; ++k) {
+                const double t = (double)x[k] - (double)y[k];
+                s += t * t;
+            }
+            out[a * nc + b] = s;
+        }
+    }
+}
+
+// Direct-form sum_k (x_k - y_k)^2 in FP64 over the FP16-rounded inputs,
+// hit iff d2 <= eps*eps (inclusive, like source/warpMma.cuh:257), every
+// ordered pair including the diagonal (like the reference). The reference has
+// no CPU join; its FP64 checker script (tests/python/pairs/pairs.py:14-29)
+// uses the expanded form and a strict '<' and is not followed here.
+//
+// Query rows [q_begin, q_end) against all n candidates, all OpenMP threads,
+// row-major output. d2_out receives the FP64 squared distances of the stored
+// pairs. Returns the number found.
+uint64_t oracle_join_fp64(const uint16_t* pts, int64_t n, int64_t d, int64_t ld, double eps,
+                          int64_t q_begin, int64_t q_end, int32_t* pairs_out, double* d2_out,
+                          uint64_t capacity) {
+    const double eps2 = eps * eps;
+    std::vector<float> f((size_t)n * (size_t)d);
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < n; ++i)
+        for (int64_t k = 0; k < d; ++k) f[(size_t)i * d + k] = half_bits_to_float(pts[i * ld + k]);
+
+    const int64_t rows = q_end - q_begin;
+    const int64_t QB = 8, CB = 64;
+    const int64_t nqb = (rows + QB - 1) / QB;
+    std::vector<std::vector<int32_t>> hit_c((size_t)rows);
+    std::vector<std::vector<double>> hit_d((size_t)rows);
+#pragma omp parallel
+    {
+        std::vector<double> blk((size_t)(QB * CB));
+#pragma omp for schedule(dynamic, 1)
+        for (int64_t qb = 0; qb < nqb; ++qb) {
+            const int64_t r0 = qb * QB;
+            const int64_t nq = (r0 + QB <= rows) ? QB : rows - r0;
+            for (int64_t c0 = 0; c0 < n; c0 += CB) {
+                const int64_t nc = (c0 + CB <= n) ? CB : n - c0;
+                f64_block(&f[(size_t)(q_begin + r0) * d], &f[(size_t)c0 * d], d, nq, nc,
+                          blk.data());
+                for (int64_t a = 0; a < nq; ++a)
+                    for (int64_t b = 0; b < nc; ++b) {
+                        const double v = blk[(size_t)(a * nc + b)];
+                        if (v <= eps2) {
+                            hit_c[(size_t)(r0 + a)].push_back((int32_t)(c0 + b));
+                            hit_d[(size_t)(r0 + a)].push_back(v);
+                        }
+                    }
+            }
+        }
+    }
+    uint64_t found = 0;
+    for (int64_t r = 0; r < rows; ++r) {
+        for (size_t h = 0; h < hit_c[(size_t)r].size(); ++h) {
+            if (found < capacity) {
+                if (pairs_out) {
+                    pairs_out[2 * found] = (int32_t)(q_begin + r);
+                    pairs_out[2 * found + 1] = hit_c[(size_t)r][h];
+                }
+                if (d2_out) d2_out[found] = hit_d[(size_t)r][h];
+            }
+            ++found;
+        }
+    }
+    return found;
+}
+
+// FP64 squared distances for an explicit list of pairs (used to apply the
+// comparison band |d2 - eps^2| <= band * eps^2 to pairs on which two FP32
+// implementations disagree).
+void oracle_pair_d2_fp64(const uint16_t* pts, int64_t d, int64_t ld, const int32_t* pairs,
+                         int64_t npairs, double* out) {
+#pragma omp parallel for schedule(static)
+    for (int64_t p = 0; p < npairs; ++p) {
+        const uint16_t* x = pts + (int64_t)pairs[2 * p] * ld;
+        const uint16_t* y = pts + (int64_t)pairs[2 * p + 1] * ld;
+        double s = 0.0;
+        for (int64_t k = 0; k < d; ++k) {
+            const double t = (double)half_bits_to_float(x[k]) - (double)half_bits_to_float(y[k]);
+            s += t * t;
+        }
+        out[p] = s;
+    }
+}
+
+int oracle_num_threads(void) { return omp_get_max_threads(); }
+
+}  // extern "C"
