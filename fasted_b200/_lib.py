@@ -1,0 +1,226 @@
+"""ctypes binding of the native library's context API (include/fasted.h, layer 2).
+
+The library is CUDA-only: loading works anywhere (so that symbol checks can run
+on a machine without a GPU), every compute call fails loudly without an sm_100
+device.  There is no CPU fallback in this package.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "lib", "libfasted.so")
+LEGACY_LIB_PATH = os.path.join(_HERE, "lib", "main.so")
+
+_i64 = ctypes.c_int64
+_u64 = ctypes.c_uint64
+_vp = ctypes.c_void_p
+
+OK, EINVAL, ECUDA, ENODEV, ESTATE, EKERNEL, EIO = 0, -1, -2, -3, -4, -5, -6
+JOIN_DIST2, JOIN_NO_SORT, JOIN_KEEP_NORMS = 1, 2, 4
+
+
+class FastedError(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__(f"fasted error {code}: {message}")
+        self.code = code
+
+
+class JoinStats(ctypes.Structure):
+    _fields_ = [
+        ("pairs_found", ctypes.c_ulonglong),
+        ("pairs_stored", ctypes.c_ulonglong),
+        ("norms_ms", ctypes.c_double),
+        ("join_ms", ctypes.c_double),
+        ("kernel_ms", ctypes.c_double),
+        ("sort_ms", ctypes.c_double),
+        ("status", ctypes.c_ulonglong),
+        ("tiles_m", ctypes.c_int),
+        ("tiles_n", ctypes.c_int),
+        ("grid", ctypes.c_int),
+    ]
+
+    def as_dict(self) -> dict:
+        return {k: getattr(self, k) for k, _ in self._fields_}
+
+
+# Every symbol include/fasted.h declares, layer 1 and layer 2.
+DECLARED_SYMBOLS = [
+    "runFromExponentialDataset", "runFromFile", "reRun", "releaseResources",
+    "fasted_last_error", "fasted_create", "fasted_destroy", "fasted_set_stream",
+    "fasted_set_points_host_f16", "fasted_set_points_device_f16", "fasted_generate_exponential",
+    "fasted_points_info", "fasted_get_points_host_f16", "fasted_row_norms", "fasted_get_norms",
+    "fasted_join", "fasted_get_pairs", "fasted_pairs_device", "fasted_brute_force_f64", "fasted_set_option",
+    "fasted_dataset_exponential_f16", "fasted_dataset_csv_shape", "fasted_dataset_csv_f16",
+]
+
+_lib = None
+
+
+def load() -> ctypes.CDLL:
+    """Load libfasted.so; raises if it has not been built (python -m fasted_b200.build)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise FileNotFoundError(
+            f"{LIB_PATH} is missing: build it with `python -m fasted_b200.build` (nvcc, sm_100a). "
+            "This package has no fallback implementation.")
+    L = ctypes.CDLL(LIB_PATH)
+    L.fasted_last_error.restype = ctypes.c_char_p
+    L.fasted_create.argtypes = [ctypes.c_int, ctypes.POINTER(_vp)]
+    L.fasted_destroy.argtypes = [_vp]
+    L.fasted_destroy.restype = None
+    L.fasted_set_stream.argtypes = [_vp, _vp]
+    L.fasted_set_points_host_f16.argtypes = [_vp, _vp, _i64, _i64, _i64]
+    L.fasted_set_points_device_f16.argtypes = [_vp, _vp, _i64, _i64, _i64]
+    L.fasted_generate_exponential.argtypes = [_vp, _i64, _i64, ctypes.c_double, ctypes.c_double, _u64]
+    L.fasted_points_info.argtypes = [_vp, ctypes.POINTER(_vp), ctypes.POINTER(_i64), ctypes.POINTER(_i64),
+                                     ctypes.POINTER(_i64)]
+    L.fasted_get_points_host_f16.argtypes = [_vp, _vp, _i64]
+    L.fasted_row_norms.argtypes = [_vp, ctypes.POINTER(ctypes.c_double)]
+    L.fasted_get_norms.argtypes = [_vp, _vp]
+    L.fasted_join.argtypes = [_vp, ctypes.c_double, _i64, _i64, _u64, ctypes.c_uint, ctypes.POINTER(JoinStats)]
+    L.fasted_get_pairs.argtypes = [_vp, _u64, _u64, _vp, _vp]
+    L.fasted_pairs_device.argtypes = [_vp, ctypes.POINTER(_vp), ctypes.POINTER(_vp)]
+    L.fasted_brute_force_f64.argtypes = [_vp, _vp, ctypes.c_int, ctypes.c_double, _vp]
+    L.fasted_set_option.argtypes = [_vp, ctypes.c_char_p, _i64]
+    L.fasted_dataset_exponential_f16.argtypes = [_i64, _i64, ctypes.c_double, ctypes.c_double, _vp, _i64]
+    L.fasted_dataset_csv_shape.argtypes = [ctypes.c_char_p, ctypes.POINTER(_i64), ctypes.POINTER(_i64)]
+    L.fasted_dataset_csv_f16.argtypes = [ctypes.c_char_p, _vp, _i64, _i64, _i64]
+    _lib = L
+    return L
+
+
+def _check(rc: int) -> None:
+    if rc != OK:
+        raise FastedError(rc, load().fasted_last_error().decode(errors="replace"))
+
+
+def dataset_exponential(n: int, d: int, lam: float = 40.0, max_value: float = 10.0) -> np.ndarray:
+    """The reference's seeded synthetic dataset (host generator), binary16 bit patterns of shape (n, d)."""
+    out = np.empty((n, d), dtype=np.uint16)
+    _check(load().fasted_dataset_exponential_f16(n, d, lam, max_value, out.ctypes.data_as(_vp), d))
+    return out
+
+
+def dataset_csv(path: str) -> np.ndarray:
+    """CSV dataset with the reference's parsing rules, binary16 bit patterns of shape (n, d)."""
+    n, d = _i64(), _i64()
+    _check(load().fasted_dataset_csv_shape(path.encode(), ctypes.byref(n), ctypes.byref(d)))
+    out = np.empty((n.value, d.value), dtype=np.uint16)
+    _check(load().fasted_dataset_csv_f16(path.encode(), out.ctypes.data_as(_vp), n.value, d.value, d.value))
+    return out
+
+
+class SelfJoin:
+    """One context = one GPU, one resident dataset, repeated joins (the reference's run / reRun cycle)."""
+
+    def __init__(self, device: int = 0):
+        self._L = load()
+        h = _vp()
+        _check(self._L.fasted_create(device, ctypes.byref(h)))
+        self._h = h
+        self.device = device
+        self._keepalive = None
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            self._L.fasted_destroy(self._h)
+            self._h = None
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # -- dataset ---------------------------------------------------------
+    def set_points(self, pts: np.ndarray, d: int | None = None) -> None:
+        """pts: (n, ld) binary16 (dtype float16 or uint16 bit patterns) on the host."""
+        if pts.dtype == np.float16:
+            pts = pts.view(np.uint16)
+        assert pts.dtype == np.uint16 and pts.ndim == 2
+        pts = np.ascontiguousarray(pts)
+        n, ld = pts.shape
+        d = ld if d is None else d
+        _check(self._L.fasted_set_points_host_f16(self._h, pts.ctypes.data_as(_vp), n, d, ld))
+
+    def set_points_ptr(self, host_ptr: int, n: int, d: int, ld: int) -> None:
+        """Raw host pointer variant (e.g. a pinned torch tensor's data_ptr())."""
+        _check(self._L.fasted_set_points_host_f16(self._h, _vp(host_ptr), n, d, ld))
+
+    def set_points_device(self, dev_ptr: int, n: int, d: int, ld: int, keepalive=None) -> None:
+        self._keepalive = keepalive
+        _check(self._L.fasted_set_points_device_f16(self._h, _vp(dev_ptr), n, d, ld))
+
+    def generate_exponential(self, n: int, d: int, lam: float = 40.0, max_value: float = 10.0,
+                             seed: int = 2137834274) -> None:
+        _check(self._L.fasted_generate_exponential(self._h, n, d, lam, max_value, seed))
+
+    def points_info(self) -> tuple[int, int, int, int]:
+        dev, n, d, ld = _vp(), _i64(), _i64(), _i64()
+        _check(self._L.fasted_points_info(self._h, ctypes.byref(dev), ctypes.byref(n), ctypes.byref(d),
+                                          ctypes.byref(ld)))
+        return int(dev.value or 0), n.value, d.value, ld.value
+
+    def get_points(self) -> np.ndarray:
+        _, n, d, _ = self.points_info()
+        out = np.empty((n, d), dtype=np.uint16)
+        _check(self._L.fasted_get_points_host_f16(self._h, out.ctypes.data_as(_vp), d))
+        return out
+
+    def get_points_into(self, host_ptr: int, ld_host: int) -> None:
+        _check(self._L.fasted_get_points_host_f16(self._h, _vp(host_ptr), ld_host))
+
+    # -- compute ---------------------------------------------------------
+    def row_norms(self) -> tuple[np.ndarray, float]:
+        ms = ctypes.c_double()
+        _check(self._L.fasted_row_norms(self._h, ctypes.byref(ms)))
+        _, n, _, _ = self.points_info()
+        out = np.empty(n, dtype=np.float32)
+        _check(self._L.fasted_get_norms(self._h, out.ctypes.data_as(_vp)))
+        return out, ms.value
+
+    def row_norms_timed(self) -> float:
+        ms = ctypes.c_double()
+        _check(self._L.fasted_row_norms(self._h, ctypes.byref(ms)))
+        return ms.value
+
+    def join(self, eps: float, q_begin: int = 0, q_end: int = -1, capacity: int = 0, flags: int = 0) -> JoinStats:
+        st = JoinStats()
+        _check(self._L.fasted_join(self._h, float(eps), q_begin, q_end, capacity, flags, ctypes.byref(st)))
+        self._last = st
+        self._last_dist = bool(flags & JOIN_DIST2)
+        return st
+
+    def pairs(self, with_dist2: bool = False):
+        st = self._last
+        m = int(st.pairs_stored)
+        pairs = np.empty((m, 2), dtype=np.int32)
+        d2 = np.empty(m, dtype=np.float32) if with_dist2 else None
+        _check(self._L.fasted_get_pairs(self._h, 0, m, pairs.ctypes.data_as(_vp),
+                                        d2.ctypes.data_as(_vp) if with_dist2 else None))
+        return (pairs, d2) if with_dist2 else pairs
+
+    def pairs_into(self, host_ptr: int, count: int) -> None:
+        _check(self._L.fasted_get_pairs(self._h, 0, count, _vp(host_ptr), None))
+
+    def brute_force_counts(self, rows, eps: float) -> np.ndarray:
+        rows = np.ascontiguousarray(rows, dtype=np.int32)
+        out = np.zeros(len(rows), dtype=np.uint64)
+        _check(self._L.fasted_brute_force_f64(self._h, rows.ctypes.data_as(_vp), len(rows), float(eps),
+                                              out.ctypes.data_as(_vp)))
+        return out
+
+    def set_option(self, name: str, value: int) -> None:
+        _check(self._L.fasted_set_option(self._h, name.encode(), value))

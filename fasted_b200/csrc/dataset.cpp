@@ -1,0 +1,167 @@
+#include "dataset.hpp"
+
+#include <cerrno>
+#include <cstdlib>
+#include <cstring>
+#include <fstream>
+#include <ios>
+#include <random>
+#include <stdexcept>
+
+#include <omp.h>
+
+namespace fasted {
+
+uint16_t float_to_half_rn(float f) {
+    uint32_t u;
+    std::memcpy(&u, &f, sizeof(u));
+    const uint32_t sign = (u >> 16) & 0x8000u;
+    const uint32_t abs = u & 0x7fffffffu;
+    if (abs > 0x7f800000u) return static_cast<uint16_t>(sign | 0x7e00u);   // NaN
+    if (abs >= 0x477ff000u) return static_cast<uint16_t>(sign | 0x7c00u);  // >= 65520 or inf
+    if (abs < 0x38800000u) {
+        // Below the smallest normal half (2^-14): result = nearest multiple of 2^-24.
+        // Adding 0.5f puts that multiple's integer count into the low mantissa bits
+        // of a float in [0.5, 1), with the FPU doing the round-to-nearest-even.
+        float a;
+        std::memcpy(&a, &abs, sizeof(a));
+        volatile float t = a + 0.5f;  // ulp of t is 2^-24
+        float tv = t;
+        uint32_t tb;
+        std::memcpy(&tb, &tv, sizeof(tb));
+        return static_cast<uint16_t>(sign | (tb - 0x3f000000u));
+    }
+    // Normal half: drop 13 mantissa bits with round-to-nearest-even, rebias the exponent.
+    const uint32_t lsb = (abs >> 13) & 1u;
+    const uint32_t rounded = abs + 0xfffu + lsb;
+    return static_cast<uint16_t>(sign | ((rounded - 0x38000000u) >> 13));
+}
+
+HostDataset make_exponential_dataset(int64_t n, int64_t d, double lambda, double max_value) {
+    if (n <= 0 || d <= 0) throw std::runtime_error("No points were generated.");
+    HostDataset ds;
+    ds.n = n;
+    ds.d = d;
+    ds.name = "Exponential_" + std::to_string(n) + "_" + std::to_string(d) + "_" + std::to_string(lambda);
+    ds.values.resize(static_cast<size_t>(n) * static_cast<size_t>(d));
+    std::mt19937 engine(2137834274u);
+    std::exponential_distribution<double> dist(lambda);
+    uint16_t* out = ds.values.data();
+    const size_t total = ds.values.size();
+    for (size_t i = 0; i < total; ++i) {
+        double v = dist(engine);
+        while (v < 0.0 || v > max_value) v = dist(engine);
+        out[i] = float_to_half_rn(static_cast<float>(v));
+    }
+    return ds;
+}
+
+std::string dataset_name_from_path(const std::string& path) {
+    const size_t slash = path.find_last_of("/\\");
+    std::string file = path.substr(slash + 1);  // npos + 1 == 0
+    const size_t dot = file.find_last_of(".");
+    return file.substr(0, dot);
+}
+
+namespace {
+
+// Converts one token like std::stod: leading white space skipped, trailing
+// characters ignored, no digits -> invalid_argument, overflow -> out_of_range.
+double parse_token(const char* begin, const char* end) {
+    char buf[64];
+    const size_t len = static_cast<size_t>(end - begin);
+    std::string big;
+    const char* z;
+    if (len < sizeof(buf)) {
+        std::memcpy(buf, begin, len);
+        buf[len] = 0;
+        z = buf;
+    } else {
+        big.assign(begin, end);
+        z = big.c_str();
+    }
+    char* stop = nullptr;
+    errno = 0;
+    const double v = std::strtod(z, &stop);
+    if (stop == z) throw std::invalid_argument("stod");
+    if (errno == ERANGE) throw std::out_of_range("stod");
+    return v;
+}
+
+// Number of ','-separated tokens std::getline would deliver for this line.
+int64_t count_tokens(const char* b, const char* e) {
+    if (b == e) return 0;
+    int64_t c = 1;
+    for (const char* p = b; p < e; ++p)
+        if (*p == ',') ++c;
+    if (e[-1] == ',') --c;  // getline yields no empty token after a trailing delimiter
+    return c;
+}
+
+}  // namespace
+
+HostDataset read_csv_dataset(const std::string& path) {
+    if (path.empty()) throw std::invalid_argument("filepath must be set.");
+    std::ifstream f(path, std::ios::binary);
+    if (!f.is_open()) throw std::ios_base::failure("Failed to open file: " + path);
+    std::string text((std::istreambuf_iterator<char>(f)), std::istreambuf_iterator<char>());
+
+    // Line table (a final line without '\n' counts; an empty tail after the last '\n' does not).
+    std::vector<std::pair<size_t, size_t>> lines;
+    size_t pos = 0;
+    while (pos < text.size()) {
+        const void* nl = std::memchr(text.data() + pos, '\n', text.size() - pos);
+        const size_t end = nl ? static_cast<size_t>(static_cast<const char*>(nl) - text.data()) : text.size();
+        lines.emplace_back(pos, end);
+        pos = end + 1;
+    }
+    if (lines.empty()) throw std::runtime_error("No points were generated.");
+
+    HostDataset ds;
+    ds.name = dataset_name_from_path(path);
+    ds.n = static_cast<int64_t>(lines.size());
+    ds.d = count_tokens(text.data() + lines[0].first, text.data() + lines[0].second);
+    if (ds.d == 0) throw std::runtime_error("No points were generated.");
+    ds.values.assign(static_cast<size_t>(ds.n) * static_cast<size_t>(ds.d), 0);
+
+    int64_t bad_line = -1;
+    int bad_kind = 0;  // 1 ragged, 2 parse
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < ds.n; ++r) {
+        const char* b = text.data() + lines[static_cast<size_t>(r)].first;
+        const char* e = text.data() + lines[static_cast<size_t>(r)].second;
+        int kind = 0;
+        if (count_tokens(b, e) != ds.d) {
+            kind = 1;
+        } else {
+            uint16_t* out = &ds.values[static_cast<size_t>(r) * static_cast<size_t>(ds.d)];
+            const char* p = b;
+            for (int64_t c = 0; c < ds.d && !kind; ++c) {
+                const char* q = static_cast<const char*>(std::memchr(p, ',', static_cast<size_t>(e - p)));
+                if (!q) q = e;
+                try {
+                    out[c] = float_to_half_rn(static_cast<float>(parse_token(p, q)));
+                } catch (const std::exception&) {
+                    kind = 2;
+                }
+                p = q + 1;
+            }
+        }
+        if (kind) {
+#pragma omp critical
+            if (bad_line < 0 || r < bad_line) {
+                bad_line = r;
+                bad_kind = kind;
+            }
+        }
+    }
+    if (bad_line >= 0) {
+        if (bad_kind == 1)
+            throw std::runtime_error("Dimensions of subsequent points didn't match the first point (line " +
+                                     std::to_string(bad_line) + ")");
+        throw std::invalid_argument("Failed to parse a value from dataset at line " + std::to_string(bad_line));
+    }
+    return ds;
+}
+
+}  // namespace fasted

@@ -1,0 +1,581 @@
+// Context API of the B200 epsilon self-join (layer 2 of include/fasted.h):
+// device memory, TMA tensor maps, kernel launches, timing, sort and egress.
+#include "fasted.h"
+
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cfloat>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <string>
+
+#include <cub/device/device_radix_sort.cuh>
+
+#include "kernels.cuh"
+
+#include "error.hpp"
+
+namespace fasted {
+thread_local std::string g_last_error;
+
+int fail(int code, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    g_last_error = buf;
+    return code;
+}
+}  // namespace fasted
+
+namespace {
+using fasted::fail;
+
+#define CU_TRY(expr)                                                                                 \
+    do {                                                                                             \
+        cudaError_t e_ = (expr);                                                                     \
+        if (e_ != cudaSuccess)                                                                       \
+            return fail(FASTED_ECUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(e_), __FILE__, \
+                        __LINE__);                                                                   \
+    } while (0)
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+}  // namespace
+
+struct fasted_ctx {
+    int device = 0;
+    int num_sms = 0;
+    cudaStream_t stream = nullptr;
+    bool owns_stream = false;
+
+    // dataset
+    __half* points = nullptr;
+    bool owns_points = false;
+    int64_t n = 0, d = 0, ld = 0;
+    float* norms = nullptr;
+    int64_t norms_cap = 0;
+    bool norms_valid = false;
+    CUtensorMap map_a{}, map_b{};
+
+    // results
+    unsigned long long* counters = nullptr;  // found, stored, status, spare
+    unsigned long long* keys = nullptr;      // device-order packed pairs
+    unsigned long long* keys_alt = nullptr;  // sort double buffer; reused for the unpacked records
+    float* dist = nullptr;
+    float* dist_alt = nullptr;
+    uint64_t capacity = 0;
+    bool have_dist_buf = false;
+    void* sort_tmp = nullptr;
+    size_t sort_tmp_bytes = 0;
+    uint64_t stored = 0;
+    void* result_pairs = nullptr;  // int2 records of the last join
+    float* result_dist = nullptr;
+    bool result_sorted = false;
+
+    cudaEvent_t ev[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
+
+    // options
+    int band_tiles = 16;
+    int grid = 0;
+};
+
+namespace {
+
+int make_map(fasted_ctx* c, CUtensorMap* map, int box_rows) {
+    EncodeTiledFn enc = get_encode_fn();
+    if (!enc) return fail(FASTED_ECUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    const cuuint64_t gdim[2] = {static_cast<cuuint64_t>(c->d), static_cast<cuuint64_t>(c->n)};
+    const cuuint64_t gstride[1] = {static_cast<cuuint64_t>(c->ld) * 2};
+    const cuuint32_t box[2] = {static_cast<cuuint32_t>(fasted::kTileK), static_cast<cuuint32_t>(box_rows)};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, c->points, gdim, gstride, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(FASTED_ECUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return FASTED_OK;
+}
+
+void release_points(fasted_ctx* c) {
+    if (c->owns_points && c->points) cudaFree(c->points);
+    c->points = nullptr;
+    c->owns_points = false;
+    c->n = c->d = c->ld = 0;
+    c->norms_valid = false;
+}
+
+int adopt_points(fasted_ctx* c, __half* dev, bool owns, int64_t n, int64_t d, int64_t ld) {
+    c->points = dev;
+    c->owns_points = owns;
+    c->n = n;
+    c->d = d;
+    c->ld = ld;
+    c->norms_valid = false;
+    c->stored = 0;
+    c->result_pairs = nullptr;
+    if (c->norms_cap < n) {
+        if (c->norms) cudaFree(c->norms);
+        c->norms = nullptr;
+        c->norms_cap = 0;
+        CU_TRY(cudaMalloc(&c->norms, static_cast<size_t>(n) * sizeof(float)));
+        c->norms_cap = n;
+    }
+    int rc = make_map(c, &c->map_a, fasted::kTileM);
+    if (rc) return rc;
+    return make_map(c, &c->map_b, fasted::kTileN);
+}
+
+int check_shape(int64_t n, int64_t d) {
+    if (n <= 0 || d <= 0) return fail(FASTED_EINVAL, "n and d must be positive (n=%lld d=%lld)", (long long)n, (long long)d);
+    if (n > 0x7fffffffLL - 1024 || d > 0x7fffffffLL - 1024)
+        return fail(FASTED_EINVAL, "n and d must fit a 32-bit index (n=%lld d=%lld)", (long long)n, (long long)d);
+    return FASTED_OK;
+}
+
+void free_pair_buffers(fasted_ctx* c) {
+    if (c->keys) cudaFree(c->keys);
+    if (c->keys_alt) cudaFree(c->keys_alt);
+    if (c->dist) cudaFree(c->dist);
+    if (c->dist_alt) cudaFree(c->dist_alt);
+    if (c->sort_tmp) cudaFree(c->sort_tmp);
+    c->keys = c->keys_alt = nullptr;
+    c->dist = c->dist_alt = nullptr;
+    c->sort_tmp = nullptr;
+    c->sort_tmp_bytes = 0;
+    c->capacity = 0;
+    c->have_dist_buf = false;
+    c->stored = 0;
+    c->result_pairs = nullptr;
+    c->result_dist = nullptr;
+}
+
+int ensure_pair_buffers(fasted_ctx* c, uint64_t capacity, bool want_dist) {
+    if (c->capacity >= capacity && c->capacity <= 2 * capacity + 1024 && (!want_dist || c->have_dist_buf))
+        return FASTED_OK;
+    free_pair_buffers(c);
+    const uint64_t cap = std::max<uint64_t>(capacity, 1);
+    CU_TRY(cudaMalloc(&c->keys, cap * 8));
+    CU_TRY(cudaMalloc(&c->keys_alt, cap * 8));
+    if (want_dist) {
+        CU_TRY(cudaMalloc(&c->dist, cap * 4));
+        CU_TRY(cudaMalloc(&c->dist_alt, cap * 4));
+    }
+    c->capacity = cap;
+    c->have_dist_buf = want_dist;
+    return FASTED_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* fasted_last_error(void) { return fasted::g_last_error.c_str(); }
+
+int fasted_create(int device, fasted_ctx** out) {
+    if (!out) return fail(FASTED_EINVAL, "out is null");
+    *out = nullptr;
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || count == 0)
+        return fail(FASTED_ENODEV, "no CUDA device: %s", e == cudaSuccess ? "device count is 0" : cudaGetErrorString(e));
+    if (device < 0 || device >= count) return fail(FASTED_EINVAL, "device %d out of range (%d devices)", device, count);
+    cudaDeviceProp prop;
+    CU_TRY(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10)
+        return fail(FASTED_ENODEV, "device %d is sm_%d%d; this library contains sm_100a code only", device, prop.major,
+                    prop.minor);
+    CU_TRY(cudaSetDevice(device));
+    fasted_ctx* c = new fasted_ctx();
+    c->device = device;
+    c->num_sms = prop.multiProcessorCount;
+    if (cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) != cudaSuccess) {
+        delete c;
+        return fail(FASTED_ECUDA, "cudaStreamCreate failed");
+    }
+    c->owns_stream = true;
+    for (auto& ev : c->ev) cudaEventCreate(&ev);
+    if (cudaMalloc(&c->counters, 8 * sizeof(unsigned long long)) != cudaSuccess) {
+        fasted_destroy(c);
+        return fail(FASTED_ECUDA, "cudaMalloc of counters failed");
+    }
+    cudaFuncSetAttribute(fasted::join_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, fasted::kJoinSmemBytes);
+    cudaFuncSetAttribute(fasted::row_norms_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         fasted::kNormSmemBytes);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        fasted_destroy(c);
+        return fail(FASTED_ECUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
+    }
+    *out = c;
+    return FASTED_OK;
+}
+
+void fasted_destroy(fasted_ctx* c) {
+    if (!c) return;
+    cudaSetDevice(c->device);
+    if (c->stream) cudaStreamSynchronize(c->stream);
+    release_points(c);
+    free_pair_buffers(c);
+    if (c->norms) cudaFree(c->norms);
+    if (c->counters) cudaFree(c->counters);
+    for (auto& ev : c->ev)
+        if (ev) cudaEventDestroy(ev);
+    if (c->owns_stream && c->stream) cudaStreamDestroy(c->stream);
+    delete c;
+}
+
+int fasted_set_stream(fasted_ctx* c, void* stream) {
+    if (!c) return fail(FASTED_EINVAL, "ctx is null");
+    if (c->owns_stream && c->stream) {
+        cudaStreamSynchronize(c->stream);
+        cudaStreamDestroy(c->stream);
+    }
+    c->stream = static_cast<cudaStream_t>(stream);
+    c->owns_stream = false;
+    return FASTED_OK;
+}
+
+int fasted_set_option(fasted_ctx* c, const char* name, int64_t value) {
+    if (!c || !name) return fail(FASTED_EINVAL, "null argument");
+    if (!strcmp(name, "band_tiles")) {
+        if (value < 1 || value > 4096) return fail(FASTED_EINVAL, "band_tiles out of range");
+        c->band_tiles = static_cast<int>(value);
+    } else if (!strcmp(name, "grid")) {
+        if (value < 0 || value > 65535) return fail(FASTED_EINVAL, "grid out of range");
+        c->grid = static_cast<int>(value);
+    } else {
+        return fail(FASTED_EINVAL, "unknown option '%s'", name);
+    }
+    return FASTED_OK;
+}
+
+int fasted_set_points_host_f16(fasted_ctx* c, const uint16_t* host, int64_t n, int64_t d, int64_t ld_host) {
+    if (!c || !host) return fail(FASTED_EINVAL, "null argument");
+    int rc = check_shape(n, d);
+    if (rc) return rc;
+    if (ld_host < d) return fail(FASTED_EINVAL, "ld_host (%lld) < d (%lld)", (long long)ld_host, (long long)d);
+    CU_TRY(cudaSetDevice(c->device));
+    CU_TRY(cudaStreamSynchronize(c->stream));
+    release_points(c);
+    const int64_t ld = (d + fasted::kTileK - 1) / fasted::kTileK * fasted::kTileK;
+    __half* dev = nullptr;
+    CU_TRY(cudaMalloc(&dev, static_cast<size_t>(n) * ld * 2));
+    cudaError_t e = cudaSuccess;
+    if (ld != d) e = cudaMemsetAsync(dev, 0, static_cast<size_t>(n) * ld * 2, c->stream);
+    if (e == cudaSuccess)
+        e = cudaMemcpy2DAsync(dev, static_cast<size_t>(ld) * 2, host, static_cast<size_t>(ld_host) * 2,
+                              static_cast<size_t>(d) * 2, static_cast<size_t>(n), cudaMemcpyHostToDevice, c->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
+    if (e != cudaSuccess) {
+        cudaFree(dev);
+        return fail(FASTED_ECUDA, "upload of points failed: %s", cudaGetErrorString(e));
+    }
+    return adopt_points(c, dev, true, n, d, ld);
+}
+
+int fasted_set_points_device_f16(fasted_ctx* c, const void* dev, int64_t n, int64_t d, int64_t ld) {
+    if (!c || !dev) return fail(FASTED_EINVAL, "null argument");
+    int rc = check_shape(n, d);
+    if (rc) return rc;
+    if (ld < d || (ld % 8) != 0) return fail(FASTED_EINVAL, "ld (%lld) must be >= d and a multiple of 8", (long long)ld);
+    if (reinterpret_cast<uintptr_t>(dev) % 16 != 0) return fail(FASTED_EINVAL, "device pointer must be 16-byte aligned");
+    CU_TRY(cudaSetDevice(c->device));
+    CU_TRY(cudaStreamSynchronize(c->stream));
+    release_points(c);
+    return adopt_points(c, static_cast<__half*>(const_cast<void*>(dev)), false, n, d, ld);
+}
+
+int fasted_generate_exponential(fasted_ctx* c, int64_t n, int64_t d, double lambda, double max_value, uint64_t seed) {
+    if (!c) return fail(FASTED_EINVAL, "ctx is null");
+    int rc = check_shape(n, d);
+    if (rc) return rc;
+    if (!(lambda > 0) || !(max_value > 0)) return fail(FASTED_EINVAL, "lambda and max_value must be positive");
+    CU_TRY(cudaSetDevice(c->device));
+    CU_TRY(cudaStreamSynchronize(c->stream));
+    release_points(c);
+    const int64_t ld = (d + fasted::kTileK - 1) / fasted::kTileK * fasted::kTileK;
+    __half* dev = nullptr;
+    CU_TRY(cudaMalloc(&dev, static_cast<size_t>(n) * ld * 2));
+    fasted::gen_exponential_kernel<<<c->num_sms * 8, 256, 0, c->stream>>>(dev, n, static_cast<int>(d),
+                                                                          static_cast<int>(ld), lambda, max_value, seed);
+    cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
+    if (e != cudaSuccess) {
+        cudaFree(dev);
+        return fail(FASTED_ECUDA, "generator kernel failed: %s", cudaGetErrorString(e));
+    }
+    return adopt_points(c, dev, true, n, d, ld);
+}
+
+int fasted_points_info(fasted_ctx* c, void** dev, int64_t* n, int64_t* d, int64_t* ld) {
+    if (!c) return fail(FASTED_EINVAL, "ctx is null");
+    if (!c->points) return fail(FASTED_ESTATE, "no dataset is resident");
+    if (dev) *dev = c->points;
+    if (n) *n = c->n;
+    if (d) *d = c->d;
+    if (ld) *ld = c->ld;
+    return FASTED_OK;
+}
+
+int fasted_get_points_host_f16(fasted_ctx* c, uint16_t* host, int64_t ld_host) {
+    if (!c || !host) return fail(FASTED_EINVAL, "null argument");
+    if (!c->points) return fail(FASTED_ESTATE, "no dataset is resident");
+    if (ld_host < c->d) return fail(FASTED_EINVAL, "ld_host < d");
+    CU_TRY(cudaSetDevice(c->device));
+    CU_TRY(cudaMemcpy2DAsync(host, static_cast<size_t>(ld_host) * 2, c->points, static_cast<size_t>(c->ld) * 2,
+                             static_cast<size_t>(c->d) * 2, static_cast<size_t>(c->n), cudaMemcpyDeviceToHost,
+                             c->stream));
+    CU_TRY(cudaStreamSynchronize(c->stream));
+    return FASTED_OK;
+}
+
+static int launch_norms(fasted_ctx* c) {
+    const int row_blocks = static_cast<int>((c->n + fasted::kNormRows - 1) / fasted::kNormRows);
+    const int k_boxes = static_cast<int>((c->d + fasted::kTileK - 1) / fasted::kTileK);
+    const int grid = std::min(row_blocks, c->num_sms * 3);
+    fasted::row_norms_kernel<<<grid, fasted::kNormRows, fasted::kNormSmemBytes, c->stream>>>(
+        c->map_a, c->norms, static_cast<int>(c->n), k_boxes, row_blocks, c->counters + 2);
+    CU_TRY(cudaGetLastError());
+    return FASTED_OK;
+}
+
+int fasted_row_norms(fasted_ctx* c, double* ms) {
+    if (!c) return fail(FASTED_EINVAL, "ctx is null");
+    if (!c->points) return fail(FASTED_ESTATE, "no dataset is resident");
+    CU_TRY(cudaSetDevice(c->device));
+    CU_TRY(cudaMemsetAsync(c->counters, 0, 8 * sizeof(unsigned long long), c->stream));
+    CU_TRY(cudaEventRecord(c->ev[0], c->stream));
+    int rc = launch_norms(c);
+    if (rc) return rc;
+    CU_TRY(cudaEventRecord(c->ev[1], c->stream));
+    CU_TRY(cudaStreamSynchronize(c->stream));
+    unsigned long long status = 0;
+    CU_TRY(cudaMemcpy(&status, c->counters + 2, 8, cudaMemcpyDeviceToHost));
+    if (status) return fail(FASTED_EKERNEL, "row-norm kernel gave up a wait (status 0x%llx)", status);
+    if (ms) {
+        float t = 0;
+        cudaEventElapsedTime(&t, c->ev[0], c->ev[1]);
+        *ms = t;
+    }
+    c->norms_valid = true;
+    return FASTED_OK;
+}
+
+int fasted_get_norms(fasted_ctx* c, float* host_out) {
+    if (!c || !host_out) return fail(FASTED_EINVAL, "null argument");
+    if (!c->norms_valid) return fail(FASTED_ESTATE, "row norms have not been computed");
+    CU_TRY(cudaSetDevice(c->device));
+    CU_TRY(cudaMemcpyAsync(host_out, c->norms, static_cast<size_t>(c->n) * 4, cudaMemcpyDeviceToHost, c->stream));
+    CU_TRY(cudaStreamSynchronize(c->stream));
+    return FASTED_OK;
+}
+
+int fasted_join(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end, uint64_t capacity, unsigned flags,
+                fasted_join_stats* stats) {
+    if (!c) return fail(FASTED_EINVAL, "ctx is null");
+    if (!c->points) return fail(FASTED_ESTATE, "no dataset is resident");
+    if (q_end < 0) q_end = c->n;
+    if (q_begin < 0 || q_begin > q_end || q_end > c->n)
+        return fail(FASTED_EINVAL, "query band [%lld, %lld) outside [0, %lld)", (long long)q_begin, (long long)q_end,
+                    (long long)c->n);
+    if (!(eps >= 0.0)) return fail(FASTED_EINVAL, "epsilon must be >= 0");
+    CU_TRY(cudaSetDevice(c->device));
+    const bool want_dist = (flags & FASTED_JOIN_DIST2) != 0;
+
+    if (capacity == 0) {
+        // The reference's sizing rule: n * 256 pairs, reduced to what fits in free memory.
+        capacity = static_cast<uint64_t>(c->n) * 256ull;
+        if (c->capacity < capacity) {
+            size_t free_b = 0, total_b = 0;
+            CU_TRY(cudaMemGetInfo(&free_b, &total_b));
+            free_b += c->capacity * (c->have_dist_buf ? 24 : 16);
+            const uint64_t per_pair = want_dist ? 24 + 2 : 16 + 2;  // keys x2 (+ dist x2) + sort scratch slack
+            const uint64_t fit = static_cast<uint64_t>(free_b * 0.9) / per_pair;
+            if (capacity > fit) capacity = fit;
+        }
+    }
+    int rc = ensure_pair_buffers(c, capacity, want_dist);
+    if (rc) return rc;
+
+    fasted::JoinParams p{};
+    p.norms = c->norms;
+    p.counters = c->counters;
+    p.keys = c->keys;
+    p.dist2 = want_dist ? c->dist : nullptr;
+    p.capacity = capacity;
+    const double e2 = eps * eps;
+    p.eps2 = e2 > FLT_MAX ? FLT_MAX : static_cast<float>(e2);
+    p.n = static_cast<int>(c->n);
+    p.q_begin = static_cast<int>(q_begin);
+    p.q_end = static_cast<int>(q_end);
+    p.k_steps = static_cast<int>((c->d + fasted::kTileK - 1) / fasted::kTileK);
+    p.tiles_m = static_cast<int>((q_end - q_begin + fasted::kTileM - 1) / fasted::kTileM);
+    p.tiles_n = static_cast<int>((c->n + fasted::kTileN - 1) / fasted::kTileN);
+    p.band_tiles = std::max(1, std::min(c->band_tiles, std::max(p.tiles_m, 1)));
+    p.total_tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
+    int grid = c->grid > 0 ? c->grid : c->num_sms;
+    if (p.total_tiles < grid) grid = static_cast<int>(std::max<long long>(p.total_tiles, 1));
+
+    CU_TRY(cudaMemsetAsync(c->counters, 0, 8 * sizeof(unsigned long long), c->stream));
+    CU_TRY(cudaEventRecord(c->ev[0], c->stream));
+    if (!(flags & FASTED_JOIN_KEEP_NORMS) || !c->norms_valid) {
+        rc = launch_norms(c);
+        if (rc) return rc;
+    }
+    CU_TRY(cudaEventRecord(c->ev[1], c->stream));
+    if (p.total_tiles > 0) {
+        fasted::join_kernel<<<grid, fasted::kJoinThreads, fasted::kJoinSmemBytes, c->stream>>>(c->map_a, c->map_b, p);
+        CU_TRY(cudaGetLastError());
+    }
+    CU_TRY(cudaEventRecord(c->ev[2], c->stream));
+    unsigned long long h[3] = {0, 0, 0};
+    CU_TRY(cudaMemcpyAsync(h, c->counters, sizeof(h), cudaMemcpyDeviceToHost, c->stream));
+    CU_TRY(cudaStreamSynchronize(c->stream));
+    c->norms_valid = (h[2] & fasted::kErrNormWait) == 0;
+    c->stored = 0;
+    c->result_pairs = nullptr;
+    c->result_dist = nullptr;
+    if (h[2]) return fail(FASTED_EKERNEL, "a device-side wait ran out (status 0x%llx)", h[2]);
+    const uint64_t stored = h[1];
+
+    CU_TRY(cudaEventRecord(c->ev[3], c->stream));
+    const unsigned long long* sorted_keys = c->keys;
+    float* sorted_dist = c->dist;
+    if (!(flags & FASTED_JOIN_NO_SORT) && stored > 1) {
+        // Row-major order of (query, candidate) == numeric order of the packed key
+        // (replaces thrust::sort with Pair::operator<, source/pair.cuh:39-45, 151-158).
+        int end_bit = 33;
+        while (end_bit < 64 && (static_cast<uint64_t>(c->n) >> (end_bit - 32)) != 0) ++end_bit;
+        cub::DoubleBuffer<unsigned long long> kb(c->keys, c->keys_alt);
+        cub::DoubleBuffer<float> vb(c->dist, c->dist_alt);
+        size_t need = 0;
+        if (want_dist)
+            CU_TRY(cub::DeviceRadixSort::SortPairs(nullptr, need, kb, vb, stored, 0, end_bit, c->stream));
+        else
+            CU_TRY(cub::DeviceRadixSort::SortKeys(nullptr, need, kb, stored, 0, end_bit, c->stream));
+        if (need > c->sort_tmp_bytes) {
+            if (c->sort_tmp) cudaFree(c->sort_tmp);
+            c->sort_tmp = nullptr;
+            c->sort_tmp_bytes = 0;
+            CU_TRY(cudaMalloc(&c->sort_tmp, need));
+            c->sort_tmp_bytes = need;
+        }
+        if (want_dist)
+            CU_TRY(cub::DeviceRadixSort::SortPairs(c->sort_tmp, need, kb, vb, stored, 0, end_bit, c->stream));
+        else
+            CU_TRY(cub::DeviceRadixSort::SortKeys(c->sort_tmp, need, kb, stored, 0, end_bit, c->stream));
+        if (kb.Current() != c->keys) std::swap(c->keys, c->keys_alt);
+        if (want_dist && vb.Current() != c->dist) std::swap(c->dist, c->dist_alt);
+        sorted_keys = c->keys;
+        sorted_dist = c->dist;
+    }
+    if (stored > 0) {
+        const int blocks = static_cast<int>(std::min<uint64_t>((stored + 255) / 256, static_cast<uint64_t>(c->num_sms) * 16));
+        fasted::unpack_pairs_kernel<<<blocks, 256, 0, c->stream>>>(sorted_keys, reinterpret_cast<int2*>(c->keys_alt),
+                                                                  stored);
+        CU_TRY(cudaGetLastError());
+    }
+    CU_TRY(cudaEventRecord(c->ev[4], c->stream));
+    CU_TRY(cudaStreamSynchronize(c->stream));
+    c->stored = stored;
+    c->result_pairs = c->keys_alt;
+    c->result_dist = want_dist ? sorted_dist : nullptr;
+    c->result_sorted = !(flags & FASTED_JOIN_NO_SORT);
+
+    if (stats) {
+        float t01 = 0, t12 = 0, t02 = 0, t34 = 0;
+        cudaEventElapsedTime(&t01, c->ev[0], c->ev[1]);
+        cudaEventElapsedTime(&t12, c->ev[1], c->ev[2]);
+        cudaEventElapsedTime(&t02, c->ev[0], c->ev[2]);
+        cudaEventElapsedTime(&t34, c->ev[3], c->ev[4]);
+        stats->pairs_found = h[0];
+        stats->pairs_stored = stored;
+        stats->norms_ms = t01;
+        stats->join_ms = t12;
+        stats->kernel_ms = t02;
+        stats->sort_ms = t34;
+        stats->status = h[2];
+        stats->tiles_m = p.tiles_m;
+        stats->tiles_n = p.tiles_n;
+        stats->grid = grid;
+    }
+    return FASTED_OK;
+}
+
+int fasted_get_pairs(fasted_ctx* c, uint64_t first, uint64_t count, int32_t* pairs_out, float* dist2_out) {
+    if (!c) return fail(FASTED_EINVAL, "ctx is null");
+    if (first + count > c->stored)
+        return fail(FASTED_EINVAL, "range [%llu, %llu) exceeds the %llu stored pairs", (unsigned long long)first,
+                    (unsigned long long)(first + count), (unsigned long long)c->stored);
+    if (count == 0) return FASTED_OK;
+    if (dist2_out && !c->result_dist) return fail(FASTED_ESTATE, "the last join did not record distances");
+    CU_TRY(cudaSetDevice(c->device));
+    if (pairs_out)
+        CU_TRY(cudaMemcpyAsync(pairs_out, static_cast<const int2*>(c->result_pairs) + first, count * 8,
+                               cudaMemcpyDeviceToHost, c->stream));
+    if (dist2_out)
+        CU_TRY(cudaMemcpyAsync(dist2_out, c->result_dist + first, count * 4, cudaMemcpyDeviceToHost, c->stream));
+    CU_TRY(cudaStreamSynchronize(c->stream));
+    return FASTED_OK;
+}
+
+int fasted_pairs_device(fasted_ctx* c, void** pairs_dev, void** dist2_dev) {
+    if (!c) return fail(FASTED_EINVAL, "ctx is null");
+    if (pairs_dev) *pairs_dev = c->result_pairs;
+    if (dist2_dev) *dist2_dev = c->result_dist;
+    return FASTED_OK;
+}
+
+int fasted_brute_force_f64(fasted_ctx* c, const int32_t* sample_rows, int n_samples, double eps,
+                           unsigned long long* counts_out) {
+    if (!c || !sample_rows || !counts_out || n_samples <= 0) return fail(FASTED_EINVAL, "bad argument");
+    if (!c->points) return fail(FASTED_ESTATE, "no dataset is resident");
+    if (c->d > 12000) return fail(FASTED_EINVAL, "brute-force check supports d <= 12000");
+    for (int i = 0; i < n_samples; ++i)
+        if (sample_rows[i] < 0 || sample_rows[i] >= c->n) return fail(FASTED_EINVAL, "sample row out of range");
+    CU_TRY(cudaSetDevice(c->device));
+    int* d_rows = nullptr;
+    unsigned long long* d_counts = nullptr;
+    CU_TRY(cudaMalloc(&d_rows, n_samples * sizeof(int)));
+    if (cudaMalloc(&d_counts, n_samples * 8) != cudaSuccess) {
+        cudaFree(d_rows);
+        return fail(FASTED_ECUDA, "cudaMalloc failed");
+    }
+    cudaMemcpyAsync(d_rows, sample_rows, n_samples * sizeof(int), cudaMemcpyHostToDevice, c->stream);
+    cudaMemsetAsync(d_counts, 0, n_samples * 8, c->stream);
+    const int threads = 256;
+    int bx = static_cast<int>(std::min<int64_t>((c->n + 7) / 8, 4096));
+    dim3 grid(bx, n_samples);
+    fasted::brute_f64_kernel<<<grid, threads, static_cast<size_t>(c->d) * 4, c->stream>>>(
+        c->points, static_cast<int>(c->n), static_cast<int>(c->d), static_cast<int>(c->ld), d_rows, n_samples,
+        eps * eps, d_counts, nullptr, 0, nullptr);
+    cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess)
+        e = cudaMemcpyAsync(counts_out, d_counts, n_samples * 8, cudaMemcpyDeviceToHost, c->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
+    cudaFree(d_rows);
+    cudaFree(d_counts);
+    if (e != cudaSuccess) return fail(FASTED_ECUDA, "brute-force kernel failed: %s", cudaGetErrorString(e));
+    return FASTED_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,535 @@
+// Device kernels of the epsilon self-join for sm_100a.
+//
+//   row_norms_kernel   FP16 rows -> FP32 squared norms (HBM-bound, TMA-staged)
+//   join_kernel        persistent TMA + tcgen05.mma pipeline with the fused
+//                      distance / threshold / pair-compaction epilogue
+//   unpack_pairs_kernel, gen_exponential_kernel, brute_f64_kernel  (helpers)
+#pragma once
+
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "ptx.cuh"
+
+namespace fasted {
+
+// ---------------------------------------------------------------------------
+// Shared constants
+// ---------------------------------------------------------------------------
+
+constexpr int kTileK = 64;     // halfs per pipeline stage = one 128-byte swizzle row
+constexpr int kUmmaK = 16;     // K of one tcgen05.mma kind::f16
+constexpr int kTileM = 128;    // query rows per CTA tile = TMEM lanes
+constexpr int kTileN = 256;    // candidate rows per tile = TMEM columns per accumulator
+constexpr int kStages = 4;     // TMA -> MMA ring depth
+constexpr int kTmemCols = 512; // two accumulator buffers of kTileN columns
+
+constexpr int kJoinThreads = 192;  // warp 0: TMA, warp 1: MMA issue + TMEM, warps 2..5: epilogue
+constexpr int kEpiThreads = 128;
+
+constexpr uint32_t kStageBytesA = kTileM * kTileK * 2;  // 16 KiB
+constexpr uint32_t kStageBytesB = kTileN * kTileK * 2;  // 32 KiB
+constexpr uint32_t kStageBytes = kStageBytesA + kStageBytesB;
+
+// Wait limit of every device-side wait.  A legitimate wait lasts at most one
+// tile main loop (tens of microseconds); after the limit the kernel records
+// an error and returns.
+constexpr uint64_t kWaitLimitNs = 2000000000ull;
+
+// Status word bits (counters[2]).
+constexpr unsigned long long kErrProducerWait = 1ull;
+constexpr unsigned long long kErrMmaWait = 2ull;
+constexpr unsigned long long kErrEpilogueWait = 4ull;
+constexpr unsigned long long kErrNormWait = 8ull;
+
+struct JoinParams {
+    const float* norms;            // [n] row norms
+    unsigned long long* counters;  // [0] pairs found, [1] pairs stored, [2] status bits
+    unsigned long long* keys;      // pair buffer: (query << 32) | candidate
+    float* dist2;                  // optional squared distances, parallel to keys (may be null)
+    unsigned long long capacity;   // pair buffer capacity
+    float eps2;                    // threshold on the squared distance (inclusive)
+    int n;                         // real number of points (candidates are rows [0, n))
+    int q_begin, q_end;            // query rows handled by this launch
+    int k_steps;                   // ceil(d / kTileK)
+    int tiles_m, tiles_n;          // tile grid of this launch
+    int band_tiles;                // tile rows per raster band
+    long long total_tiles;
+};
+
+// Persistent static schedule: CTA b handles tiles b, b + grid, b + 2*grid, ...
+// of a linear order that walks bands of `band_tiles` tile rows; inside a band
+// the tile row is the fastest index, so the CTAs that run together cover a
+// band_tiles x (grid / band_tiles) block of the tile grid and the query rows of
+// a band stay L2-resident while the band sweeps over all candidates.
+__device__ __forceinline__ void tile_coords(const JoinParams& p, long long t, int& tm, int& tn) {
+    const long long per_band = static_cast<long long>(p.band_tiles) * p.tiles_n;
+    const int band = static_cast<int>(t / per_band);
+    const long long rem = t - band * per_band;
+    const int first_row = band * p.band_tiles;
+    const int rows = min(p.band_tiles, p.tiles_m - first_row);
+    tn = static_cast<int>(rem / rows);
+    tm = first_row + static_cast<int>(rem - static_cast<long long>(tn) * rows);
+}
+
+// ---------------------------------------------------------------------------
+// Row norms
+// ---------------------------------------------------------------------------
+//
+// s_i = sequential round-toward-zero sum, over column pairs in ascending k, of
+// RZ(x_k^2 + x_{k+1}^2) with exact FP32 squares: the reduction of
+// source/sumSquared.cuh:34-40 and :59-72 of the reference, bit for bit.
+//
+// The reference runs one thread per point reading 4 bytes at a time.  Here a
+// CTA owns 128 rows; thread 0 streams [128 rows x 64 halfs] boxes through a
+// ring of TMA stages (128-byte swizzle, so that thread r reading row r's 16-byte
+// chunks is bank-conflict free) and thread r walks row r's chain.  The chain
+// is serial per row by definition, but 128 rows x several CTAs per SM keep the
+// loads far ahead of it: the kernel is bound by HBM.
+
+constexpr int kNormRows = 128;
+constexpr int kNormStages = 4;
+constexpr int kNormBoxesPerStage = 2;  // 2 x 128 B = 256 contiguous bytes per row per stage
+constexpr uint32_t kNormBoxBytes = kNormRows * kTileK * 2;
+constexpr uint32_t kNormStageBytes = kNormBoxBytes * kNormBoxesPerStage;
+constexpr int kNormSmemBytes = kNormStages * kNormStageBytes + 1024 + 64;
+
+__global__ void __launch_bounds__(kNormRows)
+row_norms_kernel(const __grid_constant__ CUtensorMap map, float* __restrict__ norms, int n, int k_boxes,
+                 int row_blocks, unsigned long long* __restrict__ status) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t bars = base + kNormStages * kNormStageBytes;  // kNormStages full barriers
+    __shared__ int abort_flag;
+
+    const int tid = threadIdx.x;
+    if (tid == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < kNormStages; ++s) ptx::mbar_init(bars + 8 * s, 1);
+        ptx::fence_mbar_init();
+        ptx::prefetch_tensormap(&map);
+    }
+    __syncthreads();
+
+    const int steps_per_block = (k_boxes + kNormBoxesPerStage - 1) / kNormBoxesPerStage;
+    // Work items of this CTA: (row block, k step) pairs in order.
+    const int my_blocks = (row_blocks - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) /
+                          static_cast<int>(gridDim.x);
+    const long long total_items = static_cast<long long>(my_blocks) * steps_per_block;
+
+    auto issue = [&](long long item) {
+        const int blk = static_cast<int>(item / steps_per_block);
+        const int step = static_cast<int>(item - static_cast<long long>(blk) * steps_per_block);
+        const int row0 = (static_cast<int>(blockIdx.x) + blk * static_cast<int>(gridDim.x)) * kNormRows;
+        const int s = static_cast<int>(item % kNormStages);
+        const uint32_t bar = bars + 8 * s;
+        const int nb = min(kNormBoxesPerStage, k_boxes - step * kNormBoxesPerStage);
+        ptx::mbar_expect_tx(bar, nb * kNormBoxBytes);
+        for (int b = 0; b < nb; ++b)
+            ptx::tma_load_2d(base + s * kNormStageBytes + b * kNormBoxBytes, &map, bar,
+                             (step * kNormBoxesPerStage + b) * kTileK, row0);
+    };
+
+    if (tid == 0) {
+        const long long pre = total_items < kNormStages ? total_items : kNormStages;
+        for (long long i = 0; i < pre; ++i) issue(i);
+    }
+
+    float acc = 0.0f;
+    bool ok = true;
+    for (long long item = 0; item < total_items; ++item) {
+        const int blk = static_cast<int>(item / steps_per_block);
+        const int step = static_cast<int>(item - static_cast<long long>(blk) * steps_per_block);
+        const int s = static_cast<int>(item % kNormStages);
+        const uint32_t parity = static_cast<uint32_t>((item / kNormStages) & 1);
+        if (step == 0) acc = 0.0f;
+        ok = ptx::mbar_wait_bounded(bars + 8 * s, parity, &abort_flag, kWaitLimitNs);
+        if (!ok) break;
+        const int nb = min(kNormBoxesPerStage, k_boxes - step * kNormBoxesPerStage);
+        for (int b = 0; b < nb; ++b) {
+            const uint8_t* box = smem_raw + (base - ptx::smem_u32(smem_raw)) + s * kNormStageBytes + b * kNormBoxBytes;
+            const uint8_t* row = box + tid * 128;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                const uint4 q = *reinterpret_cast<const uint4*>(row + ((c ^ (tid & 7)) << 4));
+                const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
+                    acc = __fadd_rz(acc, __fadd_rz(f.x * f.x, f.y * f.y));
+                }
+            }
+        }
+        if (step == steps_per_block - 1) {
+            const int r = (static_cast<int>(blockIdx.x) + blk * static_cast<int>(gridDim.x)) * kNormRows + tid;
+            if (r < n) norms[r] = acc;
+        }
+        __syncthreads();  // every thread is done with stage s
+        if (tid == 0 && item + kNormStages < total_items) issue(item + kNormStages);
+    }
+    if (!ok) {
+        // Give loads that are still in flight a bounded chance to land before the CTA exits.
+        __syncthreads();
+        if (tid == 0) {
+            atomicOr(status, kErrNormWait);
+            const uint64_t t0 = ptx::globaltimer_ns();
+            for (int s = 0; s < kNormStages; ++s)
+                for (int ph = 0; ph < 2; ++ph)
+                    while (!ptx::mbar_try_wait(bars + 8 * s, ph) && ptx::globaltimer_ns() - t0 < 20000000ull) {
+                    }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// The join
+// ---------------------------------------------------------------------------
+//
+// Replaces, for one band of query rows against all candidates, the reference's
+// FindPairsKernel (source/findPairs.cuh:360-546): tile hand-out
+// (source/rasterizer/onDemandRasterizer.cuh:78-108), global->shared staging
+// (findPairs.cuh:182-218), ldmatrix + mma.sync (source/ptxMma.cuh:95-191,
+// source/warpMma.cuh:131-190), the distance test (warpMma.cuh:220-273) and the
+// pair append (source/pair.cuh:123-133).
+//
+// Warp roles (192 threads, one CTA per SM):
+//   warp 0      one lane issues the TMA loads of A (128 x 64) and B (256 x 64)
+//               FP16 boxes into a 4-stage ring of 128B-swizzled shared memory
+//   warp 1      allocates TMEM; one lane issues 4 tcgen05.mma (M128 N256 K16)
+//               per stage into one of two 256-column FP32 accumulators and
+//               commits stage-release / accumulator-ready mbarriers
+//   warps 2..5  epilogue: tcgen05.ld the accumulator (thread = query row),
+//               d2 = (s_q + s_c) - 2a, compare with eps2, compact the hits with
+//               a warp scan and one atomicAdd per warp, store packed pairs.
+// The epilogue of tile t overlaps the main loop of tile t+1 through the two
+// accumulator buffers.
+
+struct JoinSmemAux {
+    unsigned long long full_bar[kStages];
+    unsigned long long empty_bar[kStages];
+    unsigned long long acc_full_bar[2];
+    unsigned long long acc_empty_bar[2];
+    uint32_t tmem_base;
+    int abort_flag;
+    alignas(16) float cand_norms[2][kTileN];
+};
+
+constexpr int kJoinSmemBytes = kStages * kStageBytes + 1024 + static_cast<int>(sizeof(JoinSmemAux)) + 64;
+
+__global__ void __launch_bounds__(kJoinThreads, 1)
+join_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+            const JoinParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_u32 = ptx::smem_u32(smem_raw);
+    const uint32_t tiles_u32 = (raw_u32 + 1023u) & ~1023u;
+    JoinSmemAux* aux = reinterpret_cast<JoinSmemAux*>(smem_raw + (tiles_u32 - raw_u32) + kStages * kStageBytes);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    volatile int* abort_flag = &aux->abort_flag;
+
+    if (threadIdx.x == 0) {
+        aux->abort_flag = 0;
+        for (int s = 0; s < kStages; ++s) {
+            ptx::mbar_init(ptx::smem_u32(&aux->full_bar[s]), 1);
+            ptx::mbar_init(ptx::smem_u32(&aux->empty_bar[s]), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            ptx::mbar_init(ptx::smem_u32(&aux->acc_full_bar[b]), 1);
+            ptx::mbar_init(ptx::smem_u32(&aux->acc_empty_bar[b]), 4);  // one arrive per epilogue warp
+        }
+        ptx::fence_mbar_init();
+        ptx::prefetch_tensormap(&map_a);
+        ptx::prefetch_tensormap(&map_b);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc<1>(ptx::smem_u32(&aux->tmem_base), kTmemCols);
+        ptx::tmem_relinquish<1>();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem_base = aux->tmem_base;
+
+    const long long first_tile = blockIdx.x;
+    const long long tile_step = gridDim.x;
+
+    if (warp == 0) {
+        // ------------------------- TMA producer -------------------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            long long issued = 0;
+            for (long long t = first_tile; t < p.total_tiles && ok; t += tile_step) {
+                int tm, tn;
+                tile_coords(p, t, tm, tn);
+                const int row_a = p.q_begin + tm * kTileM;
+                const int row_b = tn * kTileN;
+                for (int ks = 0; ks < p.k_steps; ++ks) {
+                    ok = ptx::mbar_wait_bounded(ptx::smem_u32(&aux->empty_bar[stage]), phase ^ 1u, abort_flag,
+                                                kWaitLimitNs);
+                    if (!ok) break;
+                    const uint32_t bar = ptx::smem_u32(&aux->full_bar[stage]);
+                    const uint32_t dst = tiles_u32 + stage * kStageBytes;
+                    ptx::mbar_expect_tx(bar, kStageBytes);
+                    ptx::tma_load_2d(dst, &map_a, bar, ks * kTileK, row_a);
+                    ptx::tma_load_2d(dst + kStageBytesA, &map_b, bar, ks * kTileK, row_b);
+                    ++issued;
+                    if (++stage == kStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+            if (!ok) {
+                atomicOr(p.counters + 2, kErrProducerWait);
+                // Bounded wait for the loads still in flight (at most kStages of them).
+                const uint64_t t0 = ptx::globaltimer_ns();
+                const long long pending = issued < kStages ? issued : kStages;
+                int s = stage;
+                uint32_t ph = phase;
+                for (long long i = 0; i < pending; ++i) {
+                    if (--s < 0) {
+                        s = kStages - 1;
+                        ph ^= 1u;
+                    }
+                    while (!ptx::mbar_try_wait(ptx::smem_u32(&aux->full_bar[s]), ph) &&
+                           ptx::globaltimer_ns() - t0 < 20000000ull) {
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------- MMA issuer ---------------------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = ptx::make_f16_idesc(kTileM, kTileN);
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            long long it = 0;
+            for (long long t = first_tile; t < p.total_tiles && ok; t += tile_step, ++it) {
+                const int buf = static_cast<int>(it & 1);
+                const uint32_t acc_phase = static_cast<uint32_t>((it >> 1) & 1);
+                ok = ptx::mbar_wait_bounded(ptx::smem_u32(&aux->acc_empty_bar[buf]), acc_phase ^ 1u, abort_flag,
+                                            kWaitLimitNs);
+                if (!ok) break;
+                ptx::tc_fence_after_sync();
+                const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(buf * kTileN);
+                for (int ks = 0; ks < p.k_steps; ++ks) {
+                    ok = ptx::mbar_wait_bounded(ptx::smem_u32(&aux->full_bar[stage]), phase, abort_flag,
+                                                kWaitLimitNs);
+                    if (!ok) break;
+                    ptx::tc_fence_after_sync();
+                    const uint32_t a_addr = tiles_u32 + stage * kStageBytes;
+                    const uint64_t desc_a = ptx::make_kmajor_sw128_desc(a_addr);
+                    const uint64_t desc_b = ptx::make_kmajor_sw128_desc(a_addr + kStageBytesA);
+#pragma unroll
+                    for (int k = 0; k < kTileK / kUmmaK; ++k) {
+                        // Advance 16 halfs = 32 bytes inside the 128-byte swizzle row: +2 in the >>4 address field.
+                        ptx::umma_f16_ss<1>(tmem_d, desc_a + 2u * k, desc_b + 2u * k, idesc,
+                                            (ks > 0 || k > 0) ? 1u : 0u);
+                    }
+                    ptx::umma_commit_1cta(ptx::smem_u32(&aux->empty_bar[stage]));
+                    if (++stage == kStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (ok) ptx::umma_commit_1cta(ptx::smem_u32(&aux->acc_full_bar[buf]));
+            }
+            if (!ok) atomicOr(p.counters + 2, kErrMmaWait);
+        }
+    } else {
+        // ------------------------- Epilogue -----------------------------
+        const int quarter = warp & 3;               // TMEM lane quarter this warp may access
+        const int row_in_tile = quarter * 32 + lane;
+        const int epi_tid = threadIdx.x - 64;       // 0..127
+        const float inf = __int_as_float(0x7f800000);
+        bool ok = true;
+        long long it = 0;
+        for (long long t = first_tile; t < p.total_tiles; t += tile_step, ++it) {
+            int tm, tn;
+            tile_coords(p, t, tm, tn);
+            const int buf = static_cast<int>(it & 1);
+            const uint32_t acc_phase = static_cast<uint32_t>((it >> 1) & 1);
+            const int q = p.q_begin + tm * kTileM + row_in_tile;
+            const int c_base = tn * kTileN;
+
+            // Stage the tile's candidate norms; padding columns get +inf so they can never hit.
+            float* cn = aux->cand_norms[buf];
+            for (int j = epi_tid; j < kTileN; j += kEpiThreads) {
+                const int c = c_base + j;
+                cn[j] = (c < p.n) ? __ldg(p.norms + c) : inf;
+            }
+            const float sq = (q < p.q_end) ? __ldg(p.norms + q) : inf;
+            ptx::named_bar_sync(1, kEpiThreads);
+
+            if (ok) ok = ptx::mbar_wait_bounded(ptx::smem_u32(&aux->acc_full_bar[buf]), acc_phase, abort_flag,
+                                                kWaitLimitNs);
+            if (!ok) continue;  // keep taking part in the named barrier, do nothing else
+            ptx::tc_fence_after_sync();
+
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                                   static_cast<uint32_t>(buf * kTileN);
+            const unsigned long long qkey = static_cast<unsigned long long>(static_cast<uint32_t>(q)) << 32;
+#pragma unroll 1
+            for (int c0 = 0; c0 < kTileN; c0 += 32) {
+                uint32_t v[32];
+                ptx::tmem_ld_32x32b_x32(taddr + c0, v);
+                ptx::tmem_ld_wait();
+                uint32_t mask = 0;
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const float d2 = (sq + cn[c0 + j]) - 2.0f * __uint_as_float(v[j]);
+                    if (d2 <= p.eps2) mask |= (1u << j);
+                }
+                if (__any_sync(0xffffffffu, mask != 0)) {
+                    const uint32_t cnt = __popc(mask);
+                    uint32_t incl = cnt;
+#pragma unroll
+                    for (int o = 1; o < 32; o <<= 1) {
+                        const uint32_t up = __shfl_up_sync(0xffffffffu, incl, o);
+                        if (lane >= o) incl += up;
+                    }
+                    const uint32_t total = __shfl_sync(0xffffffffu, incl, 31);
+                    unsigned long long base = 0;
+                    if (lane == 0) {
+                        base = atomicAdd(p.counters + 0, static_cast<unsigned long long>(total));
+                        if (base < p.capacity) {
+                            const unsigned long long room = p.capacity - base;
+                            atomicAdd(p.counters + 1, room < total ? room : static_cast<unsigned long long>(total));
+                        }
+                    }
+                    base = __shfl_sync(0xffffffffu, base, 0);
+                    unsigned long long slot = base + (incl - cnt);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        if (mask & (1u << j)) {
+                            if (slot < p.capacity) {
+                                p.keys[slot] = qkey | static_cast<unsigned long long>(static_cast<uint32_t>(c_base + c0 + j));
+                                if (p.dist2)
+                                    p.dist2[slot] = (sq + cn[c0 + j]) - 2.0f * __uint_as_float(v[j]);
+                            }
+                            ++slot;
+                        }
+                    }
+                }
+            }
+            // Hand the accumulator back to the MMA warp.
+            ptx::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&aux->acc_empty_bar[buf]));
+        }
+        if (!ok && lane == 0) atomicOr(p.counters + 2, kErrEpilogueWait);
+    }
+
+    // Teardown: everyone meets, then the allocating warp frees TMEM.
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc<1>(tmem_base, kTmemCols);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Helpers
+// ---------------------------------------------------------------------------
+
+// Sorted packed keys -> {int query; int candidate} records, the reference's
+// Pair layout (source/pair.cuh:27-30).
+__global__ void unpack_pairs_kernel(const unsigned long long* __restrict__ keys, int2* __restrict__ out,
+                                    unsigned long long count) {
+    const unsigned long long stride = static_cast<unsigned long long>(gridDim.x) * blockDim.x;
+    for (unsigned long long i = static_cast<unsigned long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < count;
+         i += stride) {
+        const unsigned long long k = keys[i];
+        out[i] = make_int2(static_cast<int>(k >> 32), static_cast<int>(k & 0xffffffffull));
+    }
+}
+
+__device__ __forceinline__ uint64_t mix64(uint64_t z) {
+    z += 0x9e3779b97f4a7c15ull;
+    z = (z ^ (z >> 30)) * 0xbf58476d1ce4e5b9ull;
+    z = (z ^ (z >> 27)) * 0x94d049bb133111ebull;
+    return z ^ (z >> 31);
+}
+
+// Counter-based synthetic data: coordinate (i, k) = Exponential(lambda) drawn
+// from a hash of (seed, i*d + k), rejected to [0, max_value], rounded
+// double -> float -> half like the reference's loader.  Used for the large
+// benchmark shapes, where the reference's sequential host generator
+// (source/DataLoader/ExponentialPointGenerator.hpp:42-52) would take minutes;
+// the distribution is the same, the stream is not.
+__global__ void gen_exponential_kernel(__half* __restrict__ out, long long n, int d, int ld, double lambda,
+                                       double max_value, unsigned long long seed) {
+    const long long chunks_per_row = ld / 8;
+    const long long total = n * chunks_per_row;
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long g = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; g < total; g += stride) {
+        const long long row = g / chunks_per_row;
+        const int k0 = static_cast<int>(g - row * chunks_per_row) * 8;
+        __align__(16) __half h[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int k = k0 + j;
+            float f = 0.0f;
+            if (k < d) {
+                const uint64_t ctr = static_cast<uint64_t>(row) * static_cast<uint64_t>(d) + static_cast<uint64_t>(k);
+                double v;
+                uint64_t attempt = 0;
+                do {
+                    const uint64_t r = mix64(mix64(seed ^ (attempt * 0xd1342543de82ef95ull)) + ctr);
+                    const double u = (static_cast<double>(r >> 11) + 0.5) * (1.0 / 9007199254740992.0);
+                    v = -log(u) / lambda;
+                    ++attempt;
+                } while (v > max_value && attempt < 64);
+                f = static_cast<float>(v);
+            }
+            h[j] = __float2half_rn(f);
+        }
+        *reinterpret_cast<uint4*>(out + row * ld + k0) = *reinterpret_cast<const uint4*>(h);
+    }
+}
+
+// FP64 brute-force squared distances of sampled query rows against all
+// candidates (accuracy reporting only; plain CUDA cores).  One CTA per
+// (sample, candidate block); counts, per sample, the candidates with
+// d2 <= eps2 and optionally records them.
+__global__ void brute_f64_kernel(const __half* __restrict__ pts, int n, int d, int ld,
+                                 const int* __restrict__ sample_rows, int n_samples, double eps2,
+                                 unsigned long long* __restrict__ counts, unsigned long long* __restrict__ keys,
+                                 unsigned long long capacity, unsigned long long* __restrict__ n_keys) {
+    extern __shared__ float qrow[];
+    const int s = blockIdx.y;
+    const int q = sample_rows[s];
+    for (int k = threadIdx.x; k < d; k += blockDim.x) qrow[k] = __half2float(pts[static_cast<long long>(q) * ld + k]);
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    unsigned long long local = 0;
+    for (int c = blockIdx.x * nwarps + warp; c < n; c += gridDim.x * nwarps) {
+        const __half* row = pts + static_cast<long long>(c) * ld;
+        double acc = 0.0;
+        for (int k = lane; k < d; k += 32) {
+            const double t = static_cast<double>(qrow[k]) - static_cast<double>(__half2float(row[k]));
+            acc += t * t;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (lane == 0 && acc <= eps2) {
+            ++local;
+            if (keys) {
+                const unsigned long long slot = atomicAdd(n_keys, 1ull);
+                if (slot < capacity)
+                    keys[slot] = (static_cast<unsigned long long>(static_cast<uint32_t>(q)) << 32) |
+                                 static_cast<unsigned long long>(static_cast<uint32_t>(c));
+            }
+        }
+    }
+    if (lane == 0 && local) atomicAdd(counts + s, local);
+}
+
+}  // namespace fasted

@@ -1,0 +1,198 @@
+/* C ABI of the B200 epsilon self-join library (libfasted.so, also loadable
+ * under the reference's file name main.so).
+ *
+ * Two layers:
+ *   1. The four entry points of the reference's shared library, with the same
+ *      names, argument meaning and by-value Results struct, so that the
+ *      reference's ctypes driver loads this library unchanged.
+ *   2. A context API with plain pointers and sizes for callers that own their
+ *      buffers (tests, benchmarks, multi-GPU band sharding).
+ *
+ * All functions are host functions; none is thread-safe with respect to the
+ * same context.  Functions of layer 2 return 0 on success and a negative
+ * FASTED_E* code on failure; fasted_last_error() gives the message.
+ * There is no CPU fallback: without a usable sm_100 device every compute call
+ * fails.
+ */
+#ifndef FASTED_H_
+#define FASTED_H_
+
+#include <stdbool.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------------
+ * Layer 1: drop-in for the reference's shared-library interface
+ * ---------------------------------------------------------------------- */
+
+/* Replaces Mma::mmaShape, source/ptxMma.cuh:27-31. */
+typedef struct mmaShape {
+    int m, n, k;
+} mmaShape;
+
+/* Replaces SimSearch::Results, source/findPairs.cuh:37-46 (56 bytes, returned
+ * by value; mirrored by results/scripts/experiment/find_pairs.py:24-50).
+ * totalTime: wall seconds from entry to after sort + device-to-host copy.
+ * TFLOPS: 2*N*N*D / kernel seconds / 1e12 over the un-padded N and D, kernel
+ * seconds = row-norm kernel + join kernel (source/findPairs.cuh:728-748).
+ * pairsFound counts every hit, self pairs and both orientations included;
+ * pairsStored counts those that fitted in the pair buffer. */
+typedef struct Results {
+    double totalTime;
+    double TFLOPS;
+    unsigned long long pairsFound;
+    unsigned long long pairsStored;
+    mmaShape inputProblemShape;
+    mmaShape paddedProblemShape;
+} Results;
+
+/* Replaces runFromExponentialDataset, source/main.cu:66-67 (declaration) and
+ * :251-261 (definition).  Generates the seeded synthetic dataset
+ * (source/DataLoader/ExponentialPointGenerator.hpp), uploads it and joins.
+ * maxValue is the rejection upper bound of the generator. */
+Results runFromExponentialDataset(int size, int dimensionality, double lambda, double maxValue, double epsilon,
+                                  bool savePairs);
+
+/* Replaces runFromFile, source/main.cu:53 and :263-273.  CSV: one point per
+ * line, comma separated, no header; the first row fixes the dimension. */
+Results runFromFile(const char* filename, double epsilon, bool savePairs);
+
+/* Replaces reRun, source/main.cu:43 and :275-278: joins the resident dataset
+ * again with another epsilon.  Calling it before a runFrom* call is an error
+ * (the reference leaves that case undefined). */
+Results reRun(double epsilon, bool savePairs);
+
+/* Replaces releaseResources, source/main.cu:73 and :280 (whose body recurses
+ * forever in the reference; the intent, SimSearch::releaseGlobalMemory at
+ * source/findPairs.cuh:766-776, is what is implemented). */
+void releaseResources(void);
+
+/* Errors in layer 1 follow the reference (source/main.cu:244-247,
+ * source/utils.cuh:22-29): message on stdout, then exit(EXIT_FAILURE).
+ *
+ * Environment switches of layer 1 (all optional):
+ *   FASTED_OUTPUT_DIR   directory for "<dataset>_<eps>.pairs" when savePairs
+ *                       is true (default /scratch/bc2497/pairsData/, the path
+ *                       hard-wired at source/main.cu:214-215)
+ *   FASTED_DEVICE       CUDA device ordinal (default 0, source/findPairs.cuh:622)
+ *   FASTED_WRITE_DIST   "1": third text column sqrt(d2) in the .pairs file
+ */
+
+/* ------------------------------------------------------------------------
+ * Layer 2: context API
+ * ---------------------------------------------------------------------- */
+
+typedef struct fasted_ctx fasted_ctx;
+
+enum {
+    FASTED_OK = 0,
+    FASTED_EINVAL = -1,   /* bad argument */
+    FASTED_ECUDA = -2,    /* CUDA runtime / driver error */
+    FASTED_ENODEV = -3,   /* no sm_100 device */
+    FASTED_ESTATE = -4,   /* call out of order (e.g. join before points) */
+    FASTED_EKERNEL = -5,  /* a device-side wait ran out; status bits in the message */
+    FASTED_EIO = -6       /* file error */
+};
+
+enum {
+    FASTED_JOIN_DIST2 = 1,       /* also record the FP32 squared distance of every stored pair */
+    FASTED_JOIN_NO_SORT = 2,     /* leave stored pairs in device order (count-only / timing runs) */
+    FASTED_JOIN_KEEP_NORMS = 4   /* reuse row norms computed by an earlier call on the same points */
+};
+
+typedef struct fasted_join_stats {
+    unsigned long long pairs_found;
+    unsigned long long pairs_stored;
+    double norms_ms;   /* row-norm kernel, device time */
+    double join_ms;    /* join kernel, device time */
+    double kernel_ms;  /* start of norms to end of join (the reference's TFLOPS interval) */
+    double sort_ms;    /* sort + unpack, device time */
+    unsigned long long status;  /* device status bits, 0 = clean */
+    int tiles_m, tiles_n;
+    int grid;
+} fasted_join_stats;
+
+const char* fasted_last_error(void);
+
+/* Creates a context on CUDA device `device` (must be compute capability 10.x). */
+int fasted_create(int device, fasted_ctx** out);
+void fasted_destroy(fasted_ctx* ctx);
+
+/* Uses `stream` (a cudaStream_t) for all work of this context; default is a
+ * stream the context creates. */
+int fasted_set_stream(fasted_ctx* ctx, void* stream);
+
+/* Dataset, replaces TransferPointsToGMem / allocateTransferPoints,
+ * source/findPairs.cuh:560-590 (one device copy instead of two: query and
+ * candidate sets are the same matrix).
+ * host: n rows of binary16 values, row stride ld_host elements (>= d).
+ * The device copy has row stride = d rounded up to a multiple of 64, zero
+ * padded (source/main.cu:207, source/DataLoader/PointListBuilder.hpp:34-39). */
+int fasted_set_points_host_f16(fasted_ctx* ctx, const uint16_t* host, int64_t n, int64_t d, int64_t ld_host);
+
+/* Borrow a device matrix (e.g. one received by an NCCL broadcast).  dev must
+ * be 16-byte aligned and ld a multiple of 8 elements; columns [d, ld) must be
+ * zero if ld > d.  The caller keeps ownership and must keep it alive. */
+int fasted_set_points_device_f16(fasted_ctx* ctx, const void* dev, int64_t n, int64_t d, int64_t ld);
+
+/* Allocate an n x d dataset on the device and fill it with the counter-based
+ * Exponential(lambda) generator (values rejected to [0, max_value], rounded
+ * double -> float -> half).  For benchmark shapes too large for the reference's
+ * sequential host generator. */
+int fasted_generate_exponential(fasted_ctx* ctx, int64_t n, int64_t d, double lambda, double max_value,
+                                uint64_t seed);
+
+/* Device pointer / shape of the resident dataset. */
+int fasted_points_info(fasted_ctx* ctx, void** dev, int64_t* n, int64_t* d, int64_t* ld);
+/* Copy the resident dataset to the host (row stride ld_host >= d). */
+int fasted_get_points_host_f16(fasted_ctx* ctx, uint16_t* host, int64_t ld_host);
+
+/* Row norms, replaces SumSqd::ComputeSquaredSums, source/sumSquared.cuh:84-118.
+ * Result stays on the device; ms (optional) receives the kernel time. */
+int fasted_row_norms(fasted_ctx* ctx, double* ms);
+int fasted_get_norms(fasted_ctx* ctx, float* host_out);
+
+/* The join, replaces SimSearch::FindPairs, source/findPairs.cuh:615-764, for
+ * query rows [q_begin, q_end) against all n candidates (q_end = -1 means n).
+ * capacity = pair-buffer size in pairs (0: the reference's n*256 rule capped by
+ * free device memory, source/findPairs.cuh:642-647, source/pair.cuh:69-91).
+ * Results stay on the device, sorted row-major unless FASTED_JOIN_NO_SORT. */
+int fasted_join(fasted_ctx* ctx, double eps, int64_t q_begin, int64_t q_end, uint64_t capacity, unsigned flags,
+                fasted_join_stats* stats);
+
+/* Copy stored pairs [first, first + count) of the last join to the host as
+ * (query, candidate) int32 records, replaces Pairs::getPairs,
+ * source/pair.cuh:139-146.  dist2_out may be null. */
+int fasted_get_pairs(fasted_ctx* ctx, uint64_t first, uint64_t count, int32_t* pairs_out, float* dist2_out);
+
+/* Device pointers of the last join's results (int2 records, float distances). */
+int fasted_pairs_device(fasted_ctx* ctx, void** pairs_dev, void** dist2_dev);
+
+/* FP64 brute-force check on the device (accuracy reporting): for each of the
+ * n_samples query rows counts the candidates with FP64 d2 <= eps*eps. */
+int fasted_brute_force_f64(fasted_ctx* ctx, const int32_t* sample_rows, int n_samples, double eps,
+                           unsigned long long* counts_out);
+
+/* Host-side dataset builders (no GPU involved), the loaders behind layer 1.
+ * Exponential: replaces SimSearch::ExponentialPointGenerator,
+ * source/DataLoader/ExponentialPointGenerator.hpp:22-52, plus the
+ * double -> float -> half rounding of source/DataLoader/PointListBuilder.hpp:57-66.
+ * CSV: replaces SimSearch::FilePointGenerator, source/DataLoader/FilePointGenerator.hpp:20-56,
+ * with the shape rule of PointListBuilder.hpp:154-163 (ragged rows are FASTED_EINVAL,
+ * unreadable files FASTED_EIO).  out rows have stride ld_out >= d; columns
+ * [d, ld_out) are zeroed. */
+int fasted_dataset_exponential_f16(int64_t n, int64_t d, double lambda, double max_value, uint16_t* out,
+                                   int64_t ld_out);
+int fasted_dataset_csv_shape(const char* path, int64_t* n, int64_t* d);
+int fasted_dataset_csv_f16(const char* path, uint16_t* out, int64_t n, int64_t d, int64_t ld_out);
+
+/* Tuning knobs: "band_tiles" (tile rows per raster band), "grid" (CTAs, 0 = one per SM). */
+int fasted_set_option(fasted_ctx* ctx, const char* name, int64_t value);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FASTED_H_ */

@@ -1,0 +1,228 @@
+"""The join through the C ABI vs the CPU oracle on the same inputs.
+
+Bar (for this FP16 -> FP32 path): pair sets identical except for pairs whose FP64 squared distance
+lies within 1e-3 * eps^2 of eps^2; emitted squared distances within 1e-3 relative."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+from conftest import GOLDEN
+from util import assert_dist_close, assert_pairs_match, assert_sorted_unique
+
+pytestmark = pytest.mark.gpu
+
+BAND = 1e-3
+
+
+def _eps_for_mean_neighbours(oracle_mod, pts, target):
+    """Epsilon giving about `target` neighbours per point, from FP64 distances of a row sample."""
+    f = pts.view(np.float16).astype(np.float64)
+    rows = f[: max(8, len(f) // 100)]
+    d2 = ((rows ** 2).sum(1)[:, None] + (f ** 2).sum(1)[None, :] - 2 * rows @ f.T).ravel()
+    q = min(1.0, (target + 1) / len(f))
+    return float(np.sqrt(max(np.quantile(d2, q), 1e-12)))
+
+
+@pytest.mark.parametrize("n,d,target", [
+    (64, 64, 4), (128, 64, 8), (256, 128, 8), (257, 64, 8), (300, 100, 8), (1000, 64, 16),
+    (1024, 192, 16), (777, 333, 8), (2048, 128, 32), (520, 1024, 8),
+])
+def test_join_matches_oracle_small(gpu_join, oracle_mod, n, d, target):
+    rng = np.random.default_rng(n * 31 + d)
+    pts = oracle_mod.double_to_half(rng.exponential(1 / 40.0, size=(n, d)))
+    eps = _eps_for_mean_neighbours(oracle_mod, pts, target)
+    gpu_join.set_points(pts)
+    st = gpu_join.join(eps, flags=1)
+    got, d2 = gpu_join.pairs(with_dist2=True)
+    want, _ = oracle_mod.join_fp16_fp32(pts, eps)
+    assert st.status == 0 and st.pairs_found == st.pairs_stored == len(got)
+    assert_sorted_unique(oracle_mod, got)
+    assert_pairs_match(oracle_mod, pts, d, eps, got, want, BAND, f"{n}x{d}")
+    assert_dist_close(oracle_mod, pts, d, got, d2)
+    # every real point pairs with itself at these epsilons, nothing refers to padding
+    assert got.min() >= 0 and got.max() < n
+    assert np.isin(oracle_mod.pair_keys(np.stack([np.arange(n)] * 2, 1)), oracle_mod.pair_keys(got)).all()
+
+
+def test_join_config1_reference_dataset(gpu_join, oracle_mod):
+    # 4096 x 128 seeded synthetic dataset, eps for ~32 neighbours per point.
+    g = json.load(open(os.path.join(GOLDEN, "config1_fp64.json")))
+    pts = oracle_mod.gen_exponential(g["n"], g["d"])
+    gpu_join.set_points(pts)
+    st = gpu_join.join(g["epsilon"], flags=1)
+    got, d2 = gpu_join.pairs(with_dist2=True)
+    want32, _ = oracle_mod.join_fp16_fp32(pts, g["epsilon"])
+    want64, _, found64 = oracle_mod.join_fp64(pts, g["epsilon"])
+    assert found64 == g["pairs_fp64"]
+    cmp32 = assert_pairs_match(oracle_mod, pts, g["d"], g["epsilon"], got, want32, BAND, "vs restated reference")
+    cmp64 = assert_pairs_match(oracle_mod, pts, g["d"], g["epsilon"], got, want64, BAND, "vs FP64")
+    assert cmp32["only_a"] + cmp32["only_b"] <= 64 and cmp64["only_a"] + cmp64["only_b"] <= 64
+    assert abs(int(st.pairs_found) - g["pairs_fp64"]) <= 64
+    assert_dist_close(oracle_mod, pts, g["d"], got, d2)
+
+
+@pytest.mark.parametrize("idx", range(4))
+def test_join_selfpair_goldens(gpu_join, oracle_mod, idx):
+    # The reference's stored results for its seeded synthetic mode at eps = 0.001: pairsFound == N.
+    rows = [r for r in json.load(open(os.path.join(GOLDEN, "selfpair_counts.json"))) if r["n"] <= 21544]
+    rows = sorted(rows, key=lambda r: (r["n"], r["d"]))[::3][:4]
+    r = rows[idx]
+    pts = oracle_mod.gen_exponential(r["n"], r["d"])
+    gpu_join.set_points(pts)
+    st = gpu_join.join(r["epsilon"])
+    got = gpu_join.pairs()
+    assert st.pairs_found == r["pairsFound"]
+    assert np.array_equal(got[:, 0], np.arange(r["n"])) and np.array_equal(got[:, 1], np.arange(r["n"]))
+
+
+def test_join_unit_vectors_gaussian(gpu_join, oracle_mod):
+    # Shape family of the mid-size config: N(0,1) rows normalised to unit length.
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal((3000, 384)).astype(np.float32)
+    x /= np.linalg.norm(x, axis=1, keepdims=True)
+    pts = oracle_mod.double_to_half(x.astype(np.float64))
+    eps = _eps_for_mean_neighbours(oracle_mod, pts, 16)
+    gpu_join.set_points(pts)
+    gpu_join.join(eps, flags=1)
+    got, d2 = gpu_join.pairs(with_dist2=True)
+    want, _ = oracle_mod.join_fp16_fp32(pts, eps)
+    assert_pairs_match(oracle_mod, pts, 384, eps, got, want, BAND, "unit vectors")
+    assert_dist_close(oracle_mod, pts, 384, got, d2)
+
+
+def test_join_dense_clusters(gpu_join, oracle_mod):
+    # Output-heavy case: tight clusters, most entries of a tile hit.
+    rng = np.random.default_rng(5)
+    centres = rng.uniform(0, 1, size=(6, 96))
+    which = rng.integers(0, 6, size=1500)
+    pts = oracle_mod.double_to_half(centres[which] + rng.normal(0, 0.05, size=(1500, 96)))
+    eps = 0.9
+    gpu_join.set_points(pts)
+    st = gpu_join.join(eps)
+    got = gpu_join.pairs()
+    want, _ = oracle_mod.join_fp16_fp32(pts, eps)
+    assert st.pairs_found > 200_000
+    assert_sorted_unique(oracle_mod, got)
+    assert_pairs_match(oracle_mod, pts, 96, eps, got, want, BAND, "dense clusters")
+
+
+def test_join_edge_epsilons(gpu_join, oracle_mod):
+    pts = oracle_mod.gen_exponential(500, 64)
+    gpu_join.set_points(pts)
+    # eps = 0: d2(i,i) is exactly 0 only when s_i + s_i == 2 a_ii bit for bit; compare with >= nothing else
+    st = gpu_join.join(0.0)
+    got = gpu_join.pairs()
+    assert (got[:, 0] == got[:, 1]).all() or len(got) == 0
+    # huge eps: everything pairs, padding never does
+    st = gpu_join.join(1e3)
+    assert st.pairs_found == 500 * 500
+    got = gpu_join.pairs()
+    assert np.array_equal(oracle_mod.pair_keys(got),
+                          oracle_mod.pair_keys(np.stack(np.meshgrid(np.arange(500), np.arange(500), indexing="ij"), -1).reshape(-1, 2)))
+    # identical points: all-zero rows pair with each other at eps 0
+    z = np.zeros((130, 64), dtype=np.uint16)
+    gpu_join.set_points(z)
+    assert gpu_join.join(0.0).pairs_found == 130 * 130
+
+
+def test_join_overflow_semantics(gpu_join, oracle_mod):
+    # Pair buffer too small: found keeps counting, stored saturates at the capacity
+    # (source/pair.cuh:123-133 of the reference).
+    pts = oracle_mod.gen_exponential(600, 64)
+    gpu_join.set_points(pts)
+    full = gpu_join.join(0.25)
+    assert full.pairs_found == full.pairs_stored > 5000
+    st = gpu_join.join(0.25, capacity=1000)
+    assert st.pairs_found == full.pairs_found and st.pairs_stored == 1000
+    got = gpu_join.pairs()
+    assert len(got) == 1000
+    gpu_join.join(0.25)
+    allp = oracle_mod.pair_keys(gpu_join.pairs())
+    assert np.isin(oracle_mod.pair_keys(got), allp).all() and len(np.unique(oracle_mod.pair_keys(got))) == 1000
+
+
+def test_join_bands_concatenate(gpu_join, oracle_mod):
+    # Query-row bands (the multi-GPU sharding unit): concatenation in band order == full join.
+    pts = oracle_mod.gen_exponential(1500, 128)
+    gpu_join.set_points(pts)
+    eps = 0.3
+    gpu_join.join(eps)
+    full = gpu_join.pairs()
+    parts = []
+    for a, b in [(0, 384), (384, 385), (385, 1000), (1000, 1500)]:
+        gpu_join.join(eps, q_begin=a, q_end=b)
+        p = gpu_join.pairs()
+        assert len(p) == 0 or (p[:, 0].min() >= a and p[:, 0].max() < b)
+        parts.append(p)
+    assert np.array_equal(np.concatenate(parts), full)
+    st = gpu_join.join(eps, q_begin=700, q_end=700)
+    assert st.pairs_found == 0
+
+
+def test_join_rerun_is_idempotent_and_monotone(gpu_join, oracle_mod):
+    pts = oracle_mod.gen_exponential(2000, 64)
+    gpu_join.set_points(pts)
+    a = gpu_join.join(0.2)
+    pa = gpu_join.pairs()
+    b = gpu_join.join(0.2, flags=4)  # keep norms
+    pb = gpu_join.pairs()
+    assert a.pairs_found == b.pairs_found and np.array_equal(pa, pb)
+    c = gpu_join.join(0.22)
+    assert c.pairs_found >= a.pairs_found
+    assert np.isin(oracle_mod.pair_keys(pa), oracle_mod.pair_keys(gpu_join.pairs())).all()
+
+
+def test_join_device_pointer_input(gpu_join, oracle_mod):
+    import torch
+    pts = oracle_mod.gen_exponential(900, 128)
+    gpu_join.set_points(pts)
+    gpu_join.join(0.3)
+    want = gpu_join.pairs()
+    t = torch.from_numpy(pts.view(np.int16)).cuda()
+    gpu_join.set_points_device(t.data_ptr(), 900, 128, 128, keepalive=t)
+    gpu_join.join(0.3)
+    assert np.array_equal(gpu_join.pairs(), want)
+
+
+def test_join_argument_errors(gpu_join, oracle_mod):
+    from fasted_b200 import FastedError
+    pts = oracle_mod.gen_exponential(100, 64)
+    gpu_join.set_points(pts)
+    with pytest.raises(FastedError):
+        gpu_join.join(0.1, q_begin=50, q_end=200)
+    with pytest.raises(FastedError):
+        gpu_join.join(-1.0)
+    with pytest.raises(FastedError):
+        gpu_join.set_points(np.zeros((0, 64), dtype=np.uint16))
+
+
+def test_join_midsize_properties(gpu_join, oracle_mod):
+    # Larger than the oracle can brute-force quickly: size-independent properties.
+    n, d = 40_000, 256
+    gpu_join.generate_exponential(n, d)
+    pts = gpu_join.get_points()
+    eps = _eps_for_mean_neighbours(oracle_mod, pts, 16)
+    st = gpu_join.join(eps, flags=1)
+    got, d2 = gpu_join.pairs(with_dist2=True)
+    assert st.pairs_found == st.pairs_stored == len(got)
+    assert_sorted_unique(oracle_mod, got)
+    keys = oracle_mod.pair_keys(got)
+    # symmetry and the diagonal
+    assert np.array_equal(np.sort(oracle_mod.pair_keys(got[:, ::-1])), keys)
+    assert np.isin(oracle_mod.pair_keys(np.stack([np.arange(n)] * 2, 1)), keys).all()
+    # every emitted pair is a true neighbour up to the band, distances agree with FP64
+    true_d2 = oracle_mod.pair_d2_fp64(pts, got, d)
+    assert (true_d2 <= eps * eps * (1 + BAND)).all()
+    assert_dist_close(oracle_mod, pts, d, got, d2)
+    # completeness on sampled rows, against both the CPU FP64 join and the device FP64 check
+    rows = np.arange(0, n, n // 64)[:64]
+    counts_dev = gpu_join.brute_force_counts(rows, eps)
+    for i, r in enumerate(rows[:8]):
+        want, _, _ = oracle_mod.join_fp64(pts, eps, q_begin=int(r), q_end=int(r) + 1)
+        mine = got[got[:, 0] == r]
+        assert_pairs_match(oracle_mod, pts, d, eps, mine, want, BAND, f"row {r}")
+        assert abs(int(counts_dev[i]) - len(want)) == 0
+    per_row = np.bincount(got[:, 0], minlength=n)[rows]
+    assert np.abs(per_row.astype(np.int64) - counts_dev.astype(np.int64)).max() <= 2

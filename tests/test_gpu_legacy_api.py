@@ -1,0 +1,84 @@
+"""The reference's own interface (four C entry points + CLI) on the GPU, driven the way the
+reference's Python scripts and shell users drive it."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+from conftest import GOLDEN, ROOT
+
+pytestmark = pytest.mark.gpu
+
+_DRIVER = r"""
+import json, sys
+sys.path.insert(0, {root!r})
+from fasted_b200.find_pairs import load_findpairs, RerunnablePairsFinder
+lib = load_findpairs()
+out = []
+finder = RerunnablePairsFinder(lambda e, s: lib.runFromExponentialDataset(1000, 64, 40.0, 10.0, e, s), lib.reRun)
+for eps, save in [(0.001, False), (0.2, True), (0.001, False)]:
+    r = finder(eps, save)
+    out.append(dict(found=r.pairsFound, stored=r.pairsStored, tflops=r.TFLOPS, total=r.totalTime,
+                    inp=[r.inputProblemShape.m, r.inputProblemShape.n, r.inputProblemShape.k],
+                    pad=[r.paddedProblemShape.m, r.paddedProblemShape.n, r.paddedProblemShape.k],
+                    sel=r.get_selectivity()))
+r = lib.runFromFile({csv!r}.encode(), 10.0, True)
+out.append(dict(found=r.pairsFound, inp=[r.inputProblemShape.m, r.inputProblemShape.n, r.inputProblemShape.k]))
+lib.releaseResources()
+lib.releaseResources()
+print("JSON" + json.dumps(out))
+"""
+
+
+def test_reference_python_driver_flow(native_lib, oracle_mod, tmp_path):
+    env = dict(os.environ, FASTED_OUTPUT_DIR=str(tmp_path))
+    code = _DRIVER.format(root=ROOT, csv=os.path.join(GOLDEN, "small.csv"))
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env, timeout=600)
+    assert r.returncode == 0, r.stdout + r.stderr
+    out = json.loads(r.stdout.split("JSON")[-1])
+    # golden: only the N self pairs at eps = 0.001 (reference's stored results for this seeded dataset)
+    assert out[0]["found"] == out[0]["stored"] == 1000 and out[0]["sel"] == 0
+    assert out[0]["inp"] == [1000, 1000, 64] and out[0]["pad"][2] == 64 and out[0]["pad"][0] >= 1000
+    assert out[2]["found"] == 1000
+    assert out[0]["tflops"] > 0 and out[0]["total"] > 0
+    # reRun with a larger eps against the oracle, and the saved file in the reference's text format
+    pts = oracle_mod.gen_exponential(1000, 64)
+    want, _ = oracle_mod.join_fp16_fp32(pts, 0.2)
+    assert abs(out[1]["found"] - len(want)) <= 4
+    path = tmp_path / ("_" + f"{0.2:.6f}" + ".pairs")  # dataset name is empty on reRun, like the reference
+    text = path.read_text().splitlines()
+    assert len(text) == out[1]["stored"]
+    got = np.array([[int(a) for a in line.split(", ")] for line in text], dtype=np.int32)
+    cmp = oracle_mod.compare_pair_sets(pts, 64, 0.2, got, want, band=1e-3)
+    assert cmp["ok"]
+    # CSV run: 5 points, huge eps -> all 25 ordered pairs; file named after the CSV stem
+    assert out[3]["found"] == 25 and out[3]["inp"] == [5, 5, 6]
+    assert (tmp_path / ("small_" + f"{10.0:.6f}" + ".pairs")).exists()
+    # the reference's stdout lines that scripts grep for
+    for needle in ["Running from a generated exponential dataset", "Building point list", "Number of points is: 1000",
+                   "Padded Search Dimensions:", "Input Search Dimensions:", "Number of pairs found 1000",
+                   "Total Kernel Elapsed time:", "Pairs found: 1000", "Estimated TFLOPS", "Running from file: "]:
+        assert needle in r.stdout, needle
+
+
+def test_rerun_before_run_is_an_error(native_lib):
+    code = ("import sys; sys.path.insert(0, %r)\n"
+            "from fasted_b200.find_pairs import load_findpairs\n"
+            "load_findpairs().reRun(0.1, False)\n") % ROOT
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 1 and "Error: Failed to run." in r.stdout
+
+
+def test_cli_synthetic_and_file(native_lib, tmp_path):
+    from fasted_b200 import _lib
+    exe = os.path.join(os.path.dirname(_lib.LIB_PATH), "main")
+    r = subprocess.run([exe, "-e", "2154", "64", "0.001"], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "Pairs found: 2154" in r.stdout and "Estimated TFLOPS" in r.stdout
+    r = subprocess.run([exe, os.path.join(GOLDEN, "small.csv"), "10"], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "Pairs found: 25" in r.stdout
+    r = subprocess.run([exe, str(tmp_path / "nope.csv"), "1"], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 1 and "Error: Failed to run." in r.stdout

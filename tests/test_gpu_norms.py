@@ -1,0 +1,52 @@
+"""Row-norm kernel vs the oracle: bit-exact (FP32 round-toward-zero chain)."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("n,d", [(1, 1), (7, 2), (128, 64), (129, 65), (300, 100), (1000, 64), (513, 384),
+                                 (2048, 128), (257, 1000), (4096, 128), (100, 4096), (3000, 777)])
+def test_norms_bit_exact(gpu_join, oracle_mod, n, d):
+    rng = np.random.default_rng(n * 7919 + d)
+    vals = rng.exponential(1 / 40.0, size=(n, d))
+    if d > 2:
+        vals[:, 1] *= -1  # signs must not matter
+    pts = oracle_mod.double_to_half(vals)
+    gpu_join.set_points(pts)
+    got, ms = gpu_join.row_norms()
+    want = oracle_mod.row_norms(pts)
+    assert got.dtype == np.float32 and got.shape == (n,)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    assert ms >= 0
+
+
+def test_norms_increasing_integers_known_answer(gpu_join, oracle_mod):
+    # tests/python/sumSquared/sumSquared.py:3-11 of the reference (matrix of source/main.cu:86-104)
+    vals = np.arange(32 * 64, dtype=np.float64).reshape(32, 64)
+    pts = oracle_mod.double_to_half(vals)
+    gpu_join.set_points(pts)
+    got, _ = gpu_join.row_norms()
+    want = (vals ** 2).sum(axis=1)
+    exact = want < 2 ** 24
+    assert np.array_equal(got[exact].astype(np.float64), want[exact])
+    assert np.array_equal(got, oracle_mod.row_norms(pts))
+
+
+def test_norms_reference_dataset(gpu_join, oracle_mod):
+    pts = oracle_mod.gen_exponential(4096, 128)
+    gpu_join.set_points(pts)
+    got, _ = gpu_join.row_norms()
+    assert np.array_equal(got, oracle_mod.row_norms(pts))
+
+
+def test_norms_large_property(gpu_join):
+    # Size-independent property at a larger size: device-generated data, norms of duplicated
+    # halves are equal and every norm is within RZ bounds of the FP64 sum.
+    gpu_join.generate_exponential(200_000, 512)
+    pts = gpu_join.get_points()
+    got, ms = gpu_join.row_norms()
+    f = pts.view(np.float16).astype(np.float64)
+    want = (f * f).sum(axis=1)
+    rel = (want - got) / want
+    assert (rel > -1e-7).all() and (rel < 512 * 2.0 ** -23).all()

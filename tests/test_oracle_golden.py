@@ -1,0 +1,127 @@
+"""The CPU oracle against the reference's own golden material (no GPU)."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+from conftest import GOLDEN
+
+
+def _load(name):
+    return json.load(open(os.path.join(GOLDEN, name)))
+
+
+def test_generator_matches_reference_loader(oracle_mod):
+    # Pins produced by the reference's ExponentialPointGenerator + PointListBuilder<half>.
+    for pin in _load("generator_pins.json"):
+        pts = oracle_mod.gen_exponential(pin["n"], pin["d"], pin["lambda"], pin["max"])
+        padded = np.zeros((pin["padded_n"], pin["padded_d"]), dtype=np.uint16)
+        padded[: pin["n"], : pin["d"]] = pts
+        assert [int(x) for x in padded.reshape(-1)[:8]] == pin["first8"]
+        assert format(oracle_mod.fnv1a64_u16(padded), "016x") == pin["fnv1a64"]
+
+
+def test_csv_matches_reference_loader(oracle_mod):
+    raw = open(os.path.join(GOLDEN, "small_csv_ref.bin"), "rb").read()
+    hdr = np.frombuffer(raw[:32], dtype=np.int64)
+    ref = np.frombuffer(raw[32:], dtype=np.uint16).reshape(int(hdr[0]), int(hdr[2]))
+    pts, d = oracle_mod.read_csv(os.path.join(GOLDEN, "small.csv"), dim_multiple=64)
+    assert d == int(hdr[3]) and pts.shape[0] == int(hdr[1])
+    assert np.array_equal(ref[: pts.shape[0]], pts)
+    assert not ref[pts.shape[0]:].any()
+
+
+def test_half_conversion_against_numpy(oracle_mod):
+    rng = np.random.default_rng(1)
+    x = np.concatenate([
+        rng.standard_normal(20000) * 10.0 ** rng.integers(-9, 6, 20000),
+        np.array([0.0, -0.0, 65504.0, 65519.9, 65520.0, 1e9, 2.0 ** -24, 2.0 ** -25, 2.0 ** -25 * 1.0001, 2.0 ** -14,
+                  (2.0 ** -14) * (1 - 2.0 ** -12), 1 + 2.0 ** -11, 1 + 3 * 2.0 ** -11]),
+    ])
+    got = oracle_mod.double_to_half(x)
+    with np.errstate(over="ignore"):
+        want = x.astype(np.float32).astype(np.float16).view(np.uint16)
+    assert np.array_equal(got, want)
+    assert np.array_equal(oracle_mod.half_to_float(got), got.view(np.float16).astype(np.float32))
+
+
+def test_row_norms_increasing_integers_known_answer(oracle_mod):
+    # tests/python/sumSquared/sumSquared.py:3-11 with the matrix of source/main.cu:86-104:
+    # row r holds 64r .. 64r+63, expected norm = sum of their squares (exact while values <= 2048).
+    rows = 32
+    vals = np.arange(rows * 64, dtype=np.float64).reshape(rows, 64)
+    pts = oracle_mod.double_to_half(vals)
+    got = oracle_mod.row_norms(pts)
+    want = (vals ** 2).sum(axis=1)
+    # Values up to 2047 are exact halfs; partial sums stay below 2^24 only for the first rows,
+    # beyond that round-toward-zero may lose low bits: compare exactly where exact, else within RZ bounds.
+    exact = want < 2 ** 24
+    assert exact.sum() >= 3
+    assert np.array_equal(got[exact].astype(np.float64), want[exact])
+    rel = (want - got.astype(np.float64)) / want.clip(min=1)
+    assert (rel >= 0).all() and (rel < 64 * 2.0 ** -23).all()  # RZ only ever loses
+
+
+def test_row_norms_round_toward_zero_chain(oracle_mod):
+    # A hand-computed chain: 1 + 2^-24-scale terms are dropped by RZ, kept (eventually) by RN.
+    row = np.zeros((1, 64), dtype=np.float64)
+    row[0, 0] = 1.0
+    row[0, 2:] = 2.0 ** -12  # squares are 2^-24 = half an ulp of 1.0
+    pts = oracle_mod.double_to_half(row)
+    got = oracle_mod.row_norms(pts)[0]
+    # pair sums are 2^-23 (exact) = one ulp of 1.0 -> every add is exact, 31 pairs
+    assert got == np.float32(1.0 + 31 * 2.0 ** -23)
+    row[0, 1] = 2.0 ** -12  # first pair: 1 + 2^-24 -> RZ gives 1.0
+    got = oracle_mod.row_norms(oracle_mod.double_to_half(row))[0]
+    assert got == np.float32(1.0 + 31 * 2.0 ** -23)
+
+
+def test_config1_fp64_golden(oracle_mod):
+    g = _load("config1_fp64.json")
+    pts = oracle_mod.gen_exponential(g["n"], g["d"])
+    assert format(oracle_mod.fnv1a64_u16(pts), "016x") == g["dataset_fnv1a64"]
+    pairs, d2, found = oracle_mod.join_fp64(pts, g["epsilon"])
+    assert found == g["pairs_fp64"] == len(pairs)
+    assert int(np.sum(oracle_mod.pair_keys(pairs), dtype=np.uint64)) == g["key_sum_mod_2_64"]
+    # row-major order, self pairs present, symmetric
+    keys = oracle_mod.pair_keys(pairs)
+    assert (np.diff(keys.astype(np.int64)) > 0).all()
+    assert np.isin(oracle_mod.pair_keys(np.stack([np.arange(g["n"])] * 2, 1)), keys).all()
+    swapped = oracle_mod.pair_keys(pairs[:, ::-1])
+    assert np.array_equal(np.sort(swapped), keys)
+
+
+def test_restated_join_vs_fp64_within_band(oracle_mod):
+    g = _load("config1_fp64.json")
+    pts = oracle_mod.gen_exponential(g["n"], g["d"])
+    p32, d32 = oracle_mod.join_fp16_fp32(pts, g["epsilon"])
+    p64, d64, _ = oracle_mod.join_fp64(pts, g["epsilon"])
+    cmp = oracle_mod.compare_pair_sets(pts, g["d"], g["epsilon"], p32, p64, band=1e-3)
+    assert cmp["ok"], cmp
+    assert cmp["only_a"] + cmp["only_b"] < 100
+    # distances of common pairs agree to 1e-3 relative
+    k32, k64 = oracle_mod.pair_keys(p32), oracle_mod.pair_keys(p64)
+    common, i32, i64 = np.intersect1d(k32, k64, return_indices=True)
+    off = d64[i64] > 0
+    assert np.max(np.abs(d32[i32][off] - d64[i64][off]) / d64[i64][off]) < 1e-3
+
+
+@pytest.mark.parametrize("idx", range(6))
+def test_selfpair_counts_from_reference_results(oracle_mod, idx):
+    # Stored results of the reference's seeded synthetic mode at eps = 0.001: only the
+    # N self pairs are found for D <= 256.
+    rows = [r for r in _load("selfpair_counts.json") if r["n"] <= 10000]
+    rows = sorted(rows, key=lambda r: r["n"] * r["n"] * r["d"])[:6]
+    r = rows[idx]
+    pts = oracle_mod.gen_exponential(r["n"], r["d"])
+    pairs, _ = oracle_mod.join_fp16_fp32(pts, r["epsilon"])
+    assert len(pairs) == r["pairsFound"]
+    assert np.array_equal(pairs[:, 0], pairs[:, 1])
+
+
+def test_band_join_concatenates_to_full_join(oracle_mod):
+    pts = oracle_mod.gen_exponential(700, 64)
+    full, _ = oracle_mod.join_fp16_fp32(pts, 0.2)
+    parts = [oracle_mod.join_fp16_fp32(pts, 0.2, q_begin=a, q_end=b)[0] for a, b in [(0, 256), (256, 512), (512, 700)]]
+    assert np.array_equal(np.concatenate(parts), full)
