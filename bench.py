@@ -1,0 +1,429 @@
+#!/usr/bin/env python
+"""Benchmark of the epsilon self-join hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c3] [--impl reference]
+
+A *step* is one pass of the hot path over the workload: row norms + the join of this rank's
+query band against all candidates (the interval the reference calls "Total Kernel Elapsed
+time", source/findPairs.cuh:728-748 of the reference).  The metric is the reference's:
+TFLOPS = 2 * N * N * D / seconds / 1e12 over the un-padded N and D.
+
+One JSON line is printed by rank 0:
+  value      device-timed throughput with the dataset already resident in HBM
+  e2e        the same metric through the public API with HOST buffers: pinned host -> device copy
+             of the dataset (plus the NCCL broadcast at N > 1), norms, join, sort, and the
+             device -> host copy of the pair list, every step
+  roofline   the join kernel against the measured tensor-core peak
+  cpu_baseline  an OpenMP FP64 brute-force self-join on a bounded sample, on the host cores
+
+`--impl reference` times the CPU baseline alone (the reference has no CPU implementation of the
+join and its GPU implementation is what this library replaces; the FP64 OpenMP brute force is
+the CPU arm its task definition names).
+
+Multi-GPU: launched by torchrun with one rank per GPU; total work is fixed (strong scaling):
+rank r joins query rows [r*B, (r+1)*B) against all N candidates after one NCCL broadcast of the
+FP16 matrix.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+# name -> shape, distribution, target mean neighbours per point, epsilon (None: tuned at start-up
+# with band joins through the library itself, like the reference's Python driver does with reRun).
+WORKLOADS = {
+    "c1": dict(n=4096, d=128, dist="exp", target=32, eps=0.3136),
+    "c2": dict(n=100_000, d=384, dist="unit_gauss", target=16, eps=None),
+    "c3": dict(n=1_000_000, d=4096, dist="exp", target=64, eps=None),
+    "c5": dict(n=4_000_000, d=2048, dist="exp", target=8, eps=None),
+}
+SEED = 2137834274  # the reference's dataset seed
+PUBLISHED_A100_TFLOPS = {"c3": 153.64}  # mean of the reference's three 1,000,000 x 4096 trials (A100 PCIe)
+NOMINAL_FP16_TFLOPS = 2250.0
+
+
+def _peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return dict(burst=p.get("bf16_tflops"), sustained=p.get("bf16_tflops_sustained"), hbm=p.get("hbm_gbs"),
+                    source="measured")
+    return dict(burst=1590.0, sustained=1400.0, hbm=6650.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU every 200 ms while running."""
+
+    def __init__(self, index: int):
+        self.index, self.samples, self.reasons = index, [], set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nv = None
+
+    def _run(self):
+        nv = self._nv
+        names = {
+            getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4): "sw_power_cap",
+            getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8): "hw_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonHwPowerBrakeSlowdown", 0x80): "hw_power_brake_slowdown",
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                try:
+                    mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self._h)
+                except Exception:
+                    mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h)
+                for bit, name in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(0.2)
+
+    def start(self):
+        if self._nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+
+    def stop(self) -> dict:
+        self._stop.set()
+        if self._thread:
+            self._thread.join()
+        med = float(np.median(self.samples)) if self.samples else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(self.samples)}
+
+
+def make_host_sample(wl: dict, rows: int) -> np.ndarray:
+    """Seeded host-side sample with the workload's distribution, binary16 bit patterns (rows, d)."""
+    rng = np.random.default_rng(SEED)
+    d = wl["d"]
+    if wl["dist"] == "exp":
+        x = rng.exponential(1.0 / 40.0, size=(rows, d))
+        x = np.minimum(x, 10.0)
+    elif wl["dist"] == "unit_gauss":
+        x = rng.standard_normal((rows, d))
+        x /= np.linalg.norm(x, axis=1, keepdims=True)
+    else:
+        raise ValueError(wl["dist"])
+    return x.astype(np.float32).astype(np.float16).view(np.uint16)
+
+
+def cpu_fp64_sample(pts: np.ndarray, d: int, eps: float, q_rows: int) -> dict:
+    """Times the OpenMP FP64 brute force (the checker's, used here only as the reported CPU baseline)."""
+    import oracle
+    c_rows = pts.shape[0]
+    t0 = time.perf_counter()
+    _, _, found = oracle.join_fp64(pts, eps, d=d, q_begin=0, q_end=q_rows, capacity=1)
+    dt = time.perf_counter() - t0
+    return {"value": 2.0 * q_rows * c_rows * d / dt / 1e12, "unit": "TFLOPS", "cores": oracle.num_threads(),
+            "kind": "port", "seconds": dt,
+            "sample": f"{q_rows} query rows x {c_rows} candidate rows x {d} dims, FP64 direct form, OpenMP"}
+
+
+def size_cpu_sample(wl: dict, budget_flop: float) -> tuple[int, int]:
+    c_rows = min(wl["n"], 32768)
+    q_rows = int(max(16, min(c_rows, budget_flop / (2.0 * c_rows * wl["d"]))))
+    return q_rows, c_rows
+
+
+def run_reference_arm(args, wl: dict, name: str) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import oracle
+    cores = oracle.num_threads()
+    q_rows, c_rows = size_cpu_sample(wl, budget_flop=1e12 * cores / 16)
+    pts = make_host_sample(wl, c_rows)
+    eps = wl["eps"] if wl["eps"] else 1.0
+    for _ in range(args.warmup):
+        cpu_fp64_sample(pts, wl["d"], eps, max(16, q_rows // 8))
+    t0 = time.perf_counter()
+    last = None
+    for _ in range(args.steps):
+        last = cpu_fp64_sample(pts, wl["d"], eps, q_rows)
+    dt = (time.perf_counter() - t0) / args.steps
+    value = 2.0 * q_rows * c_rows * wl["d"] / dt / 1e12
+    line = {
+        "impl": "reference", "metric": "self_join_tflops", "value": value, "unit": "TFLOPS", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
+        "config": {"workload": f"{name}: self-join {wl['n']} x {wl['d']} {wl['dist']}; CPU arm on a bounded sample",
+                   "n": wl["n"], "d": wl["d"], "epsilon": eps},
+        "cpu_baseline": {"value": value, "unit": "TFLOPS", "cores": cores, "kind": "port", "sample": last["sample"]},
+        "e2e": {"value": value, "unit": "TFLOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def tune_epsilon(sj, n: int, target: float, rows: int, flags_no_sort: int) -> tuple[float, float]:
+    """Epsilon whose mean neighbour count (self excluded) over the first `rows` query rows is ~target."""
+    rows = min(rows, n)
+
+    def mean_neighbours(eps: float) -> float:
+        st = sj.join(eps, q_begin=0, q_end=rows, capacity=1, flags=flags_no_sort)
+        return (st.pairs_found - rows) / rows
+
+    norms, _ = sj.row_norms()
+    hi = float(np.sqrt(4.0 * float(norms[: min(n, 65536)].max())))
+    lo = 0.0
+    m = None
+    for _ in range(40):
+        mid = 0.5 * (lo + hi)
+        m = mean_neighbours(mid)
+        if abs(m - target) <= 0.01 * target:
+            return mid, m
+        if m > target:
+            hi = mid
+        else:
+            lo = mid
+    return 0.5 * (lo + hi), m
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
+    ap.add_argument("--n", type=int, default=0, help="override the number of points")
+    ap.add_argument("--d", type=int, default=0, help="override the dimension")
+    ap.add_argument("--eps", type=float, default=0.0, help="override epsilon (default: workload table or tuned)")
+    ap.add_argument("--band-tiles", type=int, default=0)
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 0)
+
+    name = args.workload
+    wl = dict(WORKLOADS[name])
+    if args.n:
+        wl["n"], wl["eps"] = args.n, None
+    if args.d:
+        wl["d"], wl["eps"] = args.d, None
+    if args.eps:
+        wl["eps"] = args.eps
+
+    if args.impl == "reference":
+        run_reference_arm(args, wl, name)
+        return
+
+    import torch
+    import torch.distributed as dist
+    from fasted_b200 import SelfJoin, JOIN_NO_SORT
+    from fasted_b200.dist import band_bounds
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    n, d = wl["n"], wl["d"]
+    ld = -(-d // 64) * 64
+    sj = SelfJoin(local_rank)
+    sj.set_stream(torch.cuda.current_stream().cuda_stream)
+    if args.band_tiles:
+        sj.set_option("band_tiles", args.band_tiles)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- dataset: generated on rank 0's GPU, replicated by the one broadcast --------------------
+    dev_pts = torch.zeros((n, ld), dtype=torch.float16, device="cuda")
+    if rank == 0:
+        if wl["dist"] == "exp":
+            sj.fill_exponential_device(dev_pts.data_ptr(), n, d, ld, 40.0, 10.0, SEED)
+        elif wl["dist"] == "unit_gauss":
+            g = torch.Generator(device="cuda").manual_seed(SEED)
+            for a in range(0, n, 65536):
+                x = torch.randn((min(65536, n - a), d), generator=g, device="cuda", dtype=torch.float32)
+                x /= x.norm(dim=1, keepdim=True)
+                dev_pts[a:a + x.shape[0], :d] = x.to(torch.float16)
+    if world > 1:
+        dist.broadcast(dev_pts.view(torch.uint8), src=0)
+    torch.cuda.synchronize()
+    sj.set_points_device(dev_pts.data_ptr(), n, d, ld, keepalive=dev_pts)
+
+    q_begin, q_end = band_bounds(n, world, rank)
+    band_rows = q_end - q_begin
+
+    # ---- epsilon ------------------------------------------------------------------------------
+    eps = wl["eps"]
+    tuned_mean = None
+    if eps is None:
+        if rank == 0:
+            eps, tuned_mean = tune_epsilon(sj, n, wl["target"], 4096, JOIN_NO_SORT)
+        if world > 1:
+            t = torch.tensor([eps if rank == 0 else 0.0], dtype=torch.float64, device="cuda")
+            dist.broadcast(t, src=0)
+            eps = float(t.item())
+    capacity = max(1, band_rows) * 256
+
+    # ---- timed region 1: dataset resident, device-timed -----------------------------------------
+    def step_resident():
+        return sj.join(eps, q_begin=q_begin, q_end=q_end, capacity=capacity, flags=JOIN_NO_SORT)
+
+    for _ in range(args.warmup):
+        step_resident()
+    sampler = ClockSampler(local_rank)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    join_ms, norm_ms, found = [], [], 0
+    barrier()
+    sampler.start()
+    ev0.record()
+    for _ in range(args.steps):
+        st = step_resident()
+        join_ms.append(st.join_ms)
+        norm_ms.append(st.norms_ms)
+        found = int(st.pairs_found)
+    ev1.record()
+    barrier()
+    clocks = sampler.stop()
+    total_ms = ev0.elapsed_time(ev1)
+    stats = torch.tensor([total_ms, float(found), float(np.mean(join_ms)), float(np.mean(norm_ms))],
+                         dtype=torch.float64, device="cuda")
+    if world > 1:
+        mx = stats.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        sm = stats.clone()
+        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+        total_ms, found_total = float(mx[0]), int(sm[1])
+        join_ms_max, norm_ms_max = float(mx[2]), float(mx[3])
+    else:
+        found_total, join_ms_max, norm_ms_max = found, float(stats[2]), float(stats[3])
+    ms_per_step = total_ms / args.steps
+    flop = 2.0 * n * n * d
+    value = flop / (ms_per_step * 1e-3) / 1e12
+
+    # ---- timed region 2: end to end with host buffers -------------------------------------------
+    e2e = None
+    if not args.no_e2e:
+        host_pts = None
+        if rank == 0:
+            host_pts = torch.empty((n, ld), dtype=torch.float16).pin_memory()
+            host_pts.copy_(dev_pts)
+            torch.cuda.synchronize()
+        out_cap = int(min(capacity, max(1 << 20, 2 * found + 1024)))
+        host_out = torch.empty((out_cap, 2), dtype=torch.int32).pin_memory()
+
+        def step_e2e():
+            if world == 1:
+                sj.set_points_ptr(host_pts.data_ptr(), n, d, ld)
+            else:
+                if rank == 0:
+                    dev_pts.copy_(host_pts, non_blocking=True)
+                dist.broadcast(dev_pts.view(torch.uint8), src=0)
+                sj.set_points_device(dev_pts.data_ptr(), n, d, ld, keepalive=dev_pts)
+            st = sj.join(eps, q_begin=q_begin, q_end=q_end, capacity=capacity)
+            m = min(int(st.pairs_stored), out_cap)
+            sj.pairs_into(host_out.data_ptr(), m)
+            return st, m
+
+        e2e_warm = min(args.warmup, 1)
+        for _ in range(e2e_warm):
+            step_e2e()
+        barrier()
+        t0 = time.perf_counter()
+        ev0.record()
+        copied = 0
+        e2e_join_ms = []
+        for _ in range(args.steps):
+            st, copied = step_e2e()
+            e2e_join_ms.append(st.join_ms)
+        ev1.record()
+        barrier()
+        wall_ms = (time.perf_counter() - t0) * 1e3
+        e2e_ms = max(ev0.elapsed_time(ev1), wall_ms)
+        t = torch.tensor([e2e_ms], dtype=torch.float64, device="cuda")
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t[0]) / args.steps
+        e2e = {"value": flop / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOPS", "ms_per_step": e2e_ms,
+               "h2d_bytes_per_step": n * ld * 2, "d2h_bytes_per_step": copied * 8,
+               "join_kernel_ms": float(np.mean(e2e_join_ms)),
+               "api": "fasted_set_points_host_f16 + fasted_join + fasted_get_pairs (pinned host buffers)"
+               if world == 1 else "pinned host -> rank 0 GPU, NCCL broadcast, fasted_join per band, fasted_get_pairs"}
+        if world == 1:
+            sj.set_points_device(dev_pts.data_ptr(), n, d, ld, keepalive=dev_pts)
+
+    # ---- CPU baseline on rank 0, N = 1 only ------------------------------------------------------
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        import oracle
+        q_rows, c_rows = size_cpu_sample(wl, budget_flop=1e12 * oracle.num_threads() / 16)
+        sample = dev_pts[:c_rows, :d].contiguous().cpu().numpy().view(np.uint16)
+        cpu = cpu_fp64_sample(sample, d, eps, q_rows)
+
+    if rank == 0:
+        peaks = _peaks()
+        band_flop = 2.0 * band_rows * n * d  # rank 0's launch
+        achieved = band_flop / (float(np.mean(join_ms)) * 1e-3) / 1e12
+        peak = peaks["sustained"] if float(np.mean(join_ms)) > 500.0 else peaks["burst"]
+        line = {
+            "metric": "self_join_tflops", "value": value, "unit": "TFLOPS", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": (value / PUBLISHED_A100_TFLOPS[name]) if name in PUBLISHED_A100_TFLOPS and not (args.n or args.d) and world == 1 else None,
+            "dtype": "f16xf16->f32", "data": "synthetic",
+            "config": {
+                "workload": f"{name}: self-join of {n} x {d} points, {wl['dist']} (seed {SEED}), FP16, "
+                            f"eps for ~{wl['target']} neighbours per point",
+                "n": n, "d": d, "epsilon": eps, "mean_neighbours": (found_total - n) / n,
+                "parallelism": f"query-row bands x{world}" if world > 1 else "single GPU",
+                "l2": "inputs larger than L2 (no flush needed)" if n * ld * 2 > 2 * 126e6 else "inputs fit L2",
+                "baseline_note": "vs_baseline divides by the reference's published A100-PCIe figure for this shape "
+                                 "(153.64 TFLOPS at eps=0.001)" if name in PUBLISHED_A100_TFLOPS else None,
+            },
+            "pairs_found": found_total, "pairs_per_s": found_total / (ms_per_step * 1e-3),
+            "frac_of_nominal_fp16_peak": value / (NOMINAL_FP16_TFLOPS * world),
+            "kernel_ms": {"join": join_ms_max, "norms": norm_ms_max},
+            "clocks": clocks,
+            "e2e": e2e,
+            "gpu_launches": 2 * args.steps,
+            "roofline": {"bound": "tensor", "kernel": "join_kernel", "achieved": achieved, "peak": peak,
+                         "unit": "TFLOP/s", "frac": achieved / peak if peak else None, "traffic": None,
+                         "peak_source": f"{peaks['source']} cuBLAS bf16 "
+                                        f"({'sustained' if float(np.mean(join_ms)) > 500.0 else 'burst'})",
+                         "norms_kernel": {"bound": "hbm", "achieved": (n * ld * 2 + n * 4) / (float(np.mean(norm_ms)) * 1e-3) / 1e9,
+                                          "peak": peaks["hbm"], "unit": "GB/s"}},
+            "cpu_baseline": cpu,
+        }
+        if tuned_mean is not None:
+            line["config"]["epsilon_tuned"] = True
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    sj.close()
+
+
+if __name__ == "__main__":
+    main()

@@ -52,6 +52,7 @@ DECLARED_SYMBOLS = [
     "runFromExponentialDataset", "runFromFile", "reRun", "releaseResources",
     "fasted_last_error", "fasted_create", "fasted_destroy", "fasted_set_stream",
     "fasted_set_points_host_f16", "fasted_set_points_device_f16", "fasted_generate_exponential",
+    "fasted_fill_exponential_device",
     "fasted_points_info", "fasted_get_points_host_f16", "fasted_row_norms", "fasted_get_norms",
     "fasted_join", "fasted_get_pairs", "fasted_pairs_device", "fasted_brute_force_f64", "fasted_set_option",
     "fasted_dataset_exponential_f16", "fasted_dataset_csv_shape", "fasted_dataset_csv_f16",
@@ -78,6 +79,7 @@ def load() -> ctypes.CDLL:
     L.fasted_set_points_host_f16.argtypes = [_vp, _vp, _i64, _i64, _i64]
     L.fasted_set_points_device_f16.argtypes = [_vp, _vp, _i64, _i64, _i64]
     L.fasted_generate_exponential.argtypes = [_vp, _i64, _i64, ctypes.c_double, ctypes.c_double, _u64]
+    L.fasted_fill_exponential_device.argtypes = [_vp, _vp, _i64, _i64, _i64, ctypes.c_double, ctypes.c_double, _u64]
     L.fasted_points_info.argtypes = [_vp, ctypes.POINTER(_vp), ctypes.POINTER(_i64), ctypes.POINTER(_i64),
                                      ctypes.POINTER(_i64)]
     L.fasted_get_points_host_f16.argtypes = [_vp, _vp, _i64]
@@ -166,6 +168,13 @@ class SelfJoin:
     def generate_exponential(self, n: int, d: int, lam: float = 40.0, max_value: float = 10.0,
                              seed: int = 2137834274) -> None:
         _check(self._L.fasted_generate_exponential(self._h, n, d, lam, max_value, seed))
+
+    def fill_exponential_device(self, dev_ptr: int, n: int, d: int, ld: int, lam: float = 40.0,
+                                max_value: float = 10.0, seed: int = 2137834274) -> None:
+        _check(self._L.fasted_fill_exponential_device(self._h, _vp(dev_ptr), n, d, ld, lam, max_value, seed))
+
+    def set_stream(self, cuda_stream: int) -> None:
+        _check(self._L.fasted_set_stream(self._h, _vp(cuda_stream)))
 
     def points_info(self) -> tuple[int, int, int, int]:
         dev, n, d, ld = _vp(), _i64(), _i64(), _i64()

@@ -326,6 +326,22 @@ int fasted_generate_exponential(fasted_ctx* c, int64_t n, int64_t d, double lamb
     return adopt_points(c, dev, true, n, d, ld);
 }
 
+int fasted_fill_exponential_device(fasted_ctx* c, void* dev, int64_t n, int64_t d, int64_t ld, double lambda,
+                                   double max_value, uint64_t seed) {
+    if (!c || !dev) return fail(FASTED_EINVAL, "null argument");
+    int rc = check_shape(n, d);
+    if (rc) return rc;
+    if (ld < d || (ld % 8) != 0 || reinterpret_cast<uintptr_t>(dev) % 16 != 0)
+        return fail(FASTED_EINVAL, "ld must be >= d and a multiple of 8, dev 16-byte aligned");
+    if (!(lambda > 0) || !(max_value > 0)) return fail(FASTED_EINVAL, "lambda and max_value must be positive");
+    CU_TRY(cudaSetDevice(c->device));
+    fasted::gen_exponential_kernel<<<c->num_sms * 8, 256, 0, c->stream>>>(
+        static_cast<__half*>(dev), n, static_cast<int>(d), static_cast<int>(ld), lambda, max_value, seed);
+    CU_TRY(cudaGetLastError());
+    CU_TRY(cudaStreamSynchronize(c->stream));
+    return FASTED_OK;
+}
+
 int fasted_points_info(fasted_ctx* c, void** dev, int64_t* n, int64_t* d, int64_t* ld) {
     if (!c) return fail(FASTED_EINVAL, "ctx is null");
     if (!c->points) return fail(FASTED_ESTATE, "no dataset is resident");

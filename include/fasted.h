@@ -145,6 +145,12 @@ int fasted_set_points_device_f16(fasted_ctx* ctx, const void* dev, int64_t n, in
 int fasted_generate_exponential(fasted_ctx* ctx, int64_t n, int64_t d, double lambda, double max_value,
                                 uint64_t seed);
 
+/* Fill a caller-owned device matrix (n rows, row stride ld, ld a multiple of 8,
+ * 16-byte aligned) with the same generator; columns [d, ld) are zeroed.  Does
+ * not change the resident dataset. */
+int fasted_fill_exponential_device(fasted_ctx* ctx, void* dev, int64_t n, int64_t d, int64_t ld, double lambda,
+                                   double max_value, uint64_t seed);
+
 /* Device pointer / shape of the resident dataset. */
 int fasted_points_info(fasted_ctx* ctx, void** dev, int64_t* n, int64_t* d, int64_t* ld);
 /* Copy the resident dataset to the host (row stride ld_host >= d). */

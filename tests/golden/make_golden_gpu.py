@@ -1,0 +1,94 @@
+"""Runs the REFERENCE's own GPU join (oracle/_ref/ref_join, compiled unmodified from the
+reference's sources for sm_100) on a B200 and stores its outputs as fixtures:
+
+    python tests/golden/make_golden_gpu.py <out_dir>      # on the GPU box; copy *.npz into tests/golden/
+
+Each ref_gpu_<name>.npz holds the dataset recipe (n, d, epsilon, kind), the reference's
+pairsFound and its sorted pair list (int32 (m, 2)).  Datasets are the reference's seeded
+synthetic generator (kind "exp") or seeded numpy data (kind "gauss_unit", "clusters").
+Also writes ref_gpu_timing.json with the reference kernel's own TFLOPS on this GPU.
+"""
+from __future__ import annotations
+
+import json
+import os
+import re
+import subprocess
+import sys
+import tempfile
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, ROOT)
+import oracle  # noqa: E402
+
+REF_JOIN = os.path.join(ROOT, "oracle", "_ref", "ref_join")
+
+
+def dataset(kind: str, n: int, d: int) -> np.ndarray:
+    if kind == "exp":
+        return oracle.gen_exponential(n, d)
+    rng = np.random.default_rng(n * 1000003 + d)
+    if kind == "gauss_unit":
+        x = rng.standard_normal((n, d))
+        x /= np.linalg.norm(x, axis=1, keepdims=True)
+        return oracle.double_to_half(x)
+    if kind == "clusters":
+        centres = rng.uniform(0, 1, size=(8, d))
+        return oracle.double_to_half(centres[rng.integers(0, 8, n)] + rng.normal(0, 0.05, size=(n, d)))
+    raise ValueError(kind)
+
+
+def run_ref(pts: np.ndarray, eps: float, want_pairs: bool = True):
+    n, d = pts.shape
+    with tempfile.TemporaryDirectory() as tmp:
+        pin = os.path.join(tmp, "p.bin")
+        with open(pin, "wb") as f:
+            f.write(np.array([n, d], dtype=np.int64).tobytes())
+            f.write(np.ascontiguousarray(pts).tobytes())
+        prefix = os.path.join(tmp, "out")
+        r = subprocess.run([REF_JOIN, pin, repr(eps), prefix], capture_output=True, text=True, timeout=900)
+        if r.returncode != 0:
+            raise RuntimeError(r.stdout[-2000:] + r.stderr[-2000:])
+        m = re.search(r"REF_RESULTS (\S+) (\S+) (\d+) (\d+)", r.stdout)
+        total, tflops, found, stored = float(m.group(1)), float(m.group(2)), int(m.group(3)), int(m.group(4))
+        pairs = None
+        if want_pairs:
+            txt = open(prefix + ".pairs").read()
+            pairs = np.array(re.findall(r"(\d+), (\d+)", txt), dtype=np.int32).reshape(-1, 2)
+            assert len(pairs) == stored
+    return dict(total=total, tflops=tflops, found=found, stored=stored, pairs=pairs)
+
+
+CASES = [
+    ("exp_1000x64", "exp", 1000, 64, 0.2),
+    ("exp_4096x128", "exp", 4096, 128, 0.3136),
+    ("exp_2154x256_selfonly", "exp", 2154, 256, 0.001),
+    ("gauss_unit_3000x384", "gauss_unit", 3000, 384, 1.27),
+    ("clusters_1500x96", "clusters", 1500, 96, 0.9),
+    ("exp_777x333", "exp", 777, 333, 0.5),
+]
+
+
+def main(out_dir: str) -> None:
+    os.makedirs(out_dir, exist_ok=True)
+    for name, kind, n, d, eps in CASES:
+        pts = dataset(kind, n, d)
+        r = run_ref(pts, eps)
+        np.savez_compressed(os.path.join(out_dir, f"ref_gpu_{name}.npz"), n=n, d=d, epsilon=eps, kind=kind,
+                            pairs_found=r["found"], pairs=r["pairs"],
+                            dataset_fnv1a64=np.uint64(oracle.fnv1a64_u16(pts)))
+        print(name, "found", r["found"], "stored", r["stored"], flush=True)
+    timing = []
+    for n, d in [(21544, 4096), (46416, 4096)]:
+        pts = oracle.double_to_half(np.random.default_rng(1).exponential(1 / 40.0, size=(n, d)))
+        r = run_ref(pts, 0.001, want_pairs=False)
+        timing.append(dict(n=n, d=d, epsilon=0.001, tflops=r["tflops"], pairs_found=r["found"]))
+        print("timing", timing[-1], flush=True)
+    json.dump(timing, open(os.path.join(out_dir, "ref_gpu_timing.json"), "w"), indent=1)
+
+
+if __name__ == "__main__":
+    main(sys.argv[1] if len(sys.argv) > 1 else os.path.join(ROOT, "gpurun_out", "golden_gpu"))

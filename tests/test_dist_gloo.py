@@ -1,0 +1,86 @@
+"""The multi-rank band-sharding logic on CPU ranks (gloo, world size 2 and 3).  The join engine
+is injected: here the CPU oracle stands in for the GPU so that the host-side logic -- band
+bounds, the broadcast, the count reduction and the ordered gather -- is what is under test."""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from conftest import ROOT
+
+
+def test_band_bounds_cover_and_align():
+    from fasted_b200.dist import band_bounds
+    for n in [0, 1, 127, 128, 129, 1000, 4096, 100_000, 1_000_000]:
+        for world in [1, 2, 3, 4, 8]:
+            bands = [band_bounds(n, world, r) for r in range(world)]
+            assert bands[0][0] == 0 and bands[-1][1] == n
+            for (a, b), (c, d) in zip(bands, bands[1:]):
+                assert b == c and a <= b
+            for a, b in bands:
+                assert a % 128 == 0 or a == n
+            sizes = [b - a for a, b in bands if b > a]
+            if n >= 128 * world:
+                assert max(sizes) - min(sizes) <= 128 * world
+    with pytest.raises(ValueError):
+        band_bounds(10, 2, 2)
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, n, d, eps, out_dir):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import oracle
+    from fasted_b200.dist import broadcast_points, sharded_self_join
+
+    class OracleEngine:
+        def __init__(self, pts):
+            self.pts = pts
+
+        def join_band(self, eps, a, b):
+            p, _ = oracle.join_fp16_fp32(self.pts, eps, q_begin=a, q_end=b)
+            return p, len(p)
+
+    # rank 0 owns the data, the others receive it through the one broadcast
+    if rank == 0:
+        t = torch.from_numpy(oracle.gen_exponential(n, d).view(np.int16).copy())
+    else:
+        t = torch.zeros((n, d), dtype=torch.int16)
+    broadcast_points(t)
+    pts = t.numpy().view(np.uint16)
+    pairs, found, stored = sharded_self_join(OracleEngine(pts), n, eps)
+    np.save(os.path.join(out_dir, f"pairs{rank}.npy"), pairs)
+    np.save(os.path.join(out_dir, f"meta{rank}.npy"), np.array([found, stored]))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_sharded_join_equals_single_rank(oracle_mod, tmp_path, world):
+    n, d, eps = 700, 64, 0.2
+    mp.spawn(_worker, args=(world, _free_port(), n, d, eps, str(tmp_path)), nprocs=world, join=True)
+    want, _ = oracle_mod.join_fp16_fp32(oracle_mod.gen_exponential(n, d), eps)
+    got = np.load(tmp_path / "pairs0.npy")
+    assert np.array_equal(got, want)  # rank-order concatenation == global row-major order
+    metas = [np.load(tmp_path / f"meta{r}.npy") for r in range(world)]
+    assert all(int(m[0]) == len(want) for m in metas)
+    assert sum(int(m[1]) for m in metas) == len(want)
+    from fasted_b200.dist import band_bounds
+    for r in range(1, world):
+        a, b = band_bounds(n, world, r)
+        p = np.load(tmp_path / f"pairs{r}.npy")
+        assert len(p) == 0 or (p[:, 0].min() >= a and p[:, 0].max() < b)

@@ -116,8 +116,8 @@ def test_join_edge_epsilons(gpu_join, oracle_mod):
     got = gpu_join.pairs()
     assert (got[:, 0] == got[:, 1]).all() or len(got) == 0
     # huge eps: everything pairs, padding never does
-    st = gpu_join.join(1e3)
-    assert st.pairs_found == 500 * 500
+    st = gpu_join.join(1e3, capacity=500 * 500)
+    assert st.pairs_found == st.pairs_stored == 500 * 500
     got = gpu_join.pairs()
     assert np.array_equal(oracle_mod.pair_keys(got),
                           oracle_mod.pair_keys(np.stack(np.meshgrid(np.arange(500), np.arange(500), indexing="ij"), -1).reshape(-1, 2)))
@@ -125,6 +125,10 @@ def test_join_edge_epsilons(gpu_join, oracle_mod):
     z = np.zeros((130, 64), dtype=np.uint16)
     gpu_join.set_points(z)
     assert gpu_join.join(0.0).pairs_found == 130 * 130
+    # default capacity is the reference's n * 256 rule: 500 * 500 pairs do not fit 500 * 256 slots
+    gpu_join.set_points(pts)
+    st = gpu_join.join(1e3)
+    assert st.pairs_found == 500 * 500 and st.pairs_stored == 500 * 256
 
 
 def test_join_overflow_semantics(gpu_join, oracle_mod):
@@ -226,3 +230,23 @@ def test_join_midsize_properties(gpu_join, oracle_mod):
         assert abs(int(counts_dev[i]) - len(want)) == 0
     per_row = np.bincount(got[:, 0], minlength=n)[rows]
     assert np.abs(per_row.astype(np.int64) - counts_dev.astype(np.int64)).max() <= 2
+
+
+def _ref_gpu_cases():
+    import glob
+    return sorted(glob.glob(os.path.join(GOLDEN, "ref_gpu_*.npz")))
+
+
+@pytest.mark.parametrize("path", _ref_gpu_cases(), ids=lambda p: os.path.basename(p)[8:-4])
+def test_join_against_reference_gpu_output(gpu_join, oracle_mod, path):
+    # Same inputs as the reference's own kernels were run on (fixtures recorded on a B200).
+    from test_oracle_golden import _golden_dataset
+    g = np.load(path)
+    pts = _golden_dataset(oracle_mod, g)
+    eps, d = float(g["epsilon"]), int(g["d"])
+    gpu_join.set_points(pts)
+    st = gpu_join.join(eps)
+    got = gpu_join.pairs()
+    cmp = assert_pairs_match(oracle_mod, pts, d, eps, got, g["pairs"], BAND, "vs reference GPU output")
+    assert cmp["only_a"] + cmp["only_b"] <= max(8, len(g["pairs"]) // 2000)
+    assert abs(int(st.pairs_found) - int(g["pairs_found"])) <= max(8, len(g["pairs"]) // 2000)

@@ -54,8 +54,13 @@ def test_reference_python_driver_flow(native_lib, oracle_mod, tmp_path):
     got = np.array([[int(a) for a in line.split(", ")] for line in text], dtype=np.int32)
     cmp = oracle_mod.compare_pair_sets(pts, 64, 0.2, got, want, band=1e-3)
     assert cmp["ok"]
-    # CSV run: 5 points, huge eps -> all 25 ordered pairs; file named after the CSV stem
-    assert out[3]["found"] == 25 and out[3]["inp"] == [5, 5, 6]
+    # CSV run (5 points, one with an infinite coordinate): same count as the oracle on the same file;
+    # output file named after the CSV stem
+    csv_pts, csv_d = oracle_mod.read_csv(os.path.join(GOLDEN, "small.csv"))
+    csv_want, _ = oracle_mod.join_fp16_fp32(csv_pts, 10.0)
+    assert out[3]["found"] == len(csv_want) == 6 and out[3]["inp"] == [5, 5, 6]
+    text = (tmp_path / ("small_" + f"{10.0:.6f}" + ".pairs")).read_text().splitlines()
+    assert [[int(a) for a in line.split(", ")] for line in text] == csv_want.tolist()
     assert (tmp_path / ("small_" + f"{10.0:.6f}" + ".pairs")).exists()
     # the reference's stdout lines that scripts grep for
     for needle in ["Running from a generated exponential dataset", "Building point list", "Number of points is: 1000",
@@ -79,6 +84,6 @@ def test_cli_synthetic_and_file(native_lib, tmp_path):
     assert r.returncode == 0, r.stdout + r.stderr
     assert "Pairs found: 2154" in r.stdout and "Estimated TFLOPS" in r.stdout
     r = subprocess.run([exe, os.path.join(GOLDEN, "small.csv"), "10"], capture_output=True, text=True, timeout=600)
-    assert r.returncode == 0 and "Pairs found: 25" in r.stdout
+    assert r.returncode == 0 and "Pairs found: 6" in r.stdout
     r = subprocess.run([exe, str(tmp_path / "nope.csv"), "1"], capture_output=True, text=True, timeout=600)
     assert r.returncode == 1 and "Error: Failed to run." in r.stdout

@@ -125,3 +125,40 @@ def test_band_join_concatenates_to_full_join(oracle_mod):
     full, _ = oracle_mod.join_fp16_fp32(pts, 0.2)
     parts = [oracle_mod.join_fp16_fp32(pts, 0.2, q_begin=a, q_end=b)[0] for a, b in [(0, 256), (256, 512), (512, 700)]]
     assert np.array_equal(np.concatenate(parts), full)
+
+
+def _ref_gpu_cases():
+    import glob
+    return sorted(glob.glob(os.path.join(GOLDEN, "ref_gpu_*.npz")))
+
+
+def _golden_dataset(oracle_mod, g):
+    kind, n, d = str(g["kind"]), int(g["n"]), int(g["d"])
+    if kind == "exp":
+        pts = oracle_mod.gen_exponential(n, d)
+    else:
+        rng = np.random.default_rng(n * 1000003 + d)
+        if kind == "gauss_unit":
+            x = rng.standard_normal((n, d))
+            x /= np.linalg.norm(x, axis=1, keepdims=True)
+        else:
+            centres = rng.uniform(0, 1, size=(8, d))
+            x = centres[rng.integers(0, 8, n)] + rng.normal(0, 0.05, size=(n, d))
+        pts = oracle_mod.double_to_half(x)
+    assert int(oracle_mod.fnv1a64_u16(pts)) == int(g["dataset_fnv1a64"])
+    return pts
+
+
+@pytest.mark.parametrize("path", _ref_gpu_cases(), ids=lambda p: os.path.basename(p)[8:-4])
+def test_oracle_against_reference_gpu_output(oracle_mod, path):
+    # Pair lists produced by the reference's own kernels (compiled unmodified, run on a B200):
+    # the restated algorithm must reproduce them outside the comparison band.
+    g = np.load(path)
+    pts = _golden_dataset(oracle_mod, g)
+    eps, d = float(g["epsilon"]), int(g["d"])
+    mine, _ = oracle_mod.join_fp16_fp32(pts, eps)
+    ref = g["pairs"]
+    assert len(ref) == int(g["pairs_found"])
+    cmp = oracle_mod.compare_pair_sets(pts, d, eps, mine, ref, band=1e-3)
+    assert cmp["ok"], cmp
+    assert cmp["only_a"] + cmp["only_b"] <= max(8, len(ref) // 2000)
