@@ -56,6 +56,7 @@ DECLARED_SYMBOLS = [
     "fasted_points_info", "fasted_get_points_host_f16", "fasted_row_norms", "fasted_get_norms",
     "fasted_join", "fasted_get_pairs", "fasted_pairs_device", "fasted_brute_force_f64", "fasted_set_option",
     "fasted_dataset_exponential_f16", "fasted_dataset_csv_shape", "fasted_dataset_csv_f16",
+    "fasted_join_static_scratch",
 ]
 
 _lib = None
@@ -90,6 +91,8 @@ def load() -> ctypes.CDLL:
     L.fasted_pairs_device.argtypes = [_vp, ctypes.POINTER(_vp), ctypes.POINTER(_vp)]
     L.fasted_brute_force_f64.argtypes = [_vp, _vp, ctypes.c_int, ctypes.c_double, _vp]
     L.fasted_set_option.argtypes = [_vp, ctypes.c_char_p, _i64]
+    L.fasted_join_static_scratch.argtypes = [_vp, _i64, _i64, _i64, ctypes.c_double, _vp, _u64, _vp,
+                                             ctypes.POINTER(ctypes.c_ulonglong), ctypes.POINTER(ctypes.c_ulonglong)]
     L.fasted_dataset_exponential_f16.argtypes = [_i64, _i64, ctypes.c_double, ctypes.c_double, _vp, _i64]
     L.fasted_dataset_csv_shape.argtypes = [ctypes.c_char_p, ctypes.POINTER(_i64), ctypes.POINTER(_i64)]
     L.fasted_dataset_csv_f16.argtypes = [ctypes.c_char_p, _vp, _i64, _i64, _i64]
@@ -116,6 +119,16 @@ def dataset_csv(path: str) -> np.ndarray:
     out = np.empty((n.value, d.value), dtype=np.uint16)
     _check(load().fasted_dataset_csv_f16(path.encode(), out.ctypes.data_as(_vp), n.value, d.value, d.value))
     return out
+
+
+def join_static_scratch(points_dev: int, n: int, d: int, ld: int, eps: float, keys_out_dev: int, capacity: int,
+                        stream: int = 0) -> tuple[int, int]:
+    """fasted_join_static_scratch: join on caller-owned device buffers without allocating anything.
+    Returns (pairs_found, pairs_stored); records in keys_out_dev are (query << 32) | candidate, unsorted."""
+    found, stored = ctypes.c_ulonglong(), ctypes.c_ulonglong()
+    _check(load().fasted_join_static_scratch(_vp(points_dev), n, d, ld, float(eps), _vp(keys_out_dev), capacity,
+                                             _vp(stream), ctypes.byref(found), ctypes.byref(stored)))
+    return int(found.value), int(stored.value)
 
 
 class SelfJoin:

@@ -594,4 +594,134 @@ int fasted_brute_force_f64(fasted_ctx* c, const int32_t* sample_rows, int n_samp
     return FASTED_OK;
 }
 
+
+// ---------------------------------------------------------------------------
+// Join without any allocation
+// ---------------------------------------------------------------------------
+//
+// Scratch for fasted_join_static_scratch: the row norms of up to
+// kStaticMaxPoints points followed by the kernel's counter block.  It lives in
+// the library image, so every GPU that loads this library keeps these 4 MiB +
+// 256 bytes until the process exits, whether or not the entry point is used.
+// In host code the symbol below is only a stand-in: the device address comes
+// from cudaGetSymbolAddress, once per device.
+namespace {
+constexpr int64_t kStaticMaxPoints = 1 << 20;
+constexpr size_t kStaticCounterBytes = 256;
+constexpr size_t kStaticScratchBytes = static_cast<size_t>(kStaticMaxPoints) * sizeof(float) + kStaticCounterBytes;
+}  // namespace
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+namespace {
+constexpr int kMaxDevices = 64;
+unsigned char* g_static_scratch_addr[kMaxDevices] = {};  // device address of g_static_scratch, per device
+
+// One-time set-up on the current device: resolve the scratch symbol and raise
+// the kernels' dynamic shared memory limits.  Neither call allocates.
+int static_scratch_setup(int device, unsigned char** out) {
+    if (device < 0 || device >= kMaxDevices) return fail(FASTED_EINVAL, "device ordinal %d not supported", device);
+    if (!g_static_scratch_addr[device]) {
+        cudaDeviceProp prop;
+        CU_TRY(cudaGetDeviceProperties(&prop, device));
+        if (prop.major != 10)
+            return fail(FASTED_ENODEV, "device %d is sm_%d%d; this library contains sm_100a code only", device,
+                        prop.major, prop.minor);
+        void* addr = nullptr;
+        CU_TRY(cudaGetSymbolAddress(&addr, g_static_scratch));
+        CU_TRY(cudaFuncSetAttribute(fasted::join_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    fasted::kJoinSmemBytes));
+        CU_TRY(cudaFuncSetAttribute(fasted::row_norms_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    fasted::kNormSmemBytes));
+        g_static_scratch_addr[device] = static_cast<unsigned char*>(addr);
+    }
+    *out = g_static_scratch_addr[device];
+    return FASTED_OK;
+}
+
+int encode_map(CUtensorMap* map, const void* points, int64_t n, int64_t d, int64_t ld, int box_rows) {
+    EncodeTiledFn enc = get_encode_fn();
+    if (!enc) return fail(FASTED_ECUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    const cuuint64_t gdim[2] = {static_cast<cuuint64_t>(d), static_cast<cuuint64_t>(n)};
+    const cuuint64_t gstride[1] = {static_cast<cuuint64_t>(ld) * 2};
+    const cuuint32_t box[2] = {static_cast<cuuint32_t>(fasted::kTileK), static_cast<cuuint32_t>(box_rows)};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(points), gdim, gstride, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(FASTED_ECUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return FASTED_OK;
+}
+}  // namespace
+
+int fasted_join_static_scratch(const void* points_dev, int64_t n, int64_t d, int64_t ld, double eps,
+                               unsigned long long* keys_out_dev, uint64_t capacity, void* stream,
+                               unsigned long long* pairs_found, unsigned long long* pairs_stored) {
+    if (!points_dev || !pairs_found || !pairs_stored) return fail(FASTED_EINVAL, "null argument");
+    if (capacity > 0 && !keys_out_dev) return fail(FASTED_EINVAL, "keys_out_dev is null but capacity is not 0");
+    int rc = check_shape(n, d);
+    if (rc) return rc;
+    if (n > kStaticMaxPoints)
+        return fail(FASTED_EINVAL,
+                    "n = %lld exceeds the %lld points the built-in scratch area holds; use fasted_join, which allocates",
+                    (long long)n, (long long)kStaticMaxPoints);
+    if (ld < d || (ld % 8) != 0) return fail(FASTED_EINVAL, "ld (%lld) must be >= d and a multiple of 8", (long long)ld);
+    if (reinterpret_cast<uintptr_t>(points_dev) % 16 != 0) return fail(FASTED_EINVAL, "points must be 16-byte aligned");
+    if (reinterpret_cast<uintptr_t>(keys_out_dev) % 8 != 0) return fail(FASTED_EINVAL, "keys_out_dev must be 8-byte aligned");
+    if (!(eps >= 0.0)) return fail(FASTED_EINVAL, "epsilon must be >= 0");
+
+    int device = -1;
+    CU_TRY(cudaGetDevice(&device));
+    unsigned char* scratch = nullptr;
+    rc = static_scratch_setup(device, &scratch);
+    if (rc) return rc;
+    float* norms = reinterpret_cast<float*>(scratch);
+    unsigned long long* counters =
+        reinterpret_cast<unsigned long long*>(scratch + static_cast<size_t>(kStaticMaxPoints) * sizeof(float));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+    CUtensorMap map_a, map_b;
+    rc = encode_map(&map_a, points_dev, n, d, ld, fasted::kTileM);
+    if (rc) return rc;
+    rc = encode_map(&map_b, points_dev, n, d, ld, fasted::kTileN);
+    if (rc) return rc;
+
+    int num_sms = 0;
+    CU_TRY(cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, device));
+
+    fasted::JoinParams p{};
+    p.norms = norms;
+    p.counters = counters;
+    p.keys = keys_out_dev;
+    p.dist2 = nullptr;
+    p.capacity = capacity;
+    const double e2 = eps * eps;
+    p.eps2 = e2 > FLT_MAX ? FLT_MAX : static_cast<float>(e2);
+    p.n = static_cast<int>(n);
+    p.q_begin = 0;
+    p.q_end = static_cast<int>(n);
+    p.k_steps = static_cast<int>((d + fasted::kTileK - 1) / fasted::kTileK);
+    p.tiles_m = static_cast<int>((n + fasted::kTileM - 1) / fasted::kTileM);
+    p.tiles_n = static_cast<int>((n + fasted::kTileN - 1) / fasted::kTileN);
+    p.band_tiles = std::max(1, std::min(16, p.tiles_m));
+    p.total_tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
+    const int grid = static_cast<int>(std::min<long long>(p.total_tiles, num_sms));
+
+    // The scratch area keeps whatever the previous call left: the counters must start at zero
+    // (the norms are overwritten for rows [0, n) before the join reads them).
+    CU_TRY(cudaMemsetAsync(counters, 0, kStaticCounterBytes, st));
+    const int row_blocks = static_cast<int>((n + fasted::kNormRows - 1) / fasted::kNormRows);
+    fasted::row_norms_kernel<<<std::min(row_blocks, num_sms * 3), fasted::kNormRows, fasted::kNormSmemBytes, st>>>(
+        map_a, norms, static_cast<int>(n), p.k_steps, row_blocks, counters + 2);
+    CU_TRY(cudaGetLastError());
+    fasted::join_kernel<<<grid, fasted::kJoinThreads, fasted::kJoinSmemBytes, st>>>(map_a, map_b, p);
+    CU_TRY(cudaGetLastError());
+    unsigned long long h[3] = {0, 0, 0};
+    CU_TRY(cudaMemcpyAsync(h, counters, sizeof(h), cudaMemcpyDeviceToHost, st));
+    CU_TRY(cudaStreamSynchronize(st));
+    if (h[2]) return fail(FASTED_EKERNEL, "a device-side wait ran out (status 0x%llx)", h[2]);
+    *pairs_found = h[0];
+    *pairs_stored = h[1];
+    return FASTED_OK;
+}
+
 }  // extern "C"

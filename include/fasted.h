@@ -182,6 +182,37 @@ int fasted_pairs_device(fasted_ctx* ctx, void** pairs_dev, void** dist2_dev);
 int fasted_brute_force_f64(fasted_ctx* ctx, const int32_t* sample_rows, int n_samples, double eps,
                            unsigned long long* counts_out);
 
+/* Join of all n points with no memory allocation of any kind.  (This entry point has no
+ * counterpart in the reference.)
+ *
+ * Who needs it: host programs in which this library is a guest.  A database or a tensor
+ * framework usually claims nearly all of the GPU's memory for its own pool at start-up and hands
+ * out pieces of it; inside such a host a cudaMalloc from a plug-in fails or steals from the pool,
+ * and cudaMalloc/cudaFree also stall every stream of the device, which a caller on a latency
+ * budget cannot accept.  Such a caller passes buffers carved from its own pool and calls this.
+ *
+ * The caller passes the input (points_dev: n rows of binary16 on the device, row stride ld, ld a
+ * multiple of 8, 16-byte aligned, columns [d, ld) zero) and the output (keys_out_dev: room for
+ * `capacity` 64-bit records on the device).  Each record is (query << 32) | candidate, in the
+ * order the GPU found them (not sorted: sorting needs scratch proportional to the output).
+ * *pairs_found counts all hits, *pairs_stored those written (at most capacity), as in fasted_join.
+ *
+ * What the join needs besides that - the row norms and its counters - lives in an area built into
+ * the library: 4 MiB + 256 bytes of device memory per GPU, held from library load to process exit.
+ * It is sized for n <= 1,048,576 points; a larger n is rejected with FASTED_EINVAL (use
+ * fasted_join).  The area is one per GPU and shared by every call: it still holds the previous
+ * call's contents on entry (the function re-zeroes its counters and recomputes the norms every
+ * time), and two calls whose GPU work overlaps - different streams, threads or processes sharing
+ * the library image on one GPU - race on it.  Run them one after the other.
+ *
+ * Works on the current CUDA device and on `stream` (a cudaStream_t, may be 0); it returns after
+ * the stream has drained.  The first call on each device also looks up the device address of
+ * the built-in area and sets the kernels' shared-memory limits; make that first call outside any
+ * stream capture.  No cudaMalloc, cudaFree, event, stream or library allocation is made. */
+int fasted_join_static_scratch(const void* points_dev, int64_t n, int64_t d, int64_t ld, double eps,
+                               unsigned long long* keys_out_dev, uint64_t capacity, void* stream,
+                               unsigned long long* pairs_found, unsigned long long* pairs_stored);
+
 /* Host-side dataset builders (no GPU involved), the loaders behind layer 1.
  * Exponential: replaces SimSearch::ExponentialPointGenerator,
  * source/DataLoader/ExponentialPointGenerator.hpp:22-52, plus the
