@@ -213,6 +213,7 @@ def main() -> None:
     ap.add_argument("--d", type=int, default=0, help="override the dimension")
     ap.add_argument("--eps", type=float, default=0.0, help="override epsilon (default: workload table or tuned)")
     ap.add_argument("--band-tiles", type=int, default=0)
+    ap.add_argument("--cta-pair", type=int, default=-1, help="1: CTA-pair (2-SM) join kernel, 0: single-CTA kernel")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
@@ -251,6 +252,8 @@ def main() -> None:
     sj.set_stream(torch.cuda.current_stream().cuda_stream)
     if args.band_tiles:
         sj.set_option("band_tiles", args.band_tiles)
+    if args.cta_pair >= 0:
+        sj.set_option("cta_pair", args.cta_pair)
 
     def barrier():
         if world > 1:

@@ -97,6 +97,8 @@ struct fasted_ctx {
     // options
     int band_tiles = 16;
     int grid = 0;
+    int cta_pair = 0;  // 1: CTA-pair kernel (256 x 256 tiles on 2-CTA clusters)
+    int max_pair_clusters = 0;
 };
 
 namespace {
@@ -220,6 +222,28 @@ int fasted_create(int device, fasted_ctx** out) {
     cudaFuncSetAttribute(fasted::join_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, fasted::kJoinSmemBytes);
     cudaFuncSetAttribute(fasted::row_norms_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          fasted::kNormSmemBytes);
+    cudaFuncSetAttribute(fasted::join_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         fasted::kPairSmemBytes);
+    {
+        // How many 2-CTA clusters of the pair kernel the device can hold at once.
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2 * c->num_sms);
+        cfg.blockDim = dim3(fasted::kJoinThreads);
+        cfg.dynamicSmemBytes = fasted::kPairSmemBytes;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2;
+        attr.val.clusterDim.y = 1;
+        attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        int clusters = 0;
+        if (cudaOccupancyMaxActiveClusters(&clusters, fasted::join_pair_kernel, &cfg) == cudaSuccess && clusters > 0)
+            c->max_pair_clusters = clusters;
+        else
+            c->max_pair_clusters = c->num_sms / 2;
+        cudaGetLastError();
+    }
     e = cudaGetLastError();
     if (e != cudaSuccess) {
         fasted_destroy(c);
@@ -259,6 +283,9 @@ int fasted_set_option(fasted_ctx* c, const char* name, int64_t value) {
     if (!strcmp(name, "band_tiles")) {
         if (value < 1 || value > 4096) return fail(FASTED_EINVAL, "band_tiles out of range");
         c->band_tiles = static_cast<int>(value);
+    } else if (!strcmp(name, "cta_pair")) {
+        if (value != 0 && value != 1) return fail(FASTED_EINVAL, "cta_pair must be 0 or 1");
+        c->cta_pair = static_cast<int>(value);
     } else if (!strcmp(name, "grid")) {
         if (value < 0 || value > 65535) return fail(FASTED_EINVAL, "grid out of range");
         c->grid = static_cast<int>(value);
@@ -444,12 +471,23 @@ int fasted_join(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end, uint6
     p.q_begin = static_cast<int>(q_begin);
     p.q_end = static_cast<int>(q_end);
     p.k_steps = static_cast<int>((c->d + fasted::kTileK - 1) / fasted::kTileK);
-    p.tiles_m = static_cast<int>((q_end - q_begin + fasted::kTileM - 1) / fasted::kTileM);
+    const bool pair = c->cta_pair != 0;
+    const int tile_m = pair ? fasted::kPairTileM : fasted::kTileM;
+    p.tiles_m = static_cast<int>((q_end - q_begin + tile_m - 1) / tile_m);
     p.tiles_n = static_cast<int>((c->n + fasted::kTileN - 1) / fasted::kTileN);
-    p.band_tiles = std::max(1, std::min(c->band_tiles, std::max(p.tiles_m, 1)));
+    // band_tiles counts 128-row tile rows; a pair tile is two of them.
+    const int band = pair ? std::max(1, c->band_tiles / 2) : c->band_tiles;
+    p.band_tiles = std::max(1, std::min(band, std::max(p.tiles_m, 1)));
     p.total_tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
-    int grid = c->grid > 0 ? c->grid : c->num_sms;
-    if (p.total_tiles < grid) grid = static_cast<int>(std::max<long long>(p.total_tiles, 1));
+    int grid;
+    if (pair) {
+        int clusters = c->grid > 0 ? std::max(1, c->grid / 2) : c->max_pair_clusters;
+        if (p.total_tiles < clusters) clusters = static_cast<int>(std::max<long long>(p.total_tiles, 1));
+        grid = 2 * clusters;
+    } else {
+        grid = c->grid > 0 ? c->grid : c->num_sms;
+        if (p.total_tiles < grid) grid = static_cast<int>(std::max<long long>(p.total_tiles, 1));
+    }
 
     CU_TRY(cudaMemsetAsync(c->counters, 0, 8 * sizeof(unsigned long long), c->stream));
     CU_TRY(cudaEventRecord(c->ev[0], c->stream));
@@ -458,7 +496,21 @@ int fasted_join(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end, uint6
         if (rc) return rc;
     }
     CU_TRY(cudaEventRecord(c->ev[1], c->stream));
-    if (p.total_tiles > 0) {
+    if (p.total_tiles > 0 && pair) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(grid);
+        cfg.blockDim = dim3(fasted::kJoinThreads);
+        cfg.dynamicSmemBytes = fasted::kPairSmemBytes;
+        cfg.stream = c->stream;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2;
+        attr.val.clusterDim.y = 1;
+        attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        CU_TRY(cudaLaunchKernelEx(&cfg, fasted::join_pair_kernel, c->map_a, p));
+    } else if (p.total_tiles > 0) {
         fasted::join_kernel<<<grid, fasted::kJoinThreads, fasted::kJoinSmemBytes, c->stream>>>(c->map_a, c->map_b, p);
         CU_TRY(cudaGetLastError());
     }

@@ -91,7 +91,7 @@ __device__ __forceinline__ void tile_coords(const JoinParams& p, long long t, in
 
 constexpr int kNormRows = 128;
 constexpr int kNormStages = 4;
-constexpr int kNormBoxesPerStage = 2;  // 2 x 128 B = 256 contiguous bytes per row per stage
+constexpr int kNormBoxesPerStage = 1;  // 128 contiguous bytes per row per stage; 64 KiB ring -> 3 blocks per SM
 constexpr uint32_t kNormBoxBytes = kNormRows * kTileK * 2;
 constexpr uint32_t kNormStageBytes = kNormBoxBytes * kNormBoxesPerStage;
 constexpr int kNormSmemBytes = kNormStages * kNormStageBytes + 1024 + 64;
@@ -205,6 +205,62 @@ row_norms_kernel(const __grid_constant__ CUtensorMap map, float* __restrict__ no
 //               a warp scan and one atomicAdd per warp, store packed pairs.
 // The epilogue of tile t overlaps the main loop of tile t+1 through the two
 // accumulator buffers.
+
+// Epilogue of one accumulator (128 lanes x kTileN columns) for one warp: thread = query row q
+// (TMEM lane), 32 columns per tcgen05.ld.  d2 = (s_q + s_c) - 2a exactly as the reference's
+// inspectResults (source/warpMma.cuh:239-242), inclusive compare (:257); rows and columns that are
+// padding carry +inf norms and can never hit (:259).  Hits are compacted per warp: a scan of the
+// per-thread hit counts, ONE atomicAdd on the found counter (plus one on the stored counter) per
+// warp-chunk that has hits, then each thread writes its records to consecutive slots -- the
+// reference does two atomics per pair (source/pair.cuh:123-133).  Overflow keeps its rule: found
+// counts everything, stored stops at capacity.
+__device__ __forceinline__ void epilogue_tile(const JoinParams& p, uint32_t taddr, const float* cn, float sq, int q,
+                                              int c_base, int lane) {
+    const unsigned long long qkey = static_cast<unsigned long long>(static_cast<uint32_t>(q)) << 32;
+#pragma unroll 1
+    for (int c0 = 0; c0 < kTileN; c0 += 32) {
+        uint32_t v[32];
+        ptx::tmem_ld_32x32b_x32(taddr + c0, v);
+        ptx::tmem_ld_wait();
+        uint32_t mask = 0;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            const float d2 = (sq + cn[c0 + j]) - 2.0f * __uint_as_float(v[j]);
+            if (d2 <= p.eps2) mask |= (1u << j);
+        }
+        if (__any_sync(0xffffffffu, mask != 0)) {
+            const uint32_t cnt = __popc(mask);
+            uint32_t incl = cnt;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t up = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += up;
+            }
+            const uint32_t total = __shfl_sync(0xffffffffu, incl, 31);
+            unsigned long long base = 0;
+            if (lane == 0) {
+                base = atomicAdd(p.counters + 0, static_cast<unsigned long long>(total));
+                if (base < p.capacity) {
+                    const unsigned long long room = p.capacity - base;
+                    atomicAdd(p.counters + 1, room < total ? room : static_cast<unsigned long long>(total));
+                }
+            }
+            base = __shfl_sync(0xffffffffu, base, 0);
+            unsigned long long slot = base + (incl - cnt);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                if (mask & (1u << j)) {
+                    if (slot < p.capacity) {
+                        p.keys[slot] = qkey | static_cast<unsigned long long>(static_cast<uint32_t>(c_base + c0 + j));
+                        if (p.dist2) p.dist2[slot] = (sq + cn[c0 + j]) - 2.0f * __uint_as_float(v[j]);
+                    }
+                    ++slot;
+                }
+            }
+        }
+    }
+}
+
 
 struct JoinSmemAux {
     unsigned long long full_bar[kStages];
@@ -374,50 +430,7 @@ join_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                                    static_cast<uint32_t>(buf * kTileN);
-            const unsigned long long qkey = static_cast<unsigned long long>(static_cast<uint32_t>(q)) << 32;
-#pragma unroll 1
-            for (int c0 = 0; c0 < kTileN; c0 += 32) {
-                uint32_t v[32];
-                ptx::tmem_ld_32x32b_x32(taddr + c0, v);
-                ptx::tmem_ld_wait();
-                uint32_t mask = 0;
-#pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const float d2 = (sq + cn[c0 + j]) - 2.0f * __uint_as_float(v[j]);
-                    if (d2 <= p.eps2) mask |= (1u << j);
-                }
-                if (__any_sync(0xffffffffu, mask != 0)) {
-                    const uint32_t cnt = __popc(mask);
-                    uint32_t incl = cnt;
-#pragma unroll
-                    for (int o = 1; o < 32; o <<= 1) {
-                        const uint32_t up = __shfl_up_sync(0xffffffffu, incl, o);
-                        if (lane >= o) incl += up;
-                    }
-                    const uint32_t total = __shfl_sync(0xffffffffu, incl, 31);
-                    unsigned long long base = 0;
-                    if (lane == 0) {
-                        base = atomicAdd(p.counters + 0, static_cast<unsigned long long>(total));
-                        if (base < p.capacity) {
-                            const unsigned long long room = p.capacity - base;
-                            atomicAdd(p.counters + 1, room < total ? room : static_cast<unsigned long long>(total));
-                        }
-                    }
-                    base = __shfl_sync(0xffffffffu, base, 0);
-                    unsigned long long slot = base + (incl - cnt);
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        if (mask & (1u << j)) {
-                            if (slot < p.capacity) {
-                                p.keys[slot] = qkey | static_cast<unsigned long long>(static_cast<uint32_t>(c_base + c0 + j));
-                                if (p.dist2)
-                                    p.dist2[slot] = (sq + cn[c0 + j]) - 2.0f * __uint_as_float(v[j]);
-                            }
-                            ++slot;
-                        }
-                    }
-                }
-            }
+            epilogue_tile(p, taddr, cn, sq, q, c_base, lane);
             // Hand the accumulator back to the MMA warp.
             ptx::tc_fence_before_sync();
             __syncwarp();
@@ -432,6 +445,216 @@ join_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     if (warp == 1) {
         ptx::tc_fence_after_sync();
         ptx::tmem_dealloc<1>(tmem_base, kTmemCols);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// The join on CTA pairs (tcgen05 cta_group::2)
+// ---------------------------------------------------------------------------
+//
+// Same algorithm, same roles, same epilogue as join_kernel, but two CTAs on neighbouring SMs
+// (a cluster of 2) share one 256 x 256 tile: each CTA holds 128 query rows (its half of A and its
+// 128 x 256 FP32 accumulator in its own TMEM) and loads only HALF of the candidate rows of the
+// tile (128 x 64 per stage); one tcgen05.mma.cta_group::2 (M256 N256 K16), issued by the leader
+// CTA, reads A from each CTA's own shared memory and the two halves of B from both.  Per stage a
+// CTA therefore moves 32 KB from L2 instead of 48 KB and the tensor core reads B from shared memory
+// once per pair instead of once per CTA: the L2 -> SM path and the shared-memory reads are what the
+// single-CTA kernel spends its power on.  No multicast load is used: each CTA fetches its own boxes.
+//
+// Barriers: full[s] lives in the leader (one expect_tx of 64 KB by the leader's producer, completion
+// bytes from both CTAs' loads); empty[s] and acc_full[b] live in both CTAs and are signalled by two
+// commits of the leader's MMA thread (own CTA + peer); acc_empty[b] lives in the leader and counts
+// the eight epilogue warps of the pair.
+
+constexpr int kPairStages = 6;
+constexpr uint32_t kPairStageBytesA = kTileM * kTileK * 2;        // 16 KiB: 128 query rows
+constexpr uint32_t kPairStageBytesB = (kTileN / 2) * kTileK * 2;  // 16 KiB: 128 of the 256 candidate rows
+constexpr uint32_t kPairStageBytes = kPairStageBytesA + kPairStageBytesB;
+constexpr int kPairTileM = 2 * kTileM;  // query rows per CTA pair
+
+struct PairSmemAux {
+    unsigned long long full_bar[kPairStages];
+    unsigned long long empty_bar[kPairStages];
+    unsigned long long acc_full_bar[2];
+    unsigned long long acc_empty_bar[2];
+    uint32_t tmem_base;
+    int abort_flag;
+    alignas(16) float cand_norms[2][kTileN];
+};
+
+constexpr int kPairSmemBytes = kPairStages * kPairStageBytes + 1024 + static_cast<int>(sizeof(PairSmemAux)) + 64;
+
+__global__ void __launch_bounds__(kJoinThreads, 1)
+join_pair_kernel(const __grid_constant__ CUtensorMap map, const JoinParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_u32 = ptx::smem_u32(smem_raw);
+    const uint32_t tiles_u32 = (raw_u32 + 1023u) & ~1023u;
+    PairSmemAux* aux = reinterpret_cast<PairSmemAux*>(smem_raw + (tiles_u32 - raw_u32) + kPairStages * kPairStageBytes);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = ptx::cluster_cta_rank();  // 0 = leader of the pair
+    const bool leader = rank == 0;
+    volatile int* abort_flag = &aux->abort_flag;
+
+    if (threadIdx.x == 0) {
+        aux->abort_flag = 0;
+        for (int s = 0; s < kPairStages; ++s) {
+            ptx::mbar_init(ptx::smem_u32(&aux->full_bar[s]), 1);
+            ptx::mbar_init(ptx::smem_u32(&aux->empty_bar[s]), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            ptx::mbar_init(ptx::smem_u32(&aux->acc_full_bar[b]), 1);
+            ptx::mbar_init(ptx::smem_u32(&aux->acc_empty_bar[b]), 8);  // 4 epilogue warps x 2 CTAs
+        }
+        ptx::fence_mbar_init();
+        ptx::prefetch_tensormap(&map);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc<2>(ptx::smem_u32(&aux->tmem_base), kTmemCols);
+        ptx::tmem_relinquish<2>();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::cluster_sync_all();  // both CTAs' barriers exist before anything remote touches them
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem_base = aux->tmem_base;
+
+    const long long first_tile = blockIdx.x >> 1;
+    const long long tile_step = gridDim.x >> 1;
+
+    if (warp == 0) {
+        // ------------------------- TMA producer (both CTAs) -------------------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            long long issued = 0;
+            for (long long t = first_tile; t < p.total_tiles && ok; t += tile_step) {
+                int tm, tn;
+                tile_coords(p, t, tm, tn);
+                const int row_a = p.q_begin + tm * kPairTileM + static_cast<int>(rank) * kTileM;
+                const int row_b = tn * kTileN + static_cast<int>(rank) * (kTileN / 2);
+                for (int ks = 0; ks < p.k_steps; ++ks) {
+                    ok = ptx::mbar_wait_bounded(ptx::smem_u32(&aux->empty_bar[stage]), phase ^ 1u, abort_flag,
+                                                kWaitLimitNs);
+                    if (!ok) break;
+                    const uint32_t bar_local = ptx::smem_u32(&aux->full_bar[stage]);
+                    const uint32_t bar_leader = ptx::mapa_u32(bar_local, 0);
+                    const uint32_t dst = tiles_u32 + stage * kPairStageBytes;
+                    if (leader) ptx::mbar_expect_tx(bar_local, 2 * kPairStageBytes);
+                    ptx::tma_load_2d_pair(dst, &map, bar_leader, ks * kTileK, row_a);
+                    ptx::tma_load_2d_pair(dst + kPairStageBytesA, &map, bar_leader, ks * kTileK, row_b);
+                    ++issued;
+                    if (++stage == kPairStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+            // Tail: do not leave while the leader's MMA thread may still signal this CTA's empty
+            // barriers (or, on failure, while loads are in flight): walk one more lap of the ring.
+            // (Stages never used pass at once: a fresh barrier counts as released.)
+            const uint64_t t0 = ptx::globaltimer_ns();
+            for (int i = 0; i < kPairStages && issued > 0; ++i) {
+                while (!ptx::mbar_try_wait(ptx::smem_u32(&aux->empty_bar[stage]), phase ^ 1u) &&
+                       ptx::globaltimer_ns() - t0 < (ok ? kWaitLimitNs : 20000000ull)) {
+                }
+                if (++stage == kPairStages) {
+                    stage = 0;
+                    phase ^= 1u;
+                }
+            }
+            if (!ok) atomicOr(p.counters + 2, kErrProducerWait);
+        }
+    } else if (warp == 1) {
+        // ------------------------- MMA issuer (leader CTA only) ----------------------
+        if (lane == 0 && leader) {
+            constexpr uint32_t idesc = ptx::make_f16_idesc(kPairTileM, kTileN);
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            long long it = 0;
+            for (long long t = first_tile; t < p.total_tiles && ok; t += tile_step, ++it) {
+                const int buf = static_cast<int>(it & 1);
+                const uint32_t acc_phase = static_cast<uint32_t>((it >> 1) & 1);
+                ok = ptx::mbar_wait_bounded(ptx::smem_u32(&aux->acc_empty_bar[buf]), acc_phase ^ 1u, abort_flag,
+                                            kWaitLimitNs);
+                if (!ok) break;
+                ptx::tc_fence_after_sync();
+                const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(buf * kTileN);
+                for (int ks = 0; ks < p.k_steps; ++ks) {
+                    ok = ptx::mbar_wait_bounded(ptx::smem_u32(&aux->full_bar[stage]), phase, abort_flag, kWaitLimitNs);
+                    if (!ok) break;
+                    ptx::tc_fence_after_sync();
+                    const uint32_t a_addr = tiles_u32 + stage * kPairStageBytes;
+                    const uint64_t desc_a = ptx::make_kmajor_sw128_desc(a_addr);
+                    const uint64_t desc_b = ptx::make_kmajor_sw128_desc(a_addr + kPairStageBytesA);
+#pragma unroll
+                    for (int k = 0; k < kTileK / kUmmaK; ++k)
+                        ptx::umma_f16_ss<2>(tmem_d, desc_a + 2u * k, desc_b + 2u * k, idesc, (ks > 0 || k > 0) ? 1u : 0u);
+                    const uint32_t eb = ptx::smem_u32(&aux->empty_bar[stage]);
+                    ptx::umma_commit_pair(ptx::mapa_u32(eb, 0));
+                    ptx::umma_commit_pair(ptx::mapa_u32(eb, 1));
+                    if (++stage == kPairStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (ok) {
+                    const uint32_t fb = ptx::smem_u32(&aux->acc_full_bar[buf]);
+                    ptx::umma_commit_pair(ptx::mapa_u32(fb, 0));
+                    ptx::umma_commit_pair(ptx::mapa_u32(fb, 1));
+                }
+            }
+            if (!ok) atomicOr(p.counters + 2, kErrMmaWait);
+        }
+    } else {
+        // ------------------------- Epilogue (both CTAs) ------------------------------
+        const int quarter = warp & 3;
+        const int row_in_tile = quarter * 32 + lane;
+        const int epi_tid = threadIdx.x - 64;
+        const float inf = __int_as_float(0x7f800000);
+        bool ok = true;
+        long long it = 0;
+        for (long long t = first_tile; t < p.total_tiles; t += tile_step, ++it) {
+            int tm, tn;
+            tile_coords(p, t, tm, tn);
+            const int buf = static_cast<int>(it & 1);
+            const uint32_t acc_phase = static_cast<uint32_t>((it >> 1) & 1);
+            const int q = p.q_begin + tm * kPairTileM + static_cast<int>(rank) * kTileM + row_in_tile;
+            const int c_base = tn * kTileN;
+
+            float* cn = aux->cand_norms[buf];
+            for (int j = epi_tid; j < kTileN; j += kEpiThreads) {
+                const int c = c_base + j;
+                cn[j] = (c < p.n) ? __ldg(p.norms + c) : inf;
+            }
+            const float sq = (q < p.q_end) ? __ldg(p.norms + q) : inf;
+            ptx::named_bar_sync(1, kEpiThreads);
+
+            if (ok) ok = ptx::mbar_wait_bounded(ptx::smem_u32(&aux->acc_full_bar[buf]), acc_phase, abort_flag,
+                                                kWaitLimitNs);
+            if (!ok) continue;
+            ptx::tc_fence_after_sync();
+
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                                   static_cast<uint32_t>(buf * kTileN);
+            epilogue_tile(p, taddr, cn, sq, q, c_base, lane);
+            ptx::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive_cluster_addr(ptx::mapa_u32(ptx::smem_u32(&aux->acc_empty_bar[buf]), 0));
+        }
+        if (!ok && lane == 0) atomicOr(p.counters + 2, kErrEpilogueWait);
+    }
+
+    // Teardown: neither CTA may leave (or free TMEM) while its peer can still touch it.
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::cluster_sync_all();
+    if (warp == 1) {
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc<2>(tmem_base, kTmemCols);
     }
 }
 

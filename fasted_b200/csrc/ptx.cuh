@@ -124,6 +124,45 @@ __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap
         : "memory");
 }
 
+// 2-D tiled load issued by one CTA of a CTA pair: data lands in THIS CTA's shared memory, the
+// completion bytes are counted on an mbarrier that may live in either CTA of the pair (here: the
+// pair's leader).  `bar_cluster_addr` is a shared::cluster address (see mapa_u32).  No multicast:
+// every CTA fetches its own boxes.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t smem_dst, const CUtensorMap* map, uint32_t bar_cluster_addr,
+                                                 int32_t x, int32_t y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4}], [%2];" ::"r"(smem_dst),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(x), "r"(y)
+        : "memory");
+}
+
+// ---- clusters ---------------------------------------------------------------
+
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+
+// shared::cta address of this CTA -> shared::cluster address of the same offset in CTA `rank`.
+__device__ __forceinline__ uint32_t mapa_u32(uint32_t smem_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+    return r;
+}
+
+// Arrive on an mbarrier given by a shared::cluster address (own or peer CTA).
+__device__ __forceinline__ void mbar_arrive_cluster_addr(uint32_t bar_cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+
+// Hardware barrier over all threads of the cluster (both CTAs of a pair).
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
 // ---- tcgen05 ---------------------------------------------------------------
 
 __device__ __forceinline__ void tc_fence_before_sync() {
@@ -213,6 +252,13 @@ __device__ __forceinline__ void umma_f16_ss(uint32_t tmem_d, uint64_t desc_a, ui
 // far by this thread (implies tcgen05.fence::before_thread_sync).
 __device__ __forceinline__ void umma_commit_1cta(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+                 : "memory");
+}
+
+// Pair form: tracks the MMAs of both CTAs; `bar_cluster_addr` is a shared::cluster address, so the
+// same thread can signal its own CTA's barrier and, with a second commit, the peer's.
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster_addr) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr)
                  : "memory");
 }
 

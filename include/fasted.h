@@ -226,7 +226,10 @@ int fasted_dataset_exponential_f16(int64_t n, int64_t d, double lambda, double m
 int fasted_dataset_csv_shape(const char* path, int64_t* n, int64_t* d);
 int fasted_dataset_csv_f16(const char* path, uint16_t* out, int64_t n, int64_t d, int64_t ld_out);
 
-/* Tuning knobs: "band_tiles" (tile rows per raster band), "grid" (CTAs, 0 = one per SM). */
+/* Tuning knobs: "band_tiles" (128-row tile rows per raster band, default 16), "grid" (CTAs,
+ * 0 = one per SM), "cta_pair" (1 = the CTA-pair kernel: 256 x 256 tiles computed by two CTAs with
+ * tcgen05 cta_group::2; same results bit for bit; default 0 because it sustains less under the
+ * power cap on B200). */
 int fasted_set_option(fasted_ctx* ctx, const char* name, int64_t value);
 
 #ifdef __cplusplus

@@ -250,3 +250,28 @@ def test_join_against_reference_gpu_output(gpu_join, oracle_mod, path):
     cmp = assert_pairs_match(oracle_mod, pts, d, eps, got, g["pairs"], BAND, "vs reference GPU output")
     assert cmp["only_a"] + cmp["only_b"] <= max(8, len(g["pairs"]) // 2000)
     assert abs(int(st.pairs_found) - int(g["pairs_found"])) <= max(8, len(g["pairs"]) // 2000)
+
+
+@pytest.mark.parametrize("n,d,eps", [(256, 64, 1e3), (300, 100, 1e3), (1000, 256, 0.5), (2000, 512, 0.7),
+                                     (4096, 128, 0.3136), (777, 333, 0.5), (3000, 2048, 1.6)])
+def test_cta_pair_kernel_is_bit_identical(gpu_join, oracle_mod, n, d, eps):
+    # The 2-CTA (cta_group::2) kernel computes the same accumulators in the same K order:
+    # pairs and emitted distances must equal the single-CTA kernel's bit for bit.
+    rng = np.random.default_rng(n + d)
+    pts = oracle_mod.double_to_half(rng.exponential(1 / 40.0, size=(n, d)))
+    gpu_join.set_points(pts)
+    try:
+        gpu_join.set_option("cta_pair", 0)
+        a = gpu_join.join(eps, capacity=n * n, flags=1)
+        pa, da = gpu_join.pairs(with_dist2=True)
+        gpu_join.set_option("cta_pair", 1)
+        b = gpu_join.join(eps, capacity=n * n, flags=1)
+        pb, db = gpu_join.pairs(with_dist2=True)
+        # bands too
+        gpu_join.join(eps, q_begin=128, q_end=min(n, 600), capacity=n * n)
+        band = gpu_join.pairs()
+    finally:
+        gpu_join.set_option("cta_pair", 0)
+    assert a.status == b.status == 0 and a.pairs_found == b.pairs_found
+    assert np.array_equal(pa, pb) and np.array_equal(da.view(np.uint32), db.view(np.uint32))
+    assert np.array_equal(band, pa[(pa[:, 0] >= 128) & (pa[:, 0] < min(n, 600))])
