@@ -209,8 +209,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
-    ap.add_argument("--n", type=int, default=0, help="override the number of points")
-    ap.add_argument("--d", type=int, default=0, help="override the dimension")
+    ap.add_argument("--points", type=int, default=0, help="override the number of points")
+    ap.add_argument("--dims", type=int, default=0, help="override the dimension")
     ap.add_argument("--eps", type=float, default=0.0, help="override epsilon (default: workload table or tuned)")
     ap.add_argument("--band-tiles", type=int, default=0)
     ap.add_argument("--cta-pair", type=int, default=-1, help="1: CTA-pair (2-SM) join kernel, 0: single-CTA kernel")
@@ -221,10 +221,10 @@ def main() -> None:
 
     name = args.workload
     wl = dict(WORKLOADS[name])
-    if args.n:
-        wl["n"], wl["eps"] = args.n, None
-    if args.d:
-        wl["d"], wl["eps"] = args.d, None
+    if args.points:
+        wl["n"], wl["eps"] = args.points, None
+    if args.dims:
+        wl["d"], wl["eps"] = args.dims, None
     if args.eps:
         wl["eps"] = args.eps
 
@@ -394,7 +394,7 @@ def main() -> None:
         line = {
             "metric": "self_join_tflops", "value": value, "unit": "TFLOPS", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": (value / PUBLISHED_A100_TFLOPS[name]) if name in PUBLISHED_A100_TFLOPS and not (args.n or args.d) and world == 1 else None,
+            "vs_baseline": (value / PUBLISHED_A100_TFLOPS[name]) if name in PUBLISHED_A100_TFLOPS and not (args.points or args.dims) and world == 1 else None,
             "dtype": "f16xf16->f32", "data": "synthetic",
             "config": {
                 "workload": f"{name}: self-join of {n} x {d} points, {wl['dist']} (seed {SEED}), FP16, "
