@@ -216,6 +216,7 @@ def main() -> None:
     ap.add_argument("--cta-pair", type=int, default=-1, help="1: CTA-pair (2-SM) join kernel, 0: single-CTA kernel")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="skip the symmetric-mode and accuracy legs")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 0)
 
@@ -234,7 +235,7 @@ def main() -> None:
 
     import torch
     import torch.distributed as dist
-    from fasted_b200 import SelfJoin, JOIN_NO_SORT
+    from fasted_b200 import SelfJoin, JOIN_NO_SORT, JOIN_SYMMETRIC, JOIN_DIST2
     from fasted_b200.dist import band_bounds
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -327,6 +328,59 @@ def main() -> None:
     flop = 2.0 * n * n * d
     value = flop / (ms_per_step * 1e-3) / 1e12
 
+    # ---- extra leg: symmetric schedule (each unordered pair computed once, both orientations
+    # emitted; bit-identical output).  Reported beside the headline, never as the headline: the
+    # metric still divides 2*N*N*D by the time although about half of those flops are executed.
+    symmetric = None
+    if world == 1 and not args.no_extras:
+        for _ in range(min(args.warmup, 1)):
+            sj.join(eps, capacity=capacity, flags=JOIN_NO_SORT | JOIN_SYMMETRIC)
+        torch.cuda.synchronize()
+        ev0.record()
+        sym_found = 0
+        for _ in range(args.steps):
+            st = sj.join(eps, capacity=capacity, flags=JOIN_NO_SORT | JOIN_SYMMETRIC)
+            sym_found = int(st.pairs_found)
+        ev1.record()
+        torch.cuda.synchronize()
+        sym_ms = ev0.elapsed_time(ev1) / args.steps
+        symmetric = {"value": flop / (sym_ms * 1e-3) / 1e12, "unit": "TFLOPS", "ms_per_step": sym_ms,
+                     "pairs_found": sym_found, "same_pair_count_as_full": sym_found == found_total,
+                     "note": "2*N*N*D / time with the symmetric schedule; executed tensor flops are about half"}
+
+    # ---- extra leg: accuracy against an FP64 brute-force join on a band of query rows ------------
+    accuracy = None
+    if rank == 0 and not args.no_extras:
+        a_rows = min(256, n)
+        q0 = max(0, (n // 2) // 128 * 128)
+        q0 = min(q0, n - a_rows)
+        st = sj.join(eps, q_begin=q0, q_end=q0 + a_rows, capacity=a_rows * 8192, flags=JOIN_DIST2)
+        got, got_d2 = sj.pairs(with_dist2=True)
+        rows = np.arange(q0, q0 + a_rows, dtype=np.int32)
+        _, truth = sj.brute_force_pairs(rows, eps, capacity=a_rows * 8192)
+        kg = (got[:, 0].astype(np.int64) << 32) | got[:, 1].astype(np.int64)
+        kt = (truth[:, 0].astype(np.int64) << 32) | truth[:, 1].astype(np.int64)
+        inter = np.intersect1d(kg, kt, assume_unique=True)
+        cg = np.bincount(got[:, 0] - q0, minlength=a_rows)
+        ct = np.bincount(truth[:, 0] - q0, minlength=a_rows)
+        ci = np.bincount((inter >> 32) - q0, minlength=a_rows)
+        union = cg + ct - ci
+        iou = np.where(union > 0, ci / np.maximum(union, 1), 1.0)
+        off = got[:, 0] != got[:, 1]
+        gi = torch.from_numpy(got[off].astype(np.int64)).cuda()
+        d64 = torch.empty(gi.shape[0], dtype=torch.float64, device="cuda")
+        for a in range(0, gi.shape[0], 4096):
+            xa = dev_pts[gi[a:a + 4096, 0], :d].double()
+            xb = dev_pts[gi[a:a + 4096, 1], :d].double()
+            d64[a:a + 4096] = ((xa - xb) ** 2).sum(dim=1).sqrt()
+        d32 = np.sqrt(np.maximum(got_d2[off].astype(np.float64), 0.0))
+        err = d32 - d64.cpu().numpy()
+        accuracy = {"query_rows": [int(q0), int(q0 + a_rows)], "pairs_ours": int(len(kg)), "pairs_fp64": int(len(kt)),
+                    "mean_per_point_iou": float(iou.mean()), "min_per_point_iou": float(iou.min()),
+                    "distance_error_mean": float(err.mean()) if len(err) else 0.0,
+                    "distance_error_std": float(err.std()) if len(err) else 0.0,
+                    "truth": "FP64 direct-form brute force on the GPU (plain CUDA cores) over the same FP16 inputs"}
+
     # ---- timed region 2: end to end with host buffers -------------------------------------------
     e2e = None
     if not args.no_e2e:
@@ -418,6 +472,8 @@ def main() -> None:
                          "norms_kernel": {"bound": "hbm", "achieved": (n * ld * 2 + n * 4) / (float(np.mean(norm_ms)) * 1e-3) / 1e9,
                                           "peak": peaks["hbm"], "unit": "GB/s"}},
             "cpu_baseline": cpu,
+            "symmetric": symmetric,
+            "accuracy_vs_fp64": accuracy,
         }
         if tuned_mean is not None:
             line["config"]["epsilon_tuned"] = True

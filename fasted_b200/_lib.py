@@ -20,7 +20,7 @@ _u64 = ctypes.c_uint64
 _vp = ctypes.c_void_p
 
 OK, EINVAL, ECUDA, ENODEV, ESTATE, EKERNEL, EIO = 0, -1, -2, -3, -4, -5, -6
-JOIN_DIST2, JOIN_NO_SORT, JOIN_KEEP_NORMS = 1, 2, 4
+JOIN_DIST2, JOIN_NO_SORT, JOIN_KEEP_NORMS, JOIN_SYMMETRIC = 1, 2, 4, 8
 
 
 class FastedError(RuntimeError):
@@ -54,7 +54,7 @@ DECLARED_SYMBOLS = [
     "fasted_set_points_host_f16", "fasted_set_points_device_f16", "fasted_generate_exponential",
     "fasted_fill_exponential_device",
     "fasted_points_info", "fasted_get_points_host_f16", "fasted_row_norms", "fasted_get_norms",
-    "fasted_join", "fasted_get_pairs", "fasted_pairs_device", "fasted_brute_force_f64", "fasted_set_option",
+    "fasted_join", "fasted_get_pairs", "fasted_pairs_device", "fasted_brute_force_f64", "fasted_brute_force_f64_pairs", "fasted_set_option",
     "fasted_dataset_exponential_f16", "fasted_dataset_csv_shape", "fasted_dataset_csv_f16",
     "fasted_join_static_scratch",
 ]
@@ -90,6 +90,8 @@ def load() -> ctypes.CDLL:
     L.fasted_get_pairs.argtypes = [_vp, _u64, _u64, _vp, _vp]
     L.fasted_pairs_device.argtypes = [_vp, ctypes.POINTER(_vp), ctypes.POINTER(_vp)]
     L.fasted_brute_force_f64.argtypes = [_vp, _vp, ctypes.c_int, ctypes.c_double, _vp]
+    L.fasted_brute_force_f64_pairs.argtypes = [_vp, _vp, ctypes.c_int, ctypes.c_double, _vp, _vp, _u64,
+                                               ctypes.POINTER(ctypes.c_ulonglong)]
     L.fasted_set_option.argtypes = [_vp, ctypes.c_char_p, _i64]
     L.fasted_join_static_scratch.argtypes = [_vp, _i64, _i64, _i64, ctypes.c_double, _vp, _u64, _vp,
                                              ctypes.POINTER(ctypes.c_ulonglong), ctypes.POINTER(ctypes.c_ulonglong)]
@@ -243,6 +245,21 @@ class SelfJoin:
         _check(self._L.fasted_brute_force_f64(self._h, rows.ctypes.data_as(_vp), len(rows), float(eps),
                                               out.ctypes.data_as(_vp)))
         return out
+
+    def brute_force_pairs(self, rows, eps: float, capacity: int) -> tuple[np.ndarray, np.ndarray]:
+        """FP64 direct-form neighbours of the given query rows: (counts per row, sorted int32 pairs (m, 2))."""
+        rows = np.ascontiguousarray(rows, dtype=np.int32)
+        counts = np.zeros(len(rows), dtype=np.uint64)
+        keys = np.empty(capacity, dtype=np.uint64)
+        nk = ctypes.c_ulonglong()
+        _check(self._L.fasted_brute_force_f64_pairs(self._h, rows.ctypes.data_as(_vp), len(rows), float(eps),
+                                                    counts.ctypes.data_as(_vp), keys.ctypes.data_as(_vp), capacity,
+                                                    ctypes.byref(nk)))
+        if nk.value > capacity:
+            raise FastedError(EINVAL, f"{nk.value} neighbours found, capacity {capacity}")
+        k = np.sort(keys[: nk.value])
+        pairs = np.stack([(k >> np.uint64(32)).astype(np.int32), (k & np.uint64(0xFFFFFFFF)).astype(np.int32)], 1)
+        return counts, pairs
 
     def set_option(self, name: str, value: int) -> None:
         _check(self._L.fasted_set_option(self._h, name.encode(), value))

@@ -473,6 +473,11 @@ int fasted_join(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end, uint6
     p.k_steps = static_cast<int>((c->d + fasted::kTileK - 1) / fasted::kTileK);
     const bool pair = c->cta_pair != 0;
     const int tile_m = pair ? fasted::kPairTileM : fasted::kTileM;
+    const bool symmetric = (flags & FASTED_JOIN_SYMMETRIC) != 0;
+    if (symmetric && (q_begin != 0 || q_end != c->n))
+        return fail(FASTED_EINVAL, "FASTED_JOIN_SYMMETRIC needs the full query range [0, n)");
+    p.tile_m = tile_m;
+    p.symmetric = symmetric ? 1 : 0;
     p.tiles_m = static_cast<int>((q_end - q_begin + tile_m - 1) / tile_m);
     p.tiles_n = static_cast<int>((c->n + fasted::kTileN - 1) / fasted::kTileN);
     // band_tiles counts 128-row tile rows; a pair tile is two of them.
@@ -523,7 +528,8 @@ int fasted_join(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end, uint6
     c->result_pairs = nullptr;
     c->result_dist = nullptr;
     if (h[2]) return fail(FASTED_EKERNEL, "a device-side wait ran out (status 0x%llx)", h[2]);
-    const uint64_t stored = h[1];
+    // Every record with a slot below the capacity is written, the others are dropped.
+    const uint64_t stored = std::min<uint64_t>(h[0], capacity);
 
     CU_TRY(cudaEventRecord(c->ev[3], c->stream));
     const unsigned long long* sorted_keys = c->keys;
@@ -613,39 +619,53 @@ int fasted_pairs_device(fasted_ctx* c, void** pairs_dev, void** dist2_dev) {
     return FASTED_OK;
 }
 
-int fasted_brute_force_f64(fasted_ctx* c, const int32_t* sample_rows, int n_samples, double eps,
-                           unsigned long long* counts_out) {
+int fasted_brute_force_f64_pairs(fasted_ctx* c, const int32_t* sample_rows, int n_samples, double eps,
+                                 unsigned long long* counts_out, unsigned long long* keys_out, uint64_t capacity,
+                                 unsigned long long* n_keys_out) {
     if (!c || !sample_rows || !counts_out || n_samples <= 0) return fail(FASTED_EINVAL, "bad argument");
+    if (capacity > 0 && (!keys_out || !n_keys_out)) return fail(FASTED_EINVAL, "keys_out / n_keys_out is null");
     if (!c->points) return fail(FASTED_ESTATE, "no dataset is resident");
     if (c->d > 12000) return fail(FASTED_EINVAL, "brute-force check supports d <= 12000");
     for (int i = 0; i < n_samples; ++i)
         if (sample_rows[i] < 0 || sample_rows[i] >= c->n) return fail(FASTED_EINVAL, "sample row out of range");
     CU_TRY(cudaSetDevice(c->device));
     int* d_rows = nullptr;
-    unsigned long long* d_counts = nullptr;
-    CU_TRY(cudaMalloc(&d_rows, n_samples * sizeof(int)));
-    if (cudaMalloc(&d_counts, n_samples * 8) != cudaSuccess) {
-        cudaFree(d_rows);
-        return fail(FASTED_ECUDA, "cudaMalloc failed");
+    unsigned long long* d_counts = nullptr;  // n_samples counts followed by the key counter
+    unsigned long long* d_keys = nullptr;
+    cudaError_t e = cudaMalloc(&d_rows, n_samples * sizeof(int));
+    if (e == cudaSuccess) e = cudaMalloc(&d_counts, (n_samples + 1) * 8);
+    if (e == cudaSuccess && capacity > 0) e = cudaMalloc(&d_keys, capacity * 8);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(d_rows, sample_rows, n_samples * sizeof(int), cudaMemcpyHostToDevice, c->stream);
+    if (e == cudaSuccess) e = cudaMemsetAsync(d_counts, 0, (n_samples + 1) * 8, c->stream);
+    if (e == cudaSuccess) {
+        const int threads = 256;
+        const int bx = static_cast<int>(std::min<int64_t>((c->n + 7) / 8, 2048));
+        dim3 grid(bx, n_samples);
+        fasted::brute_f64_kernel<<<grid, threads, static_cast<size_t>(c->d) * 4, c->stream>>>(
+            c->points, static_cast<int>(c->n), static_cast<int>(c->d), static_cast<int>(c->ld), d_rows, n_samples,
+            eps * eps, d_counts, d_keys, capacity, d_counts + n_samples);
+        e = cudaGetLastError();
     }
-    cudaMemcpyAsync(d_rows, sample_rows, n_samples * sizeof(int), cudaMemcpyHostToDevice, c->stream);
-    cudaMemsetAsync(d_counts, 0, n_samples * 8, c->stream);
-    const int threads = 256;
-    int bx = static_cast<int>(std::min<int64_t>((c->n + 7) / 8, 4096));
-    dim3 grid(bx, n_samples);
-    fasted::brute_f64_kernel<<<grid, threads, static_cast<size_t>(c->d) * 4, c->stream>>>(
-        c->points, static_cast<int>(c->n), static_cast<int>(c->d), static_cast<int>(c->ld), d_rows, n_samples,
-        eps * eps, d_counts, nullptr, 0, nullptr);
-    cudaError_t e = cudaGetLastError();
-    if (e == cudaSuccess)
-        e = cudaMemcpyAsync(counts_out, d_counts, n_samples * 8, cudaMemcpyDeviceToHost, c->stream);
+    unsigned long long nk = 0;
+    if (e == cudaSuccess) e = cudaMemcpyAsync(counts_out, d_counts, n_samples * 8, cudaMemcpyDeviceToHost, c->stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(&nk, d_counts + n_samples, 8, cudaMemcpyDeviceToHost, c->stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
-    cudaFree(d_rows);
-    cudaFree(d_counts);
-    if (e != cudaSuccess) return fail(FASTED_ECUDA, "brute-force kernel failed: %s", cudaGetErrorString(e));
+    if (e == cudaSuccess && capacity > 0) {
+        const unsigned long long m = nk < capacity ? nk : capacity;
+        if (m) e = cudaMemcpy(keys_out, d_keys, m * 8, cudaMemcpyDeviceToHost);
+        *n_keys_out = nk;
+    }
+    if (d_rows) cudaFree(d_rows);
+    if (d_counts) cudaFree(d_counts);
+    if (d_keys) cudaFree(d_keys);
+    if (e != cudaSuccess) return fail(FASTED_ECUDA, "brute-force check failed: %s", cudaGetErrorString(e));
     return FASTED_OK;
 }
 
+int fasted_brute_force_f64(fasted_ctx* c, const int32_t* sample_rows, int n_samples, double eps,
+                           unsigned long long* counts_out) {
+    return fasted_brute_force_f64_pairs(c, sample_rows, n_samples, eps, counts_out, nullptr, 0, nullptr);
+}
 
 // ---------------------------------------------------------------------------
 // Join without any allocation
@@ -756,6 +776,8 @@ int fasted_join_static_scratch(const void* points_dev, int64_t n, int64_t d, int
     p.tiles_n = static_cast<int>((n + fasted::kTileN - 1) / fasted::kTileN);
     p.band_tiles = std::max(1, std::min(16, p.tiles_m));
     p.total_tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
+    p.tile_m = fasted::kTileM;
+    p.symmetric = 0;
     const int grid = static_cast<int>(std::min<long long>(p.total_tiles, num_sms));
 
     // The scratch area keeps whatever the previous call left: the counters must start at zero
@@ -772,7 +794,7 @@ int fasted_join_static_scratch(const void* points_dev, int64_t n, int64_t d, int
     CU_TRY(cudaStreamSynchronize(st));
     if (h[2]) return fail(FASTED_EKERNEL, "a device-side wait ran out (status 0x%llx)", h[2]);
     *pairs_found = h[0];
-    *pairs_stored = h[1];
+    *pairs_stored = h[0] < capacity ? h[0] : capacity;
     return FASTED_OK;
 }
 

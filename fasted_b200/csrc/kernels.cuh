@@ -56,23 +56,78 @@ struct JoinParams {
     int k_steps;                   // ceil(d / kTileK)
     int tiles_m, tiles_n;          // tile grid of this launch
     int band_tiles;                // tile rows per raster band
-    long long total_tiles;
+    long long total_tiles;         // upper bound of the tiles walked (grid sizing only)
+    int tile_m;                    // query rows per tile (kTileM, or 2 * kTileM for CTA pairs)
+    int symmetric;                 // 1: walk only tiles that touch j >= i and emit (i,j) and (j,i)
 };
 
-// Persistent static schedule: CTA b handles tiles b, b + grid, b + 2*grid, ...
-// of a linear order that walks bands of `band_tiles` tile rows; inside a band
-// the tile row is the fastest index, so the CTAs that run together cover a
-// band_tiles x (grid / band_tiles) block of the tile grid and the query rows of
-// a band stay L2-resident while the band sweeps over all candidates.
-__device__ __forceinline__ void tile_coords(const JoinParams& p, long long t, int& tm, int& tn) {
-    const long long per_band = static_cast<long long>(p.band_tiles) * p.tiles_n;
-    const int band = static_cast<int>(t / per_band);
-    const long long rem = t - band * per_band;
-    const int first_row = band * p.band_tiles;
-    const int rows = min(p.band_tiles, p.tiles_m - first_row);
-    tn = static_cast<int>(rem / rows);
-    tm = first_row + static_cast<int>(rem - static_cast<long long>(tn) * rows);
-}
+// Persistent static schedule: CTA (or CTA pair) b handles tiles b, b + grid, b + 2*grid, ... of a
+// linear order that walks bands of `band_tiles` tile rows; inside a band the tile row is the fastest
+// index, so the CTAs that run together cover a band_tiles x (grid / band_tiles) block of the tile
+// grid and the query rows of a band stay L2-resident while the band sweeps over the candidates.
+// (Replaces the reference's atomic work queue and its 8 x 8 super-tiles,
+// source/rasterizer/onDemandRasterizer.cuh:78-108.)
+//
+// Symmetric mode: d2(i,j) == d2(j,i), so only elements with j >= i are computed.  A band then
+// starts at the first candidate tile that reaches its diagonal, and tiles that lie entirely below
+// the diagonal are skipped.  All roles of a CTA walk the same sequence.
+struct TileIter {
+    long long rem;        // index of the current tile inside the current band
+    long long band_size;  // tiles in the current band
+    long long step;
+    int band, nbands;
+    int rows;             // tile rows in the current band
+    int tn0;              // first candidate tile of the current band
+    int tm, tn;
+    bool valid;
+
+    __device__ __forceinline__ void load_band(const JoinParams& p) {
+        const int first_row = band * p.band_tiles;
+        rows = min(p.band_tiles, p.tiles_m - first_row);
+        tn0 = 0;
+        if (p.symmetric) {
+            const int r0 = p.q_begin + first_row * p.tile_m;
+            tn0 = r0 >= kTileN ? (r0 - (kTileN - 1)) / kTileN : 0;
+            tn0 = min(tn0, p.tiles_n);
+        }
+        band_size = static_cast<long long>(rows) * (p.tiles_n - tn0);
+    }
+    __device__ __forceinline__ void settle(const JoinParams& p) {
+        for (;;) {
+            while (band < nbands && rem >= band_size) {
+                rem -= band_size;
+                if (++band < nbands) load_band(p);
+            }
+            if (band >= nbands) {
+                valid = false;
+                return;
+            }
+            const int col = static_cast<int>(rem / rows);
+            tn = tn0 + col;
+            tm = band * p.band_tiles + static_cast<int>(rem - static_cast<long long>(col) * rows);
+            if (!p.symmetric || tn * kTileN + (kTileN - 1) >= p.q_begin + tm * p.tile_m) {
+                valid = true;
+                return;
+            }
+            rem += step;  // tile entirely below the diagonal: nothing to do
+        }
+    }
+    __device__ __forceinline__ void init(const JoinParams& p, long long first, long long stride) {
+        step = stride;
+        rem = first;
+        band = 0;
+        nbands = (p.tiles_m + p.band_tiles - 1) / p.band_tiles;
+        valid = false;
+        if (nbands > 0) {
+            load_band(p);
+            settle(p);
+        }
+    }
+    __device__ __forceinline__ void advance(const JoinParams& p) {
+        rem += step;
+        settle(p);
+    }
+};
 
 // ---------------------------------------------------------------------------
 // Row norms
@@ -209,58 +264,118 @@ row_norms_kernel(const __grid_constant__ CUtensorMap map, float* __restrict__ no
 // Epilogue of one accumulator (128 lanes x kTileN columns) for one warp: thread = query row q
 // (TMEM lane), 32 columns per tcgen05.ld.  d2 = (s_q + s_c) - 2a exactly as the reference's
 // inspectResults (source/warpMma.cuh:239-242), inclusive compare (:257); rows and columns that are
-// padding carry +inf norms and can never hit (:259).  Hits are compacted per warp: a scan of the
-// per-thread hit counts, ONE atomicAdd on the found counter (plus one on the stored counter) per
-// warp-chunk that has hits, then each thread writes its records to consecutive slots -- the
-// reference does two atomics per pair (source/pair.cuh:123-133).  Overflow keeps its rule: found
-// counts everything, stored stops at capacity.
+// padding carry +inf norms and can never hit (:259).
+//
+// Pass 1 turns the whole tile row into hit bit masks (8 chunks x 32 columns per thread).  Only if
+// some thread of the warp has a hit does pass 2 run: one warp scan of the per-thread counts, ONE
+// atomicAdd on the found counter per warp and tile, then every thread writes its records to
+// consecutive slots -- the reference does two atomics per pair (source/pair.cuh:123-133).  Overflow
+// keeps its rule: found counts everything, records beyond the capacity are dropped (the host
+// derives stored = min(found, capacity)).
+//
+// Symmetric mode keeps columns c >= q and emits, for c > q, the mirrored record (c, q) as well.
 __device__ __forceinline__ void epilogue_tile(const JoinParams& p, uint32_t taddr, const float* cn, float sq, int q,
                                               int c_base, int lane) {
-    const unsigned long long qkey = static_cast<unsigned long long>(static_cast<uint32_t>(q)) << 32;
-#pragma unroll 1
-    for (int c0 = 0; c0 < kTileN; c0 += 32) {
+    constexpr int kChunks = kTileN / 32;
+    uint32_t hit[kChunks];
+    uint32_t mir[kChunks];
+    uint32_t cnt = 0;
+#pragma unroll
+    for (int ch = 0; ch < kChunks; ++ch) {
         uint32_t v[32];
-        ptx::tmem_ld_32x32b_x32(taddr + c0, v);
+        ptx::tmem_ld_32x32b_x32(taddr + ch * 32, v);
         ptx::tmem_ld_wait();
         uint32_t mask = 0;
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
-            const float d2 = (sq + cn[c0 + j]) - 2.0f * __uint_as_float(v[j]);
+            const float d2 = (sq + cn[ch * 32 + j]) - 2.0f * __uint_as_float(v[j]);
             if (d2 <= p.eps2) mask |= (1u << j);
         }
-        if (__any_sync(0xffffffffu, mask != 0)) {
-            const uint32_t cnt = __popc(mask);
-            uint32_t incl = cnt;
+        uint32_t mirror = 0;
+        if (p.symmetric) {
+            const int rel = q - (c_base + ch * 32);  // column index inside the chunk that equals q
+            const uint32_t keep = rel <= 0 ? 0xffffffffu : (rel >= 32 ? 0u : (0xffffffffu << rel));
+            const uint32_t above = rel < 0 ? 0xffffffffu : (rel >= 31 ? 0u : (0xffffffffu << (rel + 1)));
+            mirror = mask & above;
+            mask &= keep;
+        }
+        hit[ch] = mask;
+        mir[ch] = mirror;
+        cnt += __popc(mask) + __popc(mirror);
+    }
+    if (!__any_sync(0xffffffffu, cnt != 0)) return;
+
+    uint32_t incl = cnt;
 #pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const uint32_t up = __shfl_up_sync(0xffffffffu, incl, o);
-                if (lane >= o) incl += up;
+    for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += up;
+    }
+    const uint32_t total = __shfl_sync(0xffffffffu, incl, 31);
+    unsigned long long base = 0;
+    if (lane == 0) base = atomicAdd(p.counters + 0, static_cast<unsigned long long>(total));
+    base = __shfl_sync(0xffffffffu, base, 0);
+    unsigned long long slot = base + (incl - cnt);
+    const unsigned long long qkey = static_cast<unsigned long long>(static_cast<uint32_t>(q)) << 32;
+    const unsigned long long qlow = static_cast<unsigned long long>(static_cast<uint32_t>(q));
+
+    if (p.dist2 == nullptr) {
+#pragma unroll 1
+        for (int ch = 0; ch < kChunks; ++ch) {
+            // (dynamic register indexing is avoided by rotating the arrays)
+            uint32_t m = hit[0], r = mir[0];
+#pragma unroll
+            for (int k = 0; k + 1 < kChunks; ++k) {
+                hit[k] = hit[k + 1];
+                mir[k] = mir[k + 1];
             }
-            const uint32_t total = __shfl_sync(0xffffffffu, incl, 31);
-            unsigned long long base = 0;
-            if (lane == 0) {
-                base = atomicAdd(p.counters + 0, static_cast<unsigned long long>(total));
-                if (base < p.capacity) {
-                    const unsigned long long room = p.capacity - base;
-                    atomicAdd(p.counters + 1, room < total ? room : static_cast<unsigned long long>(total));
-                }
+            const uint32_t c0 = static_cast<uint32_t>(c_base + ch * 32);
+            while (m) {
+                const int j = __ffs(m) - 1;
+                m &= m - 1;
+                if (slot < p.capacity) p.keys[slot] = qkey | static_cast<unsigned long long>(c0 + j);
+                ++slot;
             }
-            base = __shfl_sync(0xffffffffu, base, 0);
-            unsigned long long slot = base + (incl - cnt);
+            while (r) {
+                const int j = __ffs(r) - 1;
+                r &= r - 1;
+                if (slot < p.capacity) p.keys[slot] = (static_cast<unsigned long long>(c0 + j) << 32) | qlow;
+                ++slot;
+            }
+        }
+    } else {
+        // Distances wanted too: read the accumulator chunk again where the warp has hits.
+#pragma unroll
+        for (int ch = 0; ch < kChunks; ++ch) {
+            const uint32_t m = hit[ch], r = mir[ch];
+            if (!__any_sync(0xffffffffu, (m | r) != 0)) continue;
+            uint32_t v[32];
+            ptx::tmem_ld_32x32b_x32(taddr + ch * 32, v);
+            ptx::tmem_ld_wait();
+            const uint32_t c0 = static_cast<uint32_t>(c_base + ch * 32);
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
-                if (mask & (1u << j)) {
-                    if (slot < p.capacity) {
-                        p.keys[slot] = qkey | static_cast<unsigned long long>(static_cast<uint32_t>(c_base + c0 + j));
-                        if (p.dist2) p.dist2[slot] = (sq + cn[c0 + j]) - 2.0f * __uint_as_float(v[j]);
+                if ((m | r) & (1u << j)) {
+                    const float d2 = (sq + cn[ch * 32 + j]) - 2.0f * __uint_as_float(v[j]);
+                    if (m & (1u << j)) {
+                        if (slot < p.capacity) {
+                            p.keys[slot] = qkey | static_cast<unsigned long long>(c0 + j);
+                            p.dist2[slot] = d2;
+                        }
+                        ++slot;
                     }
-                    ++slot;
+                    if (r & (1u << j)) {
+                        if (slot < p.capacity) {
+                            p.keys[slot] = (static_cast<unsigned long long>(c0 + j) << 32) | qlow;
+                            p.dist2[slot] = d2;
+                        }
+                        ++slot;
+                    }
                 }
             }
         }
     }
 }
-
 
 struct JoinSmemAux {
     unsigned long long full_bar[kStages];
@@ -319,9 +434,9 @@ join_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             uint32_t phase = 0;
             bool ok = true;
             long long issued = 0;
-            for (long long t = first_tile; t < p.total_tiles && ok; t += tile_step) {
-                int tm, tn;
-                tile_coords(p, t, tm, tn);
+            TileIter ti;
+            for (ti.init(p, first_tile, tile_step); ti.valid && ok; ti.advance(p)) {
+                const int tm = ti.tm, tn = ti.tn;
                 const int row_a = p.q_begin + tm * kTileM;
                 const int row_b = tn * kTileN;
                 for (int ks = 0; ks < p.k_steps; ++ks) {
@@ -366,7 +481,8 @@ join_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             uint32_t phase = 0;
             bool ok = true;
             long long it = 0;
-            for (long long t = first_tile; t < p.total_tiles && ok; t += tile_step, ++it) {
+            TileIter ti;
+            for (ti.init(p, first_tile, tile_step); ti.valid && ok; ti.advance(p), ++it) {
                 const int buf = static_cast<int>(it & 1);
                 const uint32_t acc_phase = static_cast<uint32_t>((it >> 1) & 1);
                 ok = ptx::mbar_wait_bounded(ptx::smem_u32(&aux->acc_empty_bar[buf]), acc_phase ^ 1u, abort_flag,
@@ -406,9 +522,9 @@ join_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         const float inf = __int_as_float(0x7f800000);
         bool ok = true;
         long long it = 0;
-        for (long long t = first_tile; t < p.total_tiles; t += tile_step, ++it) {
-            int tm, tn;
-            tile_coords(p, t, tm, tn);
+        TileIter ti;
+        for (ti.init(p, first_tile, tile_step); ti.valid; ti.advance(p), ++it) {
+            const int tm = ti.tm, tn = ti.tn;
             const int buf = static_cast<int>(it & 1);
             const uint32_t acc_phase = static_cast<uint32_t>((it >> 1) & 1);
             const int q = p.q_begin + tm * kTileM + row_in_tile;
@@ -530,9 +646,9 @@ join_pair_kernel(const __grid_constant__ CUtensorMap map, const JoinParams p) {
             uint32_t phase = 0;
             bool ok = true;
             long long issued = 0;
-            for (long long t = first_tile; t < p.total_tiles && ok; t += tile_step) {
-                int tm, tn;
-                tile_coords(p, t, tm, tn);
+            TileIter ti;
+            for (ti.init(p, first_tile, tile_step); ti.valid && ok; ti.advance(p)) {
+                const int tm = ti.tm, tn = ti.tn;
                 const int row_a = p.q_begin + tm * kPairTileM + static_cast<int>(rank) * kTileM;
                 const int row_b = tn * kTileN + static_cast<int>(rank) * (kTileN / 2);
                 for (int ks = 0; ks < p.k_steps; ++ks) {
@@ -575,7 +691,8 @@ join_pair_kernel(const __grid_constant__ CUtensorMap map, const JoinParams p) {
             uint32_t phase = 0;
             bool ok = true;
             long long it = 0;
-            for (long long t = first_tile; t < p.total_tiles && ok; t += tile_step, ++it) {
+            TileIter ti;
+            for (ti.init(p, first_tile, tile_step); ti.valid && ok; ti.advance(p), ++it) {
                 const int buf = static_cast<int>(it & 1);
                 const uint32_t acc_phase = static_cast<uint32_t>((it >> 1) & 1);
                 ok = ptx::mbar_wait_bounded(ptx::smem_u32(&aux->acc_empty_bar[buf]), acc_phase ^ 1u, abort_flag,
@@ -617,9 +734,9 @@ join_pair_kernel(const __grid_constant__ CUtensorMap map, const JoinParams p) {
         const float inf = __int_as_float(0x7f800000);
         bool ok = true;
         long long it = 0;
-        for (long long t = first_tile; t < p.total_tiles; t += tile_step, ++it) {
-            int tm, tn;
-            tile_coords(p, t, tm, tn);
+        TileIter ti;
+        for (ti.init(p, first_tile, tile_step); ti.valid; ti.advance(p), ++it) {
+            const int tm = ti.tm, tn = ti.tn;
             const int buf = static_cast<int>(it & 1);
             const uint32_t acc_phase = static_cast<uint32_t>((it >> 1) & 1);
             const int q = p.q_begin + tm * kPairTileM + static_cast<int>(rank) * kTileM + row_in_tile;
@@ -744,7 +861,7 @@ __global__ void brute_f64_kernel(const __half* __restrict__ pts, int n, int d, i
         for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
         if (lane == 0 && acc <= eps2) {
             ++local;
-            if (keys) {
+            if (keys && capacity) {
                 const unsigned long long slot = atomicAdd(n_keys, 1ull);
                 if (slot < capacity)
                     keys[slot] = (static_cast<unsigned long long>(static_cast<uint32_t>(q)) << 32) |

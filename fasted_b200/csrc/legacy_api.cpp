@@ -100,8 +100,14 @@ Results join_resident(double epsilon, bool save_pairs, const std::string& datase
     std::cout << "N: " << n << std::endl;
     std::cout << "K: " << d << std::endl;
 
+    // d2(i,j) == d2(j,i) bit for bit, so by default each unordered pair is computed once and both
+    // orientations are emitted; FASTED_SYMMETRIC=0 computes all N x N entries like the reference.
+    const char* sym_env = std::getenv("FASTED_SYMMETRIC");
+    const bool symmetric = !(sym_env && std::strcmp(sym_env, "0") == 0);
+    unsigned flags = write_dist ? FASTED_JOIN_DIST2 : 0u;
+    if (symmetric) flags |= FASTED_JOIN_SYMMETRIC;
     fasted_join_stats st{};
-    check(fasted_join(ctx, epsilon, 0, -1, 0, write_dist ? FASTED_JOIN_DIST2 : 0u, &st));
+    check(fasted_join(ctx, epsilon, 0, -1, 0, flags, &st));
 
     const double sort_start = now_s();
     std::printf("Number of pairs found %llu\n", st.pairs_found);

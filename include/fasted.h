@@ -79,6 +79,9 @@ void releaseResources(void);
  *                       hard-wired at source/main.cu:214-215)
  *   FASTED_DEVICE       CUDA device ordinal (default 0, source/findPairs.cuh:622)
  *   FASTED_WRITE_DIST   "1": third text column sqrt(d2) in the .pairs file
+ *   FASTED_SYMMETRIC    "0": compute all N x N entries like the reference; default: each unordered
+ *                       pair is computed once and both orientations are emitted (identical output,
+ *                       about twice the reported TFLOPS)
  */
 
 /* ------------------------------------------------------------------------
@@ -100,7 +103,9 @@ enum {
 enum {
     FASTED_JOIN_DIST2 = 1,       /* also record the FP32 squared distance of every stored pair */
     FASTED_JOIN_NO_SORT = 2,     /* leave stored pairs in device order (count-only / timing runs) */
-    FASTED_JOIN_KEEP_NORMS = 4   /* reuse row norms computed by an earlier call on the same points */
+    FASTED_JOIN_KEEP_NORMS = 4,  /* reuse row norms computed by an earlier call on the same points */
+    FASTED_JOIN_SYMMETRIC = 8    /* full self-join only: compute each unordered pair once (d2(i,j) == d2(j,i))
+                                    and emit both orientations; same output, about half the tensor work */
 };
 
 typedef struct fasted_join_stats {
@@ -212,6 +217,12 @@ int fasted_brute_force_f64(fasted_ctx* ctx, const int32_t* sample_rows, int n_sa
 int fasted_join_static_scratch(const void* points_dev, int64_t n, int64_t d, int64_t ld, double eps,
                                unsigned long long* keys_out_dev, uint64_t capacity, void* stream,
                                unsigned long long* pairs_found, unsigned long long* pairs_stored);
+
+/* Same check, also returning the neighbours themselves: keys_out receives up to `capacity`
+ * records (query << 32) | candidate in no particular order, *n_keys_out the number found. */
+int fasted_brute_force_f64_pairs(fasted_ctx* ctx, const int32_t* sample_rows, int n_samples, double eps,
+                                 unsigned long long* counts_out, unsigned long long* keys_out, uint64_t capacity,
+                                 unsigned long long* n_keys_out);
 
 /* Host-side dataset builders (no GPU involved), the loaders behind layer 1.
  * Exponential: replaces SimSearch::ExponentialPointGenerator,

@@ -275,3 +275,32 @@ def test_cta_pair_kernel_is_bit_identical(gpu_join, oracle_mod, n, d, eps):
     assert a.status == b.status == 0 and a.pairs_found == b.pairs_found
     assert np.array_equal(pa, pb) and np.array_equal(da.view(np.uint32), db.view(np.uint32))
     assert np.array_equal(band, pa[(pa[:, 0] >= 128) & (pa[:, 0] < min(n, 600))])
+
+
+@pytest.mark.parametrize("n,d,eps", [(256, 64, 1e3), (300, 100, 1e3), (1000, 256, 0.5), (4096, 128, 0.3136),
+                                     (777, 333, 0.5), (5000, 1024, 1.1), (9000, 64, 0.2)])
+def test_symmetric_schedule_is_bit_identical(gpu_join, oracle_mod, n, d, eps):
+    # Computing each unordered pair once and emitting both orientations must give exactly the
+    # full join's output: same pairs, same FP32 distances (d2(i,j) and d2(j,i) agree bit for bit).
+    from fasted_b200 import FastedError
+    rng = np.random.default_rng(3 * n + d)
+    pts = oracle_mod.double_to_half(rng.exponential(1 / 40.0, size=(n, d)))
+    gpu_join.set_points(pts)
+    a = gpu_join.join(eps, capacity=n * n, flags=1)
+    pa, da = gpu_join.pairs(with_dist2=True)
+    b = gpu_join.join(eps, capacity=n * n, flags=1 | 8)
+    pb, db = gpu_join.pairs(with_dist2=True)
+    assert a.pairs_found == b.pairs_found and b.status == 0
+    assert np.array_equal(pa, pb) and np.array_equal(da.view(np.uint32), db.view(np.uint32))
+    with pytest.raises(FastedError):
+        gpu_join.join(eps, q_begin=0, q_end=n - 1, flags=8)  # only defined for the full self-join
+
+
+def test_fp64_brute_force_pairs_match_cpu_truth(gpu_join, oracle_mod):
+    pts = oracle_mod.gen_exponential(3000, 128)
+    gpu_join.set_points(pts)
+    rows = np.arange(1000, 1064, dtype=np.int32)
+    counts, pairs = gpu_join.brute_force_pairs(rows, 0.3, capacity=64 * 3000)
+    want, _, _ = oracle_mod.join_fp64(pts, 0.3, q_begin=1000, q_end=1064)
+    cmp = oracle_mod.compare_pair_sets(pts, 128, 0.3, pairs, want, band=1e-9)
+    assert cmp["ok"] and int(counts.sum()) == len(pairs)
