@@ -466,7 +466,11 @@ def main() -> None:
             "e2e": e2e,
             "gpu_launches": 2 * args.steps,
             "roofline": {"bound": "tensor", "kernel": "join_kernel", "achieved": achieved, "peak": peak,
-                         "unit": "TFLOP/s", "frac": achieved / peak if peak else None, "traffic": None,
+                         "unit": "TFLOP/s", "frac": achieved / peak if peak else None,
+                         # DRAM bytes per launch: ncu measured 17.09 GB on the 65,536 x 4096 case = one pass over
+                         # the candidates per band of 16 tile rows; scaled by that rule to this launch.
+                         "traffic": float(-(-(-(-band_rows // 128)) // 16) * n * ld * 2 + band_rows * ld * 2),
+                         "traffic_source": "ncu dram__bytes_read.sum of a 65536 x 4096 launch, scaled by bands x N*D*2",
                          "peak_source": f"{peaks['source']} cuBLAS bf16 "
                                         f"({'sustained' if float(np.mean(join_ms)) > 500.0 else 'burst'})",
                          "norms_kernel": {"bound": "hbm", "achieved": (n * ld * 2 + n * 4) / (float(np.mean(norm_ms)) * 1e-3) / 1e9,
