@@ -178,30 +178,6 @@ def run_reference_arm(args, wl: dict, name: str) -> None:
     print(json.dumps(line), flush=True)
 
 
-def tune_epsilon(sj, n: int, target: float, rows: int, flags_no_sort: int) -> tuple[float, float]:
-    """Epsilon whose mean neighbour count (self excluded) over the first `rows` query rows is ~target."""
-    rows = min(rows, n)
-
-    def mean_neighbours(eps: float) -> float:
-        st = sj.join(eps, q_begin=0, q_end=rows, capacity=1, flags=flags_no_sort)
-        return (st.pairs_found - rows) / rows
-
-    norms, _ = sj.row_norms()
-    hi = float(np.sqrt(4.0 * float(norms[: min(n, 65536)].max())))
-    lo = 0.0
-    m = None
-    for _ in range(40):
-        mid = 0.5 * (lo + hi)
-        m = mean_neighbours(mid)
-        if abs(m - target) <= 0.01 * target:
-            return mid, m
-        if m > target:
-            hi = mid
-        else:
-            lo = mid
-    return 0.5 * (lo + hi), m
-
-
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -285,7 +261,7 @@ def main() -> None:
     tuned_mean = None
     if eps is None:
         if rank == 0:
-            eps, tuned_mean = tune_epsilon(sj, n, wl["target"], 4096, JOIN_NO_SORT)
+            eps, tuned_mean = sj.estimate_epsilon(wl["target"], 8192, 0.01)
         if world > 1:
             t = torch.tensor([eps if rank == 0 else 0.0], dtype=torch.float64, device="cuda")
             dist.broadcast(t, src=0)

@@ -54,7 +54,7 @@ DECLARED_SYMBOLS = [
     "fasted_set_points_host_f16", "fasted_set_points_device_f16", "fasted_generate_exponential",
     "fasted_fill_exponential_device",
     "fasted_points_info", "fasted_get_points_host_f16", "fasted_row_norms", "fasted_get_norms",
-    "fasted_join", "fasted_get_pairs", "fasted_pairs_device", "fasted_brute_force_f64", "fasted_brute_force_f64_pairs", "fasted_set_option",
+    "fasted_join", "fasted_estimate_epsilon", "fasted_get_pairs", "fasted_pairs_device", "fasted_brute_force_f64", "fasted_brute_force_f64_pairs", "fasted_set_option",
     "fasted_dataset_exponential_f16", "fasted_dataset_csv_shape", "fasted_dataset_csv_f16",
     "fasted_join_static_scratch",
 ]
@@ -87,6 +87,8 @@ def load() -> ctypes.CDLL:
     L.fasted_row_norms.argtypes = [_vp, ctypes.POINTER(ctypes.c_double)]
     L.fasted_get_norms.argtypes = [_vp, _vp]
     L.fasted_join.argtypes = [_vp, ctypes.c_double, _i64, _i64, _u64, ctypes.c_uint, ctypes.POINTER(JoinStats)]
+    L.fasted_estimate_epsilon.argtypes = [_vp, ctypes.c_double, _i64, ctypes.c_double, ctypes.POINTER(ctypes.c_double),
+                                          ctypes.POINTER(ctypes.c_double)]
     L.fasted_get_pairs.argtypes = [_vp, _u64, _u64, _vp, _vp]
     L.fasted_pairs_device.argtypes = [_vp, ctypes.POINTER(_vp), ctypes.POINTER(_vp)]
     L.fasted_brute_force_f64.argtypes = [_vp, _vp, ctypes.c_int, ctypes.c_double, _vp]
@@ -226,6 +228,13 @@ class SelfJoin:
         self._last = st
         self._last_dist = bool(flags & JOIN_DIST2)
         return st
+
+    def estimate_epsilon(self, target_mean_neighbours: float, sample_rows: int = 0, rel_tol: float = 0.01):
+        """(epsilon, mean neighbours on the sample) for a target mean neighbour count per point."""
+        eps, got = ctypes.c_double(), ctypes.c_double()
+        _check(self._L.fasted_estimate_epsilon(self._h, float(target_mean_neighbours), sample_rows, rel_tol,
+                                               ctypes.byref(eps), ctypes.byref(got)))
+        return eps.value, got.value
 
     def pairs(self, with_dist2: bool = False):
         st = self._last

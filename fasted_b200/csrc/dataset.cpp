@@ -1,5 +1,6 @@
 #include "dataset.hpp"
 
+#include <algorithm>
 #include <cerrno>
 #include <cstdlib>
 #include <cstring>
@@ -44,14 +45,49 @@ HostDataset make_exponential_dataset(int64_t n, int64_t d, double lambda, double
     ds.d = d;
     ds.name = "Exponential_" + std::to_string(n) + "_" + std::to_string(d) + "_" + std::to_string(lambda);
     ds.values.resize(static_cast<size_t>(n) * static_cast<size_t>(d));
-    std::mt19937 engine(2137834274u);
-    std::exponential_distribution<double> dist(lambda);
     uint16_t* out = ds.values.data();
     const size_t total = ds.values.size();
-    for (size_t i = 0; i < total; ++i) {
-        double v = dist(engine);
-        while (v < 0.0 || v > max_value) v = dist(engine);
-        out[i] = float_to_half_rn(static_cast<float>(v));
+    constexpr uint32_t kSeed = 2137834274u;
+
+    // The reference draws all N*D values from ONE sequential engine, which at 4e9 values takes
+    // minutes.  libstdc++'s exponential_distribution<double> consumes exactly two 32-bit engine
+    // outputs per draw, so value k starts at engine position 2k as long as no earlier draw was
+    // rejected.  Each thread therefore jumps its own engine copy to its chunk (discard() only
+    // regenerates state, no logarithms) and draws; if ANY draw anywhere is rejected the positions
+    // after it shift and the whole dataset is redone sequentially.  The stream is bit-identical
+    // either way.
+    const int threads = omp_get_max_threads();
+    bool parallel_ok = false;
+    if (threads > 1 && total >= (size_t(1) << 20)) {
+        long long rejections = 0;
+#pragma omp parallel reduction(+ : rejections)
+        {
+            const size_t t = static_cast<size_t>(omp_get_thread_num());
+            const size_t nt = static_cast<size_t>(omp_get_num_threads());
+            const size_t begin = total / nt * t + std::min(t, total % nt);
+            const size_t end = begin + total / nt + (t < total % nt ? 1 : 0);
+            std::mt19937 engine(kSeed);
+            engine.discard(2ull * begin);
+            std::exponential_distribution<double> dist(lambda);
+            for (size_t i = begin; i < end; ++i) {
+                const double v = dist(engine);
+                if (v < 0.0 || v > max_value) {
+                    ++rejections;
+                    break;
+                }
+                out[i] = float_to_half_rn(static_cast<float>(v));
+            }
+        }
+        parallel_ok = rejections == 0;
+    }
+    if (!parallel_ok) {
+        std::mt19937 engine(kSeed);
+        std::exponential_distribution<double> dist(lambda);
+        for (size_t i = 0; i < total; ++i) {
+            double v = dist(engine);
+            while (v < 0.0 || v > max_value) v = dist(engine);
+            out[i] = float_to_half_rn(static_cast<float>(v));
+        }
     }
     return ds;
 }

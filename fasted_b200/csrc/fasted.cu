@@ -11,7 +11,9 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <cmath>
 #include <string>
+#include <vector>
 
 #include <cub/device/device_radix_sort.cuh>
 
@@ -171,8 +173,9 @@ void free_pair_buffers(fasted_ctx* c) {
 }
 
 int ensure_pair_buffers(fasted_ctx* c, uint64_t capacity, bool want_dist) {
-    if (c->capacity >= capacity && c->capacity <= 2 * capacity + 1024 && (!want_dist || c->have_dist_buf))
-        return FASTED_OK;
+    // Buffers only grow: probes with a tiny capacity (epsilon search) must not throw away the
+    // buffers of the full join that follows.
+    if (c->capacity >= capacity && (!want_dist || c->have_dist_buf)) return FASTED_OK;
     free_pair_buffers(c);
     const uint64_t cap = std::max<uint64_t>(capacity, 1);
     CU_TRY(cudaMalloc(&c->keys, cap * 8));
@@ -592,6 +595,58 @@ int fasted_join(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end, uint6
         stats->tiles_n = p.tiles_n;
         stats->grid = grid;
     }
+    return FASTED_OK;
+}
+
+int fasted_estimate_epsilon(fasted_ctx* c, double target_mean_neighbours, int64_t sample_rows, double rel_tol,
+                            double* eps_out, double* achieved_out) {
+    if (!c || !eps_out) return fail(FASTED_EINVAL, "null argument");
+    if (!c->points) return fail(FASTED_ESTATE, "no dataset is resident");
+    if (!(target_mean_neighbours > 0) || target_mean_neighbours >= static_cast<double>(c->n))
+        return fail(FASTED_EINVAL, "target must be in (0, n)");
+    if (!(rel_tol > 0)) rel_tol = 0.01;
+    const int64_t n = c->n;
+    if (sample_rows <= 0) sample_rows = 4096;
+    sample_rows = std::min<int64_t>(sample_rows, n);
+    // Up to 8 bands of whole 128-row tiles spread evenly over the dataset.
+    const int64_t nb = std::max<int64_t>(1, std::min<int64_t>(8, sample_rows / 128));
+    const int64_t per = std::max<int64_t>(1, sample_rows / nb);
+    int64_t begin[8], end[8], rows = 0;
+    for (int64_t b = 0; b < nb; ++b) {
+        int64_t a = (n / nb * b) / 128 * 128;
+        begin[b] = std::min(a, n - std::min(per, n));
+        end[b] = std::min(n, begin[b] + per);
+        rows += end[b] - begin[b];
+    }
+    double ms = 0;
+    int rc = fasted_row_norms(c, &ms);
+    if (rc) return rc;
+    // Upper bracket: d2 <= (|q| + |c|)^2 <= 4 * max norm.
+    std::vector<float> norms(static_cast<size_t>(n));
+    rc = fasted_get_norms(c, norms.data());
+    if (rc) return rc;
+    float mx = 0.f;
+    for (float v : norms) mx = std::max(mx, v);
+    double lo = 0.0, hi = std::sqrt(4.0 * static_cast<double>(mx)) * 1.0001 + 1e-30;
+    double mid = hi, mean = 0;
+    for (int it = 0; it < 60; ++it) {
+        mid = 0.5 * (lo + hi);
+        unsigned long long found = 0;
+        for (int64_t b = 0; b < nb; ++b) {
+            fasted_join_stats st{};
+            rc = fasted_join(c, mid, begin[b], end[b], 1, FASTED_JOIN_NO_SORT | FASTED_JOIN_KEEP_NORMS, &st);
+            if (rc) return rc;
+            found += st.pairs_found;
+        }
+        mean = (static_cast<double>(found) - static_cast<double>(rows)) / static_cast<double>(rows);
+        if (std::fabs(mean - target_mean_neighbours) <= rel_tol * target_mean_neighbours) break;
+        if (mean > target_mean_neighbours)
+            hi = mid;
+        else
+            lo = mid;
+    }
+    *eps_out = mid;
+    if (achieved_out) *achieved_out = mean;
     return FASTED_OK;
 }
 

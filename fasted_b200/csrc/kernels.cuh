@@ -26,8 +26,10 @@ constexpr int kTileN = 256;    // candidate rows per tile = TMEM columns per acc
 constexpr int kStages = 4;     // TMA -> MMA ring depth
 constexpr int kTmemCols = 512; // two accumulator buffers of kTileN columns
 
-constexpr int kJoinThreads = 192;  // warp 0: TMA, warp 1: MMA issue + TMEM, warps 2..5: epilogue
-constexpr int kEpiThreads = 128;
+constexpr int kEpiWarps = 8;       // two per TMEM lane quarter, each taking half of the tile's columns
+constexpr int kEpiThreads = kEpiWarps * 32;
+constexpr int kJoinThreads = 64 + kEpiThreads;  // warp 0: TMA, warp 1: MMA issue + TMEM, warps 2..9: epilogue
+constexpr int kEpiCols = kTileN / (kEpiWarps / 4);  // accumulator columns handled by one epilogue warp
 
 constexpr uint32_t kStageBytesA = kTileM * kTileK * 2;  // 16 KiB
 constexpr uint32_t kStageBytesB = kTileN * kTileK * 2;  // 32 KiB
@@ -249,13 +251,14 @@ row_norms_kernel(const __grid_constant__ CUtensorMap map, float* __restrict__ no
 // source/warpMma.cuh:131-190), the distance test (warpMma.cuh:220-273) and the
 // pair append (source/pair.cuh:123-133).
 //
-// Warp roles (192 threads, one CTA per SM):
+// Warp roles (320 threads, one CTA per SM):
 //   warp 0      one lane issues the TMA loads of A (128 x 64) and B (256 x 64)
 //               FP16 boxes into a 4-stage ring of 128B-swizzled shared memory
 //   warp 1      allocates TMEM; one lane issues 4 tcgen05.mma (M128 N256 K16)
 //               per stage into one of two 256-column FP32 accumulators and
 //               commits stage-release / accumulator-ready mbarriers
-//   warps 2..5  epilogue: tcgen05.ld the accumulator (thread = query row),
+//   warps 2..9  epilogue: two warps per TMEM lane quarter, each taking 128 of
+//               the 256 accumulator columns: tcgen05.ld (thread = query row),
 //               d2 = (s_q + s_c) - 2a, compare with eps2, compact the hits with
 //               a warp scan and one atomicAdd per warp, store packed pairs.
 // The epilogue of tile t overlaps the main loop of tile t+1 through the two
@@ -276,20 +279,41 @@ row_norms_kernel(const __grid_constant__ CUtensorMap map, float* __restrict__ no
 // Symmetric mode keeps columns c >= q and emits, for c > q, the mirrored record (c, q) as well.
 __device__ __forceinline__ void epilogue_tile(const JoinParams& p, uint32_t taddr, const float* cn, float sq, int q,
                                               int c_base, int lane) {
-    constexpr int kChunks = kTileN / 32;
+    // taddr, cn and c_base already point at this warp's first column.
+    constexpr int kChunks = kEpiCols / 32;
     uint32_t hit[kChunks];
     uint32_t mir[kChunks];
     uint32_t cnt = 0;
+    uint32_t va[32], vb[32];
+    ptx::tmem_ld_32x32b_x32(taddr, va);
 #pragma unroll
     for (int ch = 0; ch < kChunks; ++ch) {
-        uint32_t v[32];
-        ptx::tmem_ld_32x32b_x32(taddr + ch * 32, v);
-        ptx::tmem_ld_wait();
-        uint32_t mask = 0;
+        // Chunk ch is in flight into va (even ch) or vb (odd ch); once it has landed, start the next
+        // chunk's load into the other buffer so that its latency hides behind this chunk's arithmetic.
+        uint32_t(&v)[32] = (ch & 1) ? vb : va;
+        uint32_t(&w)[32] = (ch & 1) ? va : vb;
+        ptx::tmem_ld_wait_for(v);
+        if (ch + 1 < kChunks) ptx::tmem_ld_32x32b_x32(taddr + (ch + 1) * 32, w);
+        // Fast reject: the smallest d2 of the chunk (3 instructions per element: add, fma, min; the
+        // candidate norms come as 16-byte broadcast loads).  NaNs drop out of fminf, so a NaN never hits.
+        const float4* cn4 = reinterpret_cast<const float4*>(cn + ch * 32);
+        float lo = __int_as_float(0x7f800000);
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-            const float d2 = (sq + cn[ch * 32 + j]) - 2.0f * __uint_as_float(v[j]);
-            if (d2 <= p.eps2) mask |= (1u << j);
+        for (int j4 = 0; j4 < 8; ++j4) {
+            const float4 c4 = cn4[j4];
+            const float d0 = (sq + c4.x) - 2.0f * __uint_as_float(v[4 * j4 + 0]);
+            const float d1 = (sq + c4.y) - 2.0f * __uint_as_float(v[4 * j4 + 1]);
+            const float d2 = (sq + c4.z) - 2.0f * __uint_as_float(v[4 * j4 + 2]);
+            const float d3 = (sq + c4.w) - 2.0f * __uint_as_float(v[4 * j4 + 3]);
+            lo = fminf(lo, fminf(fminf(d0, d1), fminf(d2, d3)));
+        }
+        uint32_t mask = 0;
+        if (lo <= p.eps2) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                const float d2 = (sq + cn[ch * 32 + j]) - 2.0f * __uint_as_float(v[j]);
+                if (d2 <= p.eps2) mask |= (1u << j);
+            }
         }
         uint32_t mirror = 0;
         if (p.symmetric) {
@@ -351,7 +375,7 @@ __device__ __forceinline__ void epilogue_tile(const JoinParams& p, uint32_t tadd
             if (!__any_sync(0xffffffffu, (m | r) != 0)) continue;
             uint32_t v[32];
             ptx::tmem_ld_32x32b_x32(taddr + ch * 32, v);
-            ptx::tmem_ld_wait();
+            ptx::tmem_ld_wait_for(v);
             const uint32_t c0 = static_cast<uint32_t>(c_base + ch * 32);
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
@@ -409,7 +433,7 @@ join_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         }
         for (int b = 0; b < 2; ++b) {
             ptx::mbar_init(ptx::smem_u32(&aux->acc_full_bar[b]), 1);
-            ptx::mbar_init(ptx::smem_u32(&aux->acc_empty_bar[b]), 4);  // one arrive per epilogue warp
+            ptx::mbar_init(ptx::smem_u32(&aux->acc_empty_bar[b]), kEpiWarps);  // one arrive per epilogue warp
         }
         ptx::fence_mbar_init();
         ptx::prefetch_tensormap(&map_a);
@@ -517,27 +541,39 @@ join_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     } else {
         // ------------------------- Epilogue -----------------------------
         const int quarter = warp & 3;               // TMEM lane quarter this warp may access
+        const int col_off = ((warp - 2) >> 2) * kEpiCols;  // this warp's share of the tile's columns
         const int row_in_tile = quarter * 32 + lane;
         const int epi_tid = threadIdx.x - 64;       // 0..127
         const float inf = __int_as_float(0x7f800000);
         bool ok = true;
         long long it = 0;
+        // The tile's norms (one candidate norm per epilogue thread, this thread's query norm) are
+        // fetched one tile ahead, so their global-memory latency hides behind the previous tile.
+        // Padding rows and columns get +inf and can never hit.
+        static_assert(kEpiThreads == kTileN, "one candidate norm per epilogue thread");
+        auto fetch_norms = [&](const TileIter& t, float& cand, float& query) {
+            const int c = t.tn * kTileN + epi_tid;
+            const int qq = p.q_begin + t.tm * kTileM + row_in_tile;
+            cand = (c < p.n) ? __ldg(p.norms + c) : inf;
+            query = (qq < p.q_end) ? __ldg(p.norms + qq) : inf;
+        };
         TileIter ti;
-        for (ti.init(p, first_tile, tile_step); ti.valid; ti.advance(p), ++it) {
+        ti.init(p, first_tile, tile_step);
+        float next_cand = inf, next_query = inf;
+        if (ti.valid) fetch_norms(ti, next_cand, next_query);
+        for (; ti.valid; ++it) {
             const int tm = ti.tm, tn = ti.tn;
             const int buf = static_cast<int>(it & 1);
             const uint32_t acc_phase = static_cast<uint32_t>((it >> 1) & 1);
             const int q = p.q_begin + tm * kTileM + row_in_tile;
             const int c_base = tn * kTileN;
 
-            // Stage the tile's candidate norms; padding columns get +inf so they can never hit.
             float* cn = aux->cand_norms[buf];
-            for (int j = epi_tid; j < kTileN; j += kEpiThreads) {
-                const int c = c_base + j;
-                cn[j] = (c < p.n) ? __ldg(p.norms + c) : inf;
-            }
-            const float sq = (q < p.q_end) ? __ldg(p.norms + q) : inf;
+            cn[epi_tid] = next_cand;
+            const float sq = next_query;
             ptx::named_bar_sync(1, kEpiThreads);
+            ti.advance(p);
+            if (ti.valid) fetch_norms(ti, next_cand, next_query);
 
             if (ok) ok = ptx::mbar_wait_bounded(ptx::smem_u32(&aux->acc_full_bar[buf]), acc_phase, abort_flag,
                                                 kWaitLimitNs);
@@ -546,7 +582,7 @@ join_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                                    static_cast<uint32_t>(buf * kTileN);
-            epilogue_tile(p, taddr, cn, sq, q, c_base, lane);
+            epilogue_tile(p, taddr + col_off, cn + col_off, sq, q, c_base + col_off, lane);
             // Hand the accumulator back to the MMA warp.
             ptx::tc_fence_before_sync();
             __syncwarp();
@@ -621,7 +657,7 @@ join_pair_kernel(const __grid_constant__ CUtensorMap map, const JoinParams p) {
         }
         for (int b = 0; b < 2; ++b) {
             ptx::mbar_init(ptx::smem_u32(&aux->acc_full_bar[b]), 1);
-            ptx::mbar_init(ptx::smem_u32(&aux->acc_empty_bar[b]), 8);  // 4 epilogue warps x 2 CTAs
+            ptx::mbar_init(ptx::smem_u32(&aux->acc_empty_bar[b]), 2 * kEpiWarps);  // epilogue warps of both CTAs
         }
         ptx::fence_mbar_init();
         ptx::prefetch_tensormap(&map);
@@ -729,13 +765,27 @@ join_pair_kernel(const __grid_constant__ CUtensorMap map, const JoinParams p) {
     } else {
         // ------------------------- Epilogue (both CTAs) ------------------------------
         const int quarter = warp & 3;
+        const int col_off = ((warp - 2) >> 2) * kEpiCols;
         const int row_in_tile = quarter * 32 + lane;
         const int epi_tid = threadIdx.x - 64;
         const float inf = __int_as_float(0x7f800000);
         bool ok = true;
         long long it = 0;
+        // The tile's norms (one candidate norm per epilogue thread, this thread's query norm) are
+        // fetched one tile ahead, so their global-memory latency hides behind the previous tile.
+        // Padding rows and columns get +inf and can never hit.
+        static_assert(kEpiThreads == kTileN, "one candidate norm per epilogue thread");
+        auto fetch_norms = [&](const TileIter& t, float& cand, float& query) {
+            const int c = t.tn * kTileN + epi_tid;
+            const int qq = p.q_begin + t.tm * kPairTileM + static_cast<int>(rank) * kTileM + row_in_tile;
+            cand = (c < p.n) ? __ldg(p.norms + c) : inf;
+            query = (qq < p.q_end) ? __ldg(p.norms + qq) : inf;
+        };
         TileIter ti;
-        for (ti.init(p, first_tile, tile_step); ti.valid; ti.advance(p), ++it) {
+        ti.init(p, first_tile, tile_step);
+        float next_cand = inf, next_query = inf;
+        if (ti.valid) fetch_norms(ti, next_cand, next_query);
+        for (; ti.valid; ++it) {
             const int tm = ti.tm, tn = ti.tn;
             const int buf = static_cast<int>(it & 1);
             const uint32_t acc_phase = static_cast<uint32_t>((it >> 1) & 1);
@@ -743,12 +793,11 @@ join_pair_kernel(const __grid_constant__ CUtensorMap map, const JoinParams p) {
             const int c_base = tn * kTileN;
 
             float* cn = aux->cand_norms[buf];
-            for (int j = epi_tid; j < kTileN; j += kEpiThreads) {
-                const int c = c_base + j;
-                cn[j] = (c < p.n) ? __ldg(p.norms + c) : inf;
-            }
-            const float sq = (q < p.q_end) ? __ldg(p.norms + q) : inf;
+            cn[epi_tid] = next_cand;
+            const float sq = next_query;
             ptx::named_bar_sync(1, kEpiThreads);
+            ti.advance(p);
+            if (ti.valid) fetch_norms(ti, next_cand, next_query);
 
             if (ok) ok = ptx::mbar_wait_bounded(ptx::smem_u32(&aux->acc_full_bar[buf]), acc_phase, abort_flag,
                                                 kWaitLimitNs);
@@ -757,7 +806,7 @@ join_pair_kernel(const __grid_constant__ CUtensorMap map, const JoinParams p) {
 
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                                    static_cast<uint32_t>(buf * kTileN);
-            epilogue_tile(p, taddr, cn, sq, q, c_base, lane);
+            epilogue_tile(p, taddr + col_off, cn + col_off, sq, q, c_base + col_off, lane);
             ptx::tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive_cluster_addr(ptx::mapa_u32(ptx::smem_u32(&aux->acc_empty_bar[buf]), 0));

@@ -174,6 +174,15 @@ int fasted_get_norms(fasted_ctx* ctx, float* host_out);
 int fasted_join(fasted_ctx* ctx, double eps, int64_t q_begin, int64_t q_end, uint64_t capacity, unsigned flags,
                 fasted_join_stats* stats);
 
+/* Epsilon whose mean neighbour count per point (self pair excluded) is about `target`, estimated
+ * on `sample_rows` query rows (up to 8 bands spread over the dataset; 0 = 4096) against all
+ * candidates by bisection with count-only band joins; stops within rel_tol (0 = 1 %) of the target.
+ * Replaces the search the reference's driver runs with full reRun calls
+ * (results/scripts/experiment/experiments.py:153-281: doubling, then bisection on selectivity):
+ * a probe costs sample_rows/n of a full join.  *achieved_out (optional) is the sample's mean. */
+int fasted_estimate_epsilon(fasted_ctx* ctx, double target_mean_neighbours, int64_t sample_rows, double rel_tol,
+                            double* eps_out, double* achieved_out);
+
 /* Copy stored pairs [first, first + count) of the last join to the host as
  * (query, candidate) int32 records, replaces Pairs::getPairs,
  * source/pair.cuh:139-146.  dist2_out may be null. */

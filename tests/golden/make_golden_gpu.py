@@ -72,9 +72,9 @@ CASES = [
 ]
 
 
-def main(out_dir: str) -> None:
+def main(out_dir: str, timing_only: bool = False) -> None:
     os.makedirs(out_dir, exist_ok=True)
-    for name, kind, n, d, eps in CASES:
+    for name, kind, n, d, eps in ([] if timing_only else CASES):
         pts = dataset(kind, n, d)
         r = run_ref(pts, eps)
         np.savez_compressed(os.path.join(out_dir, f"ref_gpu_{name}.npz"), n=n, d=d, epsilon=eps, kind=kind,
@@ -82,7 +82,7 @@ def main(out_dir: str) -> None:
                             dataset_fnv1a64=np.uint64(oracle.fnv1a64_u16(pts)))
         print(name, "found", r["found"], "stored", r["stored"], flush=True)
     timing = []
-    for n, d in [(21544, 4096), (46416, 4096)]:
+    for n, d in [(21544, 4096), (46416, 4096), (100000, 4096)]:
         pts = oracle.double_to_half(np.random.default_rng(1).exponential(1 / 40.0, size=(n, d)))
         r = run_ref(pts, 0.001, want_pairs=False)
         timing.append(dict(n=n, d=d, epsilon=0.001, tflops=r["tflops"], pairs_found=r["found"]))
@@ -91,4 +91,5 @@ def main(out_dir: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else os.path.join(ROOT, "gpurun_out", "golden_gpu"))
+    main(sys.argv[1] if len(sys.argv) > 1 else os.path.join(ROOT, "gpurun_out", "golden_gpu"),
+         timing_only="--timing-only" in sys.argv)

@@ -304,3 +304,15 @@ def test_fp64_brute_force_pairs_match_cpu_truth(gpu_join, oracle_mod):
     want, _, _ = oracle_mod.join_fp64(pts, 0.3, q_begin=1000, q_end=1064)
     cmp = oracle_mod.compare_pair_sets(pts, 128, 0.3, pairs, want, band=1e-9)
     assert cmp["ok"] and int(counts.sum()) == len(pairs)
+
+
+def test_estimate_epsilon_hits_target(gpu_join, oracle_mod):
+    gpu_join.generate_exponential(30_000, 256)
+    eps, got = gpu_join.estimate_epsilon(24.0, sample_rows=4096, rel_tol=0.02)
+    assert abs(got - 24.0) <= 0.02 * 24.0 + 1e-9
+    st = gpu_join.join(eps, flags=2)
+    full_mean = (st.pairs_found - 30_000) / 30_000
+    assert 0.8 * 24 <= full_mean <= 1.25 * 24  # the sample (8 bands) speaks for the whole set
+    from fasted_b200 import FastedError
+    with pytest.raises(FastedError):
+        gpu_join.estimate_epsilon(0.0)
