@@ -598,6 +598,33 @@ int fasted_join(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end, uint6
     return FASTED_OK;
 }
 
+int fasted_tile_schedule(int64_t n, int64_t q_begin, int64_t q_end, int tile_m, int band_tiles, int symmetric,
+                         int grid, int cta, int32_t* tiles_out, int64_t max_tiles, int64_t* count_out) {
+    if (n <= 0 || q_begin < 0 || q_end < q_begin || q_end > n || grid <= 0 || cta < 0 || cta >= grid || !count_out ||
+        (tile_m != fasted::kTileM && tile_m != fasted::kPairTileM) || band_tiles <= 0)
+        return fail(FASTED_EINVAL, "bad argument");
+    fasted::JoinParams p{};
+    p.n = static_cast<int>(n);
+    p.q_begin = static_cast<int>(q_begin);
+    p.q_end = static_cast<int>(q_end);
+    p.tile_m = tile_m;
+    p.symmetric = symmetric ? 1 : 0;
+    p.tiles_m = static_cast<int>((q_end - q_begin + tile_m - 1) / tile_m);
+    p.tiles_n = static_cast<int>((n + fasted::kTileN - 1) / fasted::kTileN);
+    p.band_tiles = std::max(1, std::min(band_tiles, std::max(p.tiles_m, 1)));
+    fasted::TileIter ti;
+    int64_t count = 0;
+    for (ti.init(p, cta, grid); ti.valid; ti.advance(p)) {
+        if (tiles_out && count < max_tiles) {
+            tiles_out[2 * count] = ti.tm;
+            tiles_out[2 * count + 1] = ti.tn;
+        }
+        ++count;
+    }
+    *count_out = count;
+    return FASTED_OK;
+}
+
 int fasted_estimate_epsilon(fasted_ctx* c, double target_mean_neighbours, int64_t sample_rows, double rel_tol,
                             double* eps_out, double* achieved_out) {
     if (!c || !eps_out) return fail(FASTED_EINVAL, "null argument");

@@ -83,18 +83,18 @@ struct TileIter {
     int tm, tn;
     bool valid;
 
-    __device__ __forceinline__ void load_band(const JoinParams& p) {
+    __host__ __device__ __forceinline__ void load_band(const JoinParams& p) {
         const int first_row = band * p.band_tiles;
-        rows = min(p.band_tiles, p.tiles_m - first_row);
+        rows = p.tiles_m - first_row < p.band_tiles ? p.tiles_m - first_row : p.band_tiles;
         tn0 = 0;
         if (p.symmetric) {
             const int r0 = p.q_begin + first_row * p.tile_m;
             tn0 = r0 >= kTileN ? (r0 - (kTileN - 1)) / kTileN : 0;
-            tn0 = min(tn0, p.tiles_n);
+            if (tn0 > p.tiles_n) tn0 = p.tiles_n;
         }
         band_size = static_cast<long long>(rows) * (p.tiles_n - tn0);
     }
-    __device__ __forceinline__ void settle(const JoinParams& p) {
+    __host__ __device__ __forceinline__ void settle(const JoinParams& p) {
         for (;;) {
             while (band < nbands && rem >= band_size) {
                 rem -= band_size;
@@ -114,7 +114,7 @@ struct TileIter {
             rem += step;  // tile entirely below the diagonal: nothing to do
         }
     }
-    __device__ __forceinline__ void init(const JoinParams& p, long long first, long long stride) {
+    __host__ __device__ __forceinline__ void init(const JoinParams& p, long long first, long long stride) {
         step = stride;
         rem = first;
         band = 0;
@@ -125,7 +125,7 @@ struct TileIter {
             settle(p);
         }
     }
-    __device__ __forceinline__ void advance(const JoinParams& p) {
+    __host__ __device__ __forceinline__ void advance(const JoinParams& p) {
         rem += step;
         settle(p);
     }

@@ -2,6 +2,7 @@
 // include/fasted.h): runFromExponentialDataset, runFromFile, reRun,
 // releaseResources, with the reference's stdout lines, Results struct,
 // output-file format and error behaviour, on top of the context API.
+#include <algorithm>
 #include <chrono>
 #include <cmath>
 #include <cstdio>
@@ -11,6 +12,8 @@
 #include <stdexcept>
 #include <string>
 #include <vector>
+
+#include <omp.h>
 
 #include "dataset.hpp"
 #include "fasted.h"
@@ -50,28 +53,50 @@ fasted_ctx* context() {
 
 int64_t round_up(int64_t v, int64_t m) { return (v + m - 1) / m * m; }
 
-// Writes "q, c\n" (source/pair.cuh:51-54), optionally "q, c, dist\n".
+inline char* put_uint(char* p, uint32_t v) {
+    char tmp[10];
+    int len = 0;
+    do {
+        tmp[len++] = static_cast<char>('0' + v % 10);
+        v /= 10;
+    } while (v);
+    while (len) *p++ = tmp[--len];
+    return p;
+}
+
+// Writes "q, c\n" per pair (source/pair.cuh:51-54), optionally "q, c, dist\n".  The reference streams
+// one `os << pair << std::endl` (a flush) per pair; here threads format disjoint slices into their own
+// buffers, which are then written in order.
 void write_pairs_file(const std::string& path, const std::vector<int32_t>& pairs, const std::vector<float>* dist2) {
     FILE* f = std::fopen(path.c_str(), "wb");
     if (!f) return;  // the reference ignores a failed open (std::ofstream never checked)
-    std::vector<char> buf;
-    buf.reserve(1 << 22);
-    char tmp[96];
     const size_t count = pairs.size() / 2;
-    for (size_t i = 0; i < count; ++i) {
-        int len;
-        if (dist2)
-            len = std::snprintf(tmp, sizeof(tmp), "%d, %d, %.9g\n", pairs[2 * i], pairs[2 * i + 1],
-                                std::sqrt(static_cast<double>((*dist2)[i])));
-        else
-            len = std::snprintf(tmp, sizeof(tmp), "%d, %d\n", pairs[2 * i], pairs[2 * i + 1]);
-        buf.insert(buf.end(), tmp, tmp + len);
-        if (buf.size() > (1u << 22) - 128) {
-            std::fwrite(buf.data(), 1, buf.size(), f);
-            buf.clear();
+    const size_t slice = size_t(1) << 20;  // pairs per formatting task
+    const size_t tasks = (count + slice - 1) / slice;
+    const size_t wave = static_cast<size_t>(std::max(1, omp_get_max_threads()));
+    std::vector<std::vector<char>> bufs(wave);
+    for (size_t t0 = 0; t0 < tasks; t0 += wave) {
+        const size_t nt = std::min(wave, tasks - t0);
+#pragma omp parallel for schedule(static, 1)
+        for (size_t k = 0; k < nt; ++k) {
+            const size_t begin = (t0 + k) * slice, end = std::min(count, begin + slice);
+            std::vector<char>& b = bufs[k];
+            b.resize((end - begin) * (dist2 ? 48 : 24));
+            char* p = b.data();
+            for (size_t i = begin; i < end; ++i) {
+                p = put_uint(p, static_cast<uint32_t>(pairs[2 * i]));
+                *p++ = ',';
+                *p++ = ' ';
+                p = put_uint(p, static_cast<uint32_t>(pairs[2 * i + 1]));
+                if (dist2) {
+                    p += std::snprintf(p, 24, ", %.9g", std::sqrt(static_cast<double>((*dist2)[i])));
+                }
+                *p++ = '\n';
+            }
+            b.resize(static_cast<size_t>(p - b.data()));
         }
+        for (size_t k = 0; k < nt; ++k) std::fwrite(bufs[k].data(), 1, bufs[k].size(), f);
     }
-    std::fwrite(buf.data(), 1, buf.size(), f);
     std::fclose(f);
 }
 

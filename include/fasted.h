@@ -246,6 +246,14 @@ int fasted_dataset_exponential_f16(int64_t n, int64_t d, double lambda, double m
 int fasted_dataset_csv_shape(const char* path, int64_t* n, int64_t* d);
 int fasted_dataset_csv_f16(const char* path, uint16_t* out, int64_t n, int64_t d, int64_t ld_out);
 
+/* The tile schedule of the join kernel, evaluated on the host (no GPU): the (tile row, tile
+ * column) sequence that CTA `cta` of `grid` walks for query rows [q_begin, q_end) of n points.
+ * tile_m is 128 (single-CTA kernel) or 256 (CTA pairs; cta then counts pairs); tile columns are 256
+ * candidates wide.  Replaces OnDemandRasterizer::nextChunk, source/rasterizer/onDemandRasterizer.cuh:78-108.
+ * tiles_out (optional) receives up to max_tiles (tm, tn) int32 pairs, *count_out the full count. */
+int fasted_tile_schedule(int64_t n, int64_t q_begin, int64_t q_end, int tile_m, int band_tiles, int symmetric,
+                         int grid, int cta, int32_t* tiles_out, int64_t max_tiles, int64_t* count_out);
+
 /* Tuning knobs: "band_tiles" (128-row tile rows per raster band, default 16), "grid" (CTAs,
  * 0 = one per SM), "cta_pair" (1 = the CTA-pair kernel: 256 x 256 tiles computed by two CTAs with
  * tcgen05 cta_group::2; same results bit for bit; default 0 because it sustains less under the
