@@ -53,7 +53,7 @@ DECLARED_SYMBOLS = [
     "fasted_last_error", "fasted_create", "fasted_destroy", "fasted_set_stream",
     "fasted_set_points_host_f16", "fasted_set_points_device_f16", "fasted_generate_exponential",
     "fasted_fill_exponential_device",
-    "fasted_points_info", "fasted_get_points_host_f16", "fasted_row_norms", "fasted_get_norms",
+    "fasted_points_info", "fasted_get_points_host_f16", "fasted_get_rows_host_f16", "fasted_row_norms", "fasted_get_norms",
     "fasted_join", "fasted_tile_schedule", "fasted_estimate_epsilon", "fasted_get_pairs", "fasted_pairs_device", "fasted_brute_force_f64", "fasted_brute_force_f64_pairs", "fasted_set_option",
     "fasted_dataset_exponential_f16", "fasted_dataset_csv_shape", "fasted_dataset_csv_f16",
     "fasted_join_static_scratch",
@@ -84,6 +84,7 @@ def load() -> ctypes.CDLL:
     L.fasted_points_info.argtypes = [_vp, ctypes.POINTER(_vp), ctypes.POINTER(_i64), ctypes.POINTER(_i64),
                                      ctypes.POINTER(_i64)]
     L.fasted_get_points_host_f16.argtypes = [_vp, _vp, _i64]
+    L.fasted_get_rows_host_f16.argtypes = [_vp, _vp, _i64, _vp, _i64]
     L.fasted_row_norms.argtypes = [_vp, ctypes.POINTER(ctypes.c_double)]
     L.fasted_get_norms.argtypes = [_vp, _vp]
     L.fasted_join.argtypes = [_vp, ctypes.c_double, _i64, _i64, _u64, ctypes.c_uint, ctypes.POINTER(JoinStats)]
@@ -217,6 +218,15 @@ class SelfJoin:
         _, n, d, _ = self.points_info()
         out = np.empty((n, d), dtype=np.uint16)
         _check(self._L.fasted_get_points_host_f16(self._h, out.ctypes.data_as(_vp), d))
+        return out
+
+    def get_rows(self, rows) -> np.ndarray:
+        """Selected rows of the resident dataset as binary16 bit patterns (len(rows), d)."""
+        _, _, d, _ = self.points_info()
+        rows = np.ascontiguousarray(rows, dtype=np.int64)
+        out = np.empty((len(rows), d), dtype=np.uint16)
+        _check(self._L.fasted_get_rows_host_f16(self._h, rows.ctypes.data_as(_vp), len(rows),
+                                                out.ctypes.data_as(_vp), d))
         return out
 
     def get_points_into(self, host_ptr: int, ld_host: int) -> None:

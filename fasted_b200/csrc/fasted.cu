@@ -394,6 +394,20 @@ int fasted_get_points_host_f16(fasted_ctx* c, uint16_t* host, int64_t ld_host) {
     return FASTED_OK;
 }
 
+int fasted_get_rows_host_f16(fasted_ctx* c, const int64_t* rows, int64_t count, uint16_t* host, int64_t ld_host) {
+    if (!c || !rows || !host || count < 0) return fail(FASTED_EINVAL, "bad argument");
+    if (!c->points) return fail(FASTED_ESTATE, "no dataset is resident");
+    if (ld_host < c->d) return fail(FASTED_EINVAL, "ld_host < d");
+    CU_TRY(cudaSetDevice(c->device));
+    for (int64_t i = 0; i < count; ++i) {
+        if (rows[i] < 0 || rows[i] >= c->n) return fail(FASTED_EINVAL, "row %lld out of range", (long long)rows[i]);
+        CU_TRY(cudaMemcpyAsync(host + i * ld_host, c->points + rows[i] * c->ld, static_cast<size_t>(c->d) * 2,
+                               cudaMemcpyDeviceToHost, c->stream));
+    }
+    CU_TRY(cudaStreamSynchronize(c->stream));
+    return FASTED_OK;
+}
+
 static int launch_norms(fasted_ctx* c) {
     const int row_blocks = static_cast<int>((c->n + fasted::kNormRows - 1) / fasted::kNormRows);
     const int k_boxes = static_cast<int>((c->d + fasted::kTileK - 1) / fasted::kTileK);

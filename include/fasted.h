@@ -161,6 +161,9 @@ int fasted_points_info(fasted_ctx* ctx, void** dev, int64_t* n, int64_t* d, int6
 /* Copy the resident dataset to the host (row stride ld_host >= d). */
 int fasted_get_points_host_f16(fasted_ctx* ctx, uint16_t* host, int64_t ld_host);
 
+/* Copy selected rows of the resident dataset to the host (row i of the output = row rows[i]). */
+int fasted_get_rows_host_f16(fasted_ctx* ctx, const int64_t* rows, int64_t count, uint16_t* host, int64_t ld_host);
+
 /* Row norms, replaces SumSqd::ComputeSquaredSums, source/sumSquared.cuh:84-118.
  * Result stays on the device; ms (optional) receives the kernel time. */
 int fasted_row_norms(fasted_ctx* ctx, double* ms);

@@ -316,3 +316,44 @@ def test_estimate_epsilon_hits_target(gpu_join, oracle_mod):
     from fasted_b200 import FastedError
     with pytest.raises(FastedError):
         gpu_join.estimate_epsilon(0.0)
+
+
+def test_full_size_headline_shape_properties(gpu_join, oracle_mod):
+    # The benchmark's own shape (1,000,000 x 4096, ~57 M pairs): too large for any CPU oracle, so
+    # size-independent properties: row-major order, symmetry, the diagonal, no padding index, and
+    # sampled query rows against the FP64 brute force on the device (band rule for disagreements).
+    n, d = 1_000_000, 4096
+    gpu_join.generate_exponential(n, d)
+    eps = 2.1143826828408416  # ~56 neighbours per point on this seeded dataset
+    st = gpu_join.join(eps, flags=8)  # symmetric schedule: bit-identical output, half the time
+    assert st.status == 0 and st.pairs_found == st.pairs_stored
+    assert 40 * n < st.pairs_found < 80 * n
+    got = gpu_join.pairs()
+    keys = (got[:, 0].astype(np.int64) << 32) | got[:, 1].astype(np.int64)
+    assert (np.diff(keys) > 0).all()
+    assert got.min() >= 0 and got.max() < n
+    assert int((got[:, 0] == got[:, 1]).sum()) == n
+    # symmetry: every off-diagonal pair appears in both orientations
+    up = got[got[:, 0] < got[:, 1]]
+    lo = got[got[:, 0] > got[:, 1]]
+    assert len(up) == len(lo)
+    ku = (up[:, 0].astype(np.int64) << 32) | up[:, 1].astype(np.int64)
+    kl = np.sort((lo[:, 1].astype(np.int64) << 32) | lo[:, 0].astype(np.int64))
+    assert np.array_equal(ku, kl)
+    del keys, up, lo, ku, kl
+    # sampled rows vs FP64 truth
+    rows = np.arange(123_456, 123_456 + 48, dtype=np.int32)
+    counts, truth = gpu_join.brute_force_pairs(rows, eps, capacity=48 * 65536)
+    mine = got[(got[:, 0] >= rows[0]) & (got[:, 0] <= rows[-1])]
+    kt = (truth[:, 0].astype(np.int64) << 32) | truth[:, 1].astype(np.int64)
+    km = (mine[:, 0].astype(np.int64) << 32) | mine[:, 1].astype(np.int64)
+    only = np.concatenate([np.setdiff1d(kt, km), np.setdiff1d(km, kt)])
+    assert len(only) <= 0.03 * len(kt) + 4
+    if len(only):
+        # every disagreement must sit inside the 1e-3 band around eps^2 (FP64 distances on the device)
+        pr = np.stack([only >> 32, only & 0xFFFFFFFF], 1)
+        sub = gpu_join.get_rows(np.unique(pr.ravel()))
+        lut = {int(r): i for i, r in enumerate(np.unique(pr.ravel()))}
+        f = sub.view(np.float16).astype(np.float64)
+        d2 = np.array([((f[lut[int(a)]] - f[lut[int(b)]]) ** 2).sum() for a, b in pr])
+        assert (np.abs(d2 - eps * eps) <= BAND * eps * eps).all()
