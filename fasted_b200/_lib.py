@@ -54,7 +54,7 @@ DECLARED_SYMBOLS = [
     "fasted_set_points_host_f16", "fasted_set_points_device_f16", "fasted_generate_exponential",
     "fasted_fill_exponential_device",
     "fasted_points_info", "fasted_get_points_host_f16", "fasted_get_rows_host_f16", "fasted_row_norms", "fasted_get_norms",
-    "fasted_join", "fasted_tile_schedule", "fasted_estimate_epsilon", "fasted_get_pairs", "fasted_pairs_device", "fasted_brute_force_f64", "fasted_brute_force_f64_pairs", "fasted_set_option",
+    "fasted_join", "fasted_join_symmetric_shard", "fasted_tile_schedule", "fasted_estimate_epsilon", "fasted_get_pairs", "fasted_pairs_device", "fasted_brute_force_f64", "fasted_brute_force_f64_pairs", "fasted_set_option",
     "fasted_dataset_exponential_f16", "fasted_dataset_csv_shape", "fasted_dataset_csv_f16",
     "fasted_join_static_scratch",
 ]
@@ -89,7 +89,9 @@ def load() -> ctypes.CDLL:
     L.fasted_get_norms.argtypes = [_vp, _vp]
     L.fasted_join.argtypes = [_vp, ctypes.c_double, _i64, _i64, _u64, ctypes.c_uint, ctypes.POINTER(JoinStats)]
     L.fasted_tile_schedule.argtypes = [_i64, _i64, _i64, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
-                                       ctypes.c_int, _vp, _i64, ctypes.POINTER(_i64)]
+                                       ctypes.c_int, ctypes.c_int, ctypes.c_int, _vp, _i64, ctypes.POINTER(_i64)]
+    L.fasted_join_symmetric_shard.argtypes = [_vp, ctypes.c_double, ctypes.c_int, ctypes.c_int, _u64, ctypes.c_uint,
+                                              ctypes.POINTER(JoinStats)]
     L.fasted_estimate_epsilon.argtypes = [_vp, ctypes.c_double, _i64, ctypes.c_double, ctypes.POINTER(ctypes.c_double),
                                           ctypes.POINTER(ctypes.c_double)]
     L.fasted_get_pairs.argtypes = [_vp, _u64, _u64, _vp, _vp]
@@ -139,14 +141,14 @@ def join_static_scratch(points_dev: int, n: int, d: int, ld: int, eps: float, ke
 
 
 def tile_schedule(n: int, q_begin: int, q_end: int, grid: int, cta: int, tile_m: int = 128, band_tiles: int = 16,
-                  symmetric: bool = False) -> np.ndarray:
+                  symmetric: bool = False, shard_rank: int = 0, shard_world: int = 1) -> np.ndarray:
     """The (tile row, tile column) sequence one CTA of the join kernel walks (host evaluation, no GPU)."""
     count = _i64()
-    _check(load().fasted_tile_schedule(n, q_begin, q_end, tile_m, band_tiles, int(symmetric), grid, cta, None, 0,
-                                       ctypes.byref(count)))
+    _check(load().fasted_tile_schedule(n, q_begin, q_end, tile_m, band_tiles, int(symmetric), shard_rank, shard_world,
+                                       grid, cta, None, 0, ctypes.byref(count)))
     out = np.empty((count.value, 2), dtype=np.int32)
-    _check(load().fasted_tile_schedule(n, q_begin, q_end, tile_m, band_tiles, int(symmetric), grid, cta,
-                                       out.ctypes.data_as(_vp), count.value, ctypes.byref(count)))
+    _check(load().fasted_tile_schedule(n, q_begin, q_end, tile_m, band_tiles, int(symmetric), shard_rank, shard_world,
+                                       grid, cta, out.ctypes.data_as(_vp), count.value, ctypes.byref(count)))
     return out
 
 
@@ -259,6 +261,15 @@ class SelfJoin:
         _check(self._L.fasted_estimate_epsilon(self._h, float(target_mean_neighbours), sample_rows, rel_tol,
                                                ctypes.byref(eps), ctypes.byref(got)))
         return eps.value, got.value
+
+    def join_symmetric_shard(self, eps: float, shard_rank: int, shard_world: int, capacity: int = 0,
+                             flags: int = 0) -> JoinStats:
+        st = JoinStats()
+        _check(self._L.fasted_join_symmetric_shard(self._h, float(eps), shard_rank, shard_world, capacity, flags,
+                                                   ctypes.byref(st)))
+        self._last = st
+        self._last_dist = bool(flags & JOIN_DIST2)
+        return st
 
     def pairs(self, with_dist2: bool = False):
         st = self._last

@@ -449,8 +449,8 @@ int fasted_get_norms(fasted_ctx* c, float* host_out) {
     return FASTED_OK;
 }
 
-int fasted_join(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end, uint64_t capacity, unsigned flags,
-                fasted_join_stats* stats) {
+static int join_impl(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end, uint64_t capacity, unsigned flags,
+                     int shard_rank, int shard_world, fasted_join_stats* stats) {
     if (!c) return fail(FASTED_EINVAL, "ctx is null");
     if (!c->points) return fail(FASTED_ESTATE, "no dataset is resident");
     if (q_end < 0) q_end = c->n;
@@ -495,6 +495,9 @@ int fasted_join(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end, uint6
         return fail(FASTED_EINVAL, "FASTED_JOIN_SYMMETRIC needs the full query range [0, n)");
     p.tile_m = tile_m;
     p.symmetric = symmetric ? 1 : 0;
+    p.shard_rank = shard_rank;
+    p.shard_world = shard_world;
+    if (shard_world > 1 && !symmetric) return fail(FASTED_EINVAL, "band snakes are for the symmetric schedule only");
     p.tiles_m = static_cast<int>((q_end - q_begin + tile_m - 1) / tile_m);
     p.tiles_n = static_cast<int>((c->n + fasted::kTileN - 1) / fasted::kTileN);
     // band_tiles counts 128-row tile rows; a pair tile is two of them.
@@ -612,8 +615,20 @@ int fasted_join(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end, uint6
     return FASTED_OK;
 }
 
+int fasted_join(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end, uint64_t capacity, unsigned flags,
+                fasted_join_stats* stats) {
+    return join_impl(c, eps, q_begin, q_end, capacity, flags, 0, 1, stats);
+}
+
+int fasted_join_symmetric_shard(fasted_ctx* c, double eps, int shard_rank, int shard_world, uint64_t capacity,
+                                unsigned flags, fasted_join_stats* stats) {
+    if (shard_world < 1 || shard_rank < 0 || shard_rank >= shard_world) return fail(FASTED_EINVAL, "bad shard");
+    return join_impl(c, eps, 0, -1, capacity, flags | FASTED_JOIN_SYMMETRIC, shard_rank, shard_world, stats);
+}
+
 int fasted_tile_schedule(int64_t n, int64_t q_begin, int64_t q_end, int tile_m, int band_tiles, int symmetric,
-                         int grid, int cta, int32_t* tiles_out, int64_t max_tiles, int64_t* count_out) {
+                         int shard_rank, int shard_world, int grid, int cta, int32_t* tiles_out, int64_t max_tiles,
+                         int64_t* count_out) {
     if (n <= 0 || q_begin < 0 || q_end < q_begin || q_end > n || grid <= 0 || cta < 0 || cta >= grid || !count_out ||
         (tile_m != fasted::kTileM && tile_m != fasted::kPairTileM) || band_tiles <= 0)
         return fail(FASTED_EINVAL, "bad argument");
@@ -623,6 +638,9 @@ int fasted_tile_schedule(int64_t n, int64_t q_begin, int64_t q_end, int tile_m, 
     p.q_end = static_cast<int>(q_end);
     p.tile_m = tile_m;
     p.symmetric = symmetric ? 1 : 0;
+    p.shard_rank = shard_rank;
+    p.shard_world = shard_world;
+    if (shard_world > 1 && !symmetric) return fail(FASTED_EINVAL, "band snakes are for the symmetric schedule only");
     p.tiles_m = static_cast<int>((q_end - q_begin + tile_m - 1) / tile_m);
     p.tiles_n = static_cast<int>((n + fasted::kTileN - 1) / fasted::kTileN);
     p.band_tiles = std::max(1, std::min(band_tiles, std::max(p.tiles_m, 1)));
@@ -874,6 +892,8 @@ int fasted_join_static_scratch(const void* points_dev, int64_t n, int64_t d, int
     p.total_tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
     p.tile_m = fasted::kTileM;
     p.symmetric = 0;
+    p.shard_rank = 0;
+    p.shard_world = 1;
     const int grid = static_cast<int>(std::min<long long>(p.total_tiles, num_sms));
 
     // The scratch area keeps whatever the previous call left: the counters must start at zero

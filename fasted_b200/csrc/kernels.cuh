@@ -61,6 +61,9 @@ struct JoinParams {
     long long total_tiles;         // upper bound of the tiles walked (grid sizing only)
     int tile_m;                    // query rows per tile (kTileM, or 2 * kTileM for CTA pairs)
     int symmetric;                 // 1: walk only tiles that touch j >= i and emit (i,j) and (j,i)
+    int shard_rank, shard_world;   // symmetric mode over several GPUs: this launch takes the raster bands
+                                   // r, 2G-1-r, 2G+r, 4G-1-r, ... (a snake over the G shards, which evens out
+                                   // the shrinking band lengths of the triangle); 0, 1 = everything
 };
 
 // Persistent static schedule: CTA (or CTA pair) b handles tiles b, b + grid, b + 2*grid, ... of a
@@ -77,14 +80,22 @@ struct TileIter {
     long long rem;        // index of the current tile inside the current band
     long long band_size;  // tiles in the current band
     long long step;
-    int band, nbands;
+    int band, nbands;     // index into this launch's bands, and how many it has
+    int pband;            // the current band in the global numbering
     int rows;             // tile rows in the current band
     int tn0;              // first candidate tile of the current band
     int tm, tn;
     bool valid;
 
+    // Raster band (in the global numbering) behind this launch's k-th band.
+    __host__ __device__ __forceinline__ int physical_band(const JoinParams& p, int k) const {
+        const int g = p.shard_world > 1 ? p.shard_world : 1;
+        const int r = p.shard_world > 1 ? p.shard_rank : 0;
+        return (k >> 1) * (2 * g) + ((k & 1) ? (2 * g - 1 - r) : r);
+    }
     __host__ __device__ __forceinline__ void load_band(const JoinParams& p) {
-        const int first_row = band * p.band_tiles;
+        pband = physical_band(p, band);
+        const int first_row = pband * p.band_tiles;
         rows = p.tiles_m - first_row < p.band_tiles ? p.tiles_m - first_row : p.band_tiles;
         tn0 = 0;
         if (p.symmetric) {
@@ -106,7 +117,7 @@ struct TileIter {
             }
             const int col = static_cast<int>(rem / rows);
             tn = tn0 + col;
-            tm = band * p.band_tiles + static_cast<int>(rem - static_cast<long long>(col) * rows);
+            tm = pband * p.band_tiles + static_cast<int>(rem - static_cast<long long>(col) * rows);
             if (!p.symmetric || tn * kTileN + (kTileN - 1) >= p.q_begin + tm * p.tile_m) {
                 valid = true;
                 return;
@@ -118,7 +129,9 @@ struct TileIter {
         step = stride;
         rem = first;
         band = 0;
-        nbands = (p.tiles_m + p.band_tiles - 1) / p.band_tiles;
+        const int total_bands = (p.tiles_m + p.band_tiles - 1) / p.band_tiles;
+        nbands = 0;
+        while (physical_band(p, nbands) < total_bands) ++nbands;  // physical_band grows with k
         valid = false;
         if (nbands > 0) {
             load_band(p);

@@ -33,6 +33,10 @@ class BandEngine(Protocol):
     def join_band(self, eps: float, q_begin: int, q_end: int) -> tuple[np.ndarray, int]:
         """Sorted (m, 2) int32 pairs of the band and the number of pairs found."""
 
+    def join_symmetric_shard(self, eps: float, rank: int, world: int) -> tuple[np.ndarray, int]:
+        """Sorted pairs of shard `rank` of the symmetric schedule (both orientations of every hit in
+        the shard's part of the upper triangle) and their number."""
+
 
 class GpuBandEngine:
     """BandEngine on the native library (fasted_b200.SelfJoin)."""
@@ -46,6 +50,12 @@ class GpuBandEngine:
         n = self.sj.points_info()[1]
         st = self.sj.join(eps, q_begin=q_begin, q_end=q_end, capacity=max(1, (q_end - q_begin)) * 256
                           if q_end - q_begin < n else 0, flags=self.flags)
+        self.last_stats = st
+        return self.sj.pairs(), int(st.pairs_found)
+
+
+    def join_symmetric_shard(self, eps: float, rank: int, world: int):
+        st = self.sj.join_symmetric_shard(eps, rank, world, flags=self.flags)
         self.last_stats = st
         return self.sj.pairs(), int(st.pairs_found)
 
@@ -87,3 +97,51 @@ def sharded_self_join(engine: BandEngine, n: int, eps: float, gather: bool = Tru
         if rank == 0:
             pairs = np.concatenate(parts) if parts else pairs
     return pairs, found_total, stored_local
+
+
+def sharded_self_join_symmetric(engine: BandEngine, n: int, eps: float, gather: bool = True):
+    """Symmetric schedule over the ranks: every unordered pair is computed once, on one rank.
+
+    Rank r computes the raster bands r, 2G-1-r, 2G+r, ... of the upper triangle (balanced work) and
+    emits both orientations, so its records can belong to any query row.  The ONE exchange step of
+    this variant is an all-to-all of pair records: each rank sends every other rank the records whose
+    query row lies in that rank's contiguous range (band_bounds), then sorts what it received.  After
+    it, rank order concatenation is the global row-major order, exactly as in sharded_self_join.
+    Returns (pairs, found_total, stored_local)."""
+    import torch
+    import torch.distributed as dist
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size() == 1:
+        pairs, found = engine.join_symmetric_shard(eps, 0, 1)
+        return pairs, found, len(pairs)
+    world, rank = dist.get_world_size(), dist.get_rank()
+    pairs, found = engine.join_symmetric_shard(eps, rank, world)
+    backend = dist.get_backend()
+    dev = torch.device("cuda", torch.cuda.current_device()) if backend == "nccl" else torch.device("cpu")
+
+    # records are sorted by (query, candidate): the destination ranges are contiguous slices
+    bounds = [band_bounds(n, world, r) for r in range(world)]
+    cuts = np.searchsorted(pairs[:, 0], [b for b, _ in bounds] + [n], side="left")
+    send_counts = [int(cuts[r + 1] - cuts[r]) for r in range(world)]
+    sc = torch.tensor(send_counts, dtype=torch.int64, device=dev)
+    rc = torch.empty(world, dtype=torch.int64, device=dev)
+    dist.all_to_all_single(rc, sc)
+    recv_counts = [int(x) for x in rc.tolist()]
+    send = torch.from_numpy(np.ascontiguousarray(pairs).reshape(-1)).to(dev)
+    recv = torch.empty(2 * sum(recv_counts), dtype=torch.int32, device=dev)
+    dist.all_to_all_single(recv, send, output_split_sizes=[2 * c for c in recv_counts],
+                           input_split_sizes=[2 * c for c in send_counts])
+    mine = recv.view(-1, 2)
+    key = (mine[:, 0].to(torch.int64) << 32) | mine[:, 1].to(torch.int64)
+    order = torch.argsort(key)
+    mine = mine[order].cpu().numpy()
+
+    t = torch.tensor([found], dtype=torch.int64, device=dev)
+    dist.all_reduce(t)
+    found_total = int(t.item())
+    stored_local = len(mine)
+    if gather:
+        parts = [None] * world if rank == 0 else None
+        dist.gather_object(mine, parts, dst=0)
+        if rank == 0:
+            mine = np.concatenate(parts)
+    return mine, found_total, stored_local

@@ -177,6 +177,15 @@ int fasted_get_norms(fasted_ctx* ctx, float* host_out);
 int fasted_join(fasted_ctx* ctx, double eps, int64_t q_begin, int64_t q_end, uint64_t capacity, unsigned flags,
                 fasted_join_stats* stats);
 
+/* One shard of the symmetric schedule for a self-join split over shard_world GPUs that all hold the
+ * dataset: shard r computes the raster bands r, 2G-1-r, 2G+r, ... (G = shard_world) of the upper
+ * triangle and emits both orientations of every hit, so the union of the shards' outputs is the
+ * full join's output, each pair exactly once.  A shard's output is sorted but not a contiguous
+ * query range (the mirrored records belong to other rows): see fasted_b200/dist.py for the exchange
+ * that gives every rank a contiguous range. */
+int fasted_join_symmetric_shard(fasted_ctx* ctx, double eps, int shard_rank, int shard_world, uint64_t capacity,
+                                unsigned flags, fasted_join_stats* stats);
+
 /* Epsilon whose mean neighbour count per point (self pair excluded) is about `target`, estimated
  * on `sample_rows` query rows (up to 8 bands spread over the dataset; 0 = 4096) against all
  * candidates by bisection with count-only band joins; stops within rel_tol (0 = 1 %) of the target.
@@ -255,7 +264,8 @@ int fasted_dataset_csv_f16(const char* path, uint16_t* out, int64_t n, int64_t d
  * candidates wide.  Replaces OnDemandRasterizer::nextChunk, source/rasterizer/onDemandRasterizer.cuh:78-108.
  * tiles_out (optional) receives up to max_tiles (tm, tn) int32 pairs, *count_out the full count. */
 int fasted_tile_schedule(int64_t n, int64_t q_begin, int64_t q_end, int tile_m, int band_tiles, int symmetric,
-                         int grid, int cta, int32_t* tiles_out, int64_t max_tiles, int64_t* count_out);
+                         int shard_rank, int shard_world, int grid, int cta, int32_t* tiles_out, int64_t max_tiles,
+                         int64_t* count_out);
 
 /* Tuning knobs: "band_tiles" (128-row tile rows per raster band, default 16), "grid" (CTAs,
  * 0 = one per SM), "cta_pair" (1 = the CTA-pair kernel: 256 x 256 tiles computed by two CTAs with

@@ -55,6 +55,22 @@ def _worker(rank, world, port, n, d, eps, out_dir):
             p, _ = oracle.join_fp16_fp32(self.pts, eps, q_begin=a, q_end=b)
             return p, len(p)
 
+        def join_symmetric_shard(self, eps, rank, world):
+            # what the GPU shard emits: hits (i, j) with j >= i whose row i lies in one of the shard's
+            # raster bands (band_rows query rows each, dealt out as a snake), plus their mirrors
+            from fasted_b200 import _lib
+            full, _ = oracle.join_fp16_fp32(self.pts, eps)
+            band_rows = 128  # one tile row per band keeps several bands in this small case
+            tiles = _lib.tile_schedule(len(self.pts), 0, len(self.pts), 1, 0, 128, 1, True, rank, world)
+            my_rows = np.zeros(len(self.pts), dtype=bool)
+            for tm in np.unique(tiles[:, 0]):
+                my_rows[tm * band_rows:(tm + 1) * band_rows] = True
+            up = full[(full[:, 1] >= full[:, 0]) & my_rows[full[:, 0]]]
+            mir = up[up[:, 1] > up[:, 0]][:, ::-1]
+            out = np.concatenate([up, mir])
+            out = out[np.lexsort((out[:, 1], out[:, 0]))]
+            return np.ascontiguousarray(out), len(out)
+
     # rank 0 owns the data, the others receive it through the one broadcast
     if rank == 0:
         t = torch.from_numpy(oracle.gen_exponential(n, d).view(np.int16).copy())
@@ -63,6 +79,10 @@ def _worker(rank, world, port, n, d, eps, out_dir):
     broadcast_points(t)
     pts = t.numpy().view(np.uint16)
     pairs, found, stored = sharded_self_join(OracleEngine(pts), n, eps)
+    from fasted_b200.dist import sharded_self_join_symmetric
+    spairs, sfound, sstored = sharded_self_join_symmetric(OracleEngine(pts), n, eps)
+    np.save(os.path.join(out_dir, f"spairs{rank}.npy"), spairs)
+    np.save(os.path.join(out_dir, f"smeta{rank}.npy"), np.array([sfound, sstored]))
     np.save(os.path.join(out_dir, f"pairs{rank}.npy"), pairs)
     np.save(os.path.join(out_dir, f"meta{rank}.npy"), np.array([found, stored]))
     dist.barrier()
@@ -79,7 +99,15 @@ def test_sharded_join_equals_single_rank(oracle_mod, tmp_path, world):
     metas = [np.load(tmp_path / f"meta{r}.npy") for r in range(world)]
     assert all(int(m[0]) == len(want) for m in metas)
     assert sum(int(m[1]) for m in metas) == len(want)
+    # symmetric schedule + all-to-all of records: same global list, every rank a contiguous range
+    assert np.array_equal(np.load(tmp_path / "spairs0.npy"), want)
+    smetas = [np.load(tmp_path / f"smeta{r}.npy") for r in range(world)]
+    assert all(int(m[0]) == len(want) for m in smetas) and sum(int(m[1]) for m in smetas) == len(want)
     from fasted_b200.dist import band_bounds
+    for r in range(1, world):
+        a, b = band_bounds(n, world, r)
+        sp = np.load(tmp_path / f"spairs{r}.npy")
+        assert len(sp) == 0 or (sp[:, 0].min() >= a and sp[:, 0].max() < b)
     for r in range(1, world):
         a, b = band_bounds(n, world, r)
         p = np.load(tmp_path / f"pairs{r}.npy")

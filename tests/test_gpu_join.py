@@ -357,3 +357,29 @@ def test_full_size_headline_shape_properties(gpu_join, oracle_mod):
         f = sub.view(np.float16).astype(np.float64)
         d2 = np.array([((f[lut[int(a)]] - f[lut[int(b)]]) ** 2).sum() for a, b in pr])
         assert (np.abs(d2 - eps * eps) <= BAND * eps * eps).all()
+
+
+@pytest.mark.parametrize("n,d,eps,world", [(5000, 128, 0.33, 2), (9000, 64, 0.2, 3), (20000, 256, 0.45, 8)])
+def test_symmetric_shards_union_is_the_full_join(gpu_join, oracle_mod, n, d, eps, world):
+    # The multi-GPU symmetric schedule, shard by shard on one GPU: the shards' outputs are disjoint
+    # and their union is the full join's output.
+    gpu_join.set_points(oracle_mod.gen_exponential(n, d))
+    gpu_join.set_option("band_tiles", 2)  # several raster bands even at this size
+    try:
+        gpu_join.join(eps, capacity=n * 4096)
+        want = oracle_mod.pair_keys(gpu_join.pairs())
+        parts = []
+        for r in range(world):
+            st = gpu_join.join_symmetric_shard(eps, r, world, capacity=n * 4096)
+            p = gpu_join.pairs()
+            assert st.pairs_found == len(p)
+            k = oracle_mod.pair_keys(p)
+            assert (np.diff(k.astype(np.int64)) > 0).all()
+            parts.append(k)
+    finally:
+        gpu_join.set_option("band_tiles", 16)
+    allk = np.concatenate(parts)
+    assert len(np.unique(allk)) == len(allk) == len(want)
+    assert np.array_equal(np.sort(allk), want)
+    sizes = [len(p) for p in parts]
+    assert min(sizes) > 0

@@ -46,3 +46,21 @@ def test_symmetric_schedule_covers_the_upper_triangle_once(native_lib, n, grid, 
     np.add.at(got, (allt[:, 0], allt[:, 1]), 1)
     assert np.array_equal(got, needed.astype(np.int32))
     assert needed.sum() < 0.56 * tiles_m * tiles_n or tiles_m * tiles_n < 200
+
+
+@pytest.mark.parametrize("n,world,band", [(5000, 2, 4), (70000, 8, 16), (33333, 3, 3), (300, 4, 1), (1_000_000, 8, 16)])
+def test_symmetric_shards_partition_the_triangle_evenly(native_lib, n, world, band):
+    from fasted_b200 import _lib
+    tiles_m, tiles_n = -(-n // 128), -(-n // 256)
+    got = np.zeros((tiles_m, tiles_n), dtype=np.int32)
+    loads = []
+    for r in range(world):
+        # one "CTA" walking everything = the shard's whole tile list
+        t = _lib.tile_schedule(n, 0, n, 1, 0, 128, band, True, r, world)
+        np.add.at(got, (t[:, 0], t[:, 1]), 1)
+        loads.append(len(t))
+    tm, tn = np.meshgrid(np.arange(tiles_m), np.arange(tiles_n), indexing="ij")
+    needed = (tn * 256 + 255 >= tm * 128).astype(np.int32)
+    assert np.array_equal(got, needed)
+    if tiles_m >= 8 * world * band:
+        assert (max(loads) - min(loads)) / max(loads) < 0.02  # the snake evens out the triangle
