@@ -1,0 +1,66 @@
+"""Two real GPUs (skipped on a single-GPU box): band sharding and the symmetric shard exchange over
+NCCL give the same global pair list as one GPU."""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+
+from conftest import ROOT
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, n, d, eps, out_dir):
+    sys.path.insert(0, ROOT)
+    import torch
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from fasted_b200 import SelfJoin, _lib
+    from fasted_b200.dist import GpuBandEngine, broadcast_points, sharded_self_join, sharded_self_join_symmetric
+    t = torch.zeros((n, d), dtype=torch.float16, device="cuda")
+    if rank == 0:
+        host = _lib.dataset_exponential(n, d)
+        t.copy_(torch.from_numpy(host.view(np.float16)))
+    broadcast_points(t)  # the one collective of the full schedule
+    sj = SelfJoin(rank)
+    sj.set_points_device(t.data_ptr(), n, d, d, keepalive=t)
+    sj.set_option("band_tiles", 2)
+    eng = GpuBandEngine(sj)
+    a, fa, _ = sharded_self_join(eng, n, eps)
+    b, fb, _ = sharded_self_join_symmetric(eng, n, eps)
+    if rank == 0:
+        np.save(os.path.join(out_dir, "bands.npy"), a)
+        np.save(os.path.join(out_dir, "sym.npy"), b)
+        np.save(os.path.join(out_dir, "found.npy"), np.array([fa, fb]))
+    dist.barrier()
+    sj.close()
+    dist.destroy_process_group()
+
+
+def test_two_gpu_sharding_matches_one_gpu(gpu_join, oracle_mod, tmp_path):
+    import torch
+    import torch.multiprocessing as mp
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    n, d, eps = 6000, 128, 0.33
+    mp.spawn(_worker, args=(2, _free_port(), n, d, eps, str(tmp_path)), nprocs=2, join=True)
+    gpu_join.set_points(oracle_mod.gen_exponential(n, d))
+    gpu_join.join(eps)
+    want = gpu_join.pairs()
+    assert np.array_equal(np.load(tmp_path / "bands.npy"), want)
+    assert np.array_equal(np.load(tmp_path / "sym.npy"), want)
+    assert list(np.load(tmp_path / "found.npy")) == [len(want), len(want)]
