@@ -362,7 +362,20 @@ def main() -> None:
             d64[a:a + 4096] = ((xa - xb) ** 2).sum(dim=1).sqrt()
         d32 = np.sqrt(np.maximum(got_d2[off].astype(np.float64), 0.0))
         err = d32 - d64.cpu().numpy()
+        # the same band with correctly rounded norms (option exact_norms; not the reference's numerics)
+        sj.set_option("exact_norms", 1)
+        sj.join(eps, q_begin=q0, q_end=q0 + a_rows, capacity=a_rows * 8192)
+        got2 = sj.pairs()
+        sj.set_option("exact_norms", 0)
+        sj.row_norms_timed()
+        k2 = (got2[:, 0].astype(np.int64) << 32) | got2[:, 1].astype(np.int64)
+        inter2 = np.intersect1d(k2, kt, assume_unique=True)
+        c2 = np.bincount(got2[:, 0] - q0, minlength=a_rows)
+        ci2 = np.bincount((inter2 >> 32) - q0, minlength=a_rows)
+        un2 = c2 + ct - ci2
+        iou2 = np.where(un2 > 0, ci2 / np.maximum(un2, 1), 1.0)
         accuracy = {"query_rows": [int(q0), int(q0 + a_rows)], "pairs_ours": int(len(kg)), "pairs_fp64": int(len(kt)),
+                    "with_exact_norms_option": {"pairs": int(len(k2)), "mean_per_point_iou": float(iou2.mean())},
                     "mean_per_point_iou": float(iou.mean()), "min_per_point_iou": float(iou.min()),
                     "distance_error_mean": float(err.mean()) if len(err) else 0.0,
                     "distance_error_std": float(err.std()) if len(err) else 0.0,

@@ -100,6 +100,7 @@ struct fasted_ctx {
     int band_tiles = 16;
     int grid = 0;
     int cta_pair = 0;  // 1: CTA-pair kernel (256 x 256 tiles on 2-CTA clusters)
+    int exact_norms = 0;  // 1: correctly rounded norms instead of the reference's round-toward-zero chain
     int max_pair_clusters = 0;
 };
 
@@ -223,7 +224,9 @@ int fasted_create(int device, fasted_ctx** out) {
         return fail(FASTED_ECUDA, "cudaMalloc of counters failed");
     }
     cudaFuncSetAttribute(fasted::join_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, fasted::kJoinSmemBytes);
-    cudaFuncSetAttribute(fasted::row_norms_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaFuncSetAttribute(fasted::row_norms_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         fasted::kNormSmemBytes);
+    cudaFuncSetAttribute(fasted::row_norms_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          fasted::kNormSmemBytes);
     cudaFuncSetAttribute(fasted::join_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          fasted::kPairSmemBytes);
@@ -286,6 +289,10 @@ int fasted_set_option(fasted_ctx* c, const char* name, int64_t value) {
     if (!strcmp(name, "band_tiles")) {
         if (value < 1 || value > 4096) return fail(FASTED_EINVAL, "band_tiles out of range");
         c->band_tiles = static_cast<int>(value);
+    } else if (!strcmp(name, "exact_norms")) {
+        if (value != 0 && value != 1) return fail(FASTED_EINVAL, "exact_norms must be 0 or 1");
+        c->exact_norms = static_cast<int>(value);
+        c->norms_valid = false;
     } else if (!strcmp(name, "cta_pair")) {
         if (value != 0 && value != 1) return fail(FASTED_EINVAL, "cta_pair must be 0 or 1");
         c->cta_pair = static_cast<int>(value);
@@ -412,8 +419,12 @@ static int launch_norms(fasted_ctx* c) {
     const int row_blocks = static_cast<int>((c->n + fasted::kNormRows - 1) / fasted::kNormRows);
     const int k_boxes = static_cast<int>((c->d + fasted::kTileK - 1) / fasted::kTileK);
     const int grid = std::min(row_blocks, c->num_sms * 3);
-    fasted::row_norms_kernel<<<grid, fasted::kNormRows, fasted::kNormSmemBytes, c->stream>>>(
-        c->map_a, c->norms, static_cast<int>(c->n), k_boxes, row_blocks, c->counters + 2);
+    if (c->exact_norms)
+        fasted::row_norms_kernel<true><<<grid, fasted::kNormRows, fasted::kNormSmemBytes, c->stream>>>(
+            c->map_a, c->norms, static_cast<int>(c->n), k_boxes, row_blocks, c->counters + 2);
+    else
+        fasted::row_norms_kernel<false><<<grid, fasted::kNormRows, fasted::kNormSmemBytes, c->stream>>>(
+            c->map_a, c->norms, static_cast<int>(c->n), k_boxes, row_blocks, c->counters + 2);
     CU_TRY(cudaGetLastError());
     return FASTED_OK;
 }
@@ -816,7 +827,7 @@ int static_scratch_setup(int device, unsigned char** out) {
         CU_TRY(cudaGetSymbolAddress(&addr, g_static_scratch));
         CU_TRY(cudaFuncSetAttribute(fasted::join_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     fasted::kJoinSmemBytes));
-        CU_TRY(cudaFuncSetAttribute(fasted::row_norms_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        CU_TRY(cudaFuncSetAttribute(fasted::row_norms_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     fasted::kNormSmemBytes));
         g_static_scratch_addr[device] = static_cast<unsigned char*>(addr);
     }
@@ -900,7 +911,7 @@ int fasted_join_static_scratch(const void* points_dev, int64_t n, int64_t d, int
     // (the norms are overwritten for rows [0, n) before the join reads them).
     CU_TRY(cudaMemsetAsync(counters, 0, kStaticCounterBytes, st));
     const int row_blocks = static_cast<int>((n + fasted::kNormRows - 1) / fasted::kNormRows);
-    fasted::row_norms_kernel<<<std::min(row_blocks, num_sms * 3), fasted::kNormRows, fasted::kNormSmemBytes, st>>>(
+    fasted::row_norms_kernel<false><<<std::min(row_blocks, num_sms * 3), fasted::kNormRows, fasted::kNormSmemBytes, st>>>(
         map_a, norms, static_cast<int>(n), p.k_steps, row_blocks, counters + 2);
     CU_TRY(cudaGetLastError());
     fasted::join_kernel<<<grid, fasted::kJoinThreads, fasted::kJoinSmemBytes, st>>>(map_a, map_b, p);

@@ -3,6 +3,7 @@
 //   row_norms_kernel   FP16 rows -> FP32 squared norms (HBM-bound, TMA-staged)
 //   join_kernel        persistent TMA + tcgen05.mma pipeline with the fused
 //                      distance / threshold / pair-compaction epilogue
+//   join_pair_kernel   the same on CTA pairs (tcgen05 cta_group::2), optional
 //   unpack_pairs_kernel, gen_exponential_kernel, brute_f64_kernel  (helpers)
 #pragma once
 
@@ -48,7 +49,7 @@ constexpr unsigned long long kErrNormWait = 8ull;
 
 struct JoinParams {
     const float* norms;            // [n] row norms
-    unsigned long long* counters;  // [0] pairs found, [1] pairs stored, [2] status bits
+    unsigned long long* counters;  // [0] pairs found, [1] unused (stored = min(found, capacity)), [2] status bits
     unsigned long long* keys;      // pair buffer: (query << 32) | candidate
     float* dist2;                  // optional squared distances, parallel to keys (may be null)
     unsigned long long capacity;   // pair buffer capacity
@@ -166,6 +167,12 @@ constexpr uint32_t kNormBoxBytes = kNormRows * kTileK * 2;
 constexpr uint32_t kNormStageBytes = kNormBoxBytes * kNormBoxesPerStage;
 constexpr int kNormSmemBytes = kNormStages * kNormStageBytes + 1024 + 64;
 
+// kExact = false: the reference's chain above.  kExact = true (an option, not the reference's
+// numerics): the same squares summed in FP64 and rounded once to FP32, i.e. the correctly rounded
+// norm, which matches the near-exact accumulation of tcgen05.mma better than the chain's
+// round-toward-zero bias does (the chain exists to match the truncating accumulate of the
+// reference's A100).
+template <bool kExact>
 __global__ void __launch_bounds__(kNormRows)
 row_norms_kernel(const __grid_constant__ CUtensorMap map, float* __restrict__ norms, int n, int k_boxes,
                  int row_blocks, unsigned long long* __restrict__ status) {
@@ -208,13 +215,17 @@ row_norms_kernel(const __grid_constant__ CUtensorMap map, float* __restrict__ no
     }
 
     float acc = 0.0f;
+    double acc64 = 0.0;
     bool ok = true;
     for (long long item = 0; item < total_items; ++item) {
         const int blk = static_cast<int>(item / steps_per_block);
         const int step = static_cast<int>(item - static_cast<long long>(blk) * steps_per_block);
         const int s = static_cast<int>(item % kNormStages);
         const uint32_t parity = static_cast<uint32_t>((item / kNormStages) & 1);
-        if (step == 0) acc = 0.0f;
+        if (step == 0) {
+            acc = 0.0f;
+            acc64 = 0.0;
+        }
         ok = ptx::mbar_wait_bounded(bars + 8 * s, parity, &abort_flag, kWaitLimitNs);
         if (!ok) break;
         const int nb = min(kNormBoxesPerStage, k_boxes - step * kNormBoxesPerStage);
@@ -228,13 +239,19 @@ row_norms_kernel(const __grid_constant__ CUtensorMap map, float* __restrict__ no
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
-                    acc = __fadd_rz(acc, __fadd_rz(f.x * f.x, f.y * f.y));
+                    if constexpr (kExact) {
+                        // f.x^2 + f.y^2 is formed exactly in FP64 (22-bit products), then accumulated.
+                        acc64 += static_cast<double>(f.x) * static_cast<double>(f.x) +
+                                 static_cast<double>(f.y) * static_cast<double>(f.y);
+                    } else {
+                        acc = __fadd_rz(acc, __fadd_rz(f.x * f.x, f.y * f.y));
+                    }
                 }
             }
         }
         if (step == steps_per_block - 1) {
             const int r = (static_cast<int>(blockIdx.x) + blk * static_cast<int>(gridDim.x)) * kNormRows + tid;
-            if (r < n) norms[r] = acc;
+            if (r < n) norms[r] = kExact ? static_cast<float>(acc64) : acc;
         }
         __syncthreads();  // every thread is done with stage s
         if (tid == 0 && item + kNormStages < total_items) issue(item + kNormStages);
@@ -556,7 +573,7 @@ join_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         const int quarter = warp & 3;               // TMEM lane quarter this warp may access
         const int col_off = ((warp - 2) >> 2) * kEpiCols;  // this warp's share of the tile's columns
         const int row_in_tile = quarter * 32 + lane;
-        const int epi_tid = threadIdx.x - 64;       // 0..127
+        const int epi_tid = threadIdx.x - 64;       // 0..255
         const float inf = __int_as_float(0x7f800000);
         bool ok = true;
         long long it = 0;

@@ -270,7 +270,9 @@ int fasted_tile_schedule(int64_t n, int64_t q_begin, int64_t q_end, int tile_m, 
 /* Tuning knobs: "band_tiles" (128-row tile rows per raster band, default 16), "grid" (CTAs,
  * 0 = one per SM), "cta_pair" (1 = the CTA-pair kernel: 256 x 256 tiles computed by two CTAs with
  * tcgen05 cta_group::2; same results bit for bit; default 0 because it sustains less under the
- * power cap on B200). */
+ * power cap on B200), "exact_norms" (1 = correctly rounded row norms (FP64 sum, one rounding)
+ * instead of the reference's round-toward-zero chain: NOT the reference's numerics, but closer to an
+ * FP64 join on this hardware, whose tensor-core accumulate does not truncate; default 0). */
 int fasted_set_option(fasted_ctx* ctx, const char* name, int64_t value);
 
 #ifdef __cplusplus

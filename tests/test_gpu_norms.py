@@ -50,3 +50,20 @@ def test_norms_large_property(gpu_join):
     want = (f * f).sum(axis=1)
     rel = (want - got) / want
     assert (rel > -1e-7).all() and (rel < 512 * 2.0 ** -23).all()
+
+
+def test_exact_norms_option_is_correctly_rounded(gpu_join, oracle_mod):
+    # Opt-in mode (not the reference's numerics): FP64 sum of the exact squares, one rounding.
+    rng = np.random.default_rng(9)
+    pts = oracle_mod.double_to_half(rng.exponential(1 / 40.0, size=(700, 1000)))
+    gpu_join.set_points(pts)
+    try:
+        gpu_join.set_option("exact_norms", 1)
+        got, _ = gpu_join.row_norms()
+    finally:
+        gpu_join.set_option("exact_norms", 0)
+    f = pts.view(np.float16).astype(np.float64)
+    want = (f * f).sum(axis=1).astype(np.float32)
+    assert np.array_equal(got, want)
+    ref, _ = gpu_join.row_norms()
+    assert np.array_equal(ref, oracle_mod.row_norms(pts)) and (ref <= got).all() and (ref < got).any()
