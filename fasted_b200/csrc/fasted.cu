@@ -224,9 +224,9 @@ int fasted_create(int device, fasted_ctx** out) {
         return fail(FASTED_ECUDA, "cudaMalloc of counters failed");
     }
     cudaFuncSetAttribute(fasted::join_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, fasted::kJoinSmemBytes);
-    cudaFuncSetAttribute(fasted::row_norms_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaFuncSetAttribute(fasted::row_norms_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          fasted::kNormSmemBytes);
-    cudaFuncSetAttribute(fasted::row_norms_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaFuncSetAttribute(fasted::row_norms_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          fasted::kNormSmemBytes);
     cudaFuncSetAttribute(fasted::join_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          fasted::kPairSmemBytes);
@@ -420,10 +420,10 @@ static int launch_norms(fasted_ctx* c) {
     const int k_boxes = static_cast<int>((c->d + fasted::kTileK - 1) / fasted::kTileK);
     const int grid = std::min(row_blocks, c->num_sms * 3);
     if (c->exact_norms)
-        fasted::row_norms_kernel<true><<<grid, fasted::kNormRows, fasted::kNormSmemBytes, c->stream>>>(
+        fasted::row_norms_kernel<1><<<grid, fasted::kNormRows, fasted::kNormSmemBytes, c->stream>>>(
             c->map_a, c->norms, static_cast<int>(c->n), k_boxes, row_blocks, c->counters + 2);
     else
-        fasted::row_norms_kernel<false><<<grid, fasted::kNormRows, fasted::kNormSmemBytes, c->stream>>>(
+        fasted::row_norms_kernel<0><<<grid, fasted::kNormRows, fasted::kNormSmemBytes, c->stream>>>(
             c->map_a, c->norms, static_cast<int>(c->n), k_boxes, row_blocks, c->counters + 2);
     CU_TRY(cudaGetLastError());
     return FASTED_OK;
@@ -827,7 +827,7 @@ int static_scratch_setup(int device, unsigned char** out) {
         CU_TRY(cudaGetSymbolAddress(&addr, g_static_scratch));
         CU_TRY(cudaFuncSetAttribute(fasted::join_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     fasted::kJoinSmemBytes));
-        CU_TRY(cudaFuncSetAttribute(fasted::row_norms_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        CU_TRY(cudaFuncSetAttribute(fasted::row_norms_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     fasted::kNormSmemBytes));
         g_static_scratch_addr[device] = static_cast<unsigned char*>(addr);
     }
@@ -911,7 +911,7 @@ int fasted_join_static_scratch(const void* points_dev, int64_t n, int64_t d, int
     // (the norms are overwritten for rows [0, n) before the join reads them).
     CU_TRY(cudaMemsetAsync(counters, 0, kStaticCounterBytes, st));
     const int row_blocks = static_cast<int>((n + fasted::kNormRows - 1) / fasted::kNormRows);
-    fasted::row_norms_kernel<false><<<std::min(row_blocks, num_sms * 3), fasted::kNormRows, fasted::kNormSmemBytes, st>>>(
+    fasted::row_norms_kernel<0><<<std::min(row_blocks, num_sms * 3), fasted::kNormRows, fasted::kNormSmemBytes, st>>>(
         map_a, norms, static_cast<int>(n), p.k_steps, row_blocks, counters + 2);
     CU_TRY(cudaGetLastError());
     fasted::join_kernel<<<grid, fasted::kJoinThreads, fasted::kJoinSmemBytes, st>>>(map_a, map_b, p);

@@ -172,7 +172,11 @@ constexpr int kNormSmemBytes = kNormStages * kNormStageBytes + 1024 + 64;
 // norm, which matches the near-exact accumulation of tcgen05.mma better than the chain's
 // round-toward-zero bias does (the chain exists to match the truncating accumulate of the
 // reference's A100).
-template <bool kExact>
+// (Measured at D = 4096, |p|^2 ~ 5.1: d2(i,i) is -2.3e-4 with the chain and +2.3e-4 with exact norms, so
+// tcgen05.mma's accumulate does lose low bits, about as much as the chain, in the other direction for
+// d2.  A chain truncated once per 16-wide slice leaves +1.8e-4, so it is not a simple per-instruction
+// truncation and no norm variant cancels it exactly.)
+template <int kExact>
 __global__ void __launch_bounds__(kNormRows)
 row_norms_kernel(const __grid_constant__ CUtensorMap map, float* __restrict__ norms, int n, int k_boxes,
                  int row_blocks, unsigned long long* __restrict__ status) {
@@ -239,7 +243,7 @@ row_norms_kernel(const __grid_constant__ CUtensorMap map, float* __restrict__ no
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
-                    if constexpr (kExact) {
+                    if constexpr (kExact != 0) {
                         // f.x^2 + f.y^2 is formed exactly in FP64 (22-bit products), then accumulated.
                         acc64 += static_cast<double>(f.x) * static_cast<double>(f.x) +
                                  static_cast<double>(f.y) * static_cast<double>(f.y);
@@ -251,7 +255,7 @@ row_norms_kernel(const __grid_constant__ CUtensorMap map, float* __restrict__ no
         }
         if (step == steps_per_block - 1) {
             const int r = (static_cast<int>(blockIdx.x) + blk * static_cast<int>(gridDim.x)) * kNormRows + tid;
-            if (r < n) norms[r] = kExact ? static_cast<float>(acc64) : acc;
+            if (r < n) norms[r] = kExact == 1 ? static_cast<float>(acc64) : acc;
         }
         __syncthreads();  // every thread is done with stage s
         if (tid == 0 && item + kNormStages < total_items) issue(item + kNormStages);
