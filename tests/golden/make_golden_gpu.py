@@ -69,18 +69,24 @@ CASES = [
     ("gauss_unit_3000x384", "gauss_unit", 3000, 384, 1.27),
     ("clusters_1500x96", "clusters", 1500, 96, 0.9),
     ("exp_777x333", "exp", 777, 333, 0.5),
+    ("exp_2000x4096", "exp", 2000, 4096, 2.178),
 ]
 
 
 def main(out_dir: str, timing_only: bool = False) -> None:
     os.makedirs(out_dir, exist_ok=True)
+    only = [a.split("=", 1)[1] for a in sys.argv if a.startswith("--only=")]
     for name, kind, n, d, eps in ([] if timing_only else CASES):
+        if only and name not in only:
+            continue
         pts = dataset(kind, n, d)
         r = run_ref(pts, eps)
         np.savez_compressed(os.path.join(out_dir, f"ref_gpu_{name}.npz"), n=n, d=d, epsilon=eps, kind=kind,
                             pairs_found=r["found"], pairs=r["pairs"],
                             dataset_fnv1a64=np.uint64(oracle.fnv1a64_u16(pts)))
         print(name, "found", r["found"], "stored", r["stored"], flush=True)
+    if only:
+        return
     timing = []
     for n, d in [(21544, 4096), (46416, 4096), (100000, 4096)]:
         pts = oracle.double_to_half(np.random.default_rng(1).exponential(1 / 40.0, size=(n, d)))
