@@ -467,9 +467,10 @@ def main() -> None:
             "gpu_launches": 2 * args.steps,
             "roofline": {"bound": "tensor", "kernel": "join_kernel", "achieved": achieved, "peak": peak,
                          "unit": "TFLOP/s", "frac": achieved / peak if peak else None,
-                         # DRAM bytes per launch: ncu measured 17.09 GB on the 65,536 x 4096 case = one pass over
-                         # the candidates per band of 16 tile rows; scaled by that rule to this launch.
-                         "traffic": float(-(-(-(-band_rows // 128)) // 16) * n * ld * 2 + band_rows * ld * 2),
+                         # DRAM bytes per launch: ncu measured one pass over the candidates per raster band
+                         # (17.09 GB at 16 tile rows per band, 8.55 GB at 32, on 65,536 x 4096); scaled by that
+                         # rule to this launch (bands of 16 tile rows).
+                         "traffic": float(-(-(-(-band_rows // 128)) // (args.band_tiles or 16)) * n * ld * 2 + band_rows * ld * 2),
                          "traffic_source": "ncu dram__bytes_read.sum of a 65536 x 4096 launch, scaled by bands x N*D*2",
                          "peak_source": f"{peaks['source']} cuBLAS bf16 "
                                         f"({'sustained' if float(np.mean(join_ms)) > 500.0 else 'burst'})",

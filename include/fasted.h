@@ -267,7 +267,7 @@ int fasted_tile_schedule(int64_t n, int64_t q_begin, int64_t q_end, int tile_m, 
                          int shard_rank, int shard_world, int grid, int cta, int32_t* tiles_out, int64_t max_tiles,
                          int64_t* count_out);
 
-/* Tuning knobs: "band_tiles" (128-row tile rows per raster band, default 16), "grid" (CTAs,
+/* Tuning knobs: "band_tiles" (128-row tile rows per raster band, 0 = automatic: 16, fewer for rows wider than 8 KB), "grid" (CTAs,
  * 0 = one per SM), "cta_pair" (1 = the CTA-pair kernel: 256 x 256 tiles computed by two CTAs with
  * tcgen05 cta_group::2; same results bit for bit; default 0 because it sustains less under the
  * power cap on B200), "exact_norms" (1 = correctly rounded row norms (FP64 sum, one rounding)

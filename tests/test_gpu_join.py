@@ -247,9 +247,10 @@ def test_join_against_reference_gpu_output(gpu_join, oracle_mod, path):
     gpu_join.set_points(pts)
     st = gpu_join.join(eps)
     got = gpu_join.pairs()
-    cmp = assert_pairs_match(oracle_mod, pts, d, eps, got, g["pairs"], BAND, "vs reference GPU output")
-    assert cmp["only_a"] + cmp["only_b"] <= max(8, len(g["pairs"]) // 2000)
-    assert abs(int(st.pairs_found) - int(g["pairs_found"])) <= max(8, len(g["pairs"]) // 2000)
+    # On a B200 the reference's mma.sync kernels and this library's tcgen05 kernels accumulate alike:
+    # the outputs are identical, pair for pair (the band is not needed here).
+    assert int(st.pairs_found) == int(g["pairs_found"])
+    assert np.array_equal(got, g["pairs"])
 
 
 @pytest.mark.parametrize("n,d,eps", [(256, 64, 1e3), (300, 100, 1e3), (1000, 256, 0.5), (2000, 512, 0.7),
@@ -377,7 +378,7 @@ def test_symmetric_shards_union_is_the_full_join(gpu_join, oracle_mod, n, d, eps
             assert (np.diff(k.astype(np.int64)) > 0).all()
             parts.append(k)
     finally:
-        gpu_join.set_option("band_tiles", 16)
+        gpu_join.set_option("band_tiles", 0)
     allk = np.concatenate(parts)
     assert len(np.unique(allk)) == len(allk) == len(want)
     assert np.array_equal(np.sort(allk), want)
