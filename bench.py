@@ -45,6 +45,7 @@ WORKLOADS = {
     "c1": dict(n=4096, d=128, dist="exp", target=32, eps=0.3136),
     "c2": dict(n=100_000, d=384, dist="unit_gauss", target=16, eps=None),
     "c3": dict(n=1_000_000, d=4096, dist="exp", target=64, eps=None),
+    "c4": dict(n=2_000_000, d=1024, dist="mixture", target=2000, eps=None, pairs_per_point=2600),
     "c5": dict(n=4_000_000, d=2048, dist="exp", target=8, eps=None),
 }
 SEED = 2137834274  # the reference's dataset seed
@@ -125,6 +126,10 @@ def make_host_sample(wl: dict, rows: int) -> np.ndarray:
     elif wl["dist"] == "unit_gauss":
         x = rng.standard_normal((rows, d))
         x /= np.linalg.norm(x, axis=1, keepdims=True)
+    elif wl["dist"] == "mixture":
+        centres = rng.uniform(0.0, 1.0, size=(256, d))
+        w = 1.0 / np.arange(1, 257) ** 1.1
+        x = centres[rng.choice(256, size=rows, p=w / w.sum())] + rng.normal(0.0, 0.05, size=(rows, d))
     else:
         raise ValueError(wl["dist"])
     return x.astype(np.float32).astype(np.float16).view(np.uint16)
@@ -248,6 +253,23 @@ def main() -> None:
                 x = torch.randn((min(65536, n - a), d), generator=g, device="cuda", dtype=torch.float32)
                 x /= x.norm(dim=1, keepdim=True)
                 dev_pts[a:a + x.shape[0], :d] = x.to(torch.float16)
+        elif wl["dist"] == "mixture":
+            # 256 centres ~ U[0,1]^D, cluster sizes ~ Zipf(1.1) over ranks 1..256 (largest remainder
+            # rounding to sum N), point = centre + N(0, 0.05^2) per coordinate, points of a cluster contiguous
+            g = torch.Generator(device="cuda").manual_seed(SEED)
+            centres = torch.rand((256, d), generator=g, device="cuda", dtype=torch.float32)
+            w = 1.0 / np.arange(1, 257) ** 1.1
+            exact = w / w.sum() * n
+            sizes = np.floor(exact).astype(np.int64)
+            for i in np.argsort(-(exact - sizes))[: n - int(sizes.sum())]:
+                sizes[i] += 1
+            a = 0
+            for cid, sz in enumerate(sizes):
+                for b in range(0, int(sz), 65536):
+                    m = min(65536, int(sz) - b)
+                    x = centres[cid] + 0.05 * torch.randn((m, d), generator=g, device="cuda", dtype=torch.float32)
+                    dev_pts[a:a + m, :d] = x.to(torch.float16)
+                    a += m
     if world > 1:
         dist.broadcast(dev_pts.view(torch.uint8), src=0)
     torch.cuda.synchronize()
@@ -266,7 +288,7 @@ def main() -> None:
             t = torch.tensor([eps if rank == 0 else 0.0], dtype=torch.float64, device="cuda")
             dist.broadcast(t, src=0)
             eps = float(t.item())
-    capacity = max(1, band_rows) * 256
+    capacity = max(1, band_rows) * int(wl.get("pairs_per_point", 256))
 
     # ---- timed region 1: dataset resident, device-timed -----------------------------------------
     def step_resident():

@@ -54,7 +54,7 @@ DECLARED_SYMBOLS = [
     "fasted_set_points_host_f16", "fasted_set_points_device_f16", "fasted_generate_exponential",
     "fasted_fill_exponential_device",
     "fasted_points_info", "fasted_get_points_host_f16", "fasted_get_rows_host_f16", "fasted_row_norms", "fasted_get_norms",
-    "fasted_join", "fasted_join_symmetric_shard", "fasted_tile_schedule", "fasted_estimate_epsilon", "fasted_get_pairs", "fasted_pairs_device", "fasted_brute_force_f64", "fasted_brute_force_f64_pairs", "fasted_set_option",
+    "fasted_join", "fasted_selftest_wait_timeout", "fasted_join_symmetric_shard", "fasted_tile_schedule", "fasted_estimate_epsilon", "fasted_get_pairs", "fasted_pairs_device", "fasted_brute_force_f64", "fasted_brute_force_f64_pairs", "fasted_set_option",
     "fasted_dataset_exponential_f16", "fasted_dataset_csv_shape", "fasted_dataset_csv_f16",
     "fasted_join_static_scratch",
 ]
@@ -92,6 +92,8 @@ def load() -> ctypes.CDLL:
                                        ctypes.c_int, ctypes.c_int, ctypes.c_int, _vp, _i64, ctypes.POINTER(_i64)]
     L.fasted_join_symmetric_shard.argtypes = [_vp, ctypes.c_double, ctypes.c_int, ctypes.c_int, _u64, ctypes.c_uint,
                                               ctypes.POINTER(JoinStats)]
+    L.fasted_selftest_wait_timeout.argtypes = [_vp, ctypes.c_double, ctypes.POINTER(ctypes.c_ulonglong),
+                                               ctypes.POINTER(ctypes.c_double)]
     L.fasted_estimate_epsilon.argtypes = [_vp, ctypes.c_double, _i64, ctypes.c_double, ctypes.POINTER(ctypes.c_double),
                                           ctypes.POINTER(ctypes.c_double)]
     L.fasted_get_pairs.argtypes = [_vp, _u64, _u64, _vp, _vp]
@@ -304,6 +306,13 @@ class SelfJoin:
         k = np.sort(keys[: nk.value])
         pairs = np.stack([(k >> np.uint64(32)).astype(np.int32), (k & np.uint64(0xFFFFFFFF)).astype(np.int32)], 1)
         return counts, pairs
+
+    def selftest_wait_timeout(self, limit_ms: float) -> tuple[int, float]:
+        """(status bits, milliseconds waited) of the bounded-wait self-test kernel."""
+        status, waited = ctypes.c_ulonglong(), ctypes.c_double()
+        _check(self._L.fasted_selftest_wait_timeout(self._h, float(limit_ms), ctypes.byref(status),
+                                                    ctypes.byref(waited)))
+        return int(status.value), waited.value
 
     def set_option(self, name: str, value: int) -> None:
         _check(self._L.fasted_set_option(self._h, name.encode(), value))

@@ -682,6 +682,22 @@ int fasted_tile_schedule(int64_t n, int64_t q_begin, int64_t q_end, int tile_m, 
     return FASTED_OK;
 }
 
+int fasted_selftest_wait_timeout(fasted_ctx* c, double limit_ms, unsigned long long* status_out, double* waited_ms_out) {
+    if (!c || !status_out) return fail(FASTED_EINVAL, "null argument");
+    if (!(limit_ms > 0) || limit_ms > 1000.0) return fail(FASTED_EINVAL, "limit must be in (0, 1000] ms");
+    CU_TRY(cudaSetDevice(c->device));
+    CU_TRY(cudaMemsetAsync(c->counters, 0, 8 * sizeof(unsigned long long), c->stream));
+    fasted::wait_timeout_selftest_kernel<<<1, 32, 0, c->stream>>>(static_cast<unsigned long long>(limit_ms * 1e6),
+                                                                 c->counters + 2, c->counters + 3);
+    CU_TRY(cudaGetLastError());
+    unsigned long long h[2] = {0, 0};
+    CU_TRY(cudaMemcpyAsync(h, c->counters + 2, sizeof(h), cudaMemcpyDeviceToHost, c->stream));
+    CU_TRY(cudaStreamSynchronize(c->stream));
+    *status_out = h[0];
+    if (waited_ms_out) *waited_ms_out = static_cast<double>(h[1]) / 1e6;
+    return FASTED_OK;
+}
+
 int fasted_estimate_epsilon(fasted_ctx* c, double target_mean_neighbours, int64_t sample_rows, double rel_tol,
                             double* eps_out, double* achieved_out) {
     if (!c || !eps_out) return fail(FASTED_EINVAL, "null argument");

@@ -859,6 +859,34 @@ join_pair_kernel(const __grid_constant__ CUtensorMap map, const JoinParams p) {
 }
 
 // ---------------------------------------------------------------------------
+// Self-test of the bounded wait
+// ---------------------------------------------------------------------------
+//
+// Waits, with the given limit, on an mbarrier that nothing will ever complete, the way a join
+// role would wait for a peer that never answers.  The wait must give up after the limit, raise the
+// CTA's abort flag, record its status bit and let the kernel return normally: no trap, no hang,
+// the context stays usable.  Thread 1 waits on the same barrier and must leave through the abort
+// flag raised by thread 0's timeout (or its own).
+__global__ void wait_timeout_selftest_kernel(unsigned long long limit_ns, unsigned long long* status,
+                                             unsigned long long* waited_ns) {
+    __shared__ unsigned long long bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        ptx::mbar_init(ptx::smem_u32(&bar), 1);
+        ptx::fence_mbar_init();
+    }
+    __syncthreads();
+    if (threadIdx.x < 2) {
+        const uint64_t t0 = ptx::globaltimer_ns();
+        const bool ok = ptx::mbar_wait_bounded(ptx::smem_u32(&bar), 0, &abort_flag, limit_ns);
+        const uint64_t t1 = ptx::globaltimer_ns();
+        if (!ok) atomicOr(status, threadIdx.x == 0 ? kErrProducerWait : kErrMmaWait);
+        if (threadIdx.x == 0) *waited_ns = t1 - t0;
+    }
+}
+
+// ---------------------------------------------------------------------------
 // Helpers
 // ---------------------------------------------------------------------------
 

@@ -267,6 +267,14 @@ int fasted_tile_schedule(int64_t n, int64_t q_begin, int64_t q_end, int tile_m, 
                          int shard_rank, int shard_world, int grid, int cta, int32_t* tiles_out, int64_t max_tiles,
                          int64_t* count_out);
 
+/* Self-test of the failure path every device-side wait of this library has: a one-block kernel
+ * waits, with a limit of limit_ms (at most 1000), on a barrier that nothing completes.  The wait
+ * must give up, the kernel must return normally, *status_out must carry the wait's status bits
+ * (non-zero), and the context must stay usable.  Nothing faults, traps or hangs.  (The reference
+ * has no counterpart: its CUDA errors exit the process, source/utils.cuh:22-29.) */
+int fasted_selftest_wait_timeout(fasted_ctx* ctx, double limit_ms, unsigned long long* status_out,
+                                 double* waited_ms_out);
+
 /* Tuning knobs: "band_tiles" (128-row tile rows per raster band, 0 = automatic: 16, fewer for rows wider than 8 KB), "grid" (CTAs,
  * 0 = one per SM), "cta_pair" (1 = the CTA-pair kernel: 256 x 256 tiles computed by two CTAs with
  * tcgen05 cta_group::2; same results bit for bit; default 0 because it sustains less under the
