@@ -186,6 +186,18 @@ void free_pair_buffers(fasted_ctx* c) {
     c->result_dist = nullptr;
 }
 
+// Device memory for a new dataset.  Pair buffers only ever grow, so if the dataset does not fit
+// beside them they are released (the next join sizes them again) and the allocation is retried.
+cudaError_t alloc_points(fasted_ctx* c, __half** dev, size_t bytes) {
+    cudaError_t e = cudaMalloc(dev, bytes);
+    if (e == cudaErrorMemoryAllocation && c->capacity > 0) {
+        cudaGetLastError();
+        free_pair_buffers(c);
+        e = cudaMalloc(dev, bytes);
+    }
+    return e;
+}
+
 int ensure_pair_buffers(fasted_ctx* c, uint64_t capacity, bool want_dist) {
     // Buffers only grow: probes with a tiny capacity (epsilon search) must not throw away the
     // buffers of the full join that follows.
@@ -328,7 +340,7 @@ int fasted_set_points_host_f16(fasted_ctx* c, const uint16_t* host, int64_t n, i
     release_points(c);
     const int64_t ld = (d + fasted::kTileK - 1) / fasted::kTileK * fasted::kTileK;
     __half* dev = nullptr;
-    CU_TRY(cudaMalloc(&dev, static_cast<size_t>(n) * ld * 2));
+    CU_TRY(alloc_points(c, &dev, static_cast<size_t>(n) * ld * 2));
     cudaError_t e = cudaSuccess;
     if (ld != d) e = cudaMemsetAsync(dev, 0, static_cast<size_t>(n) * ld * 2, c->stream);
     if (e == cudaSuccess)
@@ -364,7 +376,7 @@ int fasted_generate_exponential(fasted_ctx* c, int64_t n, int64_t d, double lamb
     release_points(c);
     const int64_t ld = (d + fasted::kTileK - 1) / fasted::kTileK * fasted::kTileK;
     __half* dev = nullptr;
-    CU_TRY(cudaMalloc(&dev, static_cast<size_t>(n) * ld * 2));
+    CU_TRY(alloc_points(c, &dev, static_cast<size_t>(n) * ld * 2));
     fasted::gen_exponential_kernel<<<c->num_sms * 8, 256, 0, c->stream>>>(dev, n, static_cast<int>(d),
                                                                           static_cast<int>(ld), lambda, max_value, seed);
     cudaError_t e = cudaGetLastError();
