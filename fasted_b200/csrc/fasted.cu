@@ -493,7 +493,9 @@ static int join_impl(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end, 
     if (q_begin < 0 || q_begin > q_end || q_end > c->n)
         return fail(FASTED_EINVAL, "query band [%lld, %lld) outside [0, %lld)", (long long)q_begin, (long long)q_end,
                     (long long)c->n);
-    if (!(eps >= 0.0)) return fail(FASTED_EINVAL, "epsilon must be >= 0");
+    // Only eps*eps is used, as in the reference (source/findPairs.cuh:678): a negative epsilon
+    // means the same as its absolute value; NaN is refused.
+    if (eps != eps) return fail(FASTED_EINVAL, "epsilon is NaN");
     CU_TRY(cudaSetDevice(c->device));
     const bool want_dist = (flags & FASTED_JOIN_DIST2) != 0;
 
@@ -906,7 +908,7 @@ int fasted_join_static_scratch(const void* points_dev, int64_t n, int64_t d, int
     if (ld < d || (ld % 8) != 0) return fail(FASTED_EINVAL, "ld (%lld) must be >= d and a multiple of 8", (long long)ld);
     if (reinterpret_cast<uintptr_t>(points_dev) % 16 != 0) return fail(FASTED_EINVAL, "points must be 16-byte aligned");
     if (reinterpret_cast<uintptr_t>(keys_out_dev) % 8 != 0) return fail(FASTED_EINVAL, "keys_out_dev must be 8-byte aligned");
-    if (!(eps >= 0.0)) return fail(FASTED_EINVAL, "epsilon must be >= 0");
+    if (eps != eps) return fail(FASTED_EINVAL, "epsilon is NaN");
 
     int device = -1;
     CU_TRY(cudaGetDevice(&device));

@@ -197,7 +197,10 @@ def test_join_argument_errors(gpu_join, oracle_mod):
     with pytest.raises(FastedError):
         gpu_join.join(0.1, q_begin=50, q_end=200)
     with pytest.raises(FastedError):
-        gpu_join.join(-1.0)
+        gpu_join.join(float("nan"))
+    # only eps^2 enters the test, as in the reference: a negative epsilon equals its absolute value
+    a = gpu_join.join(0.3).pairs_found
+    assert gpu_join.join(-0.3).pairs_found == a
     with pytest.raises(FastedError):
         gpu_join.set_points(np.zeros((0, 64), dtype=np.uint16))
 
@@ -384,3 +387,24 @@ def test_symmetric_shards_union_is_the_full_join(gpu_join, oracle_mod, n, d, eps
     assert np.array_equal(np.sort(allk), want)
     sizes = [len(p) for p in parts]
     assert min(sizes) > 0
+
+
+def test_join_tiny_shapes(gpu_join, oracle_mod):
+    # one point, one dimension, duplicates: the smallest inputs the interface accepts
+    one = oracle_mod.double_to_half(np.array([[0.25]]))
+    gpu_join.set_points(one)
+    st = gpu_join.join(0.0)
+    assert st.pairs_found == 1 and gpu_join.pairs().tolist() == [[0, 0]]
+    two = oracle_mod.double_to_half(np.array([[0.5, 0.125, 0.0], [0.5, 0.125, 0.0]]))
+    gpu_join.set_points(two)
+    assert gpu_join.join(0.0).pairs_found == 4
+    assert gpu_join.pairs().tolist() == [[0, 0], [0, 1], [1, 0], [1, 1]]
+    line = oracle_mod.double_to_half(np.arange(300, dtype=np.float64).reshape(300, 1) / 64.0)
+    gpu_join.set_points(line)
+    gpu_join.join(1.0 / 64.0 + 1e-9)
+    got = gpu_join.pairs()
+    want, _ = oracle_mod.join_fp16_fp32(line, 1.0 / 64.0 + 1e-9)
+    assert np.array_equal(got, want) and len(got) == 300 + 2 * 299
+    for flags in (8,):  # the symmetric schedule on the same tiny inputs
+        gpu_join.join(1.0 / 64.0 + 1e-9, flags=flags)
+        assert np.array_equal(gpu_join.pairs(), want)
