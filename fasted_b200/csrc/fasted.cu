@@ -535,6 +535,7 @@ static int join_impl(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end, 
     p.symmetric = symmetric ? 1 : 0;
     p.shard_rank = shard_rank;
     p.shard_world = shard_world;
+    p.raw_dot = (flags & FASTED_JOIN_RAW_DOT) && want_dist ? 1 : 0;
     if (shard_world > 1 && !symmetric) return fail(FASTED_EINVAL, "band snakes are for the symmetric schedule only");
     p.tiles_m = static_cast<int>((q_end - q_begin + tile_m - 1) / tile_m);
     p.tiles_n = static_cast<int>((c->n + fasted::kTileN - 1) / fasted::kTileN);
@@ -679,6 +680,7 @@ int fasted_tile_schedule(int64_t n, int64_t q_begin, int64_t q_end, int tile_m, 
     p.symmetric = symmetric ? 1 : 0;
     p.shard_rank = shard_rank;
     p.shard_world = shard_world;
+    p.raw_dot = 0;
     if (shard_world > 1 && !symmetric) return fail(FASTED_EINVAL, "band snakes are for the symmetric schedule only");
     p.tiles_m = static_cast<int>((q_end - q_begin + tile_m - 1) / tile_m);
     p.tiles_n = static_cast<int>((n + fasted::kTileN - 1) / fasted::kTileN);
@@ -947,6 +949,7 @@ int fasted_join_static_scratch(const void* points_dev, int64_t n, int64_t d, int
     p.total_tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
     p.tile_m = fasted::kTileM;
     p.symmetric = 0;
+    p.raw_dot = 0;
     p.shard_rank = 0;
     p.shard_world = 1;
     const int grid = static_cast<int>(std::min<long long>(p.total_tiles, num_sms));

@@ -61,6 +61,7 @@ struct JoinParams {
     int band_tiles;                // tile rows per raster band
     long long total_tiles;         // upper bound of the tiles walked (grid sizing only)
     int tile_m;                    // query rows per tile (kTileM, or 2 * kTileM for CTA pairs)
+    int raw_dot;                   // 1 (diagnostic): record the raw accumulator a_ij instead of d2
     int symmetric;                 // 1: walk only tiles that touch j >= i and emit (i,j) and (j,i)
     int shard_rank, shard_world;   // symmetric mode over several GPUs: this launch takes the raster bands
                                    // r, 2G-1-r, 2G+r, 4G-1-r, ... (a snake over the G shards, which evens out
@@ -414,7 +415,8 @@ __device__ __forceinline__ void epilogue_tile(const JoinParams& p, uint32_t tadd
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
                 if ((m | r) & (1u << j)) {
-                    const float d2 = (sq + cn[ch * 32 + j]) - 2.0f * __uint_as_float(v[j]);
+                    const float d2 = p.raw_dot ? __uint_as_float(v[j])
+                                               : (sq + cn[ch * 32 + j]) - 2.0f * __uint_as_float(v[j]);
                     if (m & (1u << j)) {
                         if (slot < p.capacity) {
                             p.keys[slot] = qkey | static_cast<unsigned long long>(c0 + j);

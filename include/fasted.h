@@ -104,6 +104,9 @@ enum {
     FASTED_JOIN_DIST2 = 1,       /* also record the FP32 squared distance of every stored pair */
     FASTED_JOIN_NO_SORT = 2,     /* leave stored pairs in device order (count-only / timing runs) */
     FASTED_JOIN_KEEP_NORMS = 4,  /* reuse row norms computed by an earlier call on the same points */
+    FASTED_JOIN_RAW_DOT = 16,    /* diagnostic, with FASTED_JOIN_DIST2: the distance array receives the raw FP32
+                                    Gram entry a_ij of every stored pair instead of d2 (to study the tensor
+                                    core's accumulate) */
     FASTED_JOIN_SYMMETRIC = 8    /* full self-join only: compute each unordered pair once (d2(i,j) == d2(j,i))
                                     and emit both orientations; same output, about half the tensor work */
 };

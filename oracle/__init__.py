@@ -51,6 +51,8 @@ def lib() -> ctypes.CDLL:
         L.oracle_join_fp16_fp32.restype = _u64
         L.oracle_join_fp64.argtypes = [_vp, _i64, _i64, _i64, ctypes.c_double, _i64, _i64, _vp, _vp, _u64]
         L.oracle_join_fp64.restype = _u64
+        L.oracle_gram_matrix.argtypes = [_vp, _i64, _i64, _i64, _i64, _i64, _vp]
+        L.oracle_gram_matrix.restype = None
         L.oracle_pair_d2_fp64.argtypes = [_vp, _i64, _i64, _vp, _i64, _vp]
         L.oracle_num_threads.restype = ctypes.c_int
         _lib = L
@@ -118,6 +120,17 @@ def row_norms(pts: np.ndarray, d: int | None = None) -> np.ndarray:
     d = ld if d is None else d
     out = np.empty(n, dtype=np.float32)
     lib().oracle_row_norms(_p(pts), n, d, ld, _p(out))
+    return out
+
+
+def gram_matrix(pts: np.ndarray, d: int | None = None, r_begin: int = 0, r_end: int | None = None) -> np.ndarray:
+    """Raw FP32 Gram entries under the measured tensor-core accumulate model, rows [r_begin, r_end) x all."""
+    _check_pts(pts)
+    n, ld = pts.shape
+    d = ld if d is None else d
+    r_end = n if r_end is None else r_end
+    out = np.empty((r_end - r_begin, n), dtype=np.float32)
+    lib().oracle_gram_matrix(_p(pts), n, d, ld, r_begin, r_end, _p(out))
     return out
 
 

@@ -151,16 +151,13 @@ def _golden_dataset(oracle_mod, g):
 
 @pytest.mark.parametrize("path", _ref_gpu_cases(), ids=lambda p: os.path.basename(p)[8:-4])
 def test_oracle_against_reference_gpu_output(oracle_mod, path):
-    # Pair lists produced by the reference's own kernels (compiled unmodified, run on a B200):
-    # the restated algorithm must reproduce them outside the comparison band.
+    # Pair lists produced by the reference's own kernels (compiled unmodified, run on a B200).
     g = np.load(path)
     pts = _golden_dataset(oracle_mod, g)
     eps, d = float(g["epsilon"]), int(g["d"])
     mine, _ = oracle_mod.join_fp16_fp32(pts, eps)
     ref = g["pairs"]
     assert len(ref) == int(g["pairs_found"])
-    cmp = oracle_mod.compare_pair_sets(pts, d, eps, mine, ref, band=1e-3)
-    assert cmp["ok"], cmp
-    # Inside the band the restated Gram model (one truncation per 16-wide slice) and the hardware's
-    # accumulate may disagree; the hardware loses more low bits as D grows (0.14 % of the pairs at D = 4096).
-    assert cmp["only_a"] + cmp["only_b"] <= max(8, len(ref) // 2000, len(ref) * d // 1_000_000)
+    # With the tensor-core accumulate modelled as measured on the B200, the restatement is exact:
+    # the same pairs, in the same order, as the reference's own kernels produced on that GPU.
+    assert np.array_equal(mine, ref)

@@ -30,3 +30,13 @@ def assert_dist_close(oracle_mod, pts, d, pairs, d2, rtol=1e-3):
     # round-toward-zero adds, each losing up to one ulp of the running sum: about d/8 ulps in all.
     floor = max(4e-6, d / 8 * 2.0 ** -23) * scale
     assert (err <= rtol * want + floor).all(), float(np.max(err / (rtol * want + floor)))
+
+
+def assert_identical_to_oracle(oracle_mod, pts, d, eps, got_pairs, got_d2=None, q_begin=0, q_end=None):
+    """The CPU oracle models the B200's tensor-core accumulate bit for bit, so the CUDA path must give
+    exactly the oracle's pairs (and, when recorded, exactly its FP32 squared distances)."""
+    want, want_d2 = oracle_mod.join_fp16_fp32(pts, eps, d=d, q_begin=q_begin, q_end=q_end)
+    assert np.array_equal(got_pairs, want), (len(got_pairs), len(want))
+    if got_d2 is not None:
+        assert np.array_equal(got_d2.view(np.uint32), want_d2.view(np.uint32))
+    return want
