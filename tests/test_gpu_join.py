@@ -431,3 +431,48 @@ def test_raw_accumulators_match_the_accumulate_model(gpu_join, oracle_mod, kind,
     got[pairs[:, 0], pairs[:, 1]] = a
     want = oracle_mod.gram_matrix(pts)
     assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+def test_accumulate_rule_known_answers(gpu_join, oracle_mod):
+    # Crafted K=16 dot products that pin the rule down (each line: what it shows).
+    u = 2.0 ** -23  # one FP32 ulp at 1.0
+
+    def vec(pairs, k=16):
+        x, y = np.zeros(k), np.zeros(k)
+        for i, (a, b) in enumerate(pairs):
+            x[i], y[i] = a, b
+        return x, y
+
+    cases = [
+        # 15 products of half an ulp next to 1.0 are kept (window reaches 2 bits below the ulp): 7.5 -> 7 ulps
+        (vec([(1.0, 1.0)] + [(2.0 ** -12, 2.0 ** -12)] * 15), 1 + 7 * u),
+        # quarter-ulp products are kept too: 3.75 -> 3 ulps ...
+        (vec([(1.0, 1.0)] + [(2.0 ** -12, 2.0 ** -13)] * 15), 1 + 3 * u),
+        # ... eighth-ulp products fall out of the window one by one: 1.875 ulps vanish
+        (vec([(1.0, 1.0)] + [(2.0 ** -13, 2.0 ** -13)] * 15), 1.0),
+        # the window hangs on the exponent SUM of the operands: 1.5 * 1.5 = 2.25 still keeps 2^-25 terms
+        (vec([(1.5, 1.5)] + [(2.0 ** -12, 2.0 ** -13)] * 8), 2.25 + 8 * 2.0 ** -25),
+        # 1.5 * 2 = 3 has exponent sum 1: 2^-25 terms vanish, 2^-24 terms stay
+        (vec([(1.5, 2.0)] + [(2.0 ** -12, 2.0 ** -13)] * 8), 3.0),
+        (vec([(1.5, 2.0)] + [(2.0 ** -12, 2.0 ** -12)] * 8), 3.0 + 8 * 2.0 ** -24),
+        # each term is truncated toward zero (a small negative term is dropped, not rounded down) ...
+        (vec([(1.0, 1.0), (-2.0 ** -13, 2.0 ** -13)]), 1.0),
+        # ... partial terms lose their low bits: 8 x 1.5 * 2^-25 counts as 8 x 2^-25
+        (vec([(1.0, 1.0)] + [(1.5 * 2.0 ** -12, 2.0 ** -13)] * 8), 1 + 2 * u),
+        # the final sum is truncated toward zero as well, for both signs
+        (vec([(1.0, 1.0), (2.0 ** -11, 0.75 * 2.0 ** -12)]), 1.0),
+        (vec([(-1.0, 1.0), (-2.0 ** -11, 1.75 * 2.0 ** -12)]), -(1 + u)),
+        # the accumulator of the previous instruction is one more aligned term (K = 32):
+        # 1.0 first, then sixteen 2^-26 terms: all dropped; the other way round they add up exactly first
+        (vec([(1.0, 1.0)] + [(0, 0)] * 15 + [(2.0 ** -13, 2.0 ** -13)] * 16, 32), 1.0),
+        (vec([(2.0 ** -13, 2.0 ** -13)] * 16 + [(0, 0)] * 15 + [(1.0, 1.0)], 32), 1 + 2 * u),
+    ]
+    for (x, y), want in cases:
+        pts = oracle_mod.double_to_half(np.stack([x, y]))
+        assert np.array_equal(oracle_mod.half_to_float(pts).astype(np.float64), np.stack([x, y]))
+        gpu_join.set_points(pts)
+        gpu_join.join(1e18, capacity=4, flags=1 | 16)
+        pairs, a = gpu_join.pairs(with_dist2=True)
+        got = float(a[(pairs[:, 0] == 0) & (pairs[:, 1] == 1)][0])
+        assert got == want, (x[:4], y[:4], got, want)
+        assert float(oracle_mod.gram_matrix(pts)[0, 1]) == want

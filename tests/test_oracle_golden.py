@@ -161,3 +161,25 @@ def test_oracle_against_reference_gpu_output(oracle_mod, path):
     # With the tensor-core accumulate modelled as measured on the B200, the restatement is exact:
     # the same pairs, in the same order, as the reference's own kernels produced on that GPU.
     assert np.array_equal(mine, ref)
+
+
+def test_accumulate_model_known_answers(oracle_mod):
+    # The tensor-core accumulate rule measured on the B200 (see the GPU test of the same name for the
+    # hardware side): alignment to the largest exponent, 26-bit window, truncation toward zero.
+    u = 2.0 ** -23
+
+    def dot(pairs, k=16):
+        x, y = np.zeros(k), np.zeros(k)
+        for i, (a, b) in enumerate(pairs):
+            x[i], y[i] = a, b
+        return float(oracle_mod.gram_matrix(oracle_mod.double_to_half(np.stack([x, y])))[0, 1])
+
+    assert dot([(1.0, 1.0)] + [(2.0 ** -12, 2.0 ** -12)] * 15) == 1 + 7 * u
+    assert dot([(1.0, 1.0)] + [(2.0 ** -12, 2.0 ** -13)] * 15) == 1 + 3 * u
+    assert dot([(1.0, 1.0)] + [(2.0 ** -13, 2.0 ** -13)] * 15) == 1.0
+    assert dot([(1.5, 1.5)] + [(2.0 ** -12, 2.0 ** -13)] * 8) == 2.25 + 8 * 2.0 ** -25
+    assert dot([(1.5, 2.0)] + [(2.0 ** -12, 2.0 ** -13)] * 8) == 3.0
+    assert dot([(1.0, 1.0), (-2.0 ** -13, 2.0 ** -13)]) == 1.0
+    assert dot([(-1.0, 1.0), (-2.0 ** -11, 1.75 * 2.0 ** -12)]) == -(1 + u)
+    assert dot([(1.0, 1.0)] + [(0, 0)] * 15 + [(2.0 ** -13, 2.0 ** -13)] * 16, 32) == 1.0
+    assert dot([(2.0 ** -13, 2.0 ** -13)] * 16 + [(0, 0)] * 15 + [(1.0, 1.0)], 32) == 1 + 2 * u
