@@ -304,7 +304,7 @@ row_norms_kernel(const __grid_constant__ CUtensorMap map, float* __restrict__ no
 // inspectResults (source/warpMma.cuh:239-242), inclusive compare (:257); rows and columns that are
 // padding carry +inf norms and can never hit (:259).
 //
-// Pass 1 turns the whole tile row into hit bit masks (8 chunks x 32 columns per thread).  Only if
+// Pass 1 turns the warp's share of the tile row into hit bit masks (4 chunks x 32 columns per thread).  Only if
 // some thread of the warp has a hit does pass 2 run: one warp scan of the per-thread counts, ONE
 // atomicAdd on the found counter per warp and tile, then every thread writes its records to
 // consecutive slots -- the reference does two atomics per pair (source/pair.cuh:123-133).  Overflow
@@ -319,16 +319,16 @@ __device__ __forceinline__ void epilogue_tile(const JoinParams& p, uint32_t tadd
     uint32_t hit[kChunks];
     uint32_t mir[kChunks];
     uint32_t cnt = 0;
-    uint32_t va[32], vb[32];
-    ptx::tmem_ld_32x32b_x32(taddr, va);
+    // All of this warp's accumulator columns are requested at once (4 x 32 registers) and awaited
+    // together: one TMEM round trip per tile instead of one per chunk.
+    uint32_t vv[kChunks][32];
+#pragma unroll
+    for (int ch = 0; ch < kChunks; ++ch) ptx::tmem_ld_32x32b_x32(taddr + ch * 32, vv[ch]);
+#pragma unroll
+    for (int ch = 0; ch < kChunks; ++ch) ptx::tmem_ld_wait_for(vv[ch]);
 #pragma unroll
     for (int ch = 0; ch < kChunks; ++ch) {
-        // Chunk ch is in flight into va (even ch) or vb (odd ch); once it has landed, start the next
-        // chunk's load into the other buffer so that its latency hides behind this chunk's arithmetic.
-        uint32_t(&v)[32] = (ch & 1) ? vb : va;
-        uint32_t(&w)[32] = (ch & 1) ? va : vb;
-        ptx::tmem_ld_wait_for(v);
-        if (ch + 1 < kChunks) ptx::tmem_ld_32x32b_x32(taddr + (ch + 1) * 32, w);
+        uint32_t(&v)[32] = vv[ch];
         // Fast reject: the smallest d2 of the chunk (3 instructions per element: add, fma, min; the
         // candidate norms come as 16-byte broadcast loads).  NaNs drop out of fminf, so a NaN never hits.
         const float4* cn4 = reinterpret_cast<const float4*>(cn + ch * 32);
