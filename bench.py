@@ -299,6 +299,7 @@ def main() -> None:
     sampler = ClockSampler(local_rank)
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     join_ms, norm_ms, found = [], [], 0
+    cyc, tiles0 = [], 0
     barrier()
     sampler.start()
     ev0.record()
@@ -307,6 +308,8 @@ def main() -> None:
         join_ms.append(st.join_ms)
         norm_ms.append(st.norms_ms)
         found = int(st.pairs_found)
+        cyc.append(int(st.cta0_cycles))
+        tiles0 = int(st.cta0_tiles)
     ev1.record()
     barrier()
     clocks = sampler.stop()
@@ -485,6 +488,10 @@ def main() -> None:
             "frac_of_nominal_fp16_peak": value / (NOMINAL_FP16_TFLOPS * world),
             "kernel_ms": {"join": join_ms_max, "norms": norm_ms_max},
             "clocks": clocks,
+            # from the kernel's own cycle counter (CTA 0): mean SM clock of the join launches and the share of
+            # CTA 0's cycles that its tiles' tensor work needs at full rate (k_steps x 4 MMAs x 128 clocks a tile)
+            "sm_clock_in_kernel_mhz": float(np.mean(cyc)) / (float(np.mean(join_ms)) * 1e3) if cyc and cyc[0] else None,
+            "tensor_busy_share_cta0": (tiles0 * (-(-d // 64)) * 512.0) / float(np.mean(cyc)) if cyc and cyc[0] else None,
             "e2e": e2e,
             "gpu_launches": 2 * args.steps,
             "roofline": {"bound": "tensor", "kernel": "join_kernel", "achieved": achieved, "peak": peak,

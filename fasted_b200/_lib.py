@@ -41,6 +41,8 @@ class JoinStats(ctypes.Structure):
         ("tiles_m", ctypes.c_int),
         ("tiles_n", ctypes.c_int),
         ("grid", ctypes.c_int),
+        ("cta0_cycles", ctypes.c_ulonglong),
+        ("cta0_tiles", ctypes.c_ulonglong),
     ]
 
     def as_dict(self) -> dict:

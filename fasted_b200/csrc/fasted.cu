@@ -580,7 +580,7 @@ static int join_impl(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end, 
         CU_TRY(cudaGetLastError());
     }
     CU_TRY(cudaEventRecord(c->ev[2], c->stream));
-    unsigned long long h[3] = {0, 0, 0};
+    unsigned long long h[5] = {0, 0, 0, 0, 0};
     CU_TRY(cudaMemcpyAsync(h, c->counters, sizeof(h), cudaMemcpyDeviceToHost, c->stream));
     CU_TRY(cudaStreamSynchronize(c->stream));
     c->norms_valid = (h[2] & fasted::kErrNormWait) == 0;
@@ -651,6 +651,12 @@ static int join_impl(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end, 
         stats->tiles_m = p.tiles_m;
         stats->tiles_n = p.tiles_n;
         stats->grid = grid;
+        stats->cta0_cycles = pair ? 0 : h[4];
+        stats->cta0_tiles = 0;
+        if (!pair && p.total_tiles > 0) {
+            fasted::TileIter ti;
+            for (ti.init(p, 0, grid); ti.valid; ti.advance(p)) ++stats->cta0_tiles;
+        }
     }
     return FASTED_OK;
 }

@@ -49,7 +49,8 @@ constexpr unsigned long long kErrNormWait = 8ull;
 
 struct JoinParams {
     const float* norms;            // [n] row norms
-    unsigned long long* counters;  // [0] pairs found, [1] unused (stored = min(found, capacity)), [2] status bits
+    unsigned long long* counters;  // [0] pairs found, [1] unused (stored = min(found, capacity)), [2] status bits,
+                                   // [4] SM cycles of CTA 0 (single-CTA kernel)
     unsigned long long* keys;      // pair buffer: (query << 32) | candidate
     float* dist2;                  // optional squared distances, parallel to keys (may be null)
     unsigned long long capacity;   // pair buffer capacity
@@ -486,6 +487,7 @@ join_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 
     const long long first_tile = blockIdx.x;
     const long long tile_step = gridDim.x;
+    const long long clock_start = clock64();
 
     if (warp == 0) {
         // ------------------------- TMA producer -------------------------
@@ -630,6 +632,9 @@ join_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     // Teardown: everyone meets, then the allocating warp frees TMEM.
     ptx::tc_fence_before_sync();
     __syncthreads();
+    // SM cycles CTA 0 spent on its share of the tiles: lets the host derive the mean SM clock of the
+    // launch (cycles / device time) and the share of those cycles the tensor pipe had work for.
+    if (blockIdx.x == 0 && threadIdx.x == 0) p.counters[4] = static_cast<unsigned long long>(clock64() - clock_start);
     if (warp == 1) {
         ptx::tc_fence_after_sync();
         ptx::tmem_dealloc<1>(tmem_base, kTmemCols);

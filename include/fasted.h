@@ -121,6 +121,8 @@ typedef struct fasted_join_stats {
     unsigned long long status;  /* device status bits, 0 = clean */
     int tiles_m, tiles_n;
     int grid;
+    unsigned long long cta0_cycles;  /* SM cycles CTA 0 of the join kernel ran (0 for the CTA-pair kernel) */
+    unsigned long long cta0_tiles;   /* tiles CTA 0 computed */
 } fasted_join_stats;
 
 const char* fasted_last_error(void);
