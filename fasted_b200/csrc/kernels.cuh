@@ -320,28 +320,33 @@ __device__ __forceinline__ void epilogue_tile(const JoinParams& p, uint32_t tadd
     uint32_t hit[kChunks];
     uint32_t mir[kChunks];
     uint32_t cnt = 0;
-    // All of this warp's accumulator columns are requested at once (4 x 32 registers) and awaited
-    // together: one TMEM round trip per tile instead of one per chunk.
-    uint32_t vv[kChunks][32];
-#pragma unroll
-    for (int ch = 0; ch < kChunks; ++ch) ptx::tmem_ld_32x32b_x32(taddr + ch * 32, vv[ch]);
-#pragma unroll
-    for (int ch = 0; ch < kChunks; ++ch) ptx::tmem_ld_wait_for(vv[ch]);
+    // Two register buffers: while chunk ch is tested, the load of chunk ch + 1 is in flight.
+    uint32_t va[32], vb[32];
+    ptx::tmem_ld_32x32b_x32(taddr, va);
 #pragma unroll
     for (int ch = 0; ch < kChunks; ++ch) {
-        uint32_t(&v)[32] = vv[ch];
-        // Fast reject: the smallest d2 of the chunk (3 instructions per element: add, fma, min; the
-        // candidate norms come as 16-byte broadcast loads).  NaNs drop out of fminf, so a NaN never hits.
+        uint32_t(&v)[32] = (ch & 1) ? vb : va;
+        uint32_t(&w)[32] = (ch & 1) ? va : vb;
+        ptx::tmem_ld_wait_for(v);
+        if (ch + 1 < kChunks) ptx::tmem_ld_32x32b_x32(taddr + (ch + 1) * 32, w);
+        // Fast reject: the smallest d2 of the chunk; the candidate norms come as 16-byte broadcast
+        // loads.  NaNs drop out of fminf, so a NaN never hits.
         const float4* cn4 = reinterpret_cast<const float4*>(cn + ch * 32);
         float lo = __int_as_float(0x7f800000);
+        const uint64_t sq2 = ptx::pack_f32x2(sq, sq);
+        const uint64_t m2 = ptx::pack_f32x2(-2.0f, -2.0f);
 #pragma unroll
         for (int j4 = 0; j4 < 8; ++j4) {
+            // two elements per instruction: t = s_q + s_c, d2 = fma(a, -2, t) (== t - 2a: 2a is exact)
             const float4 c4 = cn4[j4];
-            const float d0 = (sq + c4.x) - 2.0f * __uint_as_float(v[4 * j4 + 0]);
-            const float d1 = (sq + c4.y) - 2.0f * __uint_as_float(v[4 * j4 + 1]);
-            const float d2 = (sq + c4.z) - 2.0f * __uint_as_float(v[4 * j4 + 2]);
-            const float d3 = (sq + c4.w) - 2.0f * __uint_as_float(v[4 * j4 + 3]);
-            lo = fminf(lo, fminf(fminf(d0, d1), fminf(d2, d3)));
+            const uint64_t t01 = ptx::add_f32x2(sq2, ptx::pack_f32x2(c4.x, c4.y));
+            const uint64_t t23 = ptx::add_f32x2(sq2, ptx::pack_f32x2(c4.z, c4.w));
+            const uint64_t a01 = ptx::pack_f32x2(__uint_as_float(v[4 * j4 + 0]), __uint_as_float(v[4 * j4 + 1]));
+            const uint64_t a23 = ptx::pack_f32x2(__uint_as_float(v[4 * j4 + 2]), __uint_as_float(v[4 * j4 + 3]));
+            float d0, d1, d2, d3;
+            ptx::unpack_f32x2(ptx::fma_f32x2(a01, m2, t01), d0, d1);
+            ptx::unpack_f32x2(ptx::fma_f32x2(a23, m2, t23), d2, d3);
+            lo = ptx::min3_f32(ptx::min3_f32(lo, d0, d1), d2, d3);
         }
         uint32_t mask = 0;
         if (lo <= p.eps2) {
