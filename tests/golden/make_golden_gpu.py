@@ -97,5 +97,5 @@ def main(out_dir: str, timing_only: bool = False) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else os.path.join(ROOT, "gpurun_out", "golden_gpu"),
+    main(sys.argv[1] if len(sys.argv) > 1 else os.path.join(ROOT, "golden_gpu_out"),
          timing_only="--timing-only" in sys.argv)
