@@ -96,6 +96,10 @@ struct fasted_ctx {
 
     cudaEvent_t ev[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
 
+    // pinned staging for transfers from / to pageable host memory
+    void* stage_buf[2] = {nullptr, nullptr};
+    cudaEvent_t stage_ev[2] = {nullptr, nullptr};
+
     // options
     int band_tiles = 0;  // 0 = chosen per dataset (default_band_tiles)
     int grid = 0;
@@ -184,6 +188,106 @@ void free_pair_buffers(fasted_ctx* c) {
     c->stored = 0;
     c->result_pairs = nullptr;
     c->result_dist = nullptr;
+}
+
+// ---- transfers through pinned staging ---------------------------------------------------------
+//
+// A cudaMemcpy from or to pageable memory is staged by the driver chunk by chunk without overlap.
+// Here two pinned 64 MiB buffers alternate: while the DMA engine moves one, the host threads fill or
+// drain the other (the reference copies straight from its std::vector, source/findPairs.cuh:578-579,
+// and straight into one, source/pair.cuh:139-146).  Pinned or registered user memory skips all this.
+constexpr size_t kStageBytes = size_t(64) << 20;
+
+bool host_is_pinned(const void* p) {
+    cudaPointerAttributes a;
+    if (cudaPointerGetAttributes(&a, p) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    return a.type == cudaMemoryTypeHost || a.type == cudaMemoryTypeManaged;
+}
+
+cudaError_t ensure_staging(fasted_ctx* c) {
+    for (int i = 0; i < 2; ++i) {
+        if (!c->stage_buf[i]) {
+            cudaError_t e = cudaMallocHost(&c->stage_buf[i], kStageBytes);
+            if (e != cudaSuccess) return e;
+        }
+        if (!c->stage_ev[i]) {
+            cudaError_t e = cudaEventCreateWithFlags(&c->stage_ev[i], cudaEventDisableTiming);
+            if (e != cudaSuccess) return e;
+        }
+    }
+    return cudaSuccess;
+}
+
+void parallel_copy(void* dst, const void* src, size_t bytes) {
+    const size_t piece = size_t(4) << 20;
+    const long long pieces = static_cast<long long>((bytes + piece - 1) / piece);
+#pragma omp parallel for schedule(static) if (pieces > 1)
+    for (long long i = 0; i < pieces; ++i) {
+        const size_t off = static_cast<size_t>(i) * piece;
+        std::memcpy(static_cast<char*>(dst) + off, static_cast<const char*>(src) + off, std::min(piece, bytes - off));
+    }
+}
+
+// rows x row_bytes from host (pitch src_pitch) to device (pitch dst_pitch).
+cudaError_t upload_rows(fasted_ctx* c, void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t row_bytes,
+                        size_t rows) {
+    if (host_is_pinned(src) || rows * row_bytes < (size_t(8) << 20))
+        return cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, row_bytes, rows, cudaMemcpyHostToDevice, c->stream);
+    cudaError_t e = ensure_staging(c);
+    if (e != cudaSuccess) return e;
+    const size_t rows_per_chunk = std::max<size_t>(1, kStageBytes / row_bytes);
+    int which = 0;
+    for (size_t r0 = 0; r0 < rows; r0 += rows_per_chunk, which ^= 1) {
+        const size_t nr = std::min(rows_per_chunk, rows - r0);
+        e = cudaEventSynchronize(c->stage_ev[which]);  // the DMA that last read this buffer is done
+        if (e != cudaSuccess) return e;
+        const char* s = static_cast<const char*>(src) + r0 * src_pitch;
+        if (src_pitch == row_bytes) {
+            parallel_copy(c->stage_buf[which], s, nr * row_bytes);
+        } else {
+#pragma omp parallel for schedule(static)
+            for (long long r = 0; r < static_cast<long long>(nr); ++r)
+                std::memcpy(static_cast<char*>(c->stage_buf[which]) + static_cast<size_t>(r) * row_bytes,
+                            s + static_cast<size_t>(r) * src_pitch, row_bytes);
+        }
+        e = cudaMemcpy2DAsync(static_cast<char*>(dst) + r0 * dst_pitch, dst_pitch, c->stage_buf[which], row_bytes,
+                              row_bytes, nr, cudaMemcpyHostToDevice, c->stream);
+        if (e != cudaSuccess) return e;
+        e = cudaEventRecord(c->stage_ev[which], c->stream);
+        if (e != cudaSuccess) return e;
+    }
+    return cudaSuccess;
+}
+
+// bytes from device to host; returns after the data is in dst.
+cudaError_t download_bytes(fasted_ctx* c, void* dst, const void* src, size_t bytes) {
+    if (host_is_pinned(dst) || bytes < (size_t(8) << 20)) {
+        cudaError_t e = cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, c->stream);
+        return e != cudaSuccess ? e : cudaStreamSynchronize(c->stream);
+    }
+    cudaError_t e = ensure_staging(c);
+    if (e != cudaSuccess) return e;
+    const size_t chunks = (bytes + kStageBytes - 1) / kStageBytes;
+    for (size_t i = 0; i <= chunks; ++i) {
+        if (i < chunks) {  // start chunk i
+            const size_t off = i * kStageBytes, nb = std::min(kStageBytes, bytes - off);
+            e = cudaMemcpyAsync(c->stage_buf[i & 1], static_cast<const char*>(src) + off, nb, cudaMemcpyDeviceToHost,
+                                c->stream);
+            if (e != cudaSuccess) return e;
+            e = cudaEventRecord(c->stage_ev[i & 1], c->stream);
+            if (e != cudaSuccess) return e;
+        }
+        if (i > 0) {  // drain chunk i - 1 while chunk i is on its way
+            const size_t off = (i - 1) * kStageBytes, nb = std::min(kStageBytes, bytes - off);
+            e = cudaEventSynchronize(c->stage_ev[(i - 1) & 1]);
+            if (e != cudaSuccess) return e;
+            parallel_copy(static_cast<char*>(dst) + off, c->stage_buf[(i - 1) & 1], nb);
+        }
+    }
+    return cudaSuccess;
 }
 
 // Device memory for a new dataset.  Pair buffers only ever grow, so if the dataset does not fit
@@ -294,6 +398,10 @@ void fasted_destroy(fasted_ctx* c) {
     if (c->counters) cudaFree(c->counters);
     for (auto& ev : c->ev)
         if (ev) cudaEventDestroy(ev);
+    for (int i = 0; i < 2; ++i) {
+        if (c->stage_buf[i]) cudaFreeHost(c->stage_buf[i]);
+        if (c->stage_ev[i]) cudaEventDestroy(c->stage_ev[i]);
+    }
     if (c->owns_stream && c->stream) cudaStreamDestroy(c->stream);
     delete c;
 }
@@ -344,8 +452,8 @@ int fasted_set_points_host_f16(fasted_ctx* c, const uint16_t* host, int64_t n, i
     cudaError_t e = cudaSuccess;
     if (ld != d) e = cudaMemsetAsync(dev, 0, static_cast<size_t>(n) * ld * 2, c->stream);
     if (e == cudaSuccess)
-        e = cudaMemcpy2DAsync(dev, static_cast<size_t>(ld) * 2, host, static_cast<size_t>(ld_host) * 2,
-                              static_cast<size_t>(d) * 2, static_cast<size_t>(n), cudaMemcpyHostToDevice, c->stream);
+        e = upload_rows(c, dev, static_cast<size_t>(ld) * 2, host, static_cast<size_t>(ld_host) * 2,
+                        static_cast<size_t>(d) * 2, static_cast<size_t>(n));
     if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
     if (e != cudaSuccess) {
         cudaFree(dev);
@@ -780,12 +888,8 @@ int fasted_get_pairs(fasted_ctx* c, uint64_t first, uint64_t count, int32_t* pai
     if (count == 0) return FASTED_OK;
     if (dist2_out && !c->result_dist) return fail(FASTED_ESTATE, "the last join did not record distances");
     CU_TRY(cudaSetDevice(c->device));
-    if (pairs_out)
-        CU_TRY(cudaMemcpyAsync(pairs_out, static_cast<const int2*>(c->result_pairs) + first, count * 8,
-                               cudaMemcpyDeviceToHost, c->stream));
-    if (dist2_out)
-        CU_TRY(cudaMemcpyAsync(dist2_out, c->result_dist + first, count * 4, cudaMemcpyDeviceToHost, c->stream));
-    CU_TRY(cudaStreamSynchronize(c->stream));
+    if (pairs_out) CU_TRY(download_bytes(c, pairs_out, static_cast<const int2*>(c->result_pairs) + first, count * 8));
+    if (dist2_out) CU_TRY(download_bytes(c, dist2_out, c->result_dist + first, count * 4));
     return FASTED_OK;
 }
 

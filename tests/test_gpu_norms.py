@@ -67,3 +67,17 @@ def test_exact_norms_option_is_correctly_rounded(gpu_join, oracle_mod):
     assert np.array_equal(got, want)
     ref, _ = gpu_join.row_norms()
     assert np.array_equal(ref, oracle_mod.row_norms(pts)) and (ref <= got).all() and (ref < got).any()
+
+
+def test_large_pageable_upload_and_download_round_trip(gpu_join, oracle_mod):
+    # Above 8 MB, pageable host memory travels through the pinned staging buffers (both pitches).
+    rng = np.random.default_rng(4)
+    big = rng.integers(0, 0x7BFF, size=(150_000, 200), dtype=np.uint16)  # 60 MB, d not a multiple of 64
+    gpu_join.set_points(big)
+    assert np.array_equal(gpu_join.get_points(), big)
+    wide = np.zeros((90_000, 320), dtype=np.uint16)
+    wide[:, :300] = rng.integers(0, 0x7BFF, size=(90_000, 300), dtype=np.uint16)
+    gpu_join.set_points(wide, d=300)  # row stride 320 on the host, 300 real columns
+    assert np.array_equal(gpu_join.get_points(), wide[:, :300])
+    norms, _ = gpu_join.row_norms()
+    assert np.array_equal(norms[:2000], oracle_mod.row_norms(np.ascontiguousarray(wide[:2000, :300])))
