@@ -54,7 +54,7 @@ DECLARED_SYMBOLS = [
     "runFromExponentialDataset", "runFromFile", "reRun", "releaseResources",
     "fasted_last_error", "fasted_create", "fasted_destroy", "fasted_set_stream",
     "fasted_set_points_host_f16", "fasted_set_points_device_f16", "fasted_generate_exponential",
-    "fasted_fill_exponential_device",
+    "fasted_fill_exponential_device", "fasted_copy_points_from",
     "fasted_points_info", "fasted_get_points_host_f16", "fasted_get_rows_host_f16", "fasted_row_norms", "fasted_get_norms",
     "fasted_join", "fasted_selftest_wait_timeout", "fasted_join_symmetric_shard", "fasted_tile_schedule", "fasted_estimate_epsilon", "fasted_get_pairs", "fasted_pairs_device", "fasted_brute_force_f64", "fasted_brute_force_f64_pairs", "fasted_set_option",
     "fasted_dataset_exponential_f16", "fasted_dataset_csv_shape", "fasted_dataset_csv_f16",
@@ -82,6 +82,7 @@ def load() -> ctypes.CDLL:
     L.fasted_set_points_host_f16.argtypes = [_vp, _vp, _i64, _i64, _i64]
     L.fasted_set_points_device_f16.argtypes = [_vp, _vp, _i64, _i64, _i64]
     L.fasted_generate_exponential.argtypes = [_vp, _i64, _i64, ctypes.c_double, ctypes.c_double, _u64]
+    L.fasted_copy_points_from.argtypes = [_vp, _vp]
     L.fasted_fill_exponential_device.argtypes = [_vp, _vp, _i64, _i64, _i64, ctypes.c_double, ctypes.c_double, _u64]
     L.fasted_points_info.argtypes = [_vp, ctypes.POINTER(_vp), ctypes.POINTER(_i64), ctypes.POINTER(_i64),
                                      ctypes.POINTER(_i64)]
@@ -210,6 +211,10 @@ class SelfJoin:
     def fill_exponential_device(self, dev_ptr: int, n: int, d: int, ld: int, lam: float = 40.0,
                                 max_value: float = 10.0, seed: int = 2137834274) -> None:
         _check(self._L.fasted_fill_exponential_device(self._h, _vp(dev_ptr), n, d, ld, lam, max_value, seed))
+
+    def copy_points_from(self, other: "SelfJoin") -> None:
+        """Replicate another context's resident dataset (same process, any GPU) device to device."""
+        _check(self._L.fasted_copy_points_from(self._h, other._h))
 
     def set_stream(self, cuda_stream: int) -> None:
         _check(self._L.fasted_set_stream(self._h, _vp(cuda_stream)))

@@ -474,6 +474,31 @@ int fasted_set_points_device_f16(fasted_ctx* c, const void* dev, int64_t n, int6
     return adopt_points(c, static_cast<__half*>(const_cast<void*>(dev)), false, n, d, ld);
 }
 
+int fasted_copy_points_from(fasted_ctx* dst, fasted_ctx* src) {
+    if (!dst || !src || dst == src) return fail(FASTED_EINVAL, "bad argument");
+    if (!src->points) return fail(FASTED_ESTATE, "the source context has no dataset");
+    CU_TRY(cudaSetDevice(dst->device));
+    CU_TRY(cudaStreamSynchronize(dst->stream));
+    release_points(dst);
+    if (dst->device != src->device) {
+        int can = 0;
+        if (cudaDeviceCanAccessPeer(&can, dst->device, src->device) == cudaSuccess && can) {
+            cudaError_t pe = cudaDeviceEnablePeerAccess(src->device, 0);
+            if (pe != cudaSuccess) cudaGetLastError();  // already enabled is fine; the copy works either way
+        }
+    }
+    const size_t bytes = static_cast<size_t>(src->n) * src->ld * 2;
+    __half* dev = nullptr;
+    CU_TRY(alloc_points(dst, &dev, bytes));
+    cudaError_t e = cudaMemcpyPeerAsync(dev, dst->device, src->points, src->device, bytes, dst->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(dst->stream);
+    if (e != cudaSuccess) {
+        cudaFree(dev);
+        return fail(FASTED_ECUDA, "peer copy of points failed: %s", cudaGetErrorString(e));
+    }
+    return adopt_points(dst, dev, true, src->n, src->d, src->ld);
+}
+
 int fasted_generate_exponential(fasted_ctx* c, int64_t n, int64_t d, double lambda, double max_value, uint64_t seed) {
     if (!c) return fail(FASTED_EINVAL, "ctx is null");
     int rc = check_shape(n, d);

@@ -11,6 +11,7 @@
 #include <iostream>
 #include <stdexcept>
 #include <string>
+#include <thread>
 #include <vector>
 
 #include <omp.h>
@@ -21,7 +22,8 @@
 namespace {
 
 struct LegacyState {
-    fasted_ctx* ctx = nullptr;
+    fasted_ctx* ctx = nullptr;           // GPU 0 of this process (FASTED_DEVICE)
+    std::vector<fasted_ctx*> extra;      // further GPUs when FASTED_NUM_GPUS > 1
     int64_t n = 0, d = 0;
     bool have_points = false;
 };
@@ -52,6 +54,82 @@ fasted_ctx* context() {
 }
 
 int64_t round_up(int64_t v, int64_t m) { return (v + m - 1) / m * m; }
+
+// All contexts of this process: GPU 0 first.  FASTED_NUM_GPUS (default 1, "all" = every device)
+// counts devices upward from FASTED_DEVICE.
+std::vector<fasted_ctx*> all_contexts() {
+    std::vector<fasted_ctx*> v{context()};
+    int want = 1;
+    if (const char* e = std::getenv("FASTED_NUM_GPUS")) want = std::strcmp(e, "all") == 0 ? 1 << 20 : std::atoi(e);
+    int first = 0;
+    if (const char* e = std::getenv("FASTED_DEVICE")) first = std::atoi(e);
+    while (static_cast<int>(g_state.extra.size()) + 1 < want) {
+        fasted_ctx* c = nullptr;
+        if (fasted_create(first + 1 + static_cast<int>(g_state.extra.size()), &c) != FASTED_OK) {
+            if (want != (1 << 20)) throw std::runtime_error(fasted_last_error());
+            break;  // "all": stop at the last device
+        }
+        g_state.extra.push_back(c);
+    }
+    for (fasted_ctx* c : g_state.extra) v.push_back(c);
+    return v;
+}
+
+// Contiguous band of query rows of GPU g out of G (whole 128-row tiles), as in fasted_b200/dist.py.
+void band_of(int64_t n, int g, int G, int64_t* begin, int64_t* end) {
+    int64_t per = (n + G - 1) / G;
+    per = round_up(per, 128);
+    *begin = std::min<int64_t>(n, per * g);
+    *end = std::min<int64_t>(n, *begin + per);
+}
+
+// Merge G lists of (query, candidate) records, each sorted row-major and pairwise disjoint, into one
+// sorted list.  The query range is cut into one slice per thread; a slice's records are a contiguous
+// run of every list (found by bisection), so the slices merge independently into known offsets.
+void merge_sorted_lists(const std::vector<std::vector<int32_t>>& part, const std::vector<std::vector<float>>& part_d,
+                        int64_t n, int32_t* out, float* out_d) {
+    const int G = static_cast<int>(part.size());
+    const int T = std::max(1, omp_get_max_threads());
+    auto lower = [&](int g, int64_t q) {  // first record of list g whose query index is >= q
+        const int32_t* p = part[g].data();
+        size_t lo = 0, hi = part[g].size() / 2;
+        while (lo < hi) {
+            const size_t mid = (lo + hi) / 2;
+            if (p[2 * mid] < q) lo = mid + 1; else hi = mid;
+        }
+        return lo;
+    };
+#pragma omp parallel for schedule(static, 1) num_threads(T)
+    for (int t = 0; t < T; ++t) {
+        const int64_t q0 = n * t / T, q1 = n * (t + 1) / T;
+        std::vector<size_t> at(G), end(G);
+        size_t o = 0;
+        for (int g = 0; g < G; ++g) {
+            at[g] = lower(g, q0);
+            end[g] = lower(g, q1);
+            o += at[g];
+        }
+        for (;;) {
+            int best = -1;
+            uint64_t best_key = 0;
+            for (int g = 0; g < G; ++g) {
+                if (at[g] == end[g]) continue;
+                const int32_t* r = part[g].data() + 2 * at[g];
+                const uint64_t key = (static_cast<uint64_t>(static_cast<uint32_t>(r[0])) << 32) | static_cast<uint32_t>(r[1]);
+                if (best < 0 || key < best_key) {
+                    best = g;
+                    best_key = key;
+                }
+            }
+            if (best < 0) break;
+            out[2 * o] = part[best][2 * at[best]];
+            out[2 * o + 1] = part[best][2 * at[best] + 1];
+            if (out_d) out_d[o] = part_d[best][at[best]];
+            ++o;
+            ++at[best];
+        }
+    }
+}
 
 inline char* put_uint(char* p, uint32_t v) {
     char tmp[10];
@@ -132,7 +210,44 @@ Results join_resident(double epsilon, bool save_pairs, const std::string& datase
     unsigned flags = write_dist ? FASTED_JOIN_DIST2 : 0u;
     if (symmetric) flags |= FASTED_JOIN_SYMMETRIC;
     fasted_join_stats st{};
-    check(fasted_join(ctx, epsilon, 0, -1, 0, flags, &st));
+    std::vector<fasted_ctx*> gpus = all_contexts();
+    std::vector<fasted_join_stats> per_gpu(gpus.size());
+    if (gpus.size() == 1) {
+        check(fasted_join(ctx, epsilon, 0, -1, 0, flags, &st));
+        per_gpu[0] = st;
+    } else {
+        // One host thread per GPU (the join call blocks).  Symmetric: GPU g computes its snake of
+        // upper-triangle bands and emits both orientations, so every GPU's sorted list spans all
+        // query rows and the lists are merged on the host.  Full: GPU g joins the g-th contiguous band
+        // of query rows; the lists are laid end to end.  No collective either way.
+        const int G = static_cast<int>(gpus.size());
+        std::vector<int> rc(gpus.size(), FASTED_OK);
+        std::vector<std::string> err(gpus.size());
+        std::vector<std::thread> workers;
+        for (int g = 0; g < G; ++g)
+            workers.emplace_back([&, g] {
+                if (symmetric) {
+                    rc[g] = fasted_join_symmetric_shard(gpus[g], epsilon, g, G, 0, flags, &per_gpu[g]);
+                } else {
+                    int64_t b, e;
+                    band_of(n, g, G, &b, &e);
+                    rc[g] = fasted_join(gpus[g], epsilon, b, e, static_cast<uint64_t>(std::max<int64_t>(e - b, 1)) * 256,
+                                        flags, &per_gpu[g]);
+                }
+                if (rc[g] != FASTED_OK) err[g] = fasted_last_error();
+            });
+        for (auto& w : workers) w.join();
+        for (int g = 0; g < G; ++g)
+            if (rc[g] != FASTED_OK) throw std::runtime_error(err[g]);
+        for (int g = 0; g < G; ++g) {  // the slowest GPU sets the time, the counts add up
+            st.pairs_found += per_gpu[g].pairs_found;
+            st.pairs_stored += per_gpu[g].pairs_stored;
+            st.kernel_ms = std::max(st.kernel_ms, per_gpu[g].kernel_ms);
+            st.norms_ms = std::max(st.norms_ms, per_gpu[g].norms_ms);
+            st.join_ms = std::max(st.join_ms, per_gpu[g].join_ms);
+            st.sort_ms = std::max(st.sort_ms, per_gpu[g].sort_ms);
+        }
+    }
 
     const double sort_start = now_s();
     std::printf("Number of pairs found %llu\n", st.pairs_found);
@@ -141,7 +256,25 @@ Results join_resident(double epsilon, bool save_pairs, const std::string& datase
     // save them (source/findPairs.cuh:703-714); so does this.
     std::vector<int32_t> pairs(static_cast<size_t>(st.pairs_stored) * 2);
     std::vector<float> dist2(write_dist ? static_cast<size_t>(st.pairs_stored) : 0);
-    check(fasted_get_pairs(ctx, 0, st.pairs_stored, pairs.data(), write_dist ? dist2.data() : nullptr));
+    if (gpus.size() == 1 || !symmetric) {
+        // Bands are contiguous in the query index: the band lists end to end are the global order.
+        size_t at = 0;
+        for (size_t g = 0; g < gpus.size(); ++g) {
+            const uint64_t m = per_gpu[g].pairs_stored;
+            check(fasted_get_pairs(gpus[g], 0, m, pairs.data() + 2 * at, write_dist ? dist2.data() + at : nullptr));
+            at += static_cast<size_t>(m);
+        }
+    } else {
+        std::vector<std::vector<int32_t>> part(gpus.size());
+        std::vector<std::vector<float>> part_d(gpus.size());
+        for (size_t g = 0; g < gpus.size(); ++g) {
+            const uint64_t m = per_gpu[g].pairs_stored;
+            part[g].resize(static_cast<size_t>(m) * 2);
+            if (write_dist) part_d[g].resize(static_cast<size_t>(m));
+            check(fasted_get_pairs(gpus[g], 0, m, part[g].data(), write_dist ? part_d[g].data() : nullptr));
+        }
+        merge_sorted_lists(part, part_d, n, pairs.data(), write_dist ? dist2.data() : nullptr);
+    }
     if (save_pairs) {
         const std::string pairs_path = output_path + ".pairs";
         std::cout << "Output file is: " << pairs_path << std::endl;
@@ -181,6 +314,10 @@ Results run_dataset(fasted::HostDataset (*make)(void*), void* arg, double epsilo
         std::cout << "Dataset creation time: " << now_s() - start << " (sec)" << std::endl;
         const double join_start = now_s();
         check(fasted_set_points_host_f16(context(), ds.values.data(), ds.n, ds.d, ds.d));
+        {
+            std::vector<fasted_ctx*> gpus = all_contexts();
+            for (size_t g = 1; g < gpus.size(); ++g) check(fasted_copy_points_from(gpus[g], gpus[0]));
+        }
         g_state.n = ds.n;
         g_state.d = ds.d;
         g_state.have_points = true;
@@ -228,6 +365,7 @@ Results reRun(double epsilon, bool savePairs) {
 }
 
 void releaseResources(void) {
+    for (fasted_ctx* c : g_state.extra) fasted_destroy(c);
     if (g_state.ctx) fasted_destroy(g_state.ctx);
     g_state = LegacyState{};
 }

@@ -78,6 +78,10 @@ void releaseResources(void);
  *                       is true (default /scratch/bc2497/pairsData/, the path
  *                       hard-wired at source/main.cu:214-215)
  *   FASTED_DEVICE       CUDA device ordinal (default 0, source/findPairs.cuh:622)
+ *   FASTED_NUM_GPUS     number of GPUs this one process drives (default 1; "all" = every visible
+ *                       device): the dataset is uploaded once and replicated device to device, GPU g
+ *                       joins the g-th band of query rows against all candidates, the sorted band
+ *                       lists are concatenated on the host in band order
  *   FASTED_WRITE_DIST   "1": third text column sqrt(d2) in the .pairs file
  *   FASTED_SYMMETRIC    "0": compute all N x N entries like the reference; default: each unordered
  *                       pair is computed once and both orientations are emitted (identical output,
@@ -147,6 +151,11 @@ int fasted_set_points_host_f16(fasted_ctx* ctx, const uint16_t* host, int64_t n,
  * be 16-byte aligned and ld a multiple of 8 elements; columns [d, ld) must be
  * zero if ld > d.  The caller keeps ownership and must keep it alive. */
 int fasted_set_points_device_f16(fasted_ctx* ctx, const void* dev, int64_t n, int64_t d, int64_t ld);
+
+/* Replicate the resident dataset of `src` (another GPU of the same process) into `dst` with one
+ * device-to-device copy over NVLink / PCIe; dst owns its copy.  For one process driving several
+ * GPUs (layer 1 with FASTED_NUM_GPUS); one process per GPU uses an NCCL broadcast instead. */
+int fasted_copy_points_from(fasted_ctx* dst, fasted_ctx* src);
 
 /* Allocate an n x d dataset on the device and fill it with the counter-based
  * Exponential(lambda) generator (values rejected to [0, max_value], rounded

@@ -87,3 +87,56 @@ def test_cli_synthetic_and_file(native_lib, tmp_path):
     assert r.returncode == 0 and "Pairs found: 6" in r.stdout
     r = subprocess.run([exe, str(tmp_path / "nope.csv"), "1"], capture_output=True, text=True, timeout=600)
     assert r.returncode == 1 and "Error: Failed to run." in r.stdout
+
+
+def test_copy_points_between_contexts(gpu_join, oracle_mod):
+    """Device-to-device replication used by the several-GPUs-in-one-process mode; on a one-GPU box both
+    contexts sit on the same device, the call and its result are the same."""
+    import torch
+    from fasted_b200 import SelfJoin
+    pts = oracle_mod.gen_exponential(3000, 96)
+    gpu_join.set_points(pts)
+    with SelfJoin(device=1 if torch.cuda.device_count() > 1 else 0) as other:
+        other.copy_points_from(gpu_join)
+        assert other.points_info()[1:3] == (3000, 96)
+        assert np.array_equal(other.get_points(), pts.view(np.uint16))
+        st = gpu_join.join(0.3, capacity=2_000_000)
+        other.join(0.3, q_begin=1024, q_end=3000, capacity=2_000_000)
+        want = gpu_join.pairs()
+        assert st.pairs_found == st.pairs_stored > 3000
+        assert np.array_equal(other.pairs(), want[want[:, 0] >= 1024])
+        with pytest.raises(Exception):
+            other.copy_points_from(other)
+
+
+_TWO_GPU_DRIVER = r"""
+import sys
+sys.path.insert(0, {root!r})
+from fasted_b200.find_pairs import load_findpairs
+lib = load_findpairs()
+r = lib.runFromExponentialDataset(5000, 200, 40.0, 10.0, 0.36, True)
+r2 = lib.reRun(0.3, False)
+assert r.pairsFound == r.pairsStored > 5000
+lib.releaseResources()
+print("COUNTS", r.pairsFound, r.pairsStored, r2.pairsFound)
+"""
+
+
+def test_one_process_two_gpus_writes_the_same_file(native_lib, tmp_path):
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    seen = []
+    for gpus, sym in (("1", "1"), ("2", "1"), ("all", "1"), ("2", "0")):
+        out = tmp_path / (gpus + sym)
+        out.mkdir()
+        env = dict(os.environ, FASTED_OUTPUT_DIR=str(out) + "/", FASTED_NUM_GPUS=gpus, FASTED_WRITE_DIST="1",
+                   FASTED_SYMMETRIC=sym)
+        r = subprocess.run([sys.executable, "-c", _TWO_GPU_DRIVER.format(root=ROOT)], capture_output=True, text=True,
+                           env=env, timeout=600)
+        assert r.returncode == 0, r.stdout + r.stderr
+        files = list(out.iterdir())
+        assert len(files) == 1
+        seen.append((files[0].read_text(), [l for l in r.stdout.splitlines() if l.startswith("COUNTS")]))
+    assert len(seen[0][0].splitlines()) > 5000
+    assert seen[0] == seen[1] == seen[2] == seen[3]
