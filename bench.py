@@ -217,7 +217,8 @@ def main() -> None:
     import torch
     import torch.distributed as dist
     from fasted_b200 import SelfJoin, JOIN_NO_SORT, JOIN_SYMMETRIC, JOIN_DIST2
-    from fasted_b200.dist import band_bounds
+    from fasted_b200.dist import allgather_points, band_bounds
+    from fasted_b200.dist import band_rows as rows_per_band
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -243,7 +244,8 @@ def main() -> None:
         torch.cuda.synchronize()
 
     # ---- dataset: generated on rank 0's GPU, replicated by the one broadcast --------------------
-    dev_pts = torch.zeros((n, ld), dtype=torch.float16, device="cuda")
+    # (rows padded to world equal bands so that the end-to-end leg can all-gather in place)
+    dev_pts = torch.zeros((world * rows_per_band(n, world) if world > 1 else n, ld), dtype=torch.float16, device="cuda")
     if rank == 0:
         if wl["dist"] == "exp":
             sj.fill_exponential_device(dev_pts.data_ptr(), n, d, ld, 40.0, 10.0, SEED)
@@ -409,11 +411,14 @@ def main() -> None:
     # ---- timed region 2: end to end with host buffers -------------------------------------------
     e2e = None
     if not args.no_e2e:
-        host_pts = None
-        if rank == 0:
-            host_pts = torch.empty((n, ld), dtype=torch.float16).pin_memory()
-            host_pts.copy_(dev_pts)
-            torch.cuda.synchronize()
+        # N = 1: the whole matrix in pinned host memory.  N > 1: every rank holds its own band of rows in
+        # pinned host memory (the data-parallel loader: G host links in parallel), uploads it and ONE
+        # in-place NCCL all-gather completes the matrix on every GPU.
+        pad_begin = rank * rows_per_band(n, world) if world > 1 else 0
+        pad_end = pad_begin + rows_per_band(n, world) if world > 1 else n
+        host_pts = torch.empty((pad_end - pad_begin, ld), dtype=torch.float16).pin_memory()
+        host_pts.copy_(dev_pts[pad_begin:pad_end])
+        torch.cuda.synchronize()
         out_cap = int(min(capacity, max(1 << 20, 2 * found + 1024)))
         host_out = torch.empty((out_cap, 2), dtype=torch.int32).pin_memory()
 
@@ -421,9 +426,8 @@ def main() -> None:
             if world == 1:
                 sj.set_points_ptr(host_pts.data_ptr(), n, d, ld)
             else:
-                if rank == 0:
-                    dev_pts.copy_(host_pts, non_blocking=True)
-                dist.broadcast(dev_pts.view(torch.uint8), src=0)
+                dev_pts[pad_begin:pad_end].copy_(host_pts, non_blocking=True)
+                allgather_points(dev_pts, rank, world)
                 sj.set_points_device(dev_pts.data_ptr(), n, d, ld, keepalive=dev_pts)
             st = sj.join(eps, q_begin=q_begin, q_end=q_end, capacity=capacity)
             m = min(int(st.pairs_stored), out_cap)
@@ -449,11 +453,15 @@ def main() -> None:
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_ms = float(t[0]) / args.steps
+        d2h = torch.tensor([copied * 8], dtype=torch.int64, device="cuda")
+        if world > 1:
+            dist.all_reduce(d2h)  # byte counts are whole-job totals, like the value
         e2e = {"value": flop / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOPS", "ms_per_step": e2e_ms,
-               "h2d_bytes_per_step": n * ld * 2, "d2h_bytes_per_step": copied * 8,
+               "h2d_bytes_per_step": host_pts.numel() * 2 * world, "d2h_bytes_per_step": int(d2h.item()),
                "join_kernel_ms": float(np.mean(e2e_join_ms)),
                "api": "fasted_set_points_host_f16 + fasted_join + fasted_get_pairs (pinned host buffers)"
-               if world == 1 else "pinned host -> rank 0 GPU, NCCL broadcast, fasted_join per band, fasted_get_pairs"}
+               if world == 1 else "per rank: pinned host band -> its GPU, one NCCL all-gather, fasted_join on the band, "
+                                    "fasted_get_pairs; byte counts are sums over the ranks"}
         if world == 1:
             sj.set_points_device(dev_pts.data_ptr(), n, d, ld, keepalive=dev_pts)
 

@@ -70,6 +70,37 @@ def broadcast_points(points, src: int = 0):
     return points
 
 
+def band_rows(n: int, world: int, align: int = BAND_ALIGN) -> int:
+    """Rows per band (the same for every rank); world * band_rows(n, world) >= n."""
+    per = -(-n // world)
+    return -(-per // align) * align
+
+
+def allgather_points(points, rank: int, world: int):
+    """Loader variant for ranks that each hold their own band of the matrix: `points` is a torch
+    tensor of world * band_rows rows of which rows [rank*B, (rank+1)*B) are filled on this rank; ONE
+    in-place all-gather (NCCL over NVLink for CUDA tensors) fills in the rest.  It replaces the
+    broadcast when the dataset reaches the GPUs over every rank's own host link instead of rank 0's."""
+    import torch
+    import torch.distributed as dist
+    if not (dist.is_available() and dist.is_initialized()) or world == 1:
+        return points
+    if points.shape[0] % world:
+        raise ValueError("points must hold world * band_rows rows")
+    per = points.shape[0] // world
+    flat = points.view(torch.uint8).reshape(-1)
+    chunk = flat.numel() // world
+    mine = flat[rank * chunk:(rank + 1) * chunk]
+    if dist.get_backend() == "nccl":
+        dist.all_gather_into_tensor(flat, mine)
+    else:
+        parts = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(parts, mine.clone())
+        for r, part in enumerate(parts):
+            flat[r * chunk:(r + 1) * chunk].copy_(part)
+    return points
+
+
 def sharded_self_join(engine: BandEngine, n: int, eps: float, gather: bool = True):
     """Join this rank's band; returns (pairs, found_total, stored_local).
 

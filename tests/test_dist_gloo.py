@@ -78,6 +78,15 @@ def _worker(rank, world, port, n, d, eps, out_dir):
         t = torch.zeros((n, d), dtype=torch.int16)
     broadcast_points(t)
     pts = t.numpy().view(np.uint16)
+    # loader variant: every rank fills only its own band, one all-gather completes the matrix
+    from fasted_b200.dist import allgather_points, band_bounds, band_rows
+    per = band_rows(n, world)
+    full = torch.zeros((world * per, d), dtype=torch.int16)
+    a, b = band_bounds(n, world, rank)
+    full[a:b] = t[a:b]
+    allgather_points(full, rank, world)
+    np.save(os.path.join(out_dir, f"gathered_ok{rank}.npy"),
+            np.array([torch.equal(full[:n], t), bool((full[n:] == 0).all())]))
     pairs, found, stored = sharded_self_join(OracleEngine(pts), n, eps)
     from fasted_b200.dist import sharded_self_join_symmetric
     spairs, sfound, sstored = sharded_self_join_symmetric(OracleEngine(pts), n, eps)
@@ -97,6 +106,7 @@ def test_sharded_join_equals_single_rank(oracle_mod, tmp_path, world):
     got = np.load(tmp_path / "pairs0.npy")
     assert np.array_equal(got, want)  # rank-order concatenation == global row-major order
     metas = [np.load(tmp_path / f"meta{r}.npy") for r in range(world)]
+    assert all(np.load(tmp_path / f"gathered_ok{r}.npy").all() for r in range(world))
     assert all(int(m[0]) == len(want) for m in metas)
     assert sum(int(m[1]) for m in metas) == len(want)
     # symmetric schedule + all-to-all of records: same global list, every rank a contiguous range
