@@ -29,6 +29,10 @@ def band_bounds(n: int, world: int, rank: int, align: int = BAND_ALIGN) -> tuple
     return begin, end
 
 
+class BandJoinError(RuntimeError):
+    """Raised on EVERY rank when the join of at least one rank's band failed."""
+
+
 class BandEngine(Protocol):
     def join_band(self, eps: float, q_begin: int, q_end: int) -> tuple[np.ndarray, int]:
         """Sorted (m, 2) int32 pairs of the band and the number of pairs found."""
@@ -113,14 +117,24 @@ def sharded_self_join(engine: BandEngine, n: int, eps: float, gather: bool = Tru
     else:
         world, rank = 1, 0
     begin, end = band_bounds(n, world, rank)
-    pairs, found = engine.join_band(eps, begin, end)
     if world == 1:
+        pairs, found = engine.join_band(eps, begin, end)
         return pairs, found, len(pairs)
+    # A rank whose join fails must not leave the others waiting in the next collective: the error
+    # is caught, reported through the same all-reduce as the counts, and raised on every rank.
+    error = None
+    try:
+        pairs, found = engine.join_band(eps, begin, end)
+    except Exception as exc:  # noqa: BLE001 - reported to all ranks below
+        error, pairs, found = exc, np.empty((0, 2), dtype=np.int32), 0
     backend = dist.get_backend()
     dev = torch.device("cuda", torch.cuda.current_device()) if backend == "nccl" else torch.device("cpu")
-    t = torch.tensor([found], dtype=torch.int64, device=dev)
+    t = torch.tensor([found, 1 if error is not None else 0], dtype=torch.int64, device=dev)
     dist.all_reduce(t)
-    found_total = int(t.item())
+    found_total, failed = int(t[0].item()), int(t[1].item())
+    if failed:
+        raise BandJoinError(f"the band join failed on {failed} of {world} ranks"
+                            + (f"; this rank ({rank}): {error}" if error is not None else "")) from error
     stored_local = len(pairs)
     if gather:
         parts = [None] * world if rank == 0 else None
@@ -145,9 +159,19 @@ def sharded_self_join_symmetric(engine: BandEngine, n: int, eps: float, gather: 
         pairs, found = engine.join_symmetric_shard(eps, 0, 1)
         return pairs, found, len(pairs)
     world, rank = dist.get_world_size(), dist.get_rank()
-    pairs, found = engine.join_symmetric_shard(eps, rank, world)
+    error = None
+    try:
+        pairs, found = engine.join_symmetric_shard(eps, rank, world)
+    except Exception as exc:  # noqa: BLE001 - reported to all ranks before the exchange
+        error, pairs, found = exc, np.empty((0, 2), dtype=np.int32), 0
     backend = dist.get_backend()
     dev = torch.device("cuda", torch.cuda.current_device()) if backend == "nccl" else torch.device("cpu")
+    t = torch.tensor([found, 1 if error is not None else 0], dtype=torch.int64, device=dev)
+    dist.all_reduce(t)
+    found_total, failed = int(t[0].item()), int(t[1].item())
+    if failed:
+        raise BandJoinError(f"the shard join failed on {failed} of {world} ranks"
+                            + (f"; this rank ({rank}): {error}" if error is not None else "")) from error
 
     # records are sorted by (query, candidate): the destination ranges are contiguous slices
     bounds = [band_bounds(n, world, r) for r in range(world)]
@@ -166,9 +190,6 @@ def sharded_self_join_symmetric(engine: BandEngine, n: int, eps: float, gather: 
     order = torch.argsort(key)
     mine = mine[order].cpu().numpy()
 
-    t = torch.tensor([found], dtype=torch.int64, device=dev)
-    dist.all_reduce(t)
-    found_total = int(t.item())
     stored_local = len(mine)
     if gather:
         parts = [None] * world if rank == 0 else None

@@ -122,3 +122,52 @@ def test_sharded_join_equals_single_rank(oracle_mod, tmp_path, world):
         a, b = band_bounds(n, world, r)
         p = np.load(tmp_path / f"pairs{r}.npy")
         assert len(p) == 0 or (p[:, 0].min() >= a and p[:, 0].max() < b)
+
+
+def _failing_worker(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    import datetime
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=60))
+    from fasted_b200.dist import BandJoinError, sharded_self_join, sharded_self_join_symmetric
+
+    class Engine:
+        """Rank 1's GPU "fails" (the native library's error surfaces as an exception on the host)."""
+
+        def join_band(self, eps, a, b):
+            if rank == 1:
+                raise RuntimeError("FASTED_EKERNEL: a device-side wait ran out")
+            return np.array([[a, a]], dtype=np.int32), 1
+
+        def join_symmetric_shard(self, eps, r, w):
+            if rank == 1:
+                raise RuntimeError("FASTED_ECUDA: out of memory")
+            return np.array([[0, 0]], dtype=np.int32), 1
+
+    seen = []
+    for fn in (sharded_self_join, sharded_self_join_symmetric):
+        try:
+            fn(Engine(), 512, 0.1)
+            seen.append("no error")
+        except BandJoinError as exc:
+            seen.append(str(exc))
+    # the group is still usable afterwards: every rank left the collectives in step
+    t = torch.tensor([rank + 1])
+    dist.all_reduce(t)
+    seen.append(int(t.item()))
+    with open(os.path.join(out_dir, f"seen{rank}.txt"), "w") as f:
+        f.write(repr(seen))
+    dist.destroy_process_group()
+
+
+def test_a_failing_rank_is_reported_on_every_rank(tmp_path):
+    world = 3
+    mp.spawn(_failing_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    for r in range(world):
+        seen = eval((tmp_path / f"seen{r}.txt").read_text())
+        assert seen[2] == 6
+        for msg in seen[:2]:
+            assert "failed on 1 of 3 ranks" in msg
+            assert ("this rank (1)" in msg) == (r == 1)
+    assert "device-side wait ran out" in eval((tmp_path / "seen1.txt").read_text())[0]
