@@ -649,6 +649,7 @@ static int join_impl(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end, 
 
     fasted::JoinParams p{};
     p.norms = c->norms;
+    p.norms_vec4 = (reinterpret_cast<uintptr_t>(p.norms) & 15u) == 0 ? 1 : 0;
     p.counters = c->counters;
     p.keys = c->keys;
     p.dist2 = want_dist ? c->dist : nullptr;
@@ -713,7 +714,7 @@ static int join_impl(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end, 
         CU_TRY(cudaGetLastError());
     }
     CU_TRY(cudaEventRecord(c->ev[2], c->stream));
-    unsigned long long h[5] = {0, 0, 0, 0, 0};
+    unsigned long long h[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     CU_TRY(cudaMemcpyAsync(h, c->counters, sizeof(h), cudaMemcpyDeviceToHost, c->stream));
     CU_TRY(cudaStreamSynchronize(c->stream));
     c->norms_valid = (h[2] & fasted::kErrNormWait) == 0;
@@ -784,6 +785,10 @@ static int join_impl(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end, 
         stats->tiles_m = p.tiles_m;
         stats->tiles_n = p.tiles_n;
         stats->grid = grid;
+#if FASTED_EPI_VARIANT & 256
+        std::fprintf(stderr, "EPI cta0: total %llu | epi: barrier %llu wait_full %llu work %llu | mma: wait_empty %llu wait_load %llu\n",
+                     h[4], h[5], h[6], h[7], h[1], h[3]);
+#endif
         stats->cta0_cycles = pair ? 0 : h[4];
         stats->cta0_tiles = 0;
         if (!pair && p.total_tiles > 0) {
@@ -1068,6 +1073,7 @@ int fasted_join_static_scratch(const void* points_dev, int64_t n, int64_t d, int
 
     fasted::JoinParams p{};
     p.norms = norms;
+    p.norms_vec4 = (reinterpret_cast<uintptr_t>(p.norms) & 15u) == 0 ? 1 : 0;
     p.counters = counters;
     p.keys = keys_out_dev;
     p.dist2 = nullptr;

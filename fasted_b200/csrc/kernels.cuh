@@ -14,6 +14,10 @@
 
 #include "ptx.cuh"
 
+#ifndef FASTED_EPI_VARIANT
+#define FASTED_EPI_VARIANT 0
+#endif
+
 namespace fasted {
 
 // ---------------------------------------------------------------------------
@@ -49,6 +53,7 @@ constexpr unsigned long long kErrNormWait = 8ull;
 
 struct JoinParams {
     const float* norms;            // [n] row norms
+    int norms_vec4;                // 1: norms is 16-byte aligned (vector loads allowed)
     unsigned long long* counters;  // [0] pairs found, [1] unused (stored = min(found, capacity)), [2] status bits,
                                    // [4] SM cycles of CTA 0 (single-CTA kernel)
     unsigned long long* keys;      // pair buffer: (query << 32) | candidate
@@ -87,6 +92,8 @@ struct TileIter {
     int pband;            // the current band in the global numbering
     int rows;             // tile rows in the current band
     int tn0;              // first candidate tile of the current band
+    int col, row;         // position of the current tile inside the band (rem == col * rows + row)
+    int step_col, step_row;  // step / rows and step % rows of the current band
     int tm, tn;
     bool valid;
 
@@ -107,7 +114,14 @@ struct TileIter {
             if (tn0 > p.tiles_n) tn0 = p.tiles_n;
         }
         band_size = static_cast<long long>(rows) * (p.tiles_n - tn0);
+        const unsigned s32 = static_cast<unsigned>(step), r32 = static_cast<unsigned>(rows);
+        step_col = static_cast<int>(s32 / r32);
+        step_row = static_cast<int>(s32 % r32);
     }
+    __host__ __device__ __forceinline__ bool below_diagonal(const JoinParams& p) const {
+        return p.symmetric && tn * kTileN + (kTileN - 1) < p.q_begin + tm * p.tile_m;
+    }
+    // Position from rem by division: at the start and when a band ends (once per band).
     __host__ __device__ __forceinline__ void settle(const JoinParams& p) {
         for (;;) {
             while (band < nbands && rem >= band_size) {
@@ -118,10 +132,11 @@ struct TileIter {
                 valid = false;
                 return;
             }
-            const int col = static_cast<int>(rem / rows);
+            col = static_cast<int>(rem / rows);
+            row = static_cast<int>(rem - static_cast<long long>(col) * rows);
             tn = tn0 + col;
-            tm = pband * p.band_tiles + static_cast<int>(rem - static_cast<long long>(col) * rows);
-            if (!p.symmetric || tn * kTileN + (kTileN - 1) >= p.q_begin + tm * p.tile_m) {
+            tm = pband * p.band_tiles + row;
+            if (!below_diagonal(p)) {
                 valid = true;
                 return;
             }
@@ -141,9 +156,25 @@ struct TileIter {
             settle(p);
         }
     }
+    // The next tile of this CTA: inside a band the position moves by (step_col, step_row) with one
+    // carry, no division (the kernel's three roles all walk the schedule, once per tile).
     __host__ __device__ __forceinline__ void advance(const JoinParams& p) {
-        rem += step;
-        settle(p);
+        for (;;) {
+            rem += step;
+            if (rem >= band_size) {
+                settle(p);
+                return;
+            }
+            col += step_col;
+            row += step_row;
+            if (row >= rows) {
+                row -= rows;
+                ++col;
+            }
+            tn = tn0 + col;
+            tm = pband * p.band_tiles + row;
+            if (!below_diagonal(p)) return;
+        }
     }
 };
 
@@ -294,82 +325,193 @@ row_norms_kernel(const __grid_constant__ CUtensorMap map, float* __restrict__ no
 //               per stage into one of two 256-column FP32 accumulators and
 //               commits stage-release / accumulator-ready mbarriers
 //   warps 2..9  epilogue: two warps per TMEM lane quarter, each taking 128 of
-//               the 256 accumulator columns: tcgen05.ld (thread = query row),
-//               d2 = (s_q + s_c) - 2a, compare with eps2, compact the hits with
-//               a warp scan and one atomicAdd per warp, store packed pairs.
+//               the 256 accumulator columns: tcgen05.ld.16x256b (a thread holds
+//               2 rows x 16 columns per chunk), a conservative fast reject, the
+//               exact d2 = (s_q + s_c) - 2a <= eps2 where it does not reject,
+//               a warp scan and one atomicAdd per warp and tile, packed pairs
+//               written one tile later.  The warps never meet at a barrier:
+//               each stages its own norms.
 // The epilogue of tile t overlaps the main loop of tile t+1 through the two
 // accumulator buffers.
 
-// Epilogue of one accumulator (128 lanes x kTileN columns) for one warp: thread = query row q
-// (TMEM lane), 32 columns per tcgen05.ld.  d2 = (s_q + s_c) - 2a exactly as the reference's
-// inspectResults (source/warpMma.cuh:239-242), inclusive compare (:257); rows and columns that are
-// padding carry +inf norms and can never hit (:259).
+// Epilogue of one accumulator for one warp: its TMEM lane quarter (32 query rows) x kEpiCols
+// candidate columns.  The accumulator comes in four tcgen05.ld.16x256b.x8 chunks (16 rows x 64
+// columns each): a thread then holds 2 rows x 16 columns per chunk, so over the tile it needs
+// only 4 query norms and 32 candidate norms (a thread that owned one whole row would need all
+// kEpiCols candidate norms: four times the shared-memory traffic).
 //
-// Pass 1 turns the warp's share of the tile row into hit bit masks (4 chunks x 32 columns per thread).  Only if
-// some thread of the warp has a hit does pass 2 run: one warp scan of the per-thread counts, ONE
-// atomicAdd on the found counter per warp and tile, then every thread writes its records to
-// consecutive slots -- the reference does two atomics per pair (source/pair.cuh:123-133).  Overflow
-// keeps its rule: found counts everything, records beyond the capacity are dropped (the host
-// derives stored = min(found, capacity)).
+// Exact test: d2 = (s_q + s_c) - 2a as the reference's inspectResults
+// (source/warpMma.cuh:239-242), inclusive compare (:257); rows and columns that are padding carry
+// +inf norms and can never hit (:259).
+//
+// Fast reject, per chunk and row: with u_j = fma(a_j, -2, s_cj) (one packed FMA per two elements)
+// and lo = min_j u_j (one three-input min per two elements), no column of the row can hit when
+// lo + s_q > eps2 + slack * (s_q + max s_c + eps2).  The slack covers the rounding differences
+// between this expression and the exact one: both differ from the real s_q + s_c - 2a by at most
+// 2^-21 * (s_q + s_c + eps2) in total when the exact d2 is <= eps2 (two roundings to nearest each,
+// of values bounded by 3 * (s_q + s_c) + 2 * eps2 in magnitude; a much larger a makes both sums
+// negative, which never rejects); 2^-19 is used.  A row that is not rejected takes the exact path,
+// so the result is the exact test's, bit for bit.  NaNs drop out of the min and the reject is
+// written as !(x > thr), so a NaN can only send a chunk to the exact path.
+//
+// Pass 1 turns the warp's share of the tile into hit bit masks (4 chunks x 32 elements per
+// thread).  Only if some thread of the warp has a hit does pass 2 run: one warp scan of the
+// per-thread counts, ONE atomicAdd on the found counter per warp and tile, then every thread writes
+// its records to consecutive slots -- the reference does two atomics per pair
+// (source/pair.cuh:123-133).  Overflow keeps its rule: found counts everything, records beyond the
+// capacity are dropped (the host derives stored = min(found, capacity)).
 //
 // Symmetric mode keeps columns c >= q and emits, for c > q, the mirrored record (c, q) as well.
-__device__ __forceinline__ void epilogue_tile(const JoinParams& p, uint32_t taddr, const float* cn, float sq, int q,
-                                              int c_base, int lane) {
-    // taddr, cn and c_base already point at this warp's first column.
-    constexpr int kChunks = kEpiCols / 32;
-    uint32_t hit[kChunks];
-    uint32_t mir[kChunks];
-    uint32_t cnt = 0;
-    // Two register buffers: while chunk ch is tested, the load of chunk ch + 1 is in flight.
-    uint32_t va[32], vb[32];
-    ptx::tmem_ld_32x32b_x32(taddr, va);
+//
+// taddr: TMEM address of (first lane of the quarter, first column of the warp's share);
+// wcn: the warp's kEpiCols candidate norms in shared memory; sq_lane: the query norm of row
+// (q0 + lane); q0 / c0: global index of the quarter's first row / the share's first column.
+constexpr float kRejectSlack = 1.9073486328125e-6f;  // 2^-19
+
+__device__ __forceinline__ float finite_or_zero(float x) { return x < __int_as_float(0x7f800000) ? x : 0.0f; }
+
+__device__ __forceinline__ uint32_t epi_chunk_taddr(uint32_t taddr, int k) {
+    // chunk k: row block k & 1 (16 lanes each), column half k >> 1 (64 columns each)
+    return taddr + (static_cast<uint32_t>((k & 1) * 16) << 16) + static_cast<uint32_t>((k >> 1) * 64);
+}
+
+// Hits of one warp in one tile, kept in registers between the test and the writing of the records.
+struct EpiHits {
+    uint32_t hit[kEpiCols / 32];
+    uint32_t mir[kEpiCols / 32];
+    uint32_t cnt;    // this thread's records (hits + mirrored hits)
+    uint32_t excl;   // records of the lower lanes
+    unsigned long long base;  // lane 0: first slot of the warp's reservation
+    int q0, c0;
+    bool any;        // warp-uniform: some thread has a record
+};
+
+// Test of one chunk (this thread's 2 rows x 16 columns): fast reject, else the exact test.
+// sc2: the candidate norms of the chunk's column half; d0 = column - row of element 0.
+__device__ __forceinline__ void epi_test_chunk(const JoinParams& p, const uint32_t (&v)[32], const uint64_t (&sc2)[8],
+                                               float scmax, float sqA, float sqB, int d0, uint32_t& mask,
+                                               uint32_t& mirror) {
+    const float inf = __int_as_float(0x7f800000);
+    const uint64_t m2 = ptx::pack_f32x2(-2.0f, -2.0f);
+    float loA0 = inf, loA1 = inf, loB0 = inf, loB1 = inf;
 #pragma unroll
-    for (int ch = 0; ch < kChunks; ++ch) {
-        uint32_t(&v)[32] = (ch & 1) ? vb : va;
-        uint32_t(&w)[32] = (ch & 1) ? va : vb;
-        ptx::tmem_ld_wait_for(v);
-        if (ch + 1 < kChunks) ptx::tmem_ld_32x32b_x32(taddr + (ch + 1) * 32, w);
-        // Fast reject: the smallest d2 of the chunk; the candidate norms come as 16-byte broadcast
-        // loads.  NaNs drop out of fminf, so a NaN never hits.
-        const float4* cn4 = reinterpret_cast<const float4*>(cn + ch * 32);
-        float lo = __int_as_float(0x7f800000);
-        const uint64_t sq2 = ptx::pack_f32x2(sq, sq);
-        const uint64_t m2 = ptx::pack_f32x2(-2.0f, -2.0f);
-#pragma unroll
-        for (int j4 = 0; j4 < 8; ++j4) {
-            // two elements per instruction: t = s_q + s_c, d2 = fma(a, -2, t) (== t - 2a: 2a is exact)
-            const float4 c4 = cn4[j4];
-            const uint64_t t01 = ptx::add_f32x2(sq2, ptx::pack_f32x2(c4.x, c4.y));
-            const uint64_t t23 = ptx::add_f32x2(sq2, ptx::pack_f32x2(c4.z, c4.w));
-            const uint64_t a01 = ptx::pack_f32x2(__uint_as_float(v[4 * j4 + 0]), __uint_as_float(v[4 * j4 + 1]));
-            const uint64_t a23 = ptx::pack_f32x2(__uint_as_float(v[4 * j4 + 2]), __uint_as_float(v[4 * j4 + 3]));
-            float d0, d1, d2, d3;
-            ptx::unpack_f32x2(ptx::fma_f32x2(a01, m2, t01), d0, d1);
-            ptx::unpack_f32x2(ptx::fma_f32x2(a23, m2, t23), d2, d3);
-            lo = ptx::min3_f32(ptx::min3_f32(lo, d0, d1), d2, d3);
+    for (int g = 0; g < 8; ++g) {
+        const uint64_t aA = ptx::pack_f32x2(__uint_as_float(v[4 * g + 0]), __uint_as_float(v[4 * g + 1]));
+        const uint64_t aB = ptx::pack_f32x2(__uint_as_float(v[4 * g + 2]), __uint_as_float(v[4 * g + 3]));
+        float x0, x1, y0, y1;
+        ptx::unpack_f32x2(ptx::fma_f32x2(aA, m2, sc2[g]), x0, x1);
+        ptx::unpack_f32x2(ptx::fma_f32x2(aB, m2, sc2[g]), y0, y1);
+        if (g & 1) {
+            loA1 = ptx::min3_f32(loA1, x0, x1);
+            loB1 = ptx::min3_f32(loB1, y0, y1);
+        } else {
+            loA0 = ptx::min3_f32(loA0, x0, x1);
+            loB0 = ptx::min3_f32(loB0, y0, y1);
         }
-        uint32_t mask = 0;
-        if (lo <= p.eps2) {
+    }
+    const float base = scmax + p.eps2;
+    const float thrA = fmaf(kRejectSlack, finite_or_zero(sqA) + base, p.eps2);
+    const float thrB = fmaf(kRejectSlack, finite_or_zero(sqB) + base, p.eps2);
+    const bool rejA = (fminf(loA0, loA1) + sqA) > thrA;
+    const bool rejB = (fminf(loB0, loB1) + sqB) > thrB;
+    mask = 0;
+    mirror = 0;
+    if (!(rejA && rejB)) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-                const float d2 = (sq + cn[ch * 32 + j]) - 2.0f * __uint_as_float(v[j]);
-                if (d2 <= p.eps2) mask |= (1u << j);
+        for (int i = 0; i < 32; ++i) {
+            float s0, s1;
+            ptx::unpack_f32x2(sc2[i >> 2], s0, s1);
+            const float d2 = (((i & 2) ? sqB : sqA) + ((i & 1) ? s1 : s0)) - 2.0f * __uint_as_float(v[i]);
+            if (d2 <= p.eps2) mask |= (1u << i);
+        }
+        if (p.symmetric && mask) {
+            // element i lies at column - row = d0 + 8 * (i >> 2) + (i & 1) - ((i & 2) ? 8 : 0)
+            if (d0 - 8 > 0) {
+                mirror = mask;  // the whole chunk lies above the diagonal
+            } else {
+                uint32_t m = mask;
+                while (m) {
+                    const int i = __ffs(m) - 1;
+                    m &= m - 1;
+                    const int delta = d0 + 8 * (i >> 2) + (i & 1) - ((i & 2) ? 8 : 0);
+                    if (delta < 0) mask &= ~(1u << i);
+                    if (delta > 0) mirror |= (1u << i);
+                }
             }
         }
-        uint32_t mirror = 0;
-        if (p.symmetric) {
-            const int rel = q - (c_base + ch * 32);  // column index inside the chunk that equals q
-            const uint32_t keep = rel <= 0 ? 0xffffffffu : (rel >= 32 ? 0u : (0xffffffffu << rel));
-            const uint32_t above = rel < 0 ? 0xffffffffu : (rel >= 31 ? 0u : (0xffffffffu << (rel + 1)));
-            mirror = mask & above;
-            mask &= keep;
-        }
-        hit[ch] = mask;
-        mir[ch] = mirror;
-        cnt += __popc(mask) + __popc(mirror);
     }
-    if (!__any_sync(0xffffffffu, cnt != 0)) return;
+}
 
+// This thread's candidate norms of one 64-column half (columns c2, c2 + 1 of each 8-column unit)
+// and the largest finite one.
+__device__ __forceinline__ float epi_load_cand(const float* wcn_half, uint64_t (&sc2)[8]) {
+    float mx = 0.0f;
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+        const float2 x = reinterpret_cast<const float2*>(wcn_half)[4 * g];
+        sc2[g] = ptx::pack_f32x2(x.x, x.y);
+        mx = fmaxf(mx, fmaxf(finite_or_zero(x.x), finite_or_zero(x.y)));
+    }
+    return mx;
+}
+
+// Pass 1: test the warp's share of the tile, leave the hit masks in `out`, return this thread's
+// record count.
+__device__ __forceinline__ uint32_t epilogue_scan(const JoinParams& p, uint32_t taddr, const float* wcn, float sq_lane,
+                                                  int q0, int c0, int lane, float (&sq)[4], EpiHits& out) {
+    static_assert(kEpiCols == 128, "four chunks: two row blocks x two 64-column halves");
+    const int r4 = lane >> 2;        // row inside an 8-row group
+    const int c2 = (lane & 3) * 2;   // first of this thread's two columns inside an 8-column unit
+    // Query norms of this thread's four rows (r4 + 8i of the quarter).
+#pragma unroll
+    for (int i = 0; i < 4; ++i) sq[i] = __shfl_sync(0xffffffffu, sq_lane, r4 + 8 * i);
+    uint32_t cnt = 0;
+#if FASTED_EPI_VARIANT & 16
+    // Two loads of 16 rows x 128 columns: a tcgen05.ld costs about the same whatever its size.
+    uint32_t v[64];
+    ptx::tmem_ld_16x256b_x16(taddr, v);
+    uint64_t scl[8], sch[8];
+    const float mxl = epi_load_cand(wcn + c2, scl);
+    const float mxh = epi_load_cand(wcn + 64 + c2, sch);
+#pragma unroll
+    for (int b = 0; b < 2; ++b) {
+        ptx::tmem_ld_wait_for64(v);
+        const int d0 = (c0 + c2) - (q0 + 16 * b + r4);
+        epi_test_chunk(p, reinterpret_cast<const uint32_t(&)[32]>(v[0]), scl, mxl, sq[2 * b], sq[2 * b + 1], d0,
+                       out.hit[b], out.mir[b]);
+        epi_test_chunk(p, reinterpret_cast<const uint32_t(&)[32]>(v[32]), sch, mxh, sq[2 * b], sq[2 * b + 1], d0 + 64,
+                       out.hit[b + 2], out.mir[b + 2]);
+        cnt += __popc(out.hit[b]) + __popc(out.mir[b]) + __popc(out.hit[b + 2]) + __popc(out.mir[b + 2]);
+        if (b == 0) ptx::tmem_ld_16x256b_x16(taddr + (16u << 16), v);
+    }
+#else
+    // Two register buffers: while chunk k is tested, the load of chunk k + 1 is in flight.
+    constexpr int kChunks = kEpiCols / 32;
+    uint32_t va[32], vb[32];
+    ptx::tmem_ld_16x256b_x8(taddr, va);
+    uint64_t sc2[8];
+    float scmax = 0.0f;
+#pragma unroll
+    for (int k = 0; k < kChunks; ++k) {
+        const int b = k & 1, h = k >> 1;
+        uint32_t(&v)[32] = (k & 1) ? vb : va;
+        uint32_t(&w)[32] = (k & 1) ? va : vb;
+        ptx::tmem_ld_wait_for(v);
+        if (k + 1 < kChunks) ptx::tmem_ld_16x256b_x8(epi_chunk_taddr(taddr, k + 1), w);
+        if (b == 0) scmax = epi_load_cand(wcn + h * 64 + c2, sc2);
+        const int d0 = (c0 + h * 64 + c2) - (q0 + 16 * b + r4);
+        epi_test_chunk(p, v, sc2, scmax, sq[2 * b], sq[2 * b + 1], d0, out.hit[k], out.mir[k]);
+        cnt += __popc(out.hit[k]) + __popc(out.mir[k]);
+    }
+#endif
+    return cnt;
+}
+
+// Pass 2a: if the warp has records, reserve their slots with ONE atomicAdd (lane 0).  The returned
+// base is not touched here, so the caller can let a whole tile pass before it needs the value.
+__device__ __forceinline__ void epilogue_reserve(const JoinParams& p, uint32_t cnt, int q0, int c0, int lane, EpiHits& h) {
+    h.any = __any_sync(0xffffffffu, cnt != 0);
+    if (!h.any) return;
     uint32_t incl = cnt;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -377,70 +519,155 @@ __device__ __forceinline__ void epilogue_tile(const JoinParams& p, uint32_t tadd
         if (lane >= o) incl += up;
     }
     const uint32_t total = __shfl_sync(0xffffffffu, incl, 31);
-    unsigned long long base = 0;
-    if (lane == 0) base = atomicAdd(p.counters + 0, static_cast<unsigned long long>(total));
-    base = __shfl_sync(0xffffffffu, base, 0);
-    unsigned long long slot = base + (incl - cnt);
-    const unsigned long long qkey = static_cast<unsigned long long>(static_cast<uint32_t>(q)) << 32;
-    const unsigned long long qlow = static_cast<unsigned long long>(static_cast<uint32_t>(q));
+    h.cnt = cnt;
+    h.excl = incl - cnt;
+    h.q0 = q0;
+    h.c0 = c0;
+    h.base = 0;
+    if (lane == 0) h.base = atomicAdd(p.counters + 0, static_cast<unsigned long long>(total));
+}
 
-    if (p.dist2 == nullptr) {
+// Element i of chunk k: row q0 + 16 * (k & 1) + r4 + ((i & 2) ? 8 : 0),
+// column c0 + 64 * (k >> 1) + c2 + 8 * (i >> 2) + (i & 1).
+
+// Pass 2b, records only: every thread writes its records to consecutive slots.
+__device__ __forceinline__ void epilogue_emit(const JoinParams& p, EpiHits& h, int lane) {
+    constexpr int kChunks = kEpiCols / 32;
+    unsigned long long slot = __shfl_sync(0xffffffffu, h.base, 0) + h.excl;
+    const int q_thread = h.q0 + (lane >> 2);
+    const int c_thread = h.c0 + (lane & 3) * 2;
 #pragma unroll 1
-        for (int ch = 0; ch < kChunks; ++ch) {
-            // (dynamic register indexing is avoided by rotating the arrays)
-            uint32_t m = hit[0], r = mir[0];
+    for (int k = 0; k < kChunks; ++k) {
+        // (dynamic register indexing is avoided by rotating the arrays)
+        uint32_t m = h.hit[0], r = h.mir[0];
 #pragma unroll
-            for (int k = 0; k + 1 < kChunks; ++k) {
-                hit[k] = hit[k + 1];
-                mir[k] = mir[k + 1];
-            }
-            const uint32_t c0 = static_cast<uint32_t>(c_base + ch * 32);
-            while (m) {
-                const int j = __ffs(m) - 1;
-                m &= m - 1;
-                if (slot < p.capacity) p.keys[slot] = qkey | static_cast<unsigned long long>(c0 + j);
-                ++slot;
-            }
-            while (r) {
-                const int j = __ffs(r) - 1;
-                r &= r - 1;
-                if (slot < p.capacity) p.keys[slot] = (static_cast<unsigned long long>(c0 + j) << 32) | qlow;
-                ++slot;
-            }
+        for (int j = 0; j + 1 < kChunks; ++j) {
+            h.hit[j] = h.hit[j + 1];
+            h.mir[j] = h.mir[j + 1];
         }
-    } else {
-        // Distances wanted too: read the accumulator chunk again where the warp has hits.
+        const uint32_t qk = static_cast<uint32_t>(q_thread + 16 * (k & 1));
+        const uint32_t ck = static_cast<uint32_t>(c_thread + 64 * (k >> 1));
+        while (m) {
+            const int i = __ffs(m) - 1;
+            m &= m - 1;
+            const unsigned long long q = qk + ((i & 2) ? 8u : 0u);
+            const unsigned long long c = ck + 8u * (i >> 2) + (i & 1);
+            if (slot < p.capacity) p.keys[slot] = (q << 32) | c;
+            ++slot;
+        }
+        while (r) {
+            const int i = __ffs(r) - 1;
+            r &= r - 1;
+            const unsigned long long q = qk + ((i & 2) ? 8u : 0u);
+            const unsigned long long c = ck + 8u * (i >> 2) + (i & 1);
+            if (slot < p.capacity) p.keys[slot] = (c << 32) | q;
+            ++slot;
+        }
+    }
+}
+
+// Pass 2b with distances: read the accumulator chunk again where the warp has hits (the caller
+// still owns the TMEM buffer).
+__device__ __forceinline__ void epilogue_emit_dist(const JoinParams& p, const EpiHits& h, uint32_t taddr, const float* wcn,
+                                                   const float (&sq)[4], int lane) {
+    constexpr int kChunks = kEpiCols / 32;
+    unsigned long long slot = __shfl_sync(0xffffffffu, h.base, 0) + h.excl;
+    const int q_thread = h.q0 + (lane >> 2);
+    const int c2 = (lane & 3) * 2;
+    const int c_thread = h.c0 + c2;
 #pragma unroll
-        for (int ch = 0; ch < kChunks; ++ch) {
-            const uint32_t m = hit[ch], r = mir[ch];
-            if (!__any_sync(0xffffffffu, (m | r) != 0)) continue;
-            uint32_t v[32];
-            ptx::tmem_ld_32x32b_x32(taddr + ch * 32, v);
-            ptx::tmem_ld_wait_for(v);
-            const uint32_t c0 = static_cast<uint32_t>(c_base + ch * 32);
+    for (int k = 0; k < kChunks; ++k) {
+        const uint32_t m = h.hit[k], r = h.mir[k];
+        if (!__any_sync(0xffffffffu, (m | r) != 0)) continue;
+        uint32_t v[32];
+        ptx::tmem_ld_16x256b_x8(epi_chunk_taddr(taddr, k), v);
+        ptx::tmem_ld_wait_for(v);
+        const uint32_t qk = static_cast<uint32_t>(q_thread + 16 * (k & 1));
+        const uint32_t ck = static_cast<uint32_t>(c_thread + 64 * (k >> 1));
+        const float* scp = wcn + (k >> 1) * 64 + c2;
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-                if ((m | r) & (1u << j)) {
-                    const float d2 = p.raw_dot ? __uint_as_float(v[j])
-                                               : (sq + cn[ch * 32 + j]) - 2.0f * __uint_as_float(v[j]);
-                    if (m & (1u << j)) {
-                        if (slot < p.capacity) {
-                            p.keys[slot] = qkey | static_cast<unsigned long long>(c0 + j);
-                            p.dist2[slot] = d2;
-                        }
-                        ++slot;
+        for (int i = 0; i < 32; ++i) {
+            if ((m | r) & (1u << i)) {
+                const float sqr = sq[2 * (k & 1) + ((i >> 1) & 1)];
+                const float d2 = p.raw_dot ? __uint_as_float(v[i])
+                                           : (sqr + scp[8 * (i >> 2) + (i & 1)]) - 2.0f * __uint_as_float(v[i]);
+                const unsigned long long q = qk + ((i & 2) ? 8u : 0u);
+                const unsigned long long c = ck + 8u * (i >> 2) + (i & 1);
+                if (m & (1u << i)) {
+                    if (slot < p.capacity) {
+                        p.keys[slot] = (q << 32) | c;
+                        p.dist2[slot] = d2;
                     }
-                    if (r & (1u << j)) {
-                        if (slot < p.capacity) {
-                            p.keys[slot] = (static_cast<unsigned long long>(c0 + j) << 32) | qlow;
-                            p.dist2[slot] = d2;
-                        }
-                        ++slot;
+                    ++slot;
+                }
+                if (r & (1u << i)) {
+                    if (slot < p.capacity) {
+                        p.keys[slot] = (c << 32) | q;
+                        p.dist2[slot] = d2;
                     }
+                    ++slot;
                 }
             }
         }
     }
+}
+
+// One tile of one epilogue warp.  After pass 1 the accumulator goes back to the MMA warp at once
+// (`release`), the slots of THIS tile's records are reserved, and only then are the records of the
+// PREVIOUS tile written (`pend`): the atomic's round trip to L2 and back, about a microsecond and
+// otherwise paid by nearly every tile that has a hit, hides behind a whole tile.  The caller
+// writes out the last `pend` after its loop.  With distances the accumulator is read again, so
+// that mode reserves and writes before it releases.
+template <class Release>
+__device__ __forceinline__ void epilogue_tile(const JoinParams& p, uint32_t taddr, const float* wcn, float sq_lane,
+                                              int q0, int c0, int lane, EpiHits& pend, Release release) {
+    float sq[4];
+    EpiHits cur;
+    cur.any = false;
+    const uint32_t cnt = epilogue_scan(p, taddr, wcn, sq_lane, q0, c0, lane, sq, cur);
+    if (p.dist2 != nullptr) {
+        epilogue_reserve(p, cnt, q0, c0, lane, cur);
+        if (cur.any) epilogue_emit_dist(p, cur, taddr, wcn, sq, lane);
+        release();
+        return;
+    }
+    release();
+    if (pend.any) epilogue_emit(p, pend, lane);
+    // (the masks are copied, the atomic's result lands in pend.base itself: no instruction waits for it
+    // before the next tile's epilogue_emit)
+#pragma unroll
+    for (int k = 0; k < kEpiCols / 32; ++k) {
+        pend.hit[k] = cur.hit[k];
+        pend.mir[k] = cur.mir[k];
+    }
+    epilogue_reserve(p, cnt, q0, c0, lane, pend);
+}
+
+// The norms one epilogue warp needs for a tile, fetched one tile ahead (their global-memory
+// latency hides behind the previous tile): lane l takes the candidate norms of columns
+// c_first + 4l .. + 3 (the warp's kEpiCols columns, staged through the warp's own shared-memory
+// row, so the epilogue warps never meet at a barrier) and the query norm of row q_first + l.
+// Padding rows and columns get +inf and can never hit.
+__device__ __forceinline__ void fetch_warp_norms(const JoinParams& p, int c_first, int q_first, int lane, float4& cand,
+                                                 float& query) {
+    static_assert(kEpiCols == 128, "four candidate norms per lane");
+    const float inf = __int_as_float(0x7f800000);
+    const int c = c_first + 4 * lane;
+#if FASTED_EPI_VARIANT & 4
+    cand = make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+    query = 1.0f + 0.0f * q_first;
+    return;
+#endif
+    if (c + 3 < p.n && p.norms_vec4) {
+        cand = __ldg(reinterpret_cast<const float4*>(p.norms + c));
+    } else {
+        cand.x = (c + 0 < p.n) ? __ldg(p.norms + c + 0) : inf;
+        cand.y = (c + 1 < p.n) ? __ldg(p.norms + c + 1) : inf;
+        cand.z = (c + 2 < p.n) ? __ldg(p.norms + c + 2) : inf;
+        cand.w = (c + 3 < p.n) ? __ldg(p.norms + c + 3) : inf;
+    }
+    const int q = q_first + lane;
+    query = (q < p.q_end) ? __ldg(p.norms + q) : inf;
 }
 
 struct JoinSmemAux {
@@ -450,7 +677,7 @@ struct JoinSmemAux {
     unsigned long long acc_empty_bar[2];
     uint32_t tmem_base;
     int abort_flag;
-    alignas(16) float cand_norms[2][kTileN];
+    alignas(16) float warp_cand[kEpiWarps][kEpiCols];  // each epilogue warp stages its own candidate norms
 };
 
 constexpr int kJoinSmemBytes = kStages * kStageBytes + 1024 + static_cast<int>(sizeof(JoinSmemAux)) + 64;
@@ -552,16 +779,28 @@ join_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             for (ti.init(p, first_tile, tile_step); ti.valid && ok; ti.advance(p), ++it) {
                 const int buf = static_cast<int>(it & 1);
                 const uint32_t acc_phase = static_cast<uint32_t>((it >> 1) & 1);
+#if FASTED_EPI_VARIANT & 256
+                const long long mk0 = clock64();
+#endif
                 ok = ptx::mbar_wait_bounded(ptx::smem_u32(&aux->acc_empty_bar[buf]), acc_phase ^ 1u, abort_flag,
                                             kWaitLimitNs);
                 if (!ok) break;
                 ptx::tc_fence_after_sync();
+#if FASTED_EPI_VARIANT & 256
+                if (blockIdx.x == 0) p.counters[1] += static_cast<unsigned long long>(clock64() - mk0);
+#endif
                 const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(buf * kTileN);
                 for (int ks = 0; ks < p.k_steps; ++ks) {
+#if FASTED_EPI_VARIANT & 256
+                    const long long mk1 = clock64();
+#endif
                     ok = ptx::mbar_wait_bounded(ptx::smem_u32(&aux->full_bar[stage]), phase, abort_flag,
                                                 kWaitLimitNs);
                     if (!ok) break;
                     ptx::tc_fence_after_sync();
+#if FASTED_EPI_VARIANT & 256
+                    if (blockIdx.x == 0) p.counters[3] += static_cast<unsigned long long>(clock64() - mk1);
+#endif
                     const uint32_t a_addr = tiles_u32 + stage * kStageBytes;
                     const uint64_t desc_a = ptx::make_kmajor_sw128_desc(a_addr);
                     const uint64_t desc_b = ptx::make_kmajor_sw128_desc(a_addr + kStageBytesA);
@@ -584,53 +823,64 @@ join_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     } else {
         // ------------------------- Epilogue -----------------------------
         const int quarter = warp & 3;               // TMEM lane quarter this warp may access
-        const int col_off = ((warp - 2) >> 2) * kEpiCols;  // this warp's share of the tile's columns
-        const int row_in_tile = quarter * 32 + lane;
-        const int epi_tid = threadIdx.x - 64;       // 0..255
-        const float inf = __int_as_float(0x7f800000);
+        const int ewarp = warp - 2;
+        const int col_off = (ewarp >> 2) * kEpiCols;  // this warp's share of the tile's columns
+        float* wcn = aux->warp_cand[ewarp];
         bool ok = true;
         long long it = 0;
-        // The tile's norms (one candidate norm per epilogue thread, this thread's query norm) are
-        // fetched one tile ahead, so their global-memory latency hides behind the previous tile.
-        // Padding rows and columns get +inf and can never hit.
-        static_assert(kEpiThreads == kTileN, "one candidate norm per epilogue thread");
-        auto fetch_norms = [&](const TileIter& t, float& cand, float& query) {
-            const int c = t.tn * kTileN + epi_tid;
-            const int qq = p.q_begin + t.tm * kTileM + row_in_tile;
-            cand = (c < p.n) ? __ldg(p.norms + c) : inf;
-            query = (qq < p.q_end) ? __ldg(p.norms + qq) : inf;
-        };
         TileIter ti;
         ti.init(p, first_tile, tile_step);
-        float next_cand = inf, next_query = inf;
-        if (ti.valid) fetch_norms(ti, next_cand, next_query);
+        float4 next_cand;
+        float next_query;
+        EpiHits pend;
+        pend.any = false;
+        if (ti.valid)
+            fetch_warp_norms(p, ti.tn * kTileN + col_off, p.q_begin + ti.tm * kTileM + quarter * 32, lane, next_cand,
+                             next_query);
         for (; ti.valid; ++it) {
-            const int tm = ti.tm, tn = ti.tn;
             const int buf = static_cast<int>(it & 1);
             const uint32_t acc_phase = static_cast<uint32_t>((it >> 1) & 1);
-            const int q = p.q_begin + tm * kTileM + row_in_tile;
-            const int c_base = tn * kTileN;
-
-            float* cn = aux->cand_norms[buf];
-            cn[epi_tid] = next_cand;
-            const float sq = next_query;
-            ptx::named_bar_sync(1, kEpiThreads);
+            const int q0 = p.q_begin + ti.tm * kTileM + quarter * 32;
+            const int c0 = ti.tn * kTileN + col_off;
+#if FASTED_EPI_VARIANT & 256
+            const long long ck0 = clock64();
+#endif
+            __syncwarp();  // every lane is done with the previous tile's norms
+            reinterpret_cast<float4*>(wcn)[lane] = next_cand;
+            const float sq_lane = next_query;
+            __syncwarp();
             ti.advance(p);
-            if (ti.valid) fetch_norms(ti, next_cand, next_query);
-
+            if (ti.valid)
+                fetch_warp_norms(p, ti.tn * kTileN + col_off, p.q_begin + ti.tm * kTileM + quarter * 32, lane,
+                                 next_cand, next_query);
+#if FASTED_EPI_VARIANT & 256
+            const long long ck1 = clock64();
+#endif
             if (ok) ok = ptx::mbar_wait_bounded(ptx::smem_u32(&aux->acc_full_bar[buf]), acc_phase, abort_flag,
                                                 kWaitLimitNs);
-            if (!ok) continue;  // keep taking part in the named barrier, do nothing else
+            if (!ok) continue;  // walk the schedule to its end, do nothing else
             ptx::tc_fence_after_sync();
-
+#if FASTED_EPI_VARIANT & 256
+            const long long ck2 = clock64();
+#endif
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
-                                   static_cast<uint32_t>(buf * kTileN);
-            epilogue_tile(p, taddr + col_off, cn + col_off, sq, q, c_base + col_off, lane);
-            // Hand the accumulator back to the MMA warp.
-            ptx::tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&aux->acc_empty_bar[buf]));
+                                   static_cast<uint32_t>(buf * kTileN + col_off);
+            epilogue_tile(p, taddr, wcn, sq_lane, q0, c0, lane, pend, [&] {
+                // Hand the accumulator back to the MMA warp.
+                ptx::tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&aux->acc_empty_bar[buf]));
+            });
+#if FASTED_EPI_VARIANT & 256
+            if (blockIdx.x == 0 && threadIdx.x == 64) {
+                const long long ck3 = clock64();
+                p.counters[5] += static_cast<unsigned long long>(ck1 - ck0);
+                p.counters[6] += static_cast<unsigned long long>(ck2 - ck1);
+                p.counters[7] += static_cast<unsigned long long>(ck3 - ck2);
+            }
+#endif
         }
+        if (pend.any) epilogue_emit(p, pend, lane);
         if (!ok && lane == 0) atomicOr(p.counters + 2, kErrEpilogueWait);
     }
 
@@ -677,7 +927,7 @@ struct PairSmemAux {
     unsigned long long acc_empty_bar[2];
     uint32_t tmem_base;
     int abort_flag;
-    alignas(16) float cand_norms[2][kTileN];
+    alignas(16) float warp_cand[kEpiWarps][kEpiCols];  // each epilogue warp stages its own candidate norms
 };
 
 constexpr int kPairSmemBytes = kPairStages * kPairStageBytes + 1024 + static_cast<int>(sizeof(PairSmemAux)) + 64;
@@ -811,39 +1061,34 @@ join_pair_kernel(const __grid_constant__ CUtensorMap map, const JoinParams p) {
     } else {
         // ------------------------- Epilogue (both CTAs) ------------------------------
         const int quarter = warp & 3;
-        const int col_off = ((warp - 2) >> 2) * kEpiCols;
-        const int row_in_tile = quarter * 32 + lane;
-        const int epi_tid = threadIdx.x - 64;
-        const float inf = __int_as_float(0x7f800000);
+        const int ewarp = warp - 2;
+        const int col_off = (ewarp >> 2) * kEpiCols;
+        const int row_off = static_cast<int>(rank) * kTileM + quarter * 32;  // inside the pair's 256-row tile
+        float* wcn = aux->warp_cand[ewarp];
         bool ok = true;
         long long it = 0;
-        // The tile's norms (one candidate norm per epilogue thread, this thread's query norm) are
-        // fetched one tile ahead, so their global-memory latency hides behind the previous tile.
-        // Padding rows and columns get +inf and can never hit.
-        static_assert(kEpiThreads == kTileN, "one candidate norm per epilogue thread");
-        auto fetch_norms = [&](const TileIter& t, float& cand, float& query) {
-            const int c = t.tn * kTileN + epi_tid;
-            const int qq = p.q_begin + t.tm * kPairTileM + static_cast<int>(rank) * kTileM + row_in_tile;
-            cand = (c < p.n) ? __ldg(p.norms + c) : inf;
-            query = (qq < p.q_end) ? __ldg(p.norms + qq) : inf;
-        };
         TileIter ti;
         ti.init(p, first_tile, tile_step);
-        float next_cand = inf, next_query = inf;
-        if (ti.valid) fetch_norms(ti, next_cand, next_query);
+        float4 next_cand;
+        float next_query;
+        EpiHits pend;
+        pend.any = false;
+        if (ti.valid)
+            fetch_warp_norms(p, ti.tn * kTileN + col_off, p.q_begin + ti.tm * kPairTileM + row_off, lane, next_cand,
+                             next_query);
         for (; ti.valid; ++it) {
-            const int tm = ti.tm, tn = ti.tn;
             const int buf = static_cast<int>(it & 1);
             const uint32_t acc_phase = static_cast<uint32_t>((it >> 1) & 1);
-            const int q = p.q_begin + tm * kPairTileM + static_cast<int>(rank) * kTileM + row_in_tile;
-            const int c_base = tn * kTileN;
-
-            float* cn = aux->cand_norms[buf];
-            cn[epi_tid] = next_cand;
-            const float sq = next_query;
-            ptx::named_bar_sync(1, kEpiThreads);
+            const int q0 = p.q_begin + ti.tm * kPairTileM + row_off;
+            const int c0 = ti.tn * kTileN + col_off;
+            __syncwarp();
+            reinterpret_cast<float4*>(wcn)[lane] = next_cand;
+            const float sq_lane = next_query;
+            __syncwarp();
             ti.advance(p);
-            if (ti.valid) fetch_norms(ti, next_cand, next_query);
+            if (ti.valid)
+                fetch_warp_norms(p, ti.tn * kTileN + col_off, p.q_begin + ti.tm * kPairTileM + row_off, lane,
+                                 next_cand, next_query);
 
             if (ok) ok = ptx::mbar_wait_bounded(ptx::smem_u32(&aux->acc_full_bar[buf]), acc_phase, abort_flag,
                                                 kWaitLimitNs);
@@ -851,12 +1096,15 @@ join_pair_kernel(const __grid_constant__ CUtensorMap map, const JoinParams p) {
             ptx::tc_fence_after_sync();
 
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
-                                   static_cast<uint32_t>(buf * kTileN);
-            epilogue_tile(p, taddr + col_off, cn + col_off, sq, q, c_base + col_off, lane);
-            ptx::tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive_cluster_addr(ptx::mapa_u32(ptx::smem_u32(&aux->acc_empty_bar[buf]), 0));
+                                   static_cast<uint32_t>(buf * kTileN + col_off);
+            epilogue_tile(p, taddr, wcn, sq_lane, q0, c0, lane, pend, [&] {
+                ptx::tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0)
+                    ptx::mbar_arrive_cluster_addr(ptx::mapa_u32(ptx::smem_u32(&aux->acc_empty_bar[buf]), 0));
+            });
         }
+        if (pend.any) epilogue_emit(p, pend, lane);
         if (!ok && lane == 0) atomicOr(p.counters + 2, kErrEpilogueWait);
     }
 
