@@ -714,7 +714,7 @@ static int join_impl(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end, 
         CU_TRY(cudaGetLastError());
     }
     CU_TRY(cudaEventRecord(c->ev[2], c->stream));
-    unsigned long long h[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    unsigned long long h[5] = {0, 0, 0, 0, 0};
     CU_TRY(cudaMemcpyAsync(h, c->counters, sizeof(h), cudaMemcpyDeviceToHost, c->stream));
     CU_TRY(cudaStreamSynchronize(c->stream));
     c->norms_valid = (h[2] & fasted::kErrNormWait) == 0;
@@ -785,10 +785,6 @@ static int join_impl(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end, 
         stats->tiles_m = p.tiles_m;
         stats->tiles_n = p.tiles_n;
         stats->grid = grid;
-#if FASTED_EPI_VARIANT & 256
-        std::fprintf(stderr, "EPI cta0: total %llu | epi: barrier %llu wait_full %llu work %llu | mma: wait_empty %llu wait_load %llu\n",
-                     h[4], h[5], h[6], h[7], h[1], h[3]);
-#endif
         stats->cta0_cycles = pair ? 0 : h[4];
         stats->cta0_tiles = 0;
         if (!pair && p.total_tiles > 0) {

@@ -14,10 +14,6 @@
 
 #include "ptx.cuh"
 
-#ifndef FASTED_EPI_VARIANT
-#define FASTED_EPI_VARIANT 0
-#endif
-
 namespace fasted {
 
 // ---------------------------------------------------------------------------
@@ -466,25 +462,6 @@ __device__ __forceinline__ uint32_t epilogue_scan(const JoinParams& p, uint32_t 
 #pragma unroll
     for (int i = 0; i < 4; ++i) sq[i] = __shfl_sync(0xffffffffu, sq_lane, r4 + 8 * i);
     uint32_t cnt = 0;
-#if FASTED_EPI_VARIANT & 16
-    // Two loads of 16 rows x 128 columns: a tcgen05.ld costs about the same whatever its size.
-    uint32_t v[64];
-    ptx::tmem_ld_16x256b_x16(taddr, v);
-    uint64_t scl[8], sch[8];
-    const float mxl = epi_load_cand(wcn + c2, scl);
-    const float mxh = epi_load_cand(wcn + 64 + c2, sch);
-#pragma unroll
-    for (int b = 0; b < 2; ++b) {
-        ptx::tmem_ld_wait_for64(v);
-        const int d0 = (c0 + c2) - (q0 + 16 * b + r4);
-        epi_test_chunk(p, reinterpret_cast<const uint32_t(&)[32]>(v[0]), scl, mxl, sq[2 * b], sq[2 * b + 1], d0,
-                       out.hit[b], out.mir[b]);
-        epi_test_chunk(p, reinterpret_cast<const uint32_t(&)[32]>(v[32]), sch, mxh, sq[2 * b], sq[2 * b + 1], d0 + 64,
-                       out.hit[b + 2], out.mir[b + 2]);
-        cnt += __popc(out.hit[b]) + __popc(out.mir[b]) + __popc(out.hit[b + 2]) + __popc(out.mir[b + 2]);
-        if (b == 0) ptx::tmem_ld_16x256b_x16(taddr + (16u << 16), v);
-    }
-#else
     // Two register buffers: while chunk k is tested, the load of chunk k + 1 is in flight.
     constexpr int kChunks = kEpiCols / 32;
     uint32_t va[32], vb[32];
@@ -503,7 +480,6 @@ __device__ __forceinline__ uint32_t epilogue_scan(const JoinParams& p, uint32_t 
         epi_test_chunk(p, v, sc2, scmax, sq[2 * b], sq[2 * b + 1], d0, out.hit[k], out.mir[k]);
         cnt += __popc(out.hit[k]) + __popc(out.mir[k]);
     }
-#endif
     return cnt;
 }
 
@@ -653,11 +629,6 @@ __device__ __forceinline__ void fetch_warp_norms(const JoinParams& p, int c_firs
     static_assert(kEpiCols == 128, "four candidate norms per lane");
     const float inf = __int_as_float(0x7f800000);
     const int c = c_first + 4 * lane;
-#if FASTED_EPI_VARIANT & 4
-    cand = make_float4(1.0f, 1.0f, 1.0f, 1.0f);
-    query = 1.0f + 0.0f * q_first;
-    return;
-#endif
     if (c + 3 < p.n && p.norms_vec4) {
         cand = __ldg(reinterpret_cast<const float4*>(p.norms + c));
     } else {
@@ -779,28 +750,16 @@ join_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             for (ti.init(p, first_tile, tile_step); ti.valid && ok; ti.advance(p), ++it) {
                 const int buf = static_cast<int>(it & 1);
                 const uint32_t acc_phase = static_cast<uint32_t>((it >> 1) & 1);
-#if FASTED_EPI_VARIANT & 256
-                const long long mk0 = clock64();
-#endif
                 ok = ptx::mbar_wait_bounded(ptx::smem_u32(&aux->acc_empty_bar[buf]), acc_phase ^ 1u, abort_flag,
                                             kWaitLimitNs);
                 if (!ok) break;
                 ptx::tc_fence_after_sync();
-#if FASTED_EPI_VARIANT & 256
-                if (blockIdx.x == 0) p.counters[1] += static_cast<unsigned long long>(clock64() - mk0);
-#endif
                 const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(buf * kTileN);
                 for (int ks = 0; ks < p.k_steps; ++ks) {
-#if FASTED_EPI_VARIANT & 256
-                    const long long mk1 = clock64();
-#endif
                     ok = ptx::mbar_wait_bounded(ptx::smem_u32(&aux->full_bar[stage]), phase, abort_flag,
                                                 kWaitLimitNs);
                     if (!ok) break;
                     ptx::tc_fence_after_sync();
-#if FASTED_EPI_VARIANT & 256
-                    if (blockIdx.x == 0) p.counters[3] += static_cast<unsigned long long>(clock64() - mk1);
-#endif
                     const uint32_t a_addr = tiles_u32 + stage * kStageBytes;
                     const uint64_t desc_a = ptx::make_kmajor_sw128_desc(a_addr);
                     const uint64_t desc_b = ptx::make_kmajor_sw128_desc(a_addr + kStageBytesA);
@@ -842,9 +801,6 @@ join_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             const uint32_t acc_phase = static_cast<uint32_t>((it >> 1) & 1);
             const int q0 = p.q_begin + ti.tm * kTileM + quarter * 32;
             const int c0 = ti.tn * kTileN + col_off;
-#if FASTED_EPI_VARIANT & 256
-            const long long ck0 = clock64();
-#endif
             __syncwarp();  // every lane is done with the previous tile's norms
             reinterpret_cast<float4*>(wcn)[lane] = next_cand;
             const float sq_lane = next_query;
@@ -853,16 +809,10 @@ join_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             if (ti.valid)
                 fetch_warp_norms(p, ti.tn * kTileN + col_off, p.q_begin + ti.tm * kTileM + quarter * 32, lane,
                                  next_cand, next_query);
-#if FASTED_EPI_VARIANT & 256
-            const long long ck1 = clock64();
-#endif
             if (ok) ok = ptx::mbar_wait_bounded(ptx::smem_u32(&aux->acc_full_bar[buf]), acc_phase, abort_flag,
                                                 kWaitLimitNs);
             if (!ok) continue;  // walk the schedule to its end, do nothing else
             ptx::tc_fence_after_sync();
-#if FASTED_EPI_VARIANT & 256
-            const long long ck2 = clock64();
-#endif
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                                    static_cast<uint32_t>(buf * kTileN + col_off);
             epilogue_tile(p, taddr, wcn, sq_lane, q0, c0, lane, pend, [&] {
@@ -871,14 +821,6 @@ join_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&aux->acc_empty_bar[buf]));
             });
-#if FASTED_EPI_VARIANT & 256
-            if (blockIdx.x == 0 && threadIdx.x == 64) {
-                const long long ck3 = clock64();
-                p.counters[5] += static_cast<unsigned long long>(ck1 - ck0);
-                p.counters[6] += static_cast<unsigned long long>(ck2 - ck1);
-                p.counters[7] += static_cast<unsigned long long>(ck3 - ck2);
-            }
-#endif
         }
         if (pend.any) epilogue_emit(p, pend, lane);
         if (!ok && lane == 0) atomicOr(p.counters + 2, kErrEpilogueWait);
