@@ -262,22 +262,6 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster_addr) {
                  : "memory");
 }
 
-// 32 lanes x 32 consecutive 32-bit columns: thread t of the warp receives
-// lane (base_lane + t), columns [col, col + 32).
-__device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&v)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]),
-          "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]),
-          "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]),
-          "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-        : "r"(taddr)
-        : "memory");
-}
-
 // 16 lanes x 64 consecutive 32-bit columns as eight 16 x 256-bit units.  Thread t of the warp
 // receives, for unit g (columns [col + 8g, col + 8g + 8)): v[4g], v[4g+1] = lane (base_lane + t/4),
 // columns col + 8g + 2(t%4) and +1; v[4g+2], v[4g+3] = lane (base_lane + t/4 + 8), the same columns.
@@ -296,11 +280,7 @@ __device__ __forceinline__ void tmem_ld_16x256b_x8(uint32_t taddr, uint32_t (&v)
         : "memory");
 }
 
-__device__ __forceinline__ void tmem_ld_wait() {
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
-// Same wait, but naming the 32 destination registers of the load it completes as read-write
+// tcgen05.wait::ld, naming the 32 destination registers of the load it completes as read-write
 // operands: the compiler then cannot move any use of them above the wait.
 __device__ __forceinline__ void tmem_ld_wait_for(uint32_t (&v)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;"
@@ -322,11 +302,6 @@ __device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
 }
 __device__ __forceinline__ void unpack_f32x2(uint64_t v, float& lo, float& hi) {
     asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
-}
-__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
-    uint64_t r;
-    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-    return r;
 }
 __device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
     uint64_t r;
