@@ -140,3 +140,11 @@ def test_one_process_two_gpus_writes_the_same_file(native_lib, tmp_path):
         seen.append((files[0].read_text(), [l for l in r.stdout.splitlines() if l.startswith("COUNTS")]))
     assert len(seen[0][0].splitlines()) > 5000
     assert seen[0] == seen[1] == seen[2] == seen[3]
+
+
+def test_more_gpus_than_present_is_an_error(native_lib):
+    from fasted_b200 import _lib
+    exe = os.path.join(os.path.dirname(_lib.LIB_PATH), "main")
+    env = dict(os.environ, FASTED_NUM_GPUS="64")
+    r = subprocess.run([exe, "-e", "1000", "64", "0.1"], capture_output=True, text=True, env=env, timeout=600)
+    assert r.returncode == 1 and "Error: Failed to run." in r.stdout
