@@ -445,10 +445,17 @@ int fasted_set_points_host_f16(fasted_ctx* c, const uint16_t* host, int64_t n, i
     if (ld_host < d) return fail(FASTED_EINVAL, "ld_host (%lld) < d (%lld)", (long long)ld_host, (long long)d);
     CU_TRY(cudaSetDevice(c->device));
     CU_TRY(cudaStreamSynchronize(c->stream));
-    release_points(c);
     const int64_t ld = (d + fasted::kTileK - 1) / fasted::kTileK * fasted::kTileK;
     __half* dev = nullptr;
-    CU_TRY(alloc_points(c, &dev, static_cast<size_t>(n) * ld * 2));
+    if (c->owns_points && c->points && c->n * c->ld == n * ld) {
+        // Same footprint as the resident dataset (the run / run-again cycle of a parameter sweep):
+        // keep the allocation, cudaFree + cudaMalloc would stall the whole device for nothing.
+        dev = c->points;
+        c->points = nullptr;
+        c->owns_points = false;
+    }
+    release_points(c);
+    if (!dev) CU_TRY(alloc_points(c, &dev, static_cast<size_t>(n) * ld * 2));
     cudaError_t e = cudaSuccess;
     if (ld != d) e = cudaMemsetAsync(dev, 0, static_cast<size_t>(n) * ld * 2, c->stream);
     if (e == cudaSuccess)
