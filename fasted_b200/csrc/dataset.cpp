@@ -1,13 +1,17 @@
 #include "dataset.hpp"
 
 #include <algorithm>
+#include <atomic>
 #include <cerrno>
 #include <cstdlib>
 #include <cstring>
 #include <fstream>
 #include <ios>
 #include <random>
+#include <sstream>
 #include <stdexcept>
+#include <string>
+#include <vector>
 
 #include <omp.h>
 
@@ -38,6 +42,56 @@ uint16_t float_to_half_rn(float f) {
     return static_cast<uint16_t>(sign | ((rounded - 0x38000000u) >> 13));
 }
 
+namespace {
+
+// The MT19937 state (std::mt19937's parameters: n = 624, m = 397, r = 31, a = 0x9908b0df).
+struct MtState {
+    uint32_t x[624];
+};
+
+void mt_seed(MtState& s, uint32_t seed) {
+    s.x[0] = seed;
+    for (uint32_t i = 1; i < 624; ++i) s.x[i] = 1812433253u * (s.x[i - 1] ^ (s.x[i - 1] >> 30)) + i;
+}
+
+// One regeneration of the whole state.  Written as three loops whose carried dependences are 227
+// or more elements long, so that the compiler vectorises them.
+__attribute__((target_clones("avx2", "default"))) void mt_twist(MtState& s) {
+    uint32_t* x = s.x;
+    constexpr uint32_t kUpper = 0x80000000u, kLower = 0x7fffffffu, kA = 0x9908b0dfu;
+#pragma omp simd safelen(64)
+    for (int i = 0; i < 227; ++i) {
+        const uint32_t y = (x[i] & kUpper) | (x[i + 1] & kLower);
+        x[i] = x[i + 397] ^ (y >> 1) ^ ((y & 1u) ? kA : 0u);
+    }
+#pragma omp simd safelen(64)
+    for (int i = 227; i < 623; ++i) {
+        const uint32_t y = (x[i] & kUpper) | (x[i + 1] & kLower);
+        x[i] = x[i - 227] ^ (y >> 1) ^ ((y & 1u) ? kA : 0u);
+    }
+    const uint32_t y = (x[623] & kUpper) | (x[0] & kLower);
+    x[623] = x[396] ^ (y >> 1) ^ ((y & 1u) ? kA : 0u);
+}
+
+// std::mt19937 holding this state with all of its outputs consumed (the next draw twists first):
+// the engine's own text format is the 624 words followed by the position.
+std::mt19937 engine_from_state(const MtState& s) {
+    std::string text;
+    text.reserve(624 * 11 + 8);
+    for (int i = 0; i < 624; ++i) {
+        text += std::to_string(s.x[i]);
+        text += ' ';
+    }
+    text += "624";
+    std::istringstream in(text);
+    std::mt19937 engine;
+    in >> engine;
+    if (in.fail()) throw std::runtime_error("could not load the generator state");
+    return engine;
+}
+
+}  // namespace
+
 HostDataset make_exponential_dataset(int64_t n, int64_t d, double lambda, double max_value) {
     if (n <= 0 || d <= 0) throw std::runtime_error("No points were generated.");
     HostDataset ds;
@@ -52,33 +106,52 @@ HostDataset make_exponential_dataset(int64_t n, int64_t d, double lambda, double
     // The reference draws all N*D values from ONE sequential engine, which at 4e9 values takes
     // minutes.  libstdc++'s exponential_distribution<double> consumes exactly two 32-bit engine
     // outputs per draw, so value k starts at engine position 2k as long as no earlier draw was
-    // rejected.  Each thread therefore jumps its own engine copy to its chunk (discard() only
-    // regenerates state, no logarithms) and draws; if ANY draw anywhere is rejected the positions
-    // after it shift and the whole dataset is redone sequentially.  The stream is bit-identical
-    // either way.
+    // rejected.  The engine's state is advanced by a vectorised restatement of the MT19937
+    // recurrence (mt_twist, many times faster than drawing), which leaves a state snapshot at every
+    // chunk boundary; the other threads load snapshots into std::mt19937 engines and draw the chunks
+    // with the standard distribution.  If ANY draw anywhere is
+    // rejected the positions after it shift and the whole dataset is redone sequentially.  The
+    // stream is bit-identical either way.
     const int threads = omp_get_max_threads();
     bool parallel_ok = false;
     if (threads > 1 && total >= (size_t(1) << 20)) {
-        long long rejections = 0;
-#pragma omp parallel reduction(+ : rejections)
+        constexpr size_t kChunk = 312 * 2048;  // draws per chunk: 2 * kChunk outputs = 2048 whole state blocks
+        const size_t chunks = (total + kChunk - 1) / kChunk;
+        // One thread walks the state (vectorised twists only) and hands every chunk to the team as a
+        // task the moment its snapshot exists; the others draw the chunks with the standard engine and
+        // distribution meanwhile.  Chunk c starts at output 2 * c * kChunk, a multiple of 624: its
+        // snapshot is the state after that many outputs' worth of twists, about to be twisted once
+        // more by the chunk's first draw.
+        std::vector<MtState> snaps(chunks);
+        std::atomic<long long> rejections{0};
+#pragma omp parallel
+#pragma omp single
         {
-            const size_t t = static_cast<size_t>(omp_get_thread_num());
-            const size_t nt = static_cast<size_t>(omp_get_num_threads());
-            const size_t begin = total / nt * t + std::min(t, total % nt);
-            const size_t end = begin + total / nt + (t < total % nt ? 1 : 0);
-            std::mt19937 engine(kSeed);
-            engine.discard(2ull * begin);
-            std::exponential_distribution<double> dist(lambda);
-            for (size_t i = begin; i < end; ++i) {
-                const double v = dist(engine);
-                if (v < 0.0 || v > max_value) {
-                    ++rejections;
-                    break;
+            MtState st;
+            mt_seed(st, kSeed);
+            for (size_t c = 0; c < chunks; ++c) {
+                snaps[c] = st;
+#pragma omp task firstprivate(c) shared(snaps, rejections)
+                {
+                    if (!rejections.load(std::memory_order_relaxed)) {
+                        std::mt19937 engine = engine_from_state(snaps[c]);
+                        std::exponential_distribution<double> dist(lambda);
+                        const size_t begin = c * kChunk, end = std::min(total, begin + kChunk);
+                        for (size_t i = begin; i < end; ++i) {
+                            const double v = dist(engine);
+                            if (v < 0.0 || v > max_value) {
+                                rejections.fetch_add(1, std::memory_order_relaxed);
+                                break;
+                            }
+                            out[i] = float_to_half_rn(static_cast<float>(v));
+                        }
+                    }
                 }
-                out[i] = float_to_half_rn(static_cast<float>(v));
+                if (c + 1 < chunks)
+                    for (size_t k = 0; k < 2 * kChunk / 624; ++k) mt_twist(st);
             }
         }
-        parallel_ok = rejections == 0;
+        parallel_ok = rejections.load() == 0;
     }
     if (!parallel_ok) {
         std::mt19937 engine(kSeed);
