@@ -122,5 +122,5 @@ def test_host_generator_parallel_path_is_the_same_stream(native_lib, oracle_mod)
     # Above 2^20 values the generator draws in parallel chunks (engine jump-ahead); with draws that get
     # rejected it must fall back to the sequential walk.  Both must equal the reference's stream.
     from fasted_b200 import _lib
-    for n, d, lam, mx in [(1100, 1000, 40.0, 10.0), (1500, 800, 1.0, 0.5)]:
+    for n, d, lam, mx in [(1100, 1000, 40.0, 10.0), (3001, 999, 40.0, 10.0), (1500, 800, 1.0, 0.5)]:
         assert np.array_equal(_lib.dataset_exponential(n, d, lam, mx), oracle_mod.gen_exponential(n, d, lam, mx))
