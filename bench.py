@@ -157,6 +157,10 @@ def run_reference_arm(args, wl: dict, name: str) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    # torchrun sets OMP_NUM_THREADS=1 for its children; this arm is the only rank that works and is
+    # meant to use all host threads (the OpenMP runtime reads the variable when it is first loaded).
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1 and os.environ.get("OMP_NUM_THREADS") == "1":
+        os.environ["OMP_NUM_THREADS"] = str(len(os.sched_getaffinity(0)))
     import oracle
     cores = oracle.num_threads()
     q_rows, c_rows = size_cpu_sample(wl, budget_flop=1e12 * cores / 16)
