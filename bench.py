@@ -231,9 +231,9 @@ def main() -> None:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
     torch.cuda.set_device(local_rank)
     if world > 1:
-        # NCCL's version banner goes to stdout; rank 0's stdout is the one JSON line.
-        if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
-            os.environ["NCCL_DEBUG"] = "WARN"
+        # Whatever NCCL logs (its version banner, when NCCL_DEBUG asks for one) goes to stderr:
+        # rank 0's stdout is the one JSON line.
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
     n, d = wl["n"], wl["d"]
