@@ -231,8 +231,10 @@ def main() -> None:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
     torch.cuda.set_device(local_rank)
     if world > 1:
-        # Whatever NCCL logs (its version banner, when NCCL_DEBUG asks for one) goes to stderr:
-        # rank 0's stdout is the one JSON line.
+        # Rank 0's stdout is the one JSON line: NCCL's version banner (NCCL_DEBUG=VERSION prints it to
+        # stdout) is switched off, anything else NCCL is asked to log goes to stderr.
+        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
+            del os.environ["NCCL_DEBUG"]
         os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
