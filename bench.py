@@ -39,16 +39,8 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-# name -> shape, distribution, target mean neighbours per point, epsilon (None: tuned at start-up
-# with band joins through the library itself, like the reference's Python driver does with reRun).
-WORKLOADS = {
-    "c1": dict(n=4096, d=128, dist="exp", target=32, eps=0.3136),
-    "c2": dict(n=100_000, d=384, dist="unit_gauss", target=16, eps=None),
-    "c3": dict(n=1_000_000, d=4096, dist="exp", target=64, eps=None),
-    "c4": dict(n=2_000_000, d=1024, dist="mixture", target=2000, eps=None, pairs_per_point=2600),
-    "c5": dict(n=4_000_000, d=2048, dist="exp", target=8, eps=None),
-}
-SEED = 2137834274  # the reference's dataset seed
+from fasted_b200.workloads import SEED, WORKLOADS, fill_device, host_sample as make_host_sample  # noqa: E402
+
 PUBLISHED_A100_TFLOPS = {"c3": 153.64}  # mean of the reference's three 1,000,000 x 4096 trials (A100 PCIe)
 NOMINAL_FP16_TFLOPS = 2250.0
 
@@ -116,25 +108,6 @@ class ClockSampler:
                 "samples": len(self.samples)}
 
 
-def make_host_sample(wl: dict, rows: int) -> np.ndarray:
-    """Seeded host-side sample with the workload's distribution, binary16 bit patterns (rows, d)."""
-    rng = np.random.default_rng(SEED)
-    d = wl["d"]
-    if wl["dist"] == "exp":
-        x = rng.exponential(1.0 / 40.0, size=(rows, d))
-        x = np.minimum(x, 10.0)
-    elif wl["dist"] == "unit_gauss":
-        x = rng.standard_normal((rows, d))
-        x /= np.linalg.norm(x, axis=1, keepdims=True)
-    elif wl["dist"] == "mixture":
-        centres = rng.uniform(0.0, 1.0, size=(256, d))
-        w = 1.0 / np.arange(1, 257) ** 1.1
-        x = centres[rng.choice(256, size=rows, p=w / w.sum())] + rng.normal(0.0, 0.05, size=(rows, d))
-    else:
-        raise ValueError(wl["dist"])
-    return x.astype(np.float32).astype(np.float16).view(np.uint16)
-
-
 def cpu_fp64_sample(pts: np.ndarray, d: int, eps: float, q_rows: int) -> dict:
     """Times the OpenMP FP64 brute force (the checker's, used here only as the reported CPU baseline)."""
     import oracle
@@ -187,6 +160,50 @@ def run_reference_arm(args, wl: dict, name: str) -> None:
     print(json.dumps(line), flush=True)
 
 
+def reference_gpu_leg(sj_cls, dev_pts, wl: dict, eps: float, rows: int) -> dict:
+    """The reference's own kernels on this GPU beside this library, on the SAME buffer: the first `rows`
+    points of the workload.  oracle/_ref/ref_join is the reference's findPairs.cuh compiled unmodified for
+    sm_100 behind a file-in / file-out harness (test infrastructure; built where the reference checkout is
+    mounted).  Both figures use the reference's timer: row norms + join kernel, 2*n*n*d flop.  Outside
+    every timed region of the benchmark; never part of `value`."""
+    import re
+    import subprocess
+    import tempfile
+    exe = os.path.join(ROOT, "oracle", "_ref", "ref_join")
+    d = wl["d"]
+    m = min(rows, wl["n"])
+    if not os.path.exists(exe):
+        return {"unavailable": "oracle/_ref/ref_join is not built (it is compiled from the reference checkout)"}
+    with sj_cls(dev_pts.device.index or 0) as sj2:
+        sj2.set_points_device(dev_pts.data_ptr(), m, d, dev_pts.shape[1], keepalive=dev_pts)
+        for _ in range(2):
+            st = sj2.join(eps, capacity=max(m * 256, 1 << 20))
+        ours = sj2.pairs()
+        ours_tflops = 2.0 * m * m * d / (st.kernel_ms * 1e-3) / 1e12
+    if st.pairs_found > 20_000_000 or st.pairs_found != st.pairs_stored:
+        return {"unavailable": f"{st.pairs_found} pairs on the first {m} points: too many for the reference's "
+                               "one-flush-per-pair text output"}
+    with tempfile.TemporaryDirectory() as tmp:
+        pin = os.path.join(tmp, "p.bin")
+        with open(pin, "wb") as f:
+            f.write(np.array([m, d], dtype=np.int64).tobytes())
+            f.write(dev_pts[:m, :d].contiguous().cpu().numpy().view(np.uint16).tobytes())
+        prefix = os.path.join(tmp, "out")
+        try:
+            r = subprocess.run([exe, pin, repr(eps), prefix], capture_output=True, text=True, timeout=900)
+        except subprocess.TimeoutExpired:
+            return {"unavailable": "ref_join did not finish within 900 s"}
+        mm = re.search(r"REF_RESULTS (\S+) (\S+) (\d+) (\d+)", r.stdout)
+        if r.returncode != 0 or not mm:
+            return {"unavailable": "ref_join failed: " + (r.stdout[-200:] + r.stderr[-200:]).replace("\n", " ")}
+        ref_pairs = np.array(re.findall(r"(\d+), (\d+)", open(prefix + ".pairs").read()), dtype=np.int32).reshape(-1, 2)
+    return {"n": m, "d": d, "epsilon": eps, "ref_tflops": float(mm.group(2)), "ours_tflops": ours_tflops,
+            "speedup": ours_tflops / float(mm.group(2)), "ref_pairs": int(mm.group(3)), "ours_pairs": int(st.pairs_found),
+            "same_pairs": bool(np.array_equal(ref_pairs, ours)),
+            "what": "the reference's findPairs.cuh (mma.sync, compiled unmodified for sm_100) and this library on the "
+                    "same FP16 buffer on this GPU; TFLOPS = 2*n*n*d / (norm kernel + join kernel), full schedule"}
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -202,6 +219,9 @@ def main() -> None:
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the symmetric-mode and accuracy legs")
+    ap.add_argument("--no-refgpu", action="store_true", help="skip the reference's own kernels on this GPU")
+    ap.add_argument("--no-balance", action="store_true", help="N > 1: keep equal bands (no sizing by measured rate)")
+    ap.add_argument("--option", action="append", default=[], help="name=value for fasted_set_option (tuning runs)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 0)
 
@@ -211,6 +231,8 @@ def main() -> None:
         wl["n"], wl["eps"] = args.points, None
     if args.dims:
         wl["d"], wl["eps"] = args.dims, None
+    if (args.points or args.dims) and wl["dist"] == "exp_ref":
+        wl["dist"] = "exp"
     if args.eps:
         wl["eps"] = args.eps
 
@@ -220,8 +242,9 @@ def main() -> None:
 
     import torch
     import torch.distributed as dist
-    from fasted_b200 import SelfJoin, JOIN_NO_SORT, JOIN_SYMMETRIC, JOIN_DIST2
-    from fasted_b200.dist import allgather_points, band_bounds
+    from fasted_b200 import SelfJoin, JOIN_NO_SORT
+    from fasted_b200.dist import (GpuBandEngine, SharedPairBuffer, allgather_points, band_bounds, sharded_self_join,
+                                  weighted_band_bounds)
     from fasted_b200.dist import band_rows as rows_per_band
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -246,48 +269,38 @@ def main() -> None:
         sj.set_option("band_tiles", args.band_tiles)
     if args.cta_pair >= 0:
         sj.set_option("cta_pair", args.cta_pair)
+    for opt in args.option:
+        k, v = opt.split("=", 1)
+        sj.set_option(k, int(v))
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
+    def allmax(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t[0])
+
+    def allsum(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t)
+        return float(t[0])
+
     # ---- dataset: generated on rank 0's GPU, replicated by the one broadcast --------------------
     # (rows padded to world equal bands so that the end-to-end leg can all-gather in place)
     dev_pts = torch.zeros((world * rows_per_band(n, world) if world > 1 else n, ld), dtype=torch.float16, device="cuda")
     if rank == 0:
-        if wl["dist"] == "exp":
-            sj.fill_exponential_device(dev_pts.data_ptr(), n, d, ld, 40.0, 10.0, SEED)
-        elif wl["dist"] == "unit_gauss":
-            g = torch.Generator(device="cuda").manual_seed(SEED)
-            for a in range(0, n, 65536):
-                x = torch.randn((min(65536, n - a), d), generator=g, device="cuda", dtype=torch.float32)
-                x /= x.norm(dim=1, keepdim=True)
-                dev_pts[a:a + x.shape[0], :d] = x.to(torch.float16)
-        elif wl["dist"] == "mixture":
-            # 256 centres ~ U[0,1]^D, cluster sizes ~ Zipf(1.1) over ranks 1..256 (largest remainder
-            # rounding to sum N), point = centre + N(0, 0.05^2) per coordinate, points of a cluster contiguous
-            g = torch.Generator(device="cuda").manual_seed(SEED)
-            centres = torch.rand((256, d), generator=g, device="cuda", dtype=torch.float32)
-            w = 1.0 / np.arange(1, 257) ** 1.1
-            exact = w / w.sum() * n
-            sizes = np.floor(exact).astype(np.int64)
-            for i in np.argsort(-(exact - sizes))[: n - int(sizes.sum())]:
-                sizes[i] += 1
-            a = 0
-            for cid, sz in enumerate(sizes):
-                for b in range(0, int(sz), 65536):
-                    m = min(65536, int(sz) - b)
-                    x = centres[cid] + 0.05 * torch.randn((m, d), generator=g, device="cuda", dtype=torch.float32)
-                    dev_pts[a:a + m, :d] = x.to(torch.float16)
-                    a += m
+        fill_device(sj, dev_pts, wl)
     if world > 1:
         dist.broadcast(dev_pts.view(torch.uint8), src=0)
     torch.cuda.synchronize()
     sj.set_points_device(dev_pts.data_ptr(), n, d, ld, keepalive=dev_pts)
-
-    q_begin, q_end = band_bounds(n, world, rank)
-    band_rows = q_end - q_begin
 
     # ---- epsilon ------------------------------------------------------------------------------
     eps = wl["eps"]
@@ -299,14 +312,39 @@ def main() -> None:
             t = torch.tensor([eps if rank == 0 else 0.0], dtype=torch.float64, device="cuda")
             dist.broadcast(t, src=0)
             eps = float(t.item())
-    capacity = max(1, band_rows) * int(wl.get("pairs_per_point", 256))
+    per_point = int(wl.get("pairs_per_point", 256))
 
-    # ---- timed region 1: dataset resident, device-timed -----------------------------------------
+    # ---- bands: equal to begin with; at N > 1 re-sized by the rate every GPU showed in the warm-up ---
+    bounds = [band_bounds(n, world, r) for r in range(world)]
+    cap_rows = int(max(b - a for a, b in bounds) * (1.15 if world > 1 else 1.0)) + 128
+
     def step_resident():
-        return sj.join(eps, q_begin=q_begin, q_end=q_end, capacity=capacity, flags=JOIN_NO_SORT)
+        a, b = bounds[rank]
+        return sj.join(eps, q_begin=a, q_end=b, capacity=max(1, cap_rows) * per_point, flags=JOIN_NO_SORT)
+
+    def rebalance():
+        # rows per millisecond of every rank's last join -> bands in proportion (multiples of 128 rows)
+        a, b = bounds[rank]
+        st = step_resident()
+        mine = torch.tensor([(b - a) / max(st.join_ms, 1e-6)], dtype=torch.float64, device="cuda")
+        rates = torch.empty(world, dtype=torch.float64, device="cuda")
+        dist.all_gather_into_tensor(rates, mine)
+        new = weighted_band_bounds(n, rates.tolist())
+        if max(y - x for x, y in new) <= cap_rows:
+            bounds[:] = new
+        return rates.tolist()
 
     for _ in range(args.warmup):
         step_resident()
+    rates = None
+    if world > 1 and not args.no_balance:
+        rates = rebalance()
+        rates = rebalance()  # second round: on the bands the first one chose
+    q_begin, q_end = bounds[rank]
+    band_rows = q_end - q_begin
+    capacity = max(1, cap_rows) * per_point
+
+    # ---- timed region 1: dataset resident, device-timed -----------------------------------------
     sampler = ClockSampler(local_rank)
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     join_ms, norm_ms, found = [], [], 0
@@ -324,18 +362,10 @@ def main() -> None:
     ev1.record()
     barrier()
     clocks = sampler.stop()
-    total_ms = ev0.elapsed_time(ev1)
-    stats = torch.tensor([total_ms, float(found), float(np.mean(join_ms)), float(np.mean(norm_ms))],
-                         dtype=torch.float64, device="cuda")
-    if world > 1:
-        mx = stats.clone()
-        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
-        sm = stats.clone()
-        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
-        total_ms, found_total = float(mx[0]), int(sm[1])
-        join_ms_max, norm_ms_max = float(mx[2]), float(mx[3])
-    else:
-        found_total, join_ms_max, norm_ms_max = found, float(stats[2]), float(stats[3])
+    total_ms = allmax(ev0.elapsed_time(ev1))
+    found_total = int(allsum(float(found)))
+    join_ms_max, norm_ms_max = allmax(float(np.mean(join_ms))), allmax(float(np.mean(norm_ms)))
+    join_ms_min = -allmax(-float(np.mean(join_ms)))
     ms_per_step = total_ms / args.steps
     flop = 2.0 * n * n * d
     value = flop / (ms_per_step * 1e-3) / 1e12
@@ -348,7 +378,7 @@ def main() -> None:
     # the sort is outside the headline interval.
     symmetric = None
     if not args.no_extras:
-        sym_cap = max(capacity, n * 256 // world * 2)
+        sym_cap = max(capacity, n * per_point // world * 2)
         for _ in range(min(args.warmup, 1)):
             sj.join_symmetric_shard(eps, rank, world, capacity=sym_cap, flags=JOIN_NO_SORT)
         barrier()
@@ -359,14 +389,8 @@ def main() -> None:
             sym_found = int(st.pairs_found)
         ev1.record()
         barrier()
-        t = torch.tensor([ev0.elapsed_time(ev1), float(sym_found)], dtype=torch.float64, device="cuda")
-        if world > 1:
-            mx = t.clone()
-            dist.all_reduce(mx, op=dist.ReduceOp.MAX)
-            dist.all_reduce(t, op=dist.ReduceOp.SUM)
-            sym_ms, sym_found = float(mx[0]) / args.steps, int(t[1])
-        else:
-            sym_ms = float(t[0]) / args.steps
+        sym_ms = allmax(ev0.elapsed_time(ev1)) / args.steps
+        sym_found = int(allsum(float(sym_found)))
         symmetric = {"value": flop / (sym_ms * 1e-3) / 1e12, "unit": "TFLOPS", "ms_per_step": sym_ms,
                      "pairs_found": sym_found, "same_pair_count_as_full": sym_found == found_total,
                      "note": "2*N*N*D / time with the symmetric schedule; executed tensor flops are about half"}
@@ -374,74 +398,43 @@ def main() -> None:
     # ---- extra leg: accuracy against an FP64 brute-force join on a band of query rows ------------
     accuracy = None
     if rank == 0 and not args.no_extras:
-        a_rows = min(256, n)
-        q0 = max(0, (n // 2) // 128 * 128)
-        q0 = min(q0, n - a_rows)
-        st = sj.join(eps, q_begin=q0, q_end=q0 + a_rows, capacity=a_rows * 8192, flags=JOIN_DIST2)
-        got, got_d2 = sj.pairs(with_dist2=True)
-        rows = np.arange(q0, q0 + a_rows, dtype=np.int32)
-        _, truth = sj.brute_force_pairs(rows, eps, capacity=a_rows * 8192)
-        kg = (got[:, 0].astype(np.int64) << 32) | got[:, 1].astype(np.int64)
-        kt = (truth[:, 0].astype(np.int64) << 32) | truth[:, 1].astype(np.int64)
-        inter = np.intersect1d(kg, kt, assume_unique=True)
-        cg = np.bincount(got[:, 0] - q0, minlength=a_rows)
-        ct = np.bincount(truth[:, 0] - q0, minlength=a_rows)
-        ci = np.bincount((inter >> 32) - q0, minlength=a_rows)
-        union = cg + ct - ci
-        iou = np.where(union > 0, ci / np.maximum(union, 1), 1.0)
-        off = got[:, 0] != got[:, 1]
-        gi = torch.from_numpy(got[off].astype(np.int64)).cuda()
-        d64 = torch.empty(gi.shape[0], dtype=torch.float64, device="cuda")
-        for a in range(0, gi.shape[0], 4096):
-            xa = dev_pts[gi[a:a + 4096, 0], :d].double()
-            xb = dev_pts[gi[a:a + 4096, 1], :d].double()
-            d64[a:a + 4096] = ((xa - xb) ** 2).sum(dim=1).sqrt()
-        d32 = np.sqrt(np.maximum(got_d2[off].astype(np.float64), 0.0))
-        err = d32 - d64.cpu().numpy()
-        # the same band with correctly rounded norms (option exact_norms; not the reference's numerics)
-        sj.set_option("exact_norms", 1)
-        sj.join(eps, q_begin=q0, q_end=q0 + a_rows, capacity=a_rows * 8192)
-        got2 = sj.pairs()
-        sj.set_option("exact_norms", 0)
-        sj.row_norms_timed()
-        k2 = (got2[:, 0].astype(np.int64) << 32) | got2[:, 1].astype(np.int64)
-        inter2 = np.intersect1d(k2, kt, assume_unique=True)
-        c2 = np.bincount(got2[:, 0] - q0, minlength=a_rows)
-        ci2 = np.bincount((inter2 >> 32) - q0, minlength=a_rows)
-        un2 = c2 + ct - ci2
-        iou2 = np.where(un2 > 0, ci2 / np.maximum(un2, 1), 1.0)
-        accuracy = {"query_rows": [int(q0), int(q0 + a_rows)], "pairs_ours": int(len(kg)), "pairs_fp64": int(len(kt)),
-                    "with_exact_norms_option": {"pairs": int(len(k2)), "mean_per_point_iou": float(iou2.mean())},
-                    "mean_per_point_iou": float(iou.mean()), "min_per_point_iou": float(iou.min()),
-                    "distance_error_mean": float(err.mean()) if len(err) else 0.0,
-                    "distance_error_std": float(err.std()) if len(err) else 0.0,
-                    "truth": "FP64 direct-form brute force on the GPU (plain CUDA cores) over the same FP16 inputs"}
+        accuracy = accuracy_leg(sj, dev_pts, n, d, eps, per_point)
 
     # ---- timed region 2: end to end with host buffers -------------------------------------------
     e2e = None
     if not args.no_e2e:
-        # N = 1: the whole matrix in pinned host memory.  N > 1: every rank holds its own band of rows in
-        # pinned host memory (the data-parallel loader: G host links in parallel), uploads it and ONE
-        # in-place NCCL all-gather completes the matrix on every GPU.
+        # Every step: the dataset comes from pinned HOST memory, the sorted pair list ends in HOST memory.
+        # N = 1: fasted_set_points_host_f16, then fasted_join_stream, whose sort and device-to-host copy run
+        # chunk by chunk behind the join, into one pinned buffer.  N > 1: every rank holds its own band of rows
+        # on the host (the data-parallel loader: G host links in parallel), uploads it, ONE in-place NCCL
+        # all-gather completes the matrix on every GPU; every rank joins its band (sort pipelined behind the
+        # join), the per-rank counts are exchanged, and every rank's list lands in ONE shared, page-locked
+        # host buffer at its exclusive-scan offset: the global row-major list, assembled without a copy.
         pad_begin = rank * rows_per_band(n, world) if world > 1 else 0
         pad_end = pad_begin + rows_per_band(n, world) if world > 1 else n
         host_pts = torch.empty((pad_end - pad_begin, ld), dtype=torch.float16).pin_memory()
         host_pts.copy_(dev_pts[pad_begin:pad_end])
         torch.cuda.synchronize()
-        out_cap = int(min(capacity, max(1 << 20, 2 * found + 1024)))
-        host_out = torch.empty((out_cap, 2), dtype=torch.int32).pin_memory()
+        out_cap = int(min(n * per_point, max(1 << 20, int(1.05 * found_total) + 1024)))
+        engine = GpuBandEngine(sj)
+        engine.capacity_per_row = per_point
+        engine.capacity_rows = cap_rows
+        if world == 1:
+            host_out = torch.empty((out_cap, 2), dtype=torch.int32).pin_memory()
+            shared = None
+        else:
+            shared = SharedPairBuffer.collective(out_cap, register_cuda=True)
 
         def step_e2e():
             if world == 1:
                 sj.set_points_ptr(host_pts.data_ptr(), n, d, ld)
-            else:
-                dev_pts[pad_begin:pad_end].copy_(host_pts, non_blocking=True)
-                allgather_points(dev_pts, rank, world)
-                sj.set_points_device(dev_pts.data_ptr(), n, d, ld, keepalive=dev_pts)
-            st = sj.join(eps, q_begin=q_begin, q_end=q_end, capacity=capacity)
-            m = min(int(st.pairs_stored), out_cap)
-            sj.pairs_into(host_out.data_ptr(), m)
-            return st, m
+                st = sj.join_stream(eps, capacity=capacity, pairs_host=host_out.data_ptr(), host_capacity=out_cap)
+                return st, min(int(st.pairs_stored), out_cap)
+            dev_pts[pad_begin:pad_end].copy_(host_pts, non_blocking=True)
+            allgather_points(dev_pts, rank, world)
+            sj.set_points_device(dev_pts.data_ptr(), n, d, ld, keepalive=dev_pts)
+            _, _, stored = sharded_self_join(engine, n, eps, gather=False, bounds=bounds, shared=shared)
+            return engine.last_stats, stored
 
         e2e_warm = min(args.warmup, 1)
         for _ in range(e2e_warm):
@@ -450,29 +443,42 @@ def main() -> None:
         t0 = time.perf_counter()
         ev0.record()
         copied = 0
-        e2e_join_ms = []
+        e2e_join_ms, e2e_tail_ms, e2e_chunks = [], [], 0
         for _ in range(args.steps):
             st, copied = step_e2e()
             e2e_join_ms.append(st.join_ms)
+            e2e_tail_ms.append(st.tail_ms)
+            e2e_chunks = int(st.chunks)
         ev1.record()
         barrier()
         wall_ms = (time.perf_counter() - t0) * 1e3
-        e2e_ms = max(ev0.elapsed_time(ev1), wall_ms)
-        t = torch.tensor([e2e_ms], dtype=torch.float64, device="cuda")
-        if world > 1:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t[0]) / args.steps
-        d2h = torch.tensor([copied * 8], dtype=torch.int64, device="cuda")
-        if world > 1:
-            dist.all_reduce(d2h)  # byte counts are whole-job totals, like the value
+        e2e_ms = allmax(max(ev0.elapsed_time(ev1), wall_ms)) / args.steps
+        d2h = int(allsum(float(copied * 8)))  # byte counts are whole-job totals, like the value
         e2e = {"value": flop / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOPS", "ms_per_step": e2e_ms,
-               "h2d_bytes_per_step": host_pts.numel() * 2 * world, "d2h_bytes_per_step": int(d2h.item()),
-               "join_kernel_ms": float(np.mean(e2e_join_ms)),
-               "api": "fasted_set_points_host_f16 + fasted_join + fasted_get_pairs (pinned host buffers)"
-               if world == 1 else "per rank: pinned host band -> its GPU, one NCCL all-gather, fasted_join on the band, "
-                                    "fasted_get_pairs; byte counts are sums over the ranks"}
+               "h2d_bytes_per_step": host_pts.numel() * 2 * world, "d2h_bytes_per_step": d2h,
+               "join_kernel_ms": float(np.mean(e2e_join_ms)), "egress_tail_ms": float(np.mean(e2e_tail_ms)),
+               "join_launches_per_step": e2e_chunks,
+               "api": "fasted_set_points_host_f16 + fasted_join_stream (pinned host buffers; sort and device-to-host "
+                      "copy pipelined behind the join)"
+               if world == 1 else "per rank: pinned host band -> its GPU, one NCCL all-gather, fasted_join_stream on the "
+                                    "band, count exchange, fasted_get_pairs into one shared page-locked host buffer at "
+                                    "the exclusive-scan offset; byte counts are sums over the ranks"}
+        if shared is not None:
+            # the single list on the host: strictly ascending keys == every band in place, nothing missing
+            if rank == 0:
+                k = shared.array[:min(found_total, out_cap)].astype(np.int64)
+                keys = (k[:, 0] << 32) | k[:, 1]
+                e2e["single_host_list_sorted"] = bool((np.diff(keys) > 0).all()) and len(keys) == found_total
+                del k, keys
+            barrier()
+            shared.close()
         if world == 1:
             sj.set_points_device(dev_pts.data_ptr(), n, d, ld, keepalive=dev_pts)
+
+    # ---- the reference's own kernels on the same GPU and buffer (N = 1 only, outside all timing) ------
+    reference_gpu = None
+    if rank == 0 and world == 1 and not args.no_refgpu:
+        reference_gpu = reference_gpu_leg(SelfJoin, dev_pts, wl, eps, 100_000)
 
     # ---- CPU baseline on rank 0, N = 1 only ------------------------------------------------------
     cpu = None
@@ -496,21 +502,24 @@ def main() -> None:
                 "workload": f"{name}: self-join of {n} x {d} points, {wl['dist']} (seed {SEED}), FP16, "
                             f"eps for ~{wl['target']} neighbours per point",
                 "n": n, "d": d, "epsilon": eps, "mean_neighbours": (found_total - n) / n,
-                "parallelism": f"query-row bands x{world}" if world > 1 else "single GPU",
+                "parallelism": f"query-row bands x{world}" + ("" if args.no_balance else ", sized by the rate each GPU "
+                               "showed in the warm-up") if world > 1 else "single GPU",
+                "bands": bounds if world > 1 else None,
+                "band_rates_rows_per_ms": rates,
                 "l2": "inputs larger than L2 (no flush needed)" if n * ld * 2 > 2 * 126e6 else "inputs fit L2",
                 "baseline_note": "vs_baseline divides by the reference's published A100-PCIe figure for this shape "
                                  "(153.64 TFLOPS at eps=0.001)" if name in PUBLISHED_A100_TFLOPS else None,
             },
             "pairs_found": found_total, "pairs_per_s": found_total / (ms_per_step * 1e-3),
             "frac_of_nominal_fp16_peak": value / (NOMINAL_FP16_TFLOPS * world),
-            "kernel_ms": {"join": join_ms_max, "norms": norm_ms_max},
+            "kernel_ms": {"join": join_ms_max, "join_fastest_rank": join_ms_min, "norms": norm_ms_max},
             "clocks": clocks,
             # from the kernel's own cycle counter (CTA 0): mean SM clock of the join launches and the share of
             # CTA 0's cycles that its tiles' tensor work needs at full rate (k_steps x 4 MMAs x 128 clocks a tile)
             "sm_clock_in_kernel_mhz": float(np.mean(cyc)) / (float(np.mean(join_ms)) * 1e3) if cyc and cyc[0] else None,
             "tensor_busy_share_cta0": (tiles0 * (-(-d // 64)) * 512.0) / float(np.mean(cyc)) if cyc and cyc[0] else None,
             "e2e": e2e,
-            "gpu_launches": 2 * args.steps,
+            "gpu_launches": 3 * args.steps,  # per step: row_norms_kernel, join_kernel, unpack_pairs_kernel
             "roofline": {"bound": "tensor", "kernel": "join_kernel", "achieved": achieved, "peak": peak,
                          "unit": "TFLOP/s", "frac": achieved / peak if peak else None,
                          # DRAM bytes per launch: ncu measured one pass over the candidates per raster band
@@ -523,6 +532,7 @@ def main() -> None:
                          "norms_kernel": {"bound": "hbm", "achieved": (n * ld * 2 + n * 4) / (float(np.mean(norm_ms)) * 1e-3) / 1e9,
                                           "peak": peaks["hbm"], "unit": "GB/s"}},
             "cpu_baseline": cpu,
+            "reference_gpu": reference_gpu,
             "symmetric": symmetric,
             "accuracy_vs_fp64": accuracy,
         }
@@ -533,6 +543,56 @@ def main() -> None:
         dist.barrier()
         dist.destroy_process_group()
     sj.close()
+
+
+def accuracy_leg(sj, dev_pts, n: int, d: int, eps: float, per_point: int) -> dict:
+    """Pair set and distances of a band of query rows against an FP64 brute-force join on the device (the
+    reference's accuracy tables report the same two figures: per-point IoU and signed distance error)."""
+    import torch
+    from fasted_b200 import JOIN_DIST2
+    a_rows = min(256, n)
+    q0 = max(0, (n // 2) // 128 * 128)
+    q0 = min(q0, n - a_rows)
+    cap = a_rows * max(8192, 4 * per_point)
+    sj.join(eps, q_begin=q0, q_end=q0 + a_rows, capacity=cap, flags=JOIN_DIST2)
+    got, got_d2 = sj.pairs(with_dist2=True)
+    rows = np.arange(q0, q0 + a_rows, dtype=np.int32)
+    _, truth = sj.brute_force_pairs(rows, eps, capacity=cap)
+    kg = (got[:, 0].astype(np.int64) << 32) | got[:, 1].astype(np.int64)
+    kt = (truth[:, 0].astype(np.int64) << 32) | truth[:, 1].astype(np.int64)
+    inter = np.intersect1d(kg, kt, assume_unique=True)
+    cg = np.bincount(got[:, 0] - q0, minlength=a_rows)
+    ct = np.bincount(truth[:, 0] - q0, minlength=a_rows)
+    ci = np.bincount((inter >> 32) - q0, minlength=a_rows)
+    union = cg + ct - ci
+    iou = np.where(union > 0, ci / np.maximum(union, 1), 1.0)
+    off = got[:, 0] != got[:, 1]
+    gi = torch.from_numpy(got[off].astype(np.int64)).cuda()
+    d64 = torch.empty(gi.shape[0], dtype=torch.float64, device="cuda")
+    for a in range(0, gi.shape[0], 4096):
+        xa = dev_pts[gi[a:a + 4096, 0], :d].double()
+        xb = dev_pts[gi[a:a + 4096, 1], :d].double()
+        d64[a:a + 4096] = ((xa - xb) ** 2).sum(dim=1).sqrt()
+    d32 = np.sqrt(np.maximum(got_d2[off].astype(np.float64), 0.0))
+    err = d32 - d64.cpu().numpy()
+    # the same band with correctly rounded norms (option exact_norms; not the reference's numerics)
+    sj.set_option("exact_norms", 1)
+    sj.join(eps, q_begin=q0, q_end=q0 + a_rows, capacity=cap)
+    got2 = sj.pairs()
+    sj.set_option("exact_norms", 0)
+    sj.row_norms_timed()
+    k2 = (got2[:, 0].astype(np.int64) << 32) | got2[:, 1].astype(np.int64)
+    inter2 = np.intersect1d(k2, kt, assume_unique=True)
+    c2 = np.bincount(got2[:, 0] - q0, minlength=a_rows)
+    ci2 = np.bincount((inter2 >> 32) - q0, minlength=a_rows)
+    un2 = c2 + ct - ci2
+    iou2 = np.where(un2 > 0, ci2 / np.maximum(un2, 1), 1.0)
+    return {"query_rows": [int(q0), int(q0 + a_rows)], "pairs_ours": int(len(kg)), "pairs_fp64": int(len(kt)),
+            "with_exact_norms_option": {"pairs": int(len(k2)), "mean_per_point_iou": float(iou2.mean())},
+            "mean_per_point_iou": float(iou.mean()), "min_per_point_iou": float(iou.min()),
+            "distance_error_mean": float(err.mean()) if len(err) else 0.0,
+            "distance_error_std": float(err.std()) if len(err) else 0.0,
+            "truth": "FP64 direct-form brute force on the GPU (plain CUDA cores) over the same FP16 inputs"}
 
 
 if __name__ == "__main__":

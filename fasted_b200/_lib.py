@@ -43,6 +43,8 @@ class JoinStats(ctypes.Structure):
         ("grid", ctypes.c_int),
         ("cta0_cycles", ctypes.c_ulonglong),
         ("cta0_tiles", ctypes.c_ulonglong),
+        ("chunks", ctypes.c_int),
+        ("tail_ms", ctypes.c_double),
     ]
 
     def as_dict(self) -> dict:
@@ -58,8 +60,11 @@ DECLARED_SYMBOLS = [
     "fasted_points_info", "fasted_get_points_host_f16", "fasted_get_rows_host_f16", "fasted_row_norms", "fasted_get_norms",
     "fasted_join", "fasted_selftest_wait_timeout", "fasted_join_symmetric_shard", "fasted_tile_schedule", "fasted_estimate_epsilon", "fasted_get_pairs", "fasted_pairs_device", "fasted_brute_force_f64", "fasted_brute_force_f64_pairs", "fasted_set_option",
     "fasted_dataset_exponential_f16", "fasted_dataset_csv_shape", "fasted_dataset_csv_f16",
-    "fasted_join_static_scratch",
+    "fasted_join_static_scratch", "fasted_join_stream",
 ]
+
+CHUNK_FN = ctypes.CFUNCTYPE(ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_uint64,
+                            ctypes.c_uint64)
 
 _lib = None
 
@@ -91,6 +96,8 @@ def load() -> ctypes.CDLL:
     L.fasted_row_norms.argtypes = [_vp, ctypes.POINTER(ctypes.c_double)]
     L.fasted_get_norms.argtypes = [_vp, _vp]
     L.fasted_join.argtypes = [_vp, ctypes.c_double, _i64, _i64, _u64, ctypes.c_uint, ctypes.POINTER(JoinStats)]
+    L.fasted_join_stream.argtypes = [_vp, ctypes.c_double, _i64, _i64, _u64, ctypes.c_uint, _vp, _vp, _u64, CHUNK_FN,
+                                     _vp, ctypes.POINTER(JoinStats)]
     L.fasted_tile_schedule.argtypes = [_i64, _i64, _i64, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
                                        ctypes.c_int, ctypes.c_int, ctypes.c_int, _vp, _i64, ctypes.POINTER(_i64)]
     L.fasted_join_symmetric_shard.argtypes = [_vp, ctypes.c_double, ctypes.c_int, ctypes.c_int, _u64, ctypes.c_uint,
@@ -262,6 +269,36 @@ class SelfJoin:
         _check(self._L.fasted_join(self._h, float(eps), q_begin, q_end, capacity, flags, ctypes.byref(st)))
         self._last = st
         self._last_dist = bool(flags & JOIN_DIST2)
+        return st
+
+    def join_stream(self, eps: float, q_begin: int = 0, q_end: int = -1, capacity: int = 0, flags: int = 0,
+                    pairs_host: int = 0, dist2_host: int = 0, host_capacity: int = 0, on_chunk=None) -> JoinStats:
+        """fasted_join_stream: the join with sort and device-to-host copy pipelined behind it.
+        pairs_host / dist2_host are raw host addresses (e.g. a pinned tensor's data_ptr()) or 0;
+        on_chunk(pairs (m, 2) int32, dist2 (m,) float32 or None, first) sees every run of records (views that
+        are valid during the call only when no destination buffer was given)."""
+        st = JoinStats()
+        want_dist = bool(flags & JOIN_DIST2)
+
+        def trampoline(_user, pairs_ptr, dist_ptr, first, count):
+            try:
+                pr = np.ctypeslib.as_array(ctypes.cast(pairs_ptr, ctypes.POINTER(ctypes.c_int32)), shape=(count, 2))
+                d2 = (np.ctypeslib.as_array(ctypes.cast(dist_ptr, ctypes.POINTER(ctypes.c_float)), shape=(count,))
+                      if dist_ptr and want_dist else None)
+                return int(on_chunk(pr, d2, int(first)) or 0)
+            except Exception as exc:  # noqa: BLE001 - reported after the call returns
+                self._chunk_error = exc
+                return 1
+
+        self._chunk_error = None
+        cb = CHUNK_FN(trampoline) if on_chunk is not None else ctypes.cast(None, CHUNK_FN)
+        rc = self._L.fasted_join_stream(self._h, float(eps), q_begin, q_end, capacity, flags, _vp(pairs_host or None),
+                                        _vp(dist2_host or None), host_capacity, cb, None, ctypes.byref(st))
+        if self._chunk_error is not None:
+            raise self._chunk_error
+        _check(rc)
+        self._last = st
+        self._last_dist = want_dist
         return st
 
     def estimate_epsilon(self, target_mean_neighbours: float, sample_rows: int = 0, rel_tol: float = 0.01):

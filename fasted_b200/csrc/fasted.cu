@@ -96,6 +96,15 @@ struct fasted_ctx {
 
     cudaEvent_t ev[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
 
+    // egress pipeline of fasted_join_stream: a chunk's sort and its device-to-host copy run on
+    // streams of their own (highest priority) while the next chunks are being joined
+    cudaStream_t sort_stream = nullptr, copy_stream = nullptr;
+    std::vector<cudaEvent_t> chunk_ev;            // end of each chunk's join launch
+    cudaEvent_t ev_sorted = nullptr, ev_copied[2] = {nullptr, nullptr};
+    unsigned long long* chunk_end_host = nullptr;  // pinned: the found counter after each chunk
+    size_t chunk_end_cap = 0;
+    int stream_chunk_bands = 0;                    // option: raster bands per chunk (0 = automatic)
+
     // pinned staging for transfers from / to pageable host memory
     void* stage_buf[2] = {nullptr, nullptr};
     cudaEvent_t stage_ev[2] = {nullptr, nullptr};
@@ -106,6 +115,12 @@ struct fasted_ctx {
     int cta_pair = 0;  // 1: CTA-pair kernel (256 x 256 tiles on 2-CTA clusters)
     int exact_norms = 0;  // 1: correctly rounded norms instead of the reference's round-toward-zero chain
     int max_pair_clusters = 0;
+};
+
+struct JoinPlan {
+    fasted::JoinParams p;
+    int grid;
+    bool pair;
 };
 
 namespace {
@@ -234,11 +249,12 @@ void parallel_copy(void* dst, const void* src, size_t bytes) {
 // rows x row_bytes from host (pitch src_pitch) to device (pitch dst_pitch).
 cudaError_t upload_rows(fasted_ctx* c, void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t row_bytes,
                         size_t rows) {
-    if (host_is_pinned(src) || rows * row_bytes < (size_t(8) << 20))
+    // (a single row wider than a staging buffer also takes the plain copy)
+    if (host_is_pinned(src) || rows * row_bytes < (size_t(8) << 20) || row_bytes > kStageBytes)
         return cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, row_bytes, rows, cudaMemcpyHostToDevice, c->stream);
     cudaError_t e = ensure_staging(c);
     if (e != cudaSuccess) return e;
-    const size_t rows_per_chunk = std::max<size_t>(1, kStageBytes / row_bytes);
+    const size_t rows_per_chunk = kStageBytes / row_bytes;  // >= 1: wider rows took the plain copy above
     int which = 0;
     for (size_t r0 = 0; r0 < rows; r0 += rows_per_chunk, which ^= 1) {
         const size_t nr = std::min(rows_per_chunk, rows - r0);
@@ -263,10 +279,10 @@ cudaError_t upload_rows(fasted_ctx* c, void* dst, size_t dst_pitch, const void* 
 }
 
 // bytes from device to host; returns after the data is in dst.
-cudaError_t download_bytes(fasted_ctx* c, void* dst, const void* src, size_t bytes) {
+cudaError_t download_bytes(fasted_ctx* c, void* dst, const void* src, size_t bytes, cudaStream_t stream) {
     if (host_is_pinned(dst) || bytes < (size_t(8) << 20)) {
-        cudaError_t e = cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, c->stream);
-        return e != cudaSuccess ? e : cudaStreamSynchronize(c->stream);
+        cudaError_t e = cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, stream);
+        return e != cudaSuccess ? e : cudaStreamSynchronize(stream);
     }
     cudaError_t e = ensure_staging(c);
     if (e != cudaSuccess) return e;
@@ -275,9 +291,9 @@ cudaError_t download_bytes(fasted_ctx* c, void* dst, const void* src, size_t byt
         if (i < chunks) {  // start chunk i
             const size_t off = i * kStageBytes, nb = std::min(kStageBytes, bytes - off);
             e = cudaMemcpyAsync(c->stage_buf[i & 1], static_cast<const char*>(src) + off, nb, cudaMemcpyDeviceToHost,
-                                c->stream);
+                                stream);
             if (e != cudaSuccess) return e;
-            e = cudaEventRecord(c->stage_ev[i & 1], c->stream);
+            e = cudaEventRecord(c->stage_ev[i & 1], stream);
             if (e != cudaSuccess) return e;
         }
         if (i > 0) {  // drain chunk i - 1 while chunk i is on its way
@@ -306,8 +322,8 @@ int ensure_pair_buffers(fasted_ctx* c, uint64_t capacity, bool want_dist) {
     // Buffers only grow: probes with a tiny capacity (epsilon search) must not throw away the
     // buffers of the full join that follows.
     if (c->capacity >= capacity && (!want_dist || c->have_dist_buf)) return FASTED_OK;
+    const uint64_t cap = std::max<uint64_t>(std::max<uint64_t>(capacity, c->capacity), 1);
     free_pair_buffers(c);
-    const uint64_t cap = std::max<uint64_t>(capacity, 1);
     CU_TRY(cudaMalloc(&c->keys, cap * 8));
     CU_TRY(cudaMalloc(&c->keys_alt, cap * 8));
     if (want_dist) {
@@ -347,7 +363,13 @@ int fasted_create(int device, fasted_ctx** out) {
         return fail(FASTED_ECUDA, "cudaStreamCreate failed");
     }
     c->owns_stream = true;
-    for (auto& ev : c->ev) cudaEventCreate(&ev);
+    for (auto& ev : c->ev) {
+        if (cudaEventCreate(&ev) != cudaSuccess) {
+            ev = nullptr;
+            fasted_destroy(c);
+            return fail(FASTED_ECUDA, "cudaEventCreate failed");
+        }
+    }
     if (cudaMalloc(&c->counters, 8 * sizeof(unsigned long long)) != cudaSuccess) {
         fasted_destroy(c);
         return fail(FASTED_ECUDA, "cudaMalloc of counters failed");
@@ -402,6 +424,14 @@ void fasted_destroy(fasted_ctx* c) {
         if (c->stage_buf[i]) cudaFreeHost(c->stage_buf[i]);
         if (c->stage_ev[i]) cudaEventDestroy(c->stage_ev[i]);
     }
+    for (cudaEvent_t ev : c->chunk_ev)
+        if (ev) cudaEventDestroy(ev);
+    if (c->ev_sorted) cudaEventDestroy(c->ev_sorted);
+    for (auto& ev : c->ev_copied)
+        if (ev) cudaEventDestroy(ev);
+    if (c->chunk_end_host) cudaFreeHost(c->chunk_end_host);
+    if (c->sort_stream) cudaStreamDestroy(c->sort_stream);
+    if (c->copy_stream) cudaStreamDestroy(c->copy_stream);
     if (c->owns_stream && c->stream) cudaStreamDestroy(c->stream);
     delete c;
 }
@@ -429,6 +459,9 @@ int fasted_set_option(fasted_ctx* c, const char* name, int64_t value) {
     } else if (!strcmp(name, "cta_pair")) {
         if (value != 0 && value != 1) return fail(FASTED_EINVAL, "cta_pair must be 0 or 1");
         c->cta_pair = static_cast<int>(value);
+    } else if (!strcmp(name, "stream_chunk_bands")) {
+        if (value < 0 || value > (1 << 20)) return fail(FASTED_EINVAL, "stream_chunk_bands out of range");
+        c->stream_chunk_bands = static_cast<int>(value);
     } else if (!strcmp(name, "grid")) {
         if (value < 0 || value > 65535) return fail(FASTED_EINVAL, "grid out of range");
         c->grid = static_cast<int>(value);
@@ -625,35 +658,30 @@ int fasted_get_norms(fasted_ctx* c, float* host_out) {
     return FASTED_OK;
 }
 
-static int join_impl(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end, uint64_t capacity, unsigned flags,
-                     int shard_rank, int shard_world, fasted_join_stats* stats) {
-    if (!c) return fail(FASTED_EINVAL, "ctx is null");
-    if (!c->points) return fail(FASTED_ESTATE, "no dataset is resident");
-    if (q_end < 0) q_end = c->n;
-    if (q_begin < 0 || q_begin > q_end || q_end > c->n)
-        return fail(FASTED_EINVAL, "query band [%lld, %lld) outside [0, %lld)", (long long)q_begin, (long long)q_end,
-                    (long long)c->n);
-    // Only eps*eps is used, as in the reference (source/findPairs.cuh:678): a negative epsilon
-    // means the same as its absolute value; NaN is refused.
-    if (eps != eps) return fail(FASTED_EINVAL, "epsilon is NaN");
-    CU_TRY(cudaSetDevice(c->device));
-    const bool want_dist = (flags & FASTED_JOIN_DIST2) != 0;
+// ---------------------------------------------------------------------------
+// The join: planning, launch, results
+// ---------------------------------------------------------------------------
 
-    if (capacity == 0) {
-        // The reference's sizing rule: n * 256 pairs, reduced to what fits in free memory.
-        capacity = static_cast<uint64_t>(c->n) * 256ull;
-        if (c->capacity < capacity) {
-            size_t free_b = 0, total_b = 0;
-            CU_TRY(cudaMemGetInfo(&free_b, &total_b));
-            free_b += c->capacity * (c->have_dist_buf ? 24 : 16);
-            const uint64_t per_pair = want_dist ? 24 + 2 : 16 + 2;  // keys x2 (+ dist x2) + sort scratch slack
-            const uint64_t fit = static_cast<uint64_t>(free_b * 0.9) / per_pair;
-            if (capacity > fit) capacity = fit;
-        }
+// The reference's sizing rule for the pair buffer: n * 256 pairs, reduced to what fits in free
+// memory (source/findPairs.cuh:642-647, source/pair.cuh:69-91).
+static int default_capacity(fasted_ctx* c, bool want_dist, uint64_t* out) {
+    uint64_t capacity = static_cast<uint64_t>(c->n) * 256ull;
+    if (c->capacity < capacity) {
+        size_t free_b = 0, total_b = 0;
+        CU_TRY(cudaMemGetInfo(&free_b, &total_b));
+        free_b += c->capacity * (c->have_dist_buf ? 24 : 16);
+        const uint64_t per_pair = want_dist ? 24 + 2 : 16 + 2;  // keys x2 (+ dist x2) + sort scratch slack
+        const uint64_t fit = static_cast<uint64_t>(free_b * 0.9) / per_pair;
+        if (capacity > fit) capacity = fit;
     }
-    int rc = ensure_pair_buffers(c, capacity, want_dist);
-    if (rc) return rc;
+    *out = capacity;
+    return FASTED_OK;
+}
 
+// Kernel parameters and grid of one launch over query rows [q_begin, q_end).
+static int plan_join(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end, uint64_t capacity, unsigned flags,
+                     int shard_rank, int shard_world, JoinPlan* out) {
+    const bool want_dist = (flags & FASTED_JOIN_DIST2) != 0;
     fasted::JoinParams p{};
     p.norms = c->norms;
     p.norms_vec4 = (reinterpret_cast<uintptr_t>(p.norms) & 15u) == 0 ? 1 : 0;
@@ -677,6 +705,8 @@ static int join_impl(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end, 
     p.shard_rank = shard_rank;
     p.shard_world = shard_world;
     p.raw_dot = (flags & FASTED_JOIN_RAW_DOT) && want_dist ? 1 : 0;
+    p.key_shift = 32;
+    p.key_qbase = 0;
     if (shard_world > 1 && !symmetric) return fail(FASTED_EINVAL, "band snakes are for the symmetric schedule only");
     p.tiles_m = static_cast<int>((q_end - q_begin + tile_m - 1) / tile_m);
     p.tiles_n = static_cast<int>((c->n + fasted::kTileN - 1) / fasted::kTileN);
@@ -694,17 +724,17 @@ static int join_impl(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end, 
         grid = c->grid > 0 ? c->grid : c->num_sms;
         if (p.total_tiles < grid) grid = static_cast<int>(std::max<long long>(p.total_tiles, 1));
     }
+    out->p = p;
+    out->grid = grid;
+    out->pair = pair;
+    return FASTED_OK;
+}
 
-    CU_TRY(cudaMemsetAsync(c->counters, 0, 8 * sizeof(unsigned long long), c->stream));
-    CU_TRY(cudaEventRecord(c->ev[0], c->stream));
-    if (!(flags & FASTED_JOIN_KEEP_NORMS) || !c->norms_valid) {
-        rc = launch_norms(c);
-        if (rc) return rc;
-    }
-    CU_TRY(cudaEventRecord(c->ev[1], c->stream));
-    if (p.total_tiles > 0 && pair) {
+static int launch_join(fasted_ctx* c, const JoinPlan& pl) {
+    if (pl.p.total_tiles <= 0) return FASTED_OK;
+    if (pl.pair) {
         cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(grid);
+        cfg.gridDim = dim3(pl.grid);
         cfg.blockDim = dim3(fasted::kJoinThreads);
         cfg.dynamicSmemBytes = fasted::kPairSmemBytes;
         cfg.stream = c->stream;
@@ -715,19 +745,116 @@ static int join_impl(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end, 
         attr.val.clusterDim.z = 1;
         cfg.attrs = &attr;
         cfg.numAttrs = 1;
-        CU_TRY(cudaLaunchKernelEx(&cfg, fasted::join_pair_kernel, c->map_a, p));
-    } else if (p.total_tiles > 0) {
-        fasted::join_kernel<<<grid, fasted::kJoinThreads, fasted::kJoinSmemBytes, c->stream>>>(c->map_a, c->map_b, p);
+        CU_TRY(cudaLaunchKernelEx(&cfg, fasted::join_pair_kernel, c->map_a, pl.p));
+    } else {
+        fasted::join_kernel<<<pl.grid, fasted::kJoinThreads, fasted::kJoinSmemBytes, c->stream>>>(c->map_a, c->map_b,
+                                                                                                 pl.p);
         CU_TRY(cudaGetLastError());
     }
+    return FASTED_OK;
+}
+
+static int check_join_args(fasted_ctx* c, double eps, int64_t q_begin, int64_t* q_end) {
+    if (!c) return fail(FASTED_EINVAL, "ctx is null");
+    if (!c->points) return fail(FASTED_ESTATE, "no dataset is resident");
+    if (*q_end < 0) *q_end = c->n;
+    if (q_begin < 0 || q_begin > *q_end || *q_end > c->n)
+        return fail(FASTED_EINVAL, "query band [%lld, %lld) outside [0, %lld)", (long long)q_begin, (long long)*q_end,
+                    (long long)c->n);
+    // Only eps*eps is used, as in the reference (source/findPairs.cuh:678): a negative epsilon
+    // means the same as its absolute value; NaN is refused.
+    if (eps != eps) return fail(FASTED_EINVAL, "epsilon is NaN");
+    return FASTED_OK;
+}
+
+static void fill_stats(fasted_ctx* c, const JoinPlan& pl, const unsigned long long* h, uint64_t stored,
+                       fasted_join_stats* stats) {
+    if (!stats) return;
+    float t01 = 0, t12 = 0, t02 = 0, t34 = 0;
+    cudaEventElapsedTime(&t01, c->ev[0], c->ev[1]);
+    cudaEventElapsedTime(&t12, c->ev[1], c->ev[2]);
+    cudaEventElapsedTime(&t02, c->ev[0], c->ev[2]);
+    cudaEventElapsedTime(&t34, c->ev[3], c->ev[4]);
+    stats->pairs_found = h[0];
+    stats->pairs_stored = stored;
+    stats->norms_ms = t01;
+    stats->join_ms = t12;
+    stats->kernel_ms = t02;
+    stats->sort_ms = t34;
+    stats->status = h[2];
+    stats->tiles_m = pl.p.tiles_m;
+    stats->tiles_n = pl.p.tiles_n;
+    stats->grid = pl.grid;
+    stats->cta0_cycles = pl.pair ? 0 : h[4];
+    stats->cta0_tiles = 0;
+    stats->chunks = 1;
+    stats->tail_ms = 0;
+    if (!pl.pair && pl.p.total_tiles > 0) {
+        fasted::TileIter ti;
+        for (ti.init(pl.p, 0, pl.grid); ti.valid; ti.advance(pl.p)) ++stats->cta0_tiles;
+    }
+}
+
+static int unpack_blocks(fasted_ctx* c, uint64_t count) {
+    return static_cast<int>(std::min<uint64_t>((count + 255) / 256, static_cast<uint64_t>(c->num_sms) * 16));
+}
+
+static int join_impl(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end, uint64_t capacity, unsigned flags,
+                     int shard_rank, int shard_world, fasted_join_stats* stats) {
+    int rc = check_join_args(c, eps, q_begin, &q_end);
+    if (rc) return rc;
+    CU_TRY(cudaSetDevice(c->device));
+    const bool want_dist = (flags & FASTED_JOIN_DIST2) != 0;
+    if (capacity == 0) {
+        rc = default_capacity(c, want_dist, &capacity);
+        if (rc) return rc;
+    }
+    rc = ensure_pair_buffers(c, capacity, want_dist);
+    if (rc) return rc;
+    JoinPlan pl;
+    rc = plan_join(c, eps, q_begin, q_end, capacity, flags, shard_rank, shard_world, &pl);
+    if (rc) return rc;
+
+    CU_TRY(cudaMemsetAsync(c->counters, 0, 8 * sizeof(unsigned long long), c->stream));
+    CU_TRY(cudaEventRecord(c->ev[0], c->stream));
+    if (!(flags & FASTED_JOIN_KEEP_NORMS) || !c->norms_valid) {
+        rc = launch_norms(c);
+        if (rc) return rc;
+    }
+    CU_TRY(cudaEventRecord(c->ev[1], c->stream));
+    rc = launch_join(c, pl);
+    if (rc) return rc;
     CU_TRY(cudaEventRecord(c->ev[2], c->stream));
     unsigned long long h[5] = {0, 0, 0, 0, 0};
-    CU_TRY(cudaMemcpyAsync(h, c->counters, sizeof(h), cudaMemcpyDeviceToHost, c->stream));
-    CU_TRY(cudaStreamSynchronize(c->stream));
-    c->norms_valid = (h[2] & fasted::kErrNormWait) == 0;
     c->stored = 0;
     c->result_pairs = nullptr;
     c->result_dist = nullptr;
+
+    if (flags & FASTED_JOIN_NO_SORT) {
+        // Device order is the result: the records are unpacked by a kernel that reads the count on the
+        // device, so the call needs the host only once, at its end (what a sweep of small joins pays
+        // per call is launch and synchronisation latency, not kernel time).
+        CU_TRY(cudaEventRecord(c->ev[3], c->stream));
+        fasted::unpack_pairs_kernel<<<unpack_blocks(c, capacity), 256, 0, c->stream>>>(
+            c->keys, reinterpret_cast<int2*>(c->keys_alt), capacity, c->counters, 0ull, 32, 0);
+        CU_TRY(cudaGetLastError());
+        CU_TRY(cudaEventRecord(c->ev[4], c->stream));
+        CU_TRY(cudaMemcpyAsync(h, c->counters, sizeof(h), cudaMemcpyDeviceToHost, c->stream));
+        CU_TRY(cudaStreamSynchronize(c->stream));
+        c->norms_valid = (h[2] & fasted::kErrNormWait) == 0;
+        if (h[2]) return fail(FASTED_EKERNEL, "a device-side wait ran out (status 0x%llx)", h[2]);
+        const uint64_t stored = std::min<uint64_t>(h[0], capacity);
+        c->stored = stored;
+        c->result_pairs = c->keys_alt;
+        c->result_dist = want_dist ? c->dist : nullptr;
+        c->result_sorted = false;
+        fill_stats(c, pl, h, stored, stats);
+        return FASTED_OK;
+    }
+
+    CU_TRY(cudaMemcpyAsync(h, c->counters, sizeof(h), cudaMemcpyDeviceToHost, c->stream));
+    CU_TRY(cudaStreamSynchronize(c->stream));
+    c->norms_valid = (h[2] & fasted::kErrNormWait) == 0;
     if (h[2]) return fail(FASTED_EKERNEL, "a device-side wait ran out (status 0x%llx)", h[2]);
     // Every record with a slot below the capacity is written, the others are dropped.
     const uint64_t stored = std::min<uint64_t>(h[0], capacity);
@@ -735,7 +862,7 @@ static int join_impl(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end, 
     CU_TRY(cudaEventRecord(c->ev[3], c->stream));
     const unsigned long long* sorted_keys = c->keys;
     float* sorted_dist = c->dist;
-    if (!(flags & FASTED_JOIN_NO_SORT) && stored > 1) {
+    if (stored > 1) {
         // Row-major order of (query, candidate) == numeric order of the packed key
         // (replaces thrust::sort with Pair::operator<, source/pair.cuh:39-45, 151-158).
         int end_bit = 33;
@@ -764,9 +891,8 @@ static int join_impl(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end, 
         sorted_dist = c->dist;
     }
     if (stored > 0) {
-        const int blocks = static_cast<int>(std::min<uint64_t>((stored + 255) / 256, static_cast<uint64_t>(c->num_sms) * 16));
-        fasted::unpack_pairs_kernel<<<blocks, 256, 0, c->stream>>>(sorted_keys, reinterpret_cast<int2*>(c->keys_alt),
-                                                                  stored);
+        fasted::unpack_pairs_kernel<<<unpack_blocks(c, stored), 256, 0, c->stream>>>(
+            sorted_keys, reinterpret_cast<int2*>(c->keys_alt), stored, nullptr, 0ull, 32, 0);
         CU_TRY(cudaGetLastError());
     }
     CU_TRY(cudaEventRecord(c->ev[4], c->stream));
@@ -774,31 +900,8 @@ static int join_impl(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end, 
     c->stored = stored;
     c->result_pairs = c->keys_alt;
     c->result_dist = want_dist ? sorted_dist : nullptr;
-    c->result_sorted = !(flags & FASTED_JOIN_NO_SORT);
-
-    if (stats) {
-        float t01 = 0, t12 = 0, t02 = 0, t34 = 0;
-        cudaEventElapsedTime(&t01, c->ev[0], c->ev[1]);
-        cudaEventElapsedTime(&t12, c->ev[1], c->ev[2]);
-        cudaEventElapsedTime(&t02, c->ev[0], c->ev[2]);
-        cudaEventElapsedTime(&t34, c->ev[3], c->ev[4]);
-        stats->pairs_found = h[0];
-        stats->pairs_stored = stored;
-        stats->norms_ms = t01;
-        stats->join_ms = t12;
-        stats->kernel_ms = t02;
-        stats->sort_ms = t34;
-        stats->status = h[2];
-        stats->tiles_m = p.tiles_m;
-        stats->tiles_n = p.tiles_n;
-        stats->grid = grid;
-        stats->cta0_cycles = pair ? 0 : h[4];
-        stats->cta0_tiles = 0;
-        if (!pair && p.total_tiles > 0) {
-            fasted::TileIter ti;
-            for (ti.init(p, 0, grid); ti.valid; ti.advance(p)) ++stats->cta0_tiles;
-        }
-    }
+    c->result_sorted = true;
+    fill_stats(c, pl, h, stored, stats);
     return FASTED_OK;
 }
 
@@ -811,6 +914,254 @@ int fasted_join_symmetric_shard(fasted_ctx* c, double eps, int shard_rank, int s
                                 unsigned flags, fasted_join_stats* stats) {
     if (shard_world < 1 || shard_rank < 0 || shard_rank >= shard_world) return fail(FASTED_EINVAL, "bad shard");
     return join_impl(c, eps, 0, -1, capacity, flags | FASTED_JOIN_SYMMETRIC, shard_rank, shard_world, stats);
+}
+
+// ---------------------------------------------------------------------------
+// The join with pipelined egress
+// ---------------------------------------------------------------------------
+//
+// The reference sorts the whole pair list after its kernel and then copies it to the host
+// (source/findPairs.cuh:699-716, source/pair.cuh:139-158): three serial phases.  Here the query range
+// is cut into chunks of whole raster bands, one join launch per chunk, all enqueued at once.  The
+// launches share one found counter, so chunk k's records occupy the slots between the counter's
+// value after chunk k-1 and after chunk k; and because chunks are contiguous, ascending ranges of
+// query rows, the chunks' sorted lists laid end to end ARE the global row-major order.  While the GPU
+// joins chunk k+1 the host picks up chunk k: its slice is sorted (keys packed relative to the chunk,
+// so the radix sort sees only bits(n) + bits(chunk rows) significant bits), unpacked and copied to
+// the host on two high-priority streams.  When the last launch retires, only the last chunk's sort
+// and copy are still to come.
+
+static int ensure_stream_pipeline(fasted_ctx* c, size_t chunks) {
+    if (!c->sort_stream) {
+        int lo = 0, hi = 0;
+        CU_TRY(cudaDeviceGetStreamPriorityRange(&lo, &hi));
+        CU_TRY(cudaStreamCreateWithPriority(&c->sort_stream, cudaStreamNonBlocking, hi));
+        CU_TRY(cudaStreamCreateWithPriority(&c->copy_stream, cudaStreamNonBlocking, hi));
+        CU_TRY(cudaEventCreateWithFlags(&c->ev_sorted, cudaEventDisableTiming));
+        for (auto& ev : c->ev_copied) CU_TRY(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+    }
+    while (c->chunk_ev.size() < chunks) {
+        cudaEvent_t ev = nullptr;
+        CU_TRY(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+        c->chunk_ev.push_back(ev);
+    }
+    if (c->chunk_end_cap < chunks) {
+        if (c->chunk_end_host) cudaFreeHost(c->chunk_end_host);
+        c->chunk_end_host = nullptr;
+        c->chunk_end_cap = 0;
+        CU_TRY(cudaMallocHost(&c->chunk_end_host, chunks * sizeof(unsigned long long)));
+        c->chunk_end_cap = chunks;
+    }
+    return FASTED_OK;
+}
+
+static int bits_of(uint64_t v) {  // number of bits needed to write v (at least 1)
+    int b = 1;
+    while (b < 64 && (v >> b) != 0) ++b;
+    return b;
+}
+
+int fasted_join_stream(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end, uint64_t capacity, unsigned flags,
+                       int32_t* pairs_host, float* dist2_host, uint64_t host_capacity, fasted_chunk_fn on_chunk,
+                       void* user, fasted_join_stats* stats) {
+    int rc = check_join_args(c, eps, q_begin, &q_end);
+    if (rc) return rc;
+    if (flags & (FASTED_JOIN_SYMMETRIC | FASTED_JOIN_NO_SORT | FASTED_JOIN_RAW_DOT))
+        return fail(FASTED_EINVAL, "fasted_join_stream takes FASTED_JOIN_DIST2 and FASTED_JOIN_KEEP_NORMS only");
+    const bool want_dist = (flags & FASTED_JOIN_DIST2) != 0;
+    if (dist2_host && !want_dist) return fail(FASTED_EINVAL, "dist2_host given without FASTED_JOIN_DIST2");
+    CU_TRY(cudaSetDevice(c->device));
+    if (capacity == 0) {
+        rc = default_capacity(c, want_dist, &capacity);
+        if (rc) return rc;
+    }
+    rc = ensure_pair_buffers(c, capacity, want_dist);
+    if (rc) return rc;
+
+    // Chunks of whole raster bands: at most 64 of them, each at least about a millisecond of tensor work.
+    JoinPlan whole;
+    rc = plan_join(c, eps, q_begin, q_end, capacity, flags, 0, 1, &whole);
+    if (rc) return rc;
+    const int64_t band_rows = static_cast<int64_t>(whole.p.band_tiles) * whole.p.tile_m;
+    const int64_t rows = q_end - q_begin;
+    const int64_t total_bands = std::max<int64_t>(1, (rows + band_rows - 1) / band_rows);
+    int64_t bands_per_chunk = c->stream_chunk_bands;
+    if (bands_per_chunk <= 0) {
+        const double min_rows = 2e12 / (2.0 * static_cast<double>(c->n) * static_cast<double>(c->ld));
+        bands_per_chunk = std::max<int64_t>((total_bands + 63) / 64,
+                                            static_cast<int64_t>(std::ceil(min_rows / static_cast<double>(band_rows))));
+    }
+    bands_per_chunk = std::max<int64_t>(1, std::min<int64_t>(bands_per_chunk, total_bands));
+    const int64_t chunk_rows = bands_per_chunk * band_rows;
+    const size_t chunks = static_cast<size_t>((rows + chunk_rows - 1) / chunk_rows);
+    rc = ensure_stream_pipeline(c, chunks + 8);
+    if (rc) return rc;
+    const int key_shift = bits_of(static_cast<uint64_t>(c->n - 1));
+    const int sort_bits = std::min(64, key_shift + bits_of(static_cast<uint64_t>(std::max<int64_t>(chunk_rows - 1, 1))));
+
+    // Sort scratch for the largest slice a chunk can have (the library sort's scratch is bounded: it
+    // works through long inputs in portions), allocated before anything is enqueued.
+    {
+        cub::DoubleBuffer<unsigned long long> kb(c->keys, c->keys_alt);
+        cub::DoubleBuffer<float> vb(c->dist, c->dist_alt);
+        size_t need = 0;
+        if (want_dist)
+            CU_TRY(cub::DeviceRadixSort::SortPairs(nullptr, need, kb, vb, capacity, 0, sort_bits, c->sort_stream));
+        else
+            CU_TRY(cub::DeviceRadixSort::SortKeys(nullptr, need, kb, capacity, 0, sort_bits, c->sort_stream));
+        if (need > c->sort_tmp_bytes) {
+            if (c->sort_tmp) cudaFree(c->sort_tmp);
+            c->sort_tmp = nullptr;
+            c->sort_tmp_bytes = 0;
+            CU_TRY(cudaMalloc(&c->sort_tmp, need));
+            c->sort_tmp_bytes = need;
+        }
+    }
+    if (on_chunk && !pairs_host) {
+        cudaError_t e = ensure_staging(c);
+        if (e != cudaSuccess) return fail(FASTED_ECUDA, "pinned staging: %s", cudaGetErrorString(e));
+    }
+    const bool host_pinned = pairs_host && host_is_pinned(pairs_host) && (!dist2_host || host_is_pinned(dist2_host));
+
+    // ---- enqueue everything the join stream will do ----
+    c->stored = 0;
+    c->result_pairs = nullptr;
+    c->result_dist = nullptr;
+    CU_TRY(cudaMemsetAsync(c->counters, 0, 8 * sizeof(unsigned long long), c->stream));
+    CU_TRY(cudaEventRecord(c->ev[0], c->stream));
+    if (!(flags & FASTED_JOIN_KEEP_NORMS) || !c->norms_valid) {
+        rc = launch_norms(c);
+        if (rc) return rc;
+    }
+    CU_TRY(cudaEventRecord(c->ev[1], c->stream));
+    std::vector<int64_t> chunk_q0(chunks);
+    for (size_t k = 0; k < chunks; ++k) {
+        const int64_t b = q_begin + static_cast<int64_t>(k) * chunk_rows, e = std::min<int64_t>(q_end, b + chunk_rows);
+        chunk_q0[k] = b;
+        JoinPlan pl;
+        rc = plan_join(c, eps, b, e, capacity, flags, 0, 1, &pl);
+        if (rc) return rc;
+        pl.p.key_shift = key_shift;
+        pl.p.key_qbase = static_cast<int>(b);
+        rc = launch_join(c, pl);
+        if (rc) return rc;
+        CU_TRY(cudaMemcpyAsync(c->chunk_end_host + k, c->counters, sizeof(unsigned long long), cudaMemcpyDeviceToHost,
+                               c->stream));
+        CU_TRY(cudaEventRecord(c->chunk_ev[k], c->stream));
+    }
+    CU_TRY(cudaEventRecord(c->ev[2], c->stream));
+    // (pinned destination: a copy into pageable memory would hold the host here until the last chunk)
+    unsigned long long* h = c->chunk_end_host + chunks;
+    CU_TRY(cudaMemcpyAsync(h, c->counters, 5 * sizeof(unsigned long long), cudaMemcpyDeviceToHost, c->stream));
+
+    // ---- pick the chunks up as they retire ----
+    int abort_rc = FASTED_OK;
+    uint64_t prev_end = 0;
+    double tail_start = 0;
+    auto now_ms = [] {
+        timespec ts;
+        clock_gettime(CLOCK_MONOTONIC, &ts);
+        return ts.tv_sec * 1e3 + ts.tv_nsec * 1e-6;
+    };
+    for (size_t k = 0; k < chunks && abort_rc == FASTED_OK; ++k) {
+        CU_TRY(cudaEventSynchronize(c->chunk_ev[k]));
+        if (k + 1 == chunks) tail_start = now_ms();
+        const uint64_t end_k = c->chunk_end_host[k];
+        const uint64_t a = std::min<uint64_t>(prev_end, capacity), b = std::min<uint64_t>(end_k, capacity);
+        prev_end = end_k;
+        if (b <= a) continue;
+        const uint64_t m = b - a;
+        // sort the slice (on the sort stream; the join stream is already past it)
+        cub::DoubleBuffer<unsigned long long> kb(c->keys + a, c->keys_alt + a);
+        cub::DoubleBuffer<float> vb(want_dist ? c->dist + a : nullptr, want_dist ? c->dist_alt + a : nullptr);
+        if (m > 1) {
+            size_t need = c->sort_tmp_bytes;
+            if (want_dist)
+                CU_TRY(cub::DeviceRadixSort::SortPairs(c->sort_tmp, need, kb, vb, m, 0, sort_bits, c->sort_stream));
+            else
+                CU_TRY(cub::DeviceRadixSort::SortKeys(c->sort_tmp, need, kb, m, 0, sort_bits, c->sort_stream));
+        }
+        fasted::unpack_pairs_kernel<<<unpack_blocks(c, m), 256, 0, c->sort_stream>>>(
+            kb.Current(), reinterpret_cast<int2*>(c->keys_alt + a), m, nullptr, 0ull, key_shift,
+            static_cast<int>(chunk_q0[k]));
+        CU_TRY(cudaGetLastError());
+        if (want_dist && vb.Current() != c->dist_alt + a)
+            CU_TRY(cudaMemcpyAsync(c->dist_alt + a, vb.Current(), m * sizeof(float), cudaMemcpyDeviceToDevice,
+                                   c->sort_stream));
+        CU_TRY(cudaEventRecord(c->ev_sorted, c->sort_stream));
+        CU_TRY(cudaStreamWaitEvent(c->copy_stream, c->ev_sorted, 0));
+
+        // copy it to the host
+        const int2* src_pairs = reinterpret_cast<const int2*>(c->keys_alt) + a;
+        const float* src_dist = want_dist ? c->dist_alt + a : nullptr;
+        if (pairs_host) {
+            const uint64_t hb = std::min<uint64_t>(b, host_capacity);
+            const uint64_t hm = hb > a ? hb - a : 0;
+            if (hm > 0) {
+                if (host_pinned) {
+                    CU_TRY(cudaMemcpyAsync(pairs_host + 2 * a, src_pairs, hm * 8, cudaMemcpyDeviceToHost, c->copy_stream));
+                    if (dist2_host)
+                        CU_TRY(cudaMemcpyAsync(dist2_host + a, src_dist, hm * 4, cudaMemcpyDeviceToHost, c->copy_stream));
+                    CU_TRY(cudaStreamSynchronize(c->copy_stream));
+                } else {
+                    CU_TRY(download_bytes(c, pairs_host + 2 * a, src_pairs, hm * 8, c->copy_stream));
+                    if (dist2_host) CU_TRY(download_bytes(c, dist2_host + a, src_dist, hm * 4, c->copy_stream));
+                }
+                if (on_chunk && on_chunk(user, pairs_host + 2 * a, dist2_host ? dist2_host + a : nullptr, a, hm) != 0)
+                    abort_rc = fail(FASTED_EINVAL, "the chunk callback asked to stop");
+            }
+        } else if (on_chunk) {
+            // No destination of the caller's: runs of records pass through the two pinned staging
+            // buffers; while the callback reads one, the DMA engine fills the other.
+            const uint64_t run = (kStageBytes / (want_dist ? 12 : 8)) & ~uint64_t(1023);
+            const uint64_t runs = (m + run - 1) / run;
+            for (uint64_t i = 0; i <= runs && abort_rc == FASTED_OK; ++i) {
+                if (i < runs) {
+                    const uint64_t off = i * run, cnt = std::min(run, m - off);
+                    char* buf = static_cast<char*>(c->stage_buf[i & 1]);
+                    CU_TRY(cudaMemcpyAsync(buf, src_pairs + off, cnt * 8, cudaMemcpyDeviceToHost, c->copy_stream));
+                    if (want_dist)
+                        CU_TRY(cudaMemcpyAsync(buf + run * 8, src_dist + off, cnt * 4, cudaMemcpyDeviceToHost,
+                                               c->copy_stream));
+                    CU_TRY(cudaEventRecord(c->ev_copied[i & 1], c->copy_stream));
+                }
+                if (i > 0) {
+                    const uint64_t off = (i - 1) * run, cnt = std::min(run, m - off);
+                    const char* buf = static_cast<const char*>(c->stage_buf[(i - 1) & 1]);
+                    CU_TRY(cudaEventSynchronize(c->ev_copied[(i - 1) & 1]));
+                    if (on_chunk(user, reinterpret_cast<const int32_t*>(buf),
+                                 want_dist ? reinterpret_cast<const float*>(buf + run * 8) : nullptr, a + off, cnt) != 0)
+                        abort_rc = fail(FASTED_EINVAL, "the chunk callback asked to stop");
+                }
+            }
+        } else {
+            CU_TRY(cudaStreamSynchronize(c->sort_stream));
+        }
+    }
+    CU_TRY(cudaStreamSynchronize(c->sort_stream));
+    CU_TRY(cudaStreamSynchronize(c->copy_stream));
+    CU_TRY(cudaStreamSynchronize(c->stream));
+    const double tail_ms = tail_start > 0 ? now_ms() - tail_start : 0.0;
+    c->norms_valid = (h[2] & fasted::kErrNormWait) == 0;
+    if (h[2]) return fail(FASTED_EKERNEL, "a device-side wait ran out (status 0x%llx)", h[2]);
+    if (abort_rc != FASTED_OK) return abort_rc;
+    const uint64_t stored = std::min<uint64_t>(h[0], capacity);
+    c->stored = stored;
+    c->result_pairs = c->keys_alt;
+    c->result_dist = want_dist ? c->dist_alt : nullptr;
+    c->result_sorted = true;
+    // (ev[3], ev[4] bracket nothing here: the sorts overlap the join)
+    CU_TRY(cudaEventRecord(c->ev[3], c->stream));
+    CU_TRY(cudaEventRecord(c->ev[4], c->stream));
+    CU_TRY(cudaStreamSynchronize(c->stream));
+    fill_stats(c, whole, h, stored, stats);
+    if (stats) {
+        stats->chunks = static_cast<int>(chunks);
+        stats->tail_ms = tail_ms;
+        stats->cta0_cycles = 0;  // the counter holds the last chunk's only
+        stats->cta0_tiles = 0;
+    }
+    return FASTED_OK;
 }
 
 int fasted_tile_schedule(int64_t n, int64_t q_begin, int64_t q_end, int tile_m, int band_tiles, int symmetric,
@@ -828,6 +1179,8 @@ int fasted_tile_schedule(int64_t n, int64_t q_begin, int64_t q_end, int tile_m, 
     p.shard_rank = shard_rank;
     p.shard_world = shard_world;
     p.raw_dot = 0;
+    p.key_shift = 32;
+    p.key_qbase = 0;
     if (shard_world > 1 && !symmetric) return fail(FASTED_EINVAL, "band snakes are for the symmetric schedule only");
     p.tiles_m = static_cast<int>((q_end - q_begin + tile_m - 1) / tile_m);
     p.tiles_n = static_cast<int>((n + fasted::kTileN - 1) / fasted::kTileN);
@@ -921,8 +1274,8 @@ int fasted_get_pairs(fasted_ctx* c, uint64_t first, uint64_t count, int32_t* pai
     if (count == 0) return FASTED_OK;
     if (dist2_out && !c->result_dist) return fail(FASTED_ESTATE, "the last join did not record distances");
     CU_TRY(cudaSetDevice(c->device));
-    if (pairs_out) CU_TRY(download_bytes(c, pairs_out, static_cast<const int2*>(c->result_pairs) + first, count * 8));
-    if (dist2_out) CU_TRY(download_bytes(c, dist2_out, c->result_dist + first, count * 4));
+    if (pairs_out) CU_TRY(download_bytes(c, pairs_out, static_cast<const int2*>(c->result_pairs) + first, count * 8, c->stream));
+    if (dist2_out) CU_TRY(download_bytes(c, dist2_out, c->result_dist + first, count * 4, c->stream));
     return FASTED_OK;
 }
 
@@ -999,28 +1352,23 @@ constexpr size_t kStaticScratchBytes = static_cast<size_t>(kStaticMaxPoints) * s
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
 namespace {
-constexpr int kMaxDevices = 64;
-unsigned char* g_static_scratch_addr[kMaxDevices] = {};  // device address of g_static_scratch, per device
-
-// One-time set-up on the current device: resolve the scratch symbol and raise
-// the kernels' dynamic shared memory limits.  Neither call allocates.
+// Set-up on the current device: resolve the scratch symbol and raise the kernels' dynamic shared
+// memory limits.  Done on every call (both are table look-ups, neither allocates), so that nothing
+// cached can go stale when the device's context is reset between calls.  The first fasted call of a
+// process on a device makes the CUDA runtime load this library's module there (kernel images and
+// the scratch array): that one-time load is the only moment device memory is taken.
 int static_scratch_setup(int device, unsigned char** out) {
-    if (device < 0 || device >= kMaxDevices) return fail(FASTED_EINVAL, "device ordinal %d not supported", device);
-    if (!g_static_scratch_addr[device]) {
-        cudaDeviceProp prop;
-        CU_TRY(cudaGetDeviceProperties(&prop, device));
-        if (prop.major != 10)
-            return fail(FASTED_ENODEV, "device %d is sm_%d%d; this library contains sm_100a code only", device,
-                        prop.major, prop.minor);
-        void* addr = nullptr;
-        CU_TRY(cudaGetSymbolAddress(&addr, g_static_scratch));
-        CU_TRY(cudaFuncSetAttribute(fasted::join_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    fasted::kJoinSmemBytes));
-        CU_TRY(cudaFuncSetAttribute(fasted::row_norms_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    fasted::kNormSmemBytes));
-        g_static_scratch_addr[device] = static_cast<unsigned char*>(addr);
-    }
-    *out = g_static_scratch_addr[device];
+    int major = 0;
+    CU_TRY(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device));
+    if (major != 10)
+        return fail(FASTED_ENODEV, "device %d is sm_%dx; this library contains sm_100a code only", device, major);
+    void* addr = nullptr;
+    CU_TRY(cudaGetSymbolAddress(&addr, g_static_scratch));
+    CU_TRY(cudaFuncSetAttribute(fasted::join_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                fasted::kJoinSmemBytes));
+    CU_TRY(cudaFuncSetAttribute(fasted::row_norms_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                fasted::kNormSmemBytes));
+    *out = static_cast<unsigned char*>(addr);
     return FASTED_OK;
 }
 
@@ -1096,6 +1444,8 @@ int fasted_join_static_scratch(const void* points_dev, int64_t n, int64_t d, int
     p.raw_dot = 0;
     p.shard_rank = 0;
     p.shard_world = 1;
+    p.key_shift = 32;
+    p.key_qbase = 0;
     const int grid = static_cast<int>(std::min<long long>(p.total_tiles, num_sms));
 
     // The scratch area keeps whatever the previous call left: the counters must start at zero

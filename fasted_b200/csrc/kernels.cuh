@@ -68,7 +68,15 @@ struct JoinParams {
     int shard_rank, shard_world;   // symmetric mode over several GPUs: this launch takes the raster bands
                                    // r, 2G-1-r, 2G+r, 4G-1-r, ... (a snake over the G shards, which evens out
                                    // the shrinking band lengths of the triangle); 0, 1 = everything
+    int key_shift, key_qbase;      // record = ((query - key_qbase) << key_shift) | candidate.  32 and 0 give the
+                                   // plain (query << 32) | candidate; a launch over one chunk of query rows can
+                                   // pack tighter, so that the chunk's sort has fewer significant bits to look at
 };
+
+__device__ __forceinline__ unsigned long long pack_record(const JoinParams& p, unsigned long long q,
+                                                          unsigned long long c) {
+    return ((q - static_cast<unsigned long long>(p.key_qbase)) << p.key_shift) | c;
+}
 
 // Persistent static schedule: CTA (or CTA pair) b handles tiles b, b + grid, b + 2*grid, ... of a
 // linear order that walks bands of `band_tiles` tile rows; inside a band the tile row is the fastest
@@ -260,38 +268,44 @@ row_norms_kernel(const __grid_constant__ CUtensorMap map, float* __restrict__ no
             acc64 = 0.0;
         }
         ok = ptx::mbar_wait_bounded(bars + 8 * s, parity, &abort_flag, kWaitLimitNs);
-        if (!ok) break;
-        const int nb = min(kNormBoxesPerStage, k_boxes - step * kNormBoxesPerStage);
-        for (int b = 0; b < nb; ++b) {
-            const uint8_t* box = smem_raw + (base - ptx::smem_u32(smem_raw)) + s * kNormStageBytes + b * kNormBoxBytes;
-            const uint8_t* row = box + tid * 128;
+        if (ok) {
+            const int nb = min(kNormBoxesPerStage, k_boxes - step * kNormBoxesPerStage);
+            for (int b = 0; b < nb; ++b) {
+                const uint8_t* box =
+                    smem_raw + (base - ptx::smem_u32(smem_raw)) + s * kNormStageBytes + b * kNormBoxBytes;
+                const uint8_t* row = box + tid * 128;
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                const uint4 q = *reinterpret_cast<const uint4*>(row + ((c ^ (tid & 7)) << 4));
-                const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+                for (int c = 0; c < 8; ++c) {
+                    const uint4 q = *reinterpret_cast<const uint4*>(row + ((c ^ (tid & 7)) << 4));
+                    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
-                    if constexpr (kExact != 0) {
-                        // f.x^2 + f.y^2 is formed exactly in FP64 (22-bit products), then accumulated.
-                        acc64 += static_cast<double>(f.x) * static_cast<double>(f.x) +
-                                 static_cast<double>(f.y) * static_cast<double>(f.y);
-                    } else {
-                        acc = __fadd_rz(acc, __fadd_rz(f.x * f.x, f.y * f.y));
+                    for (int j = 0; j < 4; ++j) {
+                        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
+                        if constexpr (kExact != 0) {
+                            // f.x^2 + f.y^2 is formed exactly in FP64 (22-bit products), then accumulated.
+                            acc64 += static_cast<double>(f.x) * static_cast<double>(f.x) +
+                                     static_cast<double>(f.y) * static_cast<double>(f.y);
+                        } else {
+                            acc = __fadd_rz(acc, __fadd_rz(f.x * f.x, f.y * f.y));
+                        }
                     }
                 }
             }
+            if (step == steps_per_block - 1) {
+                const int r = (static_cast<int>(blockIdx.x) + blk * static_cast<int>(gridDim.x)) * kNormRows + tid;
+                if (r < n) norms[r] = kExact == 1 ? static_cast<float>(acc64) : acc;
+            }
         }
-        if (step == steps_per_block - 1) {
-            const int r = (static_cast<int>(blockIdx.x) + blk * static_cast<int>(gridDim.x)) * kNormRows + tid;
-            if (r < n) norms[r] = kExact == 1 ? static_cast<float>(acc64) : acc;
+        // Every thread is done with stage s.  The same barrier carries the verdict of the waits, so
+        // that all threads leave the loop together if any of them gave up.
+        if (__syncthreads_or(ok ? 0 : 1)) {
+            ok = false;
+            break;
         }
-        __syncthreads();  // every thread is done with stage s
         if (tid == 0 && item + kNormStages < total_items) issue(item + kNormStages);
     }
     if (!ok) {
         // Give loads that are still in flight a bounded chance to land before the CTA exits.
-        __syncthreads();
         if (tid == 0) {
             atomicOr(status, kErrNormWait);
             const uint64_t t0 = ptx::globaltimer_ns();
@@ -528,7 +542,7 @@ __device__ __forceinline__ void epilogue_emit(const JoinParams& p, EpiHits& h, i
             m &= m - 1;
             const unsigned long long q = qk + ((i & 2) ? 8u : 0u);
             const unsigned long long c = ck + 8u * (i >> 2) + (i & 1);
-            if (slot < p.capacity) p.keys[slot] = (q << 32) | c;
+            if (slot < p.capacity) p.keys[slot] = pack_record(p, q, c);
             ++slot;
         }
         while (r) {
@@ -536,7 +550,7 @@ __device__ __forceinline__ void epilogue_emit(const JoinParams& p, EpiHits& h, i
             r &= r - 1;
             const unsigned long long q = qk + ((i & 2) ? 8u : 0u);
             const unsigned long long c = ck + 8u * (i >> 2) + (i & 1);
-            if (slot < p.capacity) p.keys[slot] = (c << 32) | q;
+            if (slot < p.capacity) p.keys[slot] = pack_record(p, c, q);
             ++slot;
         }
     }
@@ -571,14 +585,14 @@ __device__ __forceinline__ void epilogue_emit_dist(const JoinParams& p, const Ep
                 const unsigned long long c = ck + 8u * (i >> 2) + (i & 1);
                 if (m & (1u << i)) {
                     if (slot < p.capacity) {
-                        p.keys[slot] = (q << 32) | c;
+                        p.keys[slot] = pack_record(p, q, c);
                         p.dist2[slot] = d2;
                     }
                     ++slot;
                 }
                 if (r & (1u << i)) {
                     if (slot < p.capacity) {
-                        p.keys[slot] = (c << 32) | q;
+                        p.keys[slot] = pack_record(p, c, q);
                         p.dist2[slot] = d2;
                     }
                     ++slot;
@@ -1092,15 +1106,24 @@ __global__ void wait_timeout_selftest_kernel(unsigned long long limit_ns, unsign
 // Helpers
 // ---------------------------------------------------------------------------
 
-// Sorted packed keys -> {int query; int candidate} records, the reference's
-// Pair layout (source/pair.cuh:27-30).
-__global__ void unpack_pairs_kernel(const unsigned long long* __restrict__ keys, int2* __restrict__ out,
-                                    unsigned long long count) {
+// Packed records -> {int query; int candidate}, the reference's Pair layout (source/pair.cuh:27-30).
+// Record = ((query - qbase) << shift) | candidate (see JoinParams::key_shift).  The number of records is
+// `count`, or, when found_dev is given, min(*found_dev - first_slot, count) read on the device, so
+// that the host need not know it before the launch.  keys and out may be the same buffer.
+__global__ void unpack_pairs_kernel(const unsigned long long* keys, int2* out, unsigned long long count,
+                                    const unsigned long long* __restrict__ found_dev, unsigned long long first_slot,
+                                    int shift, int qbase) {
+    if (found_dev != nullptr) {
+        const unsigned long long f = *found_dev;
+        const unsigned long long avail = f > first_slot ? f - first_slot : 0ull;
+        if (avail < count) count = avail;
+    }
+    const unsigned long long mask = shift >= 64 ? ~0ull : ((1ull << shift) - 1ull);
     const unsigned long long stride = static_cast<unsigned long long>(gridDim.x) * blockDim.x;
     for (unsigned long long i = static_cast<unsigned long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < count;
          i += stride) {
         const unsigned long long k = keys[i];
-        out[i] = make_int2(static_cast<int>(k >> 32), static_cast<int>(k & 0xffffffffull));
+        out[i] = make_int2(static_cast<int>(k >> shift) + qbase, static_cast<int>(k & mask));
     }
 }
 

@@ -10,6 +10,7 @@
 #include <cstring>
 #include <exception>
 #include <iostream>
+#include <memory>
 #include <stdexcept>
 #include <string>
 #include <thread>
@@ -144,44 +145,66 @@ inline char* put_uint(char* p, uint32_t v) {
 }
 
 // Writes "q, c\n" per pair (source/pair.cuh:51-54), optionally "q, c, dist\n".  The reference streams
-// one `os << pair << std::endl` (a flush) per pair; here threads format disjoint slices into their own
-// buffers, which are then written in order.
-void write_pairs_file(const std::string& path, const std::vector<int32_t>& pairs, const std::vector<float>* dist2) {
-    FILE* f = std::fopen(path.c_str(), "wb");
-    if (!f) return;  // the reference ignores a failed open (std::ofstream never checked)
-    const size_t count = pairs.size() / 2;
-    const size_t slice = size_t(1) << 20;  // pairs per formatting task
-    const size_t tasks = (count + slice - 1) / slice;
-    const size_t wave = static_cast<size_t>(std::max(1, omp_get_max_threads()));
-    std::vector<std::vector<char>> bufs(wave);
-    for (size_t t0 = 0; t0 < tasks; t0 += wave) {
-        const size_t nt = std::min(wave, tasks - t0);
-#pragma omp parallel for schedule(static, 1)
-        for (size_t k = 0; k < nt; ++k) {
-            const size_t begin = (t0 + k) * slice, end = std::min(count, begin + slice);
-            std::vector<char>& b = bufs[k];
-            b.resize((end - begin) * (dist2 ? 48 : 24));
-            char* p = b.data();
-            for (size_t i = begin; i < end; ++i) {
-                p = put_uint(p, static_cast<uint32_t>(pairs[2 * i]));
-                *p++ = ',';
-                *p++ = ' ';
-                p = put_uint(p, static_cast<uint32_t>(pairs[2 * i + 1]));
-                if (dist2) {
-                    p += std::snprintf(p, 24, ", %.9g", std::sqrt(static_cast<double>((*dist2)[i])));
-                }
-                *p++ = '\n';
-            }
-            b.resize(static_cast<size_t>(p - b.data()));
-        }
-        for (size_t k = 0; k < nt; ++k) std::fwrite(bufs[k].data(), 1, bufs[k].size(), f);
+// one `os << pair << std::endl` (a flush) per pair; here every append is formatted by all host threads
+// into slices of their own, which are then written in order.  Appends may come while the GPU is still
+// joining later query rows (fasted_join_stream), so the text is produced behind the join as well.
+class PairsWriter {
+public:
+    explicit PairsWriter(const std::string& path) : f_(std::fopen(path.c_str(), "wb")) {}
+    // (the reference ignores a failed open: its std::ofstream is never checked)
+    ~PairsWriter() {
+        if (f_) std::fclose(f_);
     }
-    std::fclose(f);
+    void append(const int32_t* pairs, const float* dist2, size_t count) {
+        if (!f_ || count == 0) return;
+        const size_t slice = size_t(1) << 18;  // pairs per formatting task
+        const size_t tasks = (count + slice - 1) / slice;
+        const size_t wave = static_cast<size_t>(std::max(1, omp_get_max_threads()));
+        if (bufs_.size() < wave) bufs_.resize(wave);
+        for (size_t t0 = 0; t0 < tasks; t0 += wave) {
+            const size_t nt = std::min(wave, tasks - t0);
+#pragma omp parallel for schedule(static, 1)
+            for (size_t k = 0; k < nt; ++k) {
+                const size_t begin = (t0 + k) * slice, end = std::min(count, begin + slice);
+                std::vector<char>& b = bufs_[k];
+                b.resize((end - begin) * (dist2 ? 48 : 24));
+                char* p = b.data();
+                for (size_t i = begin; i < end; ++i) {
+                    p = put_uint(p, static_cast<uint32_t>(pairs[2 * i]));
+                    *p++ = ',';
+                    *p++ = ' ';
+                    p = put_uint(p, static_cast<uint32_t>(pairs[2 * i + 1]));
+                    if (dist2) p += std::snprintf(p, 24, ", %.9g", std::sqrt(static_cast<double>(dist2[i])));
+                    *p++ = '\n';
+                }
+                b.resize(static_cast<size_t>(p - b.data()));
+            }
+            for (size_t k = 0; k < nt; ++k) std::fwrite(bufs_[k].data(), 1, bufs_[k].size(), f_);
+        }
+    }
+
+private:
+    FILE* f_;
+    std::vector<std::vector<char>> bufs_;
+};
+
+struct StreamSink {
+    PairsWriter* writer;   // null: the records are brought to the host and dropped, as the reference
+                           // does when savePairs is false (source/findPairs.cuh:703-714)
+    uint64_t delivered;
+};
+
+int stream_sink(void* user, const int32_t* pairs, const float* dist2, uint64_t /*first*/, uint64_t count) {
+    StreamSink* s = static_cast<StreamSink*>(user);
+    if (s->writer) s->writer->append(pairs, dist2, static_cast<size_t>(count));
+    s->delivered += count;
+    return 0;
 }
 
 // The body of the reference's run() + FindPairs() (source/main.cu:198-248,
 // source/findPairs.cuh:615-764) on the resident dataset.
-Results join_resident(double epsilon, bool save_pairs, const std::string& dataset_name, double start_time) {
+Results join_resident(double epsilon, bool save_pairs, const std::string& dataset_name, double start_time,
+                      bool keep_norms) {
     fasted_ctx* ctx = context();
     const int64_t n = g_state.n, d = g_state.d;
     const int64_t n_pad = round_up(n, 256), d_pad = round_up(d, 64);
@@ -204,82 +227,108 @@ Results join_resident(double epsilon, bool save_pairs, const std::string& datase
     std::cout << "N: " << n << std::endl;
     std::cout << "K: " << d << std::endl;
 
-    // d2(i,j) == d2(j,i) bit for bit, so by default each unordered pair is computed once and both
-    // orientations are emitted; FASTED_SYMMETRIC=0 computes all N x N entries like the reference.
+    // Default: all N x N entries are computed, like the reference, so that "Estimated TFLOPS" counts
+    // executed work.  FASTED_SYMMETRIC=1: d2(i,j) == d2(j,i) bit for bit, so each unordered pair is
+    // computed once and both orientations are emitted -- identical output in about half the time; the
+    // TFLOPS line still divides 2*N*N*D by the time, and the schedule line says so.
     const char* sym_env = std::getenv("FASTED_SYMMETRIC");
-    const bool symmetric = !(sym_env && std::strcmp(sym_env, "0") == 0);
+    const bool symmetric = sym_env && std::strcmp(sym_env, "1") == 0;
     unsigned flags = write_dist ? FASTED_JOIN_DIST2 : 0u;
     if (symmetric) flags |= FASTED_JOIN_SYMMETRIC;
+    if (keep_norms) flags |= FASTED_JOIN_KEEP_NORMS;  // reRun: the dataset, hence its norms, is unchanged
+    std::cout << "Schedule: "
+              << (symmetric ? "symmetric (each unordered pair computed once; executed flops are about half of 2*N*N*D)"
+                            : "full (all N x N entries computed)")
+              << std::endl;
     fasted_join_stats st{};
     std::vector<fasted_ctx*> gpus = all_contexts();
     std::vector<fasted_join_stats> per_gpu(gpus.size());
-    if (gpus.size() == 1) {
-        check(fasted_join(ctx, epsilon, 0, -1, 0, flags, &st));
-        per_gpu[0] = st;
-    } else {
-        // One host thread per GPU (the join call blocks).  Symmetric: GPU g computes its snake of
-        // upper-triangle bands and emits both orientations, so every GPU's sorted list spans all
-        // query rows and the lists are merged on the host.  Full: GPU g joins the g-th contiguous band
-        // of query rows; the lists are laid end to end.  No collective either way.
-        const int G = static_cast<int>(gpus.size());
-        std::vector<int> rc(gpus.size(), FASTED_OK);
-        std::vector<std::string> err(gpus.size());
-        std::vector<std::thread> workers;
-        for (int g = 0; g < G; ++g)
-            workers.emplace_back([&, g] {
-                if (symmetric) {
-                    rc[g] = fasted_join_symmetric_shard(gpus[g], epsilon, g, G, 0, flags, &per_gpu[g]);
-                } else {
-                    int64_t b, e;
-                    band_of(n, g, G, &b, &e);
-                    rc[g] = fasted_join(gpus[g], epsilon, b, e, static_cast<uint64_t>(std::max<int64_t>(e - b, 1)) * 256,
-                                        flags, &per_gpu[g]);
-                }
-                if (rc[g] != FASTED_OK) err[g] = fasted_last_error();
-            });
-        for (auto& w : workers) w.join();
-        for (int g = 0; g < G; ++g)
-            if (rc[g] != FASTED_OK) throw std::runtime_error(err[g]);
-        for (int g = 0; g < G; ++g) {  // the slowest GPU sets the time, the counts add up
-            st.pairs_found += per_gpu[g].pairs_found;
-            st.pairs_stored += per_gpu[g].pairs_stored;
-            st.kernel_ms = std::max(st.kernel_ms, per_gpu[g].kernel_ms);
-            st.norms_ms = std::max(st.norms_ms, per_gpu[g].norms_ms);
-            st.join_ms = std::max(st.join_ms, per_gpu[g].join_ms);
-            st.sort_ms = std::max(st.sort_ms, per_gpu[g].sort_ms);
-        }
-    }
+    const std::string pairs_path = output_path + ".pairs";
+    double sort_start = now_s();
 
-    const double sort_start = now_s();
-    std::printf("Number of pairs found %llu\n", st.pairs_found);
-    std::printf("Number of pairs stored %llu\n", st.pairs_stored);
-    // The reference copies every stored pair to the host even when it does not
-    // save them (source/findPairs.cuh:703-714); so does this.
-    std::vector<int32_t> pairs(static_cast<size_t>(st.pairs_stored) * 2);
-    std::vector<float> dist2(write_dist ? static_cast<size_t>(st.pairs_stored) : 0);
-    if (gpus.size() == 1 || !symmetric) {
-        // Bands are contiguous in the query index: the band lists end to end are the global order.
-        size_t at = 0;
-        for (size_t g = 0; g < gpus.size(); ++g) {
-            const uint64_t m = per_gpu[g].pairs_stored;
-            check(fasted_get_pairs(gpus[g], 0, m, pairs.data() + 2 * at, write_dist ? dist2.data() + at : nullptr));
-            at += static_cast<size_t>(m);
+    if (gpus.size() == 1 && !symmetric) {
+        // One GPU, full schedule: sort, device-to-host copy and the text file all run behind the join,
+        // chunk of query rows by chunk (fasted_join_stream); nothing of the list is kept on the host.
+        std::unique_ptr<PairsWriter> writer;
+        if (save_pairs) {
+            std::cout << "Output file is: " << pairs_path << std::endl;
+            writer.reset(new PairsWriter(pairs_path));
         }
+        StreamSink sink{writer.get(), 0};
+        check(fasted_join_stream(ctx, epsilon, 0, -1, 0, flags, nullptr, nullptr, 0, stream_sink, &sink, &st));
+        writer.reset();
+        std::printf("Number of pairs found %llu\n", st.pairs_found);
+        std::printf("Number of pairs stored %llu\n", st.pairs_stored);
+        sort_start = now_s() - st.tail_ms / 1e3;
     } else {
-        std::vector<std::vector<int32_t>> part(gpus.size());
-        std::vector<std::vector<float>> part_d(gpus.size());
-        for (size_t g = 0; g < gpus.size(); ++g) {
-            const uint64_t m = per_gpu[g].pairs_stored;
-            part[g].resize(static_cast<size_t>(m) * 2);
-            if (write_dist) part_d[g].resize(static_cast<size_t>(m));
-            check(fasted_get_pairs(gpus[g], 0, m, part[g].data(), write_dist ? part_d[g].data() : nullptr));
+        if (gpus.size() == 1) {
+            check(fasted_join(ctx, epsilon, 0, -1, 0, flags, &st));
+            per_gpu[0] = st;
+        } else {
+            // One host thread per GPU (the join call blocks).  Symmetric: GPU g computes its snake of
+            // upper-triangle bands and emits both orientations, so every GPU's sorted list spans all
+            // query rows and the lists are merged on the host.  Full: GPU g joins the g-th contiguous band
+            // of query rows; the lists are laid end to end.  No collective either way.
+            const int G = static_cast<int>(gpus.size());
+            std::vector<int> rc(gpus.size(), FASTED_OK);
+            std::vector<std::string> err(gpus.size());
+            std::vector<std::thread> workers;
+            for (int g = 0; g < G; ++g)
+                workers.emplace_back([&, g] {
+                    if (symmetric) {
+                        rc[g] = fasted_join_symmetric_shard(gpus[g], epsilon, g, G, 0, flags, &per_gpu[g]);
+                    } else {
+                        int64_t b, e;
+                        band_of(n, g, G, &b, &e);
+                        rc[g] = fasted_join(gpus[g], epsilon, b, e,
+                                            static_cast<uint64_t>(std::max<int64_t>(e - b, 1)) * 256, flags, &per_gpu[g]);
+                    }
+                    if (rc[g] != FASTED_OK) err[g] = fasted_last_error();
+                });
+            for (auto& w : workers) w.join();
+            for (int g = 0; g < G; ++g)
+                if (rc[g] != FASTED_OK) throw std::runtime_error(err[g]);
+            for (int g = 0; g < G; ++g) {  // the slowest GPU sets the time, the counts add up
+                st.pairs_found += per_gpu[g].pairs_found;
+                st.pairs_stored += per_gpu[g].pairs_stored;
+                st.kernel_ms = std::max(st.kernel_ms, per_gpu[g].kernel_ms);
+                st.norms_ms = std::max(st.norms_ms, per_gpu[g].norms_ms);
+                st.join_ms = std::max(st.join_ms, per_gpu[g].join_ms);
+                st.sort_ms = std::max(st.sort_ms, per_gpu[g].sort_ms);
+            }
         }
-        merge_sorted_lists(part, part_d, n, pairs.data(), write_dist ? dist2.data() : nullptr);
-    }
-    if (save_pairs) {
-        const std::string pairs_path = output_path + ".pairs";
-        std::cout << "Output file is: " << pairs_path << std::endl;
-        write_pairs_file(pairs_path, pairs, write_dist ? &dist2 : nullptr);
+
+        sort_start = now_s();
+        std::printf("Number of pairs found %llu\n", st.pairs_found);
+        std::printf("Number of pairs stored %llu\n", st.pairs_stored);
+        // The reference copies every stored pair to the host even when it does not
+        // save them (source/findPairs.cuh:703-714); so does this.
+        std::vector<int32_t> pairs(static_cast<size_t>(st.pairs_stored) * 2);
+        std::vector<float> dist2(write_dist ? static_cast<size_t>(st.pairs_stored) : 0);
+        if (gpus.size() == 1 || !symmetric) {
+            // Bands are contiguous in the query index: the band lists end to end are the global order.
+            size_t at = 0;
+            for (size_t g = 0; g < gpus.size(); ++g) {
+                const uint64_t m = per_gpu[g].pairs_stored;
+                check(fasted_get_pairs(gpus[g], 0, m, pairs.data() + 2 * at, write_dist ? dist2.data() + at : nullptr));
+                at += static_cast<size_t>(m);
+            }
+        } else {
+            std::vector<std::vector<int32_t>> part(gpus.size());
+            std::vector<std::vector<float>> part_d(gpus.size());
+            for (size_t g = 0; g < gpus.size(); ++g) {
+                const uint64_t m = per_gpu[g].pairs_stored;
+                part[g].resize(static_cast<size_t>(m) * 2);
+                if (write_dist) part_d[g].resize(static_cast<size_t>(m));
+                check(fasted_get_pairs(gpus[g], 0, m, part[g].data(), write_dist ? part_d[g].data() : nullptr));
+            }
+            merge_sorted_lists(part, part_d, n, pairs.data(), write_dist ? dist2.data() : nullptr);
+        }
+        if (save_pairs) {
+            std::cout << "Output file is: " << pairs_path << std::endl;
+            PairsWriter writer(pairs_path);
+            writer.append(pairs.data(), write_dist ? dist2.data() : nullptr, pairs.size() / 2);
+        }
     }
     const double end_time = now_s();
 
@@ -351,7 +400,7 @@ Results run_dataset(fasted::HostDataset (*make)(void*), void* arg, double epsilo
         g_state.n = ds.n;
         g_state.d = ds.d;
         g_state.have_points = true;
-        return join_resident(epsilon, save_pairs, ds.name, join_start);
+        return join_resident(epsilon, save_pairs, ds.name, join_start, false);
     } catch (const std::exception& e) {
         die(e.what());
     }
@@ -388,7 +437,7 @@ Results runFromFile(const char* filename, double epsilon, bool savePairs) {
 Results reRun(double epsilon, bool savePairs) {
     try {
         if (!g_state.have_points) throw std::runtime_error("reRun called before runFromFile/runFromExponentialDataset");
-        return join_resident(epsilon, savePairs, "", now_s());
+        return join_resident(epsilon, savePairs, "", now_s(), true);
     } catch (const std::exception& e) {
         die(e.what());
     }

@@ -6,11 +6,16 @@ bands are independent: rank r joins query rows [r*B, (r+1)*B) against all N cand
 because bands are contiguous in the query index, concatenating the per-rank sorted pair lists
 in rank order gives the global row-major order the reference produces on one GPU
 (source/pair.cuh:39-45 of the reference).  No other collective is on the data path; the
-pair counts are summed with a scalar all-reduce.
+per-rank pair counts are exchanged with one all-gather of three integers, and the bands' lists
+meet in one shared host buffer (SharedPairBuffer), each at the offset its predecessors' counts give.
 """
 from __future__ import annotations
 
-from typing import Callable, Protocol
+import mmap
+import os
+import tempfile
+import uuid
+from typing import Callable, Protocol, Sequence
 
 import numpy as np
 
@@ -27,6 +32,109 @@ def band_bounds(n: int, world: int, rank: int, align: int = BAND_ALIGN) -> tuple
     begin = min(n, rank * per)
     end = min(n, begin + per)
     return begin, end
+
+
+def weighted_band_bounds(n: int, weights: Sequence[float], align: int = BAND_ALIGN) -> list[tuple[int, int]]:
+    """Contiguous bands of query rows, one per rank, whose sizes are proportional to `weights` (each
+    rank's measured join rate, rows per millisecond): the job's step time is the slowest rank's, and
+    GPUs under their own power caps do not run at the same clock, so equal bands leave the faster
+    ones idle.  Bands start on multiples of `align` rows and cover [0, n) without overlap; a rank
+    whose weight is zero or negative gets an empty band."""
+    w = [max(float(x), 0.0) for x in weights]
+    if n < 0 or not w:
+        raise ValueError("bad band arguments")
+    if sum(w) <= 0.0:
+        w = [1.0] * len(w)
+    units = -(-n // align)  # whole tiles to hand out
+    total = sum(w)
+    cuts, acc = [0], 0.0
+    for x in w:
+        acc += x
+        cuts.append(min(units, max(cuts[-1], int(round(acc / total * units)))))
+    cuts[-1] = units
+    return [(min(n, a * align), min(n, b * align)) for a, b in zip(cuts, cuts[1:])]
+
+
+class SharedPairBuffer:
+    """ONE host buffer for the whole job's pair list, mapped by every rank of the node.
+
+    The reference's caller receives one row-major list (source/pair.cuh:39-45, 139-146 of the
+    reference).  With one process per GPU the list is assembled without any copy between processes:
+    the buffer is a shared mapping (a file under /dev/shm, or under the temporary directory when
+    /dev/shm is too small), every rank maps it, page-locks its view with cudaHostRegister so that
+    its GPU writes into it by DMA, and copies its band's sorted records to the offset that the
+    exclusive scan of the per-rank counts gives.  Rank 0 creates the file and removes its name as soon
+    as every rank has mapped it, so nothing is left behind if a rank dies later."""
+
+    def __init__(self, capacity_pairs: int, path: str | None = None, register_cuda: bool = False):
+        self.capacity = max(int(capacity_pairs), 1)
+        self.nbytes = self.capacity * 8
+        self.created = path is None
+        if path is None:
+            root = "/dev/shm"
+            try:
+                st = os.statvfs(root)
+                if st.f_bavail * st.f_frsize < self.nbytes + (64 << 20):
+                    root = tempfile.gettempdir()
+            except OSError:
+                root = tempfile.gettempdir()
+            path = os.path.join(root, f"fasted_pairs_{os.getpid()}_{uuid.uuid4().hex}")
+            fd = os.open(path, os.O_CREAT | os.O_EXCL | os.O_RDWR, 0o600)
+            os.ftruncate(fd, self.nbytes)
+        else:
+            fd = os.open(path, os.O_RDWR)
+        self.path = path
+        try:
+            self._mm = mmap.mmap(fd, self.nbytes)  # MAP_SHARED
+        finally:
+            os.close(fd)
+        self.array = np.frombuffer(self._mm, dtype=np.int32).reshape(-1, 2)
+        self.address = self.array.ctypes.data
+        self.registered = False
+        if register_cuda:
+            import torch
+            rc = torch.cuda.cudart().cudaHostRegister(self.address, self.nbytes, 0)
+            self.registered = int(rc) == 0  # not registered: copies go through the library's pinned staging
+
+    def unlink(self) -> None:
+        if self.path and os.path.exists(self.path):
+            os.unlink(self.path)
+
+    def close(self) -> None:
+        if getattr(self, "_mm", None) is None:
+            return
+        if self.registered:
+            import torch
+            torch.cuda.cudart().cudaHostUnregister(self.address)
+            self.registered = False
+        self.array = None
+        try:
+            self._mm.close()
+        except BufferError:
+            pass  # a caller still holds a view; the mapping goes when the view does
+        self._mm = None
+
+    @classmethod
+    def collective(cls, capacity_pairs: int, register_cuda: bool = False) -> "SharedPairBuffer":
+        """Called by every rank: rank 0 creates the buffer, the others map it."""
+        import torch.distributed as dist
+        if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size() == 1:
+            buf = cls(capacity_pairs, register_cuda=register_cuda)
+            buf.unlink()
+            return buf
+        rank = dist.get_rank()
+        box = [None]
+        buf = None
+        if rank == 0:
+            buf = cls(capacity_pairs, register_cuda=register_cuda)
+            box = [(buf.path, buf.capacity)]
+        dist.broadcast_object_list(box, src=0)
+        if rank != 0:
+            buf = cls(box[0][1], path=box[0][0], register_cuda=register_cuda)
+        dist.barrier()
+        if rank == 0:
+            buf.unlink()
+        return buf
 
 
 class BandJoinError(RuntimeError):
@@ -49,14 +157,28 @@ class GpuBandEngine:
         self.sj = self_join
         self.flags = flags
         self.last_stats = None
+        self.capacity_per_row = 256   # the reference's pair-buffer rule (n * 256), per band row
+        self.capacity_rows = 0        # 0: size the buffer by the band; else by this many rows (stable across bands)
 
     def join_band(self, eps: float, q_begin: int, q_end: int):
-        n = self.sj.points_info()[1]
-        st = self.sj.join(eps, q_begin=q_begin, q_end=q_end, capacity=max(1, (q_end - q_begin)) * 256
-                          if q_end - q_begin < n else 0, flags=self.flags)
+        st = self.sj.join(eps, q_begin=q_begin, q_end=q_end,
+                          capacity=max(1, self.capacity_rows or (q_end - q_begin)) * self.capacity_per_row,
+                          flags=self.flags)
         self.last_stats = st
         return self.sj.pairs(), int(st.pairs_found)
 
+
+    def join_band_device(self, eps: float, q_begin: int, q_end: int, capacity: int = 0):
+        """Join the band and leave its sorted list on the device (the sort runs chunk by chunk behind
+        the join): returns (stored, found).  copy_band_to() then places it anywhere on the host."""
+        if not capacity:
+            capacity = max(1, self.capacity_rows or (q_end - q_begin)) * self.capacity_per_row
+        st = self.sj.join_stream(eps, q_begin=q_begin, q_end=q_end, capacity=capacity, flags=self.flags)
+        self.last_stats = st
+        return int(st.pairs_stored), int(st.pairs_found)
+
+    def copy_band_to(self, host_address: int, count: int) -> None:
+        self.sj.pairs_into(host_address, count)
 
     def join_symmetric_shard(self, eps: float, rank: int, world: int):
         st = self.sj.join_symmetric_shard(eps, rank, world, flags=self.flags)
@@ -105,43 +227,81 @@ def allgather_points(points, rank: int, world: int):
     return points
 
 
-def sharded_self_join(engine: BandEngine, n: int, eps: float, gather: bool = True):
+def _exchange_counts(dist, torch, values: list[int]) -> list[list[int]]:
+    """All-gather of a few integers per rank (the only collective after the join)."""
+    world = dist.get_world_size()
+    backend = dist.get_backend()
+    dev = torch.device("cuda", torch.cuda.current_device()) if backend == "nccl" else torch.device("cpu")
+    mine = torch.tensor(values, dtype=torch.int64, device=dev)
+    out = torch.empty(world * len(values), dtype=torch.int64, device=dev)
+    if backend == "nccl":
+        dist.all_gather_into_tensor(out, mine)
+    else:
+        parts = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(parts, mine)
+        out = torch.cat(parts)
+    return out.view(world, len(values)).tolist()
+
+
+def sharded_self_join(engine: BandEngine, n: int, eps: float, gather: bool = True, bounds=None,
+                      shared: SharedPairBuffer | None = None):
     """Join this rank's band; returns (pairs, found_total, stored_local).
 
-    With gather=True rank 0 receives the concatenation of all bands (row-major order) and the
-    other ranks their own band; found_total is the sum over ranks on every rank."""
+    Every rank's sorted band list goes into ONE shared host buffer at the offset the exclusive scan of
+    the per-rank counts gives (band order == global row-major order), so with gather=True rank 0 simply
+    reads the whole list there; the other ranks return their own band.  found_total is the sum over
+    ranks on every rank.  bounds: the ranks' bands (default: equal bands, band_bounds); shared: a
+    buffer made by SharedPairBuffer.collective to reuse (default: one sized to the result, per call;
+    the returned arrays are then copies)."""
     import torch
     import torch.distributed as dist
     if dist.is_available() and dist.is_initialized():
         world, rank = dist.get_world_size(), dist.get_rank()
     else:
         world, rank = 1, 0
-    begin, end = band_bounds(n, world, rank)
+    begin, end = bounds[rank] if bounds is not None else band_bounds(n, world, rank)
     if world == 1:
         pairs, found = engine.join_band(eps, begin, end)
         return pairs, found, len(pairs)
     # A rank whose join fails must not leave the others waiting in the next collective: the error
-    # is caught, reported through the same all-reduce as the counts, and raised on every rank.
-    error = None
+    # is caught, reported through the same exchange as the counts, and raised on every rank.
+    error, pairs, found, stored = None, None, 0, 0
+    on_device = hasattr(engine, "join_band_device")
     try:
-        pairs, found = engine.join_band(eps, begin, end)
+        if on_device:
+            stored, found = engine.join_band_device(eps, begin, end)
+        else:
+            pairs, found = engine.join_band(eps, begin, end)
+            stored = len(pairs)
     except Exception as exc:  # noqa: BLE001 - reported to all ranks below
-        error, pairs, found = exc, np.empty((0, 2), dtype=np.int32), 0
-    backend = dist.get_backend()
-    dev = torch.device("cuda", torch.cuda.current_device()) if backend == "nccl" else torch.device("cpu")
-    t = torch.tensor([found, 1 if error is not None else 0], dtype=torch.int64, device=dev)
-    dist.all_reduce(t)
-    found_total, failed = int(t[0].item()), int(t[1].item())
+        error, pairs, found, stored, on_device = exc, np.empty((0, 2), dtype=np.int32), 0, 0, False
+    table = _exchange_counts(dist, torch, [stored, found, 1 if error is not None else 0])
+    failed = sum(row[2] for row in table)
     if failed:
         raise BandJoinError(f"the band join failed on {failed} of {world} ranks"
                             + (f"; this rank ({rank}): {error}" if error is not None else "")) from error
-    stored_local = len(pairs)
-    if gather:
-        parts = [None] * world if rank == 0 else None
-        dist.gather_object(pairs, parts, dst=0)
-        if rank == 0:
-            pairs = np.concatenate(parts) if parts else pairs
-    return pairs, found_total, stored_local
+    found_total = sum(row[1] for row in table)
+    total = sum(row[0] for row in table)
+    offset = sum(row[0] for row in table[:rank])
+    own = shared is None
+    if own:
+        shared = SharedPairBuffer.collective(total, register_cuda=on_device)
+    elif shared.capacity < total:
+        raise ValueError(f"the shared buffer holds {shared.capacity} pairs, the result has {total}")
+    if on_device:
+        engine.copy_band_to(shared.address + 8 * offset, stored)
+    else:
+        shared.array[offset:offset + stored] = pairs
+    dist.barrier()  # every band is in place
+    if gather and rank == 0:
+        out = shared.array[:total]
+    else:
+        out = shared.array[offset:offset + stored]
+    if own:
+        out = out.copy()
+        dist.barrier()  # nobody unmaps while rank 0 still reads
+        shared.close()
+    return out, found_total, stored
 
 
 def sharded_self_join_symmetric(engine: BandEngine, n: int, eps: float, gather: bool = True):
@@ -192,8 +352,13 @@ def sharded_self_join_symmetric(engine: BandEngine, n: int, eps: float, gather: 
 
     stored_local = len(mine)
     if gather:
-        parts = [None] * world if rank == 0 else None
-        dist.gather_object(mine, parts, dst=0)
+        table = _exchange_counts(dist, torch, [stored_local])
+        total, offset = sum(r[0] for r in table), sum(r[0] for r in table[:rank])
+        shared = SharedPairBuffer.collective(total)
+        shared.array[offset:offset + stored_local] = mine
+        dist.barrier()
         if rank == 0:
-            mine = np.concatenate(parts)
+            mine = shared.array[:total].copy()
+        dist.barrier()
+        shared.close()
     return mine, found_total, stored_local

@@ -9,7 +9,10 @@
  *      buffers (tests, benchmarks, multi-GPU band sharding).
  *
  * All functions are host functions; none is thread-safe with respect to the
- * same context.  Functions of layer 2 return 0 on success and a negative
+ * same context.  Every wait inside a kernel gives up after 2 s of wall time
+ * (the GPU's global timer, not SM cycles) and the call then fails with
+ * FASTED_EKERNEL: on a GPU that is time-sliced with other processes a long
+ * preemption counts toward that limit, so give the library a GPU of its own.  Functions of layer 2 return 0 on success and a negative
  * FASTED_E* code on failure; fasted_last_error() gives the message.
  * There is no CPU fallback: without a usable sm_100 device every compute call
  * fails.
@@ -127,6 +130,9 @@ typedef struct fasted_join_stats {
     int grid;
     unsigned long long cta0_cycles;  /* SM cycles CTA 0 of the join kernel ran (0 for the CTA-pair kernel) */
     unsigned long long cta0_tiles;   /* tiles CTA 0 computed */
+    int chunks;      /* join launches the query range was cut into (1 except for fasted_join_stream) */
+    double tail_ms;  /* fasted_join_stream: host wall time from the end of the last join launch until the
+                        last record was delivered (what the egress pipeline could not hide) */
 } fasted_join_stats;
 
 const char* fasted_last_error(void);
@@ -191,6 +197,30 @@ int fasted_get_norms(fasted_ctx* ctx, float* host_out);
 int fasted_join(fasted_ctx* ctx, double eps, int64_t q_begin, int64_t q_end, uint64_t capacity, unsigned flags,
                 fasted_join_stats* stats);
 
+/* The join with pipelined egress: sort + device-to-host copy overlap the join itself.  Replaces the
+ * reference's serial tail Pairs::sort -> Pairs::getPairs after the kernel (source/pair.cuh:139-158,
+ * source/findPairs.cuh:699-716).  The query range is cut into chunks of whole raster bands (one join
+ * launch each, all enqueued at once); as soon as a chunk's launch retires its records are sorted,
+ * unpacked and copied to the host on separate streams while the GPU joins the next chunks.  Chunks are
+ * ascending ranges of query rows, so the chunks' lists laid end to end are the global row-major order
+ * of source/pair.cuh:39-45: the output is identical to fasted_join + fasted_get_pairs.
+ *
+ * pairs_host (optional): room for host_capacity (query, candidate) int32 records; record i of the
+ * whole list lands at pairs_host[2*i], records beyond host_capacity are not copied.  Pinned (or
+ * registered) memory is written by DMA while the join runs; pageable memory goes through the
+ * context's pinned staging buffers.  dist2_host (optional, needs FASTED_JOIN_DIST2): the distances.
+ * on_chunk (optional): called on the calling thread for consecutive runs of records, in order, once a
+ * run is on the host: pairs / dist2 point at the run (inside pairs_host / dist2_host when those are
+ * given, else into a staging buffer that is valid during the call only), first = index of the run's
+ * first record in the whole list.  A non-zero return value stops the delivery (the call then fails
+ * with FASTED_EINVAL after the GPU work has drained).
+ * flags: FASTED_JOIN_DIST2, FASTED_JOIN_KEEP_NORMS.  Afterwards fasted_get_pairs works as after
+ * fasted_join.  Option "stream_chunk_bands" (fasted_set_option) fixes the raster bands per chunk. */
+typedef int (*fasted_chunk_fn)(void* user, const int32_t* pairs, const float* dist2, uint64_t first, uint64_t count);
+int fasted_join_stream(fasted_ctx* ctx, double eps, int64_t q_begin, int64_t q_end, uint64_t capacity, unsigned flags,
+                       int32_t* pairs_host, float* dist2_host, uint64_t host_capacity, fasted_chunk_fn on_chunk,
+                       void* user, fasted_join_stats* stats);
+
 /* One shard of the symmetric schedule for a self-join split over shard_world GPUs that all hold the
  * dataset: shard r computes the raster bands r, 2G-1-r, 2G+r, ... (G = shard_world) of the upper
  * triangle and emits both orientations of every hit, so the union of the shards' outputs is the
@@ -238,17 +268,27 @@ int fasted_brute_force_f64(fasted_ctx* ctx, const int32_t* sample_rows, int n_sa
  * *pairs_found counts all hits, *pairs_stored those written (at most capacity), as in fasted_join.
  *
  * What the join needs besides that - the row norms and its counters - lives in an area built into
- * the library: 4 MiB + 256 bytes of device memory per GPU, held from library load to process exit.
- * It is sized for n <= 1,048,576 points; a larger n is rejected with FASTED_EINVAL (use
- * fasted_join).  The area is one per GPU and shared by every call: it still holds the previous
- * call's contents on entry (the function re-zeroes its counters and recomputes the norms every
- * time), and two calls whose GPU work overlaps - different streams, threads or processes sharing
- * the library image on one GPU - race on it.  Run them one after the other.
+ * the library: 4 MiB + 256 bytes of device memory, one instance per process and GPU, held from the
+ * moment the CUDA runtime loads this library's module on that GPU until the process exits.  It is
+ * sized for n <= 1,048,576 points; a larger n is rejected with FASTED_EINVAL (use fasted_join).
+ * Every call on a GPU shares the area: it still holds the previous call's contents on entry (the
+ * function re-zeroes its counters and recomputes the norms every time), and two calls of one
+ * process whose GPU work overlaps - different streams or host threads - race on it.  Run them one
+ * after the other.  (Another process has its own CUDA context and therefore its own instance.)
+ *
+ * When the memory is taken: with CUDA's default lazy module loading, the kernels and the built-in
+ * area are placed on a GPU by the first call of ANY function of this library that touches that GPU.
+ * If that first call is this one, it is the one call that does take device memory (the area plus
+ * the kernel images, a few MiB) and it fails with FASTED_ECUDA if the host has left none.  A guest
+ * should therefore make one warm-up call (n = 1, capacity = 0 is enough) before its host claims the
+ * pool, or run with CUDA_MODULE_LOADING=EAGER so that loading the library does it.  Every later
+ * call leaves the amount of free device memory exactly as it found it.
  *
  * Works on the current CUDA device and on `stream` (a cudaStream_t, may be 0); it returns after
- * the stream has drained.  The first call on each device also looks up the device address of
- * the built-in area and sets the kernels' shared-memory limits; make that first call outside any
- * stream capture.  No cudaMalloc, cudaFree, event, stream or library allocation is made. */
+ * the stream has drained.  Each call looks up the device address of the built-in area and sets
+ * the kernels' shared-memory limits (table look-ups, nothing is cached between calls); make the
+ * first call on a device outside any stream capture.  No cudaMalloc, cudaFree, event, stream or
+ * library allocation is made. */
 int fasted_join_static_scratch(const void* points_dev, int64_t n, int64_t d, int64_t ld, double eps,
                                unsigned long long* keys_out_dev, uint64_t capacity, void* stream,
                                unsigned long long* pairs_found, unsigned long long* pairs_stored);

@@ -49,6 +49,8 @@ def lib() -> ctypes.CDLL:
         L.oracle_row_norms.argtypes = [_vp, _i64, _i64, _i64, _vp]
         L.oracle_join_fp16_fp32.argtypes = [_vp, _i64, _i64, _i64, _vp, ctypes.c_double, _i64, _i64, _vp, _vp, _u64]
         L.oracle_join_fp16_fp32.restype = _u64
+        L.oracle_join_band_screened.argtypes = [_vp, _i64, _i64, _i64, _vp, ctypes.c_double, _i64, _i64, _vp, _vp, _u64]
+        L.oracle_join_band_screened.restype = _u64
         L.oracle_join_fp64.argtypes = [_vp, _i64, _i64, _i64, ctypes.c_double, _i64, _i64, _vp, _vp, _u64]
         L.oracle_join_fp64.restype = _u64
         L.oracle_gram_matrix.argtypes = [_vp, _i64, _i64, _i64, _i64, _i64, _vp]
@@ -148,6 +150,23 @@ def join_fp16_fp32(pts: np.ndarray, eps: float, d: int | None = None, q_begin: i
     pairs = np.empty((found, 2), dtype=np.int32)
     d2 = np.empty(found, dtype=np.float32)
     lib().oracle_join_fp16_fp32(_p(pts), n, d, ld, _p(norms), eps, q_begin, q_end, _p(pairs), _p(d2), found)
+    return pairs, d2
+
+
+def join_band_screened(pts: np.ndarray, eps: float, q_begin: int, q_end: int, d: int | None = None,
+                       norms: np.ndarray | None = None):
+    """join_fp16_fp32 for a band of query rows of a large dataset: the same output, with the accumulate
+    model evaluated only for entries that a conservative FP32 screen cannot rule out."""
+    _check_pts(pts)
+    n, ld = pts.shape
+    d = ld if d is None else d
+    if norms is None:
+        norms = row_norms(pts, d)
+    norms = np.ascontiguousarray(norms, dtype=np.float32)
+    found = lib().oracle_join_band_screened(_p(pts), n, d, ld, _p(norms), eps, q_begin, q_end, None, None, 0)
+    pairs = np.empty((found, 2), dtype=np.int32)
+    d2 = np.empty(found, dtype=np.float32)
+    lib().oracle_join_band_screened(_p(pts), n, d, ld, _p(norms), eps, q_begin, q_end, _p(pairs), _p(d2), found)
     return pairs, d2
 
 

@@ -14,6 +14,7 @@
 
 #include <cfenv>
 #include <cmath>
+#include <algorithm>
 #include <cstdint>
 #include <cstdio>
 #include <cstring>
@@ -350,6 +351,102 @@ uint64_t oracle_join_fp16_fp32(const uint16_t* pts, int64_t n, int64_t d, int64_
             }
             ++found;
         }
+    }
+    return found;
+}
+
+// The same join for a band of query rows of a LARGE dataset (millions of candidates): identical
+// output, affordable because the expensive accumulate model is evaluated only where it can matter.
+// Every (query, candidate) entry is first screened with a plain FP32 dot product (16 independent
+// partial sums, so the loop vectorises without reassociation): with
+//     approx = s_i + s_j - 2 * dot          (double, from the FP32 dot)
+// the entry is handed to the exact model iff approx <= eps2 + margin * (s_i + s_j + eps2).
+// The model's d2 differs from the true d2 by at most the rounding of its two ingredients: the
+// round-toward-zero norm chain loses less than one ulp per add (d/2 adds: below d * 2^-24 relative),
+// the truncating accumulate less than (17 * 2^-25 + 2^-23) of the running magnitude per 16-wide
+// slice (d/16 slices), the screen's own FP32 dot less than d/16 * 2^-23 -- together well under
+// d * 3e-7 relative to s_i + s_j.  margin = max(2e-3, d * 1e-6) is several times that, so no entry
+// the model would accept is ever screened out, and entries the screen lets through are decided by
+// the model alone.  Candidate rows are converted block by block: no FP32 copy of the whole matrix.
+// `norms` are the n row norms from oracle_row_norms.  Output: row-major sorted, as above.
+// out[r] = dot(q[r], c) for `rows` query rows: 16 independent partial sums per row.
+ORACLE_CLONES
+__attribute__((optimize("O3"))) static void screen_dots(const float* q, const float* c, int64_t d, int64_t rows,
+                                                        float* out) {
+    for (int64_t r = 0; r < rows; ++r) {
+        const float* a = q + r * d;
+        float acc[16] = {0};
+        int64_t k = 0;
+        for (; k + 16 <= d; k += 16)
+            for (int l = 0; l < 16; ++l) acc[l] += a[k + l] * c[k + l];
+        for (; k < d; ++k) acc[k & 15] += a[k] * c[k];
+        float s = 0.0f;
+        for (int l = 0; l < 16; ++l) s += acc[l];
+        out[r] = s;
+    }
+}
+
+uint64_t oracle_join_band_screened(const uint16_t* pts, int64_t n, int64_t d, int64_t ld, const float* norms,
+                                   double eps, int64_t q_begin, int64_t q_end, int32_t* pairs_out, float* d2_out,
+                                   uint64_t capacity) {
+    const float eps2 = (float)(eps * eps);
+    const double margin = std::max(2e-3, (double)d * 1e-6);
+    const int64_t rows = q_end - q_begin;
+    std::vector<float> qf((size_t)rows * (size_t)d);
+    std::vector<int16_t> qe((size_t)rows * (size_t)d);
+    for (int64_t r = 0; r < rows; ++r)
+        for (int64_t k = 0; k < d; ++k) {
+            qf[(size_t)r * d + k] = half_bits_to_float(pts[(q_begin + r) * ld + k]);
+            qe[(size_t)r * d + k] = (int16_t)half_exponent(pts[(q_begin + r) * ld + k]);
+        }
+    struct Hit {
+        int32_t q, c;
+        float d2;
+    };
+    std::vector<std::vector<Hit>> per_thread((size_t)omp_get_max_threads());
+#pragma omp parallel
+    {
+        std::vector<Hit>& mine = per_thread[(size_t)omp_get_thread_num()];
+        std::vector<float> cf((size_t)d), dots((size_t)rows);
+        std::vector<int16_t> ce((size_t)d);
+#pragma omp for schedule(dynamic, 64)
+        for (int64_t j = 0; j < n; ++j) {
+            for (int64_t k = 0; k < d; ++k) cf[(size_t)k] = half_bits_to_float(pts[j * ld + k]);
+            screen_dots(qf.data(), cf.data(), d, rows, dots.data());
+            bool have_exp = false;
+            for (int64_t r = 0; r < rows; ++r) {
+                const int64_t i = q_begin + r;
+                const double ssum = (double)norms[i] + (double)norms[j];
+                const double approx = ssum - 2.0 * (double)dots[(size_t)r];
+                if (!(approx <= (double)eps2 + margin * (ssum + (double)eps2))) continue;
+                if (!have_exp) {
+                    for (int64_t k = 0; k < d; ++k) ce[(size_t)k] = (int16_t)half_exponent(pts[j * ld + k]);
+                    have_exp = true;
+                }
+                float g;
+                {
+                    RoundTowardZero rz;
+                    g = gram_entry(&qf[(size_t)r * d], &qe[(size_t)r * d], cf.data(), ce.data(), d);
+                }
+                volatile float t = norms[i] + norms[j];
+                volatile float d2 = t - 2.0f * g;
+                if (d2 <= eps2) mine.push_back(Hit{(int32_t)i, (int32_t)j, (float)d2});
+            }
+        }
+    }
+    std::vector<Hit> all;
+    for (auto& v : per_thread) all.insert(all.end(), v.begin(), v.end());
+    std::sort(all.begin(), all.end(), [](const Hit& a, const Hit& b) { return a.q != b.q ? a.q < b.q : a.c < b.c; });
+    uint64_t found = 0;
+    for (const Hit& h : all) {
+        if (found < capacity) {
+            if (pairs_out) {
+                pairs_out[2 * found] = h.q;
+                pairs_out[2 * found + 1] = h.c;
+            }
+            if (d2_out) d2_out[found] = h.d2;
+        }
+        ++found;
     }
     return found;
 }

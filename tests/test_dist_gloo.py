@@ -31,6 +31,41 @@ def test_band_bounds_cover_and_align():
         band_bounds(10, 2, 2)
 
 
+def test_weighted_band_bounds_follow_the_rates():
+    from fasted_b200.dist import weighted_band_bounds
+    for n in [0, 1, 129, 1000, 100_000, 1_000_000]:
+        for w in [[1.0], [1, 1], [3, 1], [1.0, 1.1, 0.9, 1.0], [1, 0, 2], [0, 0, 0], [5, 4, 6, 5, 5, 5, 4.5, 5.5]]:
+            bands = weighted_band_bounds(n, w)
+            assert len(bands) == len(w) and bands[0][0] == 0 and bands[-1][1] == n
+            for (a, b), (c, d) in zip(bands, bands[1:]):
+                assert b == c and a <= b
+            assert all(a % 128 == 0 or a == n for a, _ in bands)
+            if n >= 100_000 and sum(w) > 0:
+                for (a, b), x in zip(bands, w):
+                    assert abs((b - a) - n * x / sum(w)) <= 256  # proportional up to tile rounding
+    assert weighted_band_bounds(1000, [1, 0, 2])[1] == (384, 384)  # a stalled rank gets nothing
+    with pytest.raises(ValueError):
+        weighted_band_bounds(10, [])
+
+
+def test_shared_pair_buffer_is_one_mapping_for_two_openers():
+    from fasted_b200.dist import SharedPairBuffer
+    a = SharedPairBuffer(1000)
+    try:
+        assert os.path.exists(a.path) and a.array.shape == (1000, 2)
+        b = SharedPairBuffer(1000, path=a.path)
+        a.array[10:20] = np.arange(20, dtype=np.int32).reshape(10, 2)
+        assert np.array_equal(b.array[10:20], a.array[10:20]) and b.address != 0
+        a.unlink()
+        assert not os.path.exists(a.path)
+        b.array[0] = (7, 8)  # the mapping outlives the name
+        assert a.array[0].tolist() == [7, 8]
+        b.close()
+    finally:
+        a.unlink()
+        a.close()
+
+
 def _free_port():
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
@@ -88,6 +123,15 @@ def _worker(rank, world, port, n, d, eps, out_dir):
     np.save(os.path.join(out_dir, f"gathered_ok{rank}.npy"),
             np.array([torch.equal(full[:n], t), bool((full[n:] == 0).all())]))
     pairs, found, stored = sharded_self_join(OracleEngine(pts), n, eps)
+    # the same with bands sized by (made-up) measured rates and a shared buffer that the caller owns
+    from fasted_b200.dist import SharedPairBuffer, weighted_band_bounds
+    wb = weighted_band_bounds(n, [1.0 + 0.5 * r for r in range(world)])
+    shared = SharedPairBuffer.collective(found + 5)
+    wpairs, wfound, wstored = sharded_self_join(OracleEngine(pts), n, eps, bounds=wb, shared=shared)
+    np.save(os.path.join(out_dir, f"wpairs{rank}.npy"), np.array(wpairs))
+    np.save(os.path.join(out_dir, f"wmeta{rank}.npy"), np.array([wfound, wstored, wb[rank][0], wb[rank][1]]))
+    dist.barrier()
+    shared.close()
     from fasted_b200.dist import sharded_self_join_symmetric
     spairs, sfound, sstored = sharded_self_join_symmetric(OracleEngine(pts), n, eps)
     np.save(os.path.join(out_dir, f"spairs{rank}.npy"), spairs)
@@ -109,6 +153,14 @@ def test_sharded_join_equals_single_rank(oracle_mod, tmp_path, world):
     assert all(np.load(tmp_path / f"gathered_ok{r}.npy").all() for r in range(world))
     assert all(int(m[0]) == len(want) for m in metas)
     assert sum(int(m[1]) for m in metas) == len(want)
+    # weighted bands, caller-owned shared buffer: the same list; every rank wrote its own band only
+    assert np.array_equal(np.load(tmp_path / "wpairs0.npy"), want)
+    wm = [np.load(tmp_path / f"wmeta{r}.npy") for r in range(world)]
+    assert all(int(m[0]) == len(want) for m in wm) and sum(int(m[1]) for m in wm) == len(want)
+    assert [int(m[3] - m[2]) for m in wm] == sorted(int(m[3] - m[2]) for m in wm)  # sizes grow with the rates
+    for r in range(1, world):
+        p = np.load(tmp_path / f"wpairs{r}.npy")
+        assert len(p) == int(wm[r][1]) and (len(p) == 0 or (p[:, 0].min() >= wm[r][2] and p[:, 0].max() < wm[r][3]))
     # symmetric schedule + all-to-all of records: same global list, every rank a contiguous range
     assert np.array_equal(np.load(tmp_path / "spairs0.npy"), want)
     smetas = [np.load(tmp_path / f"smeta{r}.npy") for r in range(world)]

@@ -256,6 +256,27 @@ def test_join_against_reference_gpu_output(gpu_join, oracle_mod, path):
     assert np.array_equal(got, g["pairs"])
 
 
+def _refsum_cases():
+    import glob
+    return sorted(glob.glob(os.path.join(GOLDEN, "refsum_gpu_*.npz")))
+
+
+@pytest.mark.parametrize("path", _refsum_cases(), ids=lambda p: os.path.basename(p)[11:-4])
+def test_join_against_reference_gpu_digest(gpu_join, oracle_mod, path):
+    # A full-size run of the reference's own kernels on a B200 (benchmark configuration 2's shape:
+    # 100,000 unit vectors x 384), kept as pair count + order-independent digests of the pair list.
+    from test_oracle_golden import _golden_dataset, _key_digests
+    g = np.load(path)
+    pts = _golden_dataset(oracle_mod, g)
+    gpu_join.set_points(pts)
+    st = gpu_join.join(float(g["epsilon"]))
+    got = gpu_join.pairs()
+    assert int(st.pairs_found) == int(g["pairs_found"]) == len(got)
+    ksum, kxor = _key_digests(got)
+    assert ksum == int(g["key_sum"]) and kxor == int(g["key_xor_mix"])
+    assert np.array_equal(got[:4096], g["first_pairs"])
+
+
 @pytest.mark.parametrize("n,d,eps", [(256, 64, 1e3), (300, 100, 1e3), (1000, 256, 0.5), (2000, 512, 0.7),
                                      (4096, 128, 0.3136), (777, 333, 0.5), (3000, 2048, 1.6)])
 def test_cta_pair_kernel_is_bit_identical(gpu_join, oracle_mod, n, d, eps):
@@ -345,22 +366,75 @@ def test_full_size_headline_shape_properties(gpu_join, oracle_mod):
     kl = np.sort((lo[:, 1].astype(np.int64) << 32) | lo[:, 0].astype(np.int64))
     assert np.array_equal(ku, kl)
     del keys, up, lo, ku, kl
-    # sampled rows vs FP64 truth
+    # sampled rows vs FP64 truth: every disagreement must sit inside the 1e-3 band around eps^2
+    # (the bit-exact check of this shape against the oracle is test_full_size_band_is_bit_identical_to_the_oracle)
     rows = np.arange(123_456, 123_456 + 48, dtype=np.int32)
     counts, truth = gpu_join.brute_force_pairs(rows, eps, capacity=48 * 65536)
     mine = got[(got[:, 0] >= rows[0]) & (got[:, 0] <= rows[-1])]
     kt = (truth[:, 0].astype(np.int64) << 32) | truth[:, 1].astype(np.int64)
     km = (mine[:, 0].astype(np.int64) << 32) | mine[:, 1].astype(np.int64)
     only = np.concatenate([np.setdiff1d(kt, km), np.setdiff1d(km, kt)])
-    assert len(only) <= 0.03 * len(kt) + 4
     if len(only):
-        # every disagreement must sit inside the 1e-3 band around eps^2 (FP64 distances on the device)
         pr = np.stack([only >> 32, only & 0xFFFFFFFF], 1)
         sub = gpu_join.get_rows(np.unique(pr.ravel()))
         lut = {int(r): i for i, r in enumerate(np.unique(pr.ravel()))}
         f = sub.view(np.float16).astype(np.float64)
         d2 = np.array([((f[lut[int(a)]] - f[lut[int(b)]]) ** 2).sum() for a, b in pr])
         assert (np.abs(d2 - eps * eps) <= BAND * eps * eps).all()
+
+
+def _free_host_bytes():
+    import psutil
+    return psutil.virtual_memory().available
+
+
+@pytest.mark.parametrize("name,q_begin,rows", [("c2", 40_960, 256), ("c3", 500_096, 64), ("c4", 1_200_000 // 128 * 128, 64),
+                                               ("c5", 2_345_600, 64)])
+def test_full_size_band_is_bit_identical_to_the_oracle(gpu_join, oracle_mod, name, q_begin, rows):
+    # The benchmark's own configurations at FULL size (the same seeded data bench.py generates): a band
+    # of query rows against all N candidates must give exactly the oracle's pairs AND its FP32 squared
+    # distances, bit for bit.  The whole matrix is copied to the host once; the oracle evaluates the
+    # accumulate model wherever a conservative screen cannot rule a pair out (oracle.join_band_screened,
+    # pinned against the plain restatement by the CPU tests).
+    import torch
+    from fasted_b200.workloads import WORKLOADS, fill_device, padded_dim
+    wl = WORKLOADS[name]
+    n, d = wl["n"], wl["d"]
+    ld = padded_dim(d)
+    need_dev = n * ld * 2 + rows * wl.get("pairs_per_point", 256) * 64
+    need_host = n * d * 2 * 2 + (4 << 30)
+    if torch.cuda.mem_get_info()[0] < need_dev + (8 << 30) or _free_host_bytes() < need_host:
+        pytest.skip("not enough free device or host memory for this configuration")
+    dev = torch.zeros((n, ld), dtype=torch.float16, device="cuda")
+    fill_device(gpu_join, dev, wl)
+    torch.cuda.synchronize()
+    gpu_join.set_points_device(dev.data_ptr(), n, d, ld, keepalive=dev)
+    try:
+        eps = wl["eps"]
+        if eps is None:
+            eps, _ = gpu_join.estimate_epsilon(wl["target"], 4096, 0.02)
+        cap = rows * max(8192, 4 * wl.get("pairs_per_point", 256))
+        st = gpu_join.join(eps, q_begin=q_begin, q_end=q_begin + rows, capacity=cap, flags=1)
+        assert st.status == 0 and st.pairs_found == st.pairs_stored >= rows
+        got, got_d2 = gpu_join.pairs(with_dist2=True)
+        # the streaming entry point on the same band: identical list
+        sgot = np.full((len(got), 2), -1, dtype=np.int32)
+        gpu_join.join_stream(eps, q_begin=q_begin, q_end=q_begin + rows, capacity=cap, pairs_host=sgot.ctypes.data,
+                             host_capacity=len(got))
+        assert np.array_equal(sgot, got)
+        host = np.empty((n, d), dtype=np.uint16)
+        gpu_join.get_points_into(host.ctypes.data, d)
+        norms_gpu, _ = gpu_join.row_norms()
+    finally:
+        gpu_join.set_points(np.zeros((1, 64), dtype=np.uint16))  # drop the borrowed matrix
+        del dev
+        torch.cuda.empty_cache()
+    norms = oracle_mod.row_norms(host, d)
+    assert np.array_equal(norms_gpu.view(np.uint32), norms.view(np.uint32))  # all N row norms, bit for bit
+    want, want_d2 = oracle_mod.join_band_screened(host, eps, q_begin, q_begin + rows, d=d, norms=norms)
+    assert len(want) >= rows * min(wl["target"], 4) // 4 + rows  # the band has real neighbours, not only self pairs
+    assert np.array_equal(got, want), (len(got), len(want))
+    assert np.array_equal(got_d2.view(np.uint32), want_d2.view(np.uint32))
 
 
 @pytest.mark.parametrize("n,d,eps,world", [(5000, 128, 0.33, 2), (9000, 64, 0.2, 3), (20000, 256, 0.45, 8)])

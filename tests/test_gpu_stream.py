@@ -1,0 +1,135 @@
+"""fasted_join_stream: the join whose sort and device-to-host copy run chunk by chunk behind the join
+(the reference's serial tail is Pairs::sort -> Pairs::getPairs, source/pair.cuh:139-158 and
+source/findPairs.cuh:699-716 of the reference).  Its output must be identical, record for record and
+distance bit for distance bit, to fasted_join + fasted_get_pairs, whatever the chunking, the kind of
+host memory and the delivery mode; the overflow rule (found counts everything, stored saturates at the
+capacity) holds in total."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def _points(oracle_mod, n, d, seed):
+    rng = np.random.default_rng(seed)
+    return oracle_mod.double_to_half(rng.exponential(1 / 40.0, size=(n, d)))
+
+
+@pytest.mark.parametrize("n,d,eps,band_tiles,chunk_bands", [
+    (4096, 128, 0.3136, 0, 0),      # automatic chunking (one or two chunks at this size)
+    (5000, 200, 0.36, 2, 1),        # 20 chunks of 256 rows
+    (3001, 64, 0.25, 1, 3),         # ragged last chunk, d a single K step
+    (9000, 1024, 1.1, 4, 2),
+    (700, 333, 0.5, 1, 1),          # d not a multiple of 64
+])
+def test_stream_equals_join_then_get_pairs(gpu_join, oracle_mod, n, d, eps, band_tiles, chunk_bands):
+    import torch
+    pts = _points(oracle_mod, n, d, n + d)
+    gpu_join.set_points(pts)
+    gpu_join.set_option("band_tiles", band_tiles)
+    gpu_join.set_option("stream_chunk_bands", chunk_bands)
+    try:
+        st0 = gpu_join.join(eps, flags=1)
+        want, want_d2 = gpu_join.pairs(with_dist2=True)
+        m = len(want)
+        assert m == st0.pairs_found > n
+        # (a) pinned destination, with distances
+        hp = torch.full((m + 7, 2), -1, dtype=torch.int32).pin_memory()
+        hd = torch.full((m + 7,), -1.0, dtype=torch.float32).pin_memory()
+        seen = []
+        st = gpu_join.join_stream(eps, flags=1, pairs_host=hp.data_ptr(), dist2_host=hd.data_ptr(), host_capacity=m + 7,
+                                  on_chunk=lambda p, d2, first: seen.append((first, len(p), p[0].tolist(), float(d2[0]))))
+        assert st.status == 0 and st.pairs_found == st.pairs_stored == m
+        assert np.array_equal(hp.numpy()[:m], want) and (hp.numpy()[m:] == -1).all()
+        assert np.array_equal(hd.numpy()[:m].view(np.uint32), want_d2.view(np.uint32)) and (hd.numpy()[m:] == -1).all()
+        # the callback saw consecutive runs that tile [0, m), each pointing into the destination
+        assert [f for f, *_ in seen] == list(np.cumsum([0] + [c for _, c, *_ in seen[:-1]]))
+        assert sum(c for _, c, *_ in seen) == m
+        assert all(want[f].tolist() == p0 and want_d2[f] == d0 for f, _, p0, d0 in seen)
+        if chunk_bands:
+            rows_per_chunk = chunk_bands * (band_tiles or 16) * 128
+            assert st.chunks == -(-n // rows_per_chunk)
+            assert len(seen) <= st.chunks
+        # fasted_get_pairs works afterwards, as after fasted_join
+        again, again_d2 = gpu_join.pairs(with_dist2=True)
+        assert np.array_equal(again, want) and np.array_equal(again_d2.view(np.uint32), want_d2.view(np.uint32))
+        # (b) pageable destination, no distances, no callback
+        out = np.full((m, 2), -1, dtype=np.int32)
+        st = gpu_join.join_stream(eps, pairs_host=out.ctypes.data, host_capacity=m)
+        assert st.pairs_found == m and np.array_equal(out, want)
+        # (c) callback only: the runs pass through the library's staging buffers
+        got, got_d2 = [], []
+        st = gpu_join.join_stream(eps, flags=1, on_chunk=lambda p, d2, first: (got.append(p.copy()), got_d2.append(d2.copy())) and 0)
+        assert np.array_equal(np.concatenate(got), want)
+        assert np.array_equal(np.concatenate(got_d2).view(np.uint32), want_d2.view(np.uint32))
+        # (d) a band of query rows
+        b0, b1 = 128, min(n, 128 + 5 * 128 + 17)
+        band = np.full((m, 2), -1, dtype=np.int32)
+        st = gpu_join.join_stream(eps, q_begin=b0, q_end=b1, pairs_host=band.ctypes.data, host_capacity=m)
+        sel = want[(want[:, 0] >= b0) & (want[:, 0] < b1)]
+        assert st.pairs_found == len(sel) and np.array_equal(band[:len(sel)], sel)
+    finally:
+        gpu_join.set_option("band_tiles", 0)
+        gpu_join.set_option("stream_chunk_bands", 0)
+
+
+def test_stream_against_the_oracle(gpu_join, oracle_mod):
+    from util import assert_identical_to_oracle
+    pts = oracle_mod.gen_exponential(3000, 192)
+    gpu_join.set_points(pts)
+    gpu_join.set_option("band_tiles", 2)
+    gpu_join.set_option("stream_chunk_bands", 2)
+    try:
+        got, got_d2 = [], []
+        gpu_join.join_stream(0.36, flags=1, on_chunk=lambda p, d2, first: (got.append(p.copy()), got_d2.append(d2.copy())) and 0)
+    finally:
+        gpu_join.set_option("band_tiles", 0)
+        gpu_join.set_option("stream_chunk_bands", 0)
+    assert_identical_to_oracle(oracle_mod, pts, 192, 0.36, np.concatenate(got), np.concatenate(got_d2))
+
+
+def test_stream_overflow_clip_and_abort(gpu_join, oracle_mod):
+    from fasted_b200 import FastedError
+    pts = _points(oracle_mod, 4000, 96, 5)
+    gpu_join.set_points(pts)
+    gpu_join.set_option("band_tiles", 2)
+    gpu_join.set_option("stream_chunk_bands", 1)
+    try:
+        full = gpu_join.join(0.3)
+        want = gpu_join.pairs()
+        m = len(want)
+        allk = oracle_mod.pair_keys(want)
+        # pair buffer smaller than the result: found keeps counting, stored saturates; what is delivered
+        # is sorted chunk by chunk, free of duplicates, and part of the full result
+        cap = m // 3
+        out = np.full((m, 2), -1, dtype=np.int32)
+        st = gpu_join.join_stream(0.3, capacity=cap, pairs_host=out.ctypes.data, host_capacity=m)
+        assert st.pairs_found == m and st.pairs_stored == cap
+        k = oracle_mod.pair_keys(out[:cap])
+        assert len(np.unique(k)) == cap and np.isin(k, allk).all() and (out[cap:] == -1).all()
+        # the chunks that fitted completely come first and are exact
+        whole_rows = out[:cap][:, 0].max()
+        head = want[want[:, 0] < (whole_rows // 256) * 256]
+        assert np.array_equal(out[:len(head)], head)
+        # host buffer smaller than the result: the head of the list is copied, nothing beyond it
+        small = np.full((1000 + 5, 2), -1, dtype=np.int32)
+        st = gpu_join.join_stream(0.3, pairs_host=small.ctypes.data, host_capacity=1000)
+        assert st.pairs_stored == m and np.array_equal(small[:1000], want[:1000]) and (small[1000:] == -1).all()
+        # a callback that asks to stop: the call fails after the GPU work has drained, the context stays usable
+        calls = []
+        with pytest.raises(FastedError):
+            gpu_join.join_stream(0.3, on_chunk=lambda p, d2, first: calls.append(first) or 1)
+        assert calls == [0]
+        with pytest.raises(ZeroDivisionError):
+            gpu_join.join_stream(0.3, on_chunk=lambda p, d2, first: 1 // 0)
+        assert gpu_join.join(0.3).pairs_found == full.pairs_found
+        # flags that make no sense here are refused
+        for bad in (2, 8, 16):
+            with pytest.raises(FastedError):
+                gpu_join.join_stream(0.3, flags=bad)
+        # empty query range
+        st = gpu_join.join_stream(0.3, q_begin=128, q_end=128, on_chunk=lambda *a: 1)
+        assert st.pairs_found == 0
+    finally:
+        gpu_join.set_option("band_tiles", 0)
+        gpu_join.set_option("stream_chunk_bands", 0)

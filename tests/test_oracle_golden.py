@@ -149,6 +149,33 @@ def _golden_dataset(oracle_mod, g):
     return pts
 
 
+def _key_digests(pairs):
+    """Order-independent digests of a pair list, as tests/golden/make_golden_gpu.py stores them."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("make_golden_gpu", os.path.join(GOLDEN, "make_golden_gpu.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod.key_digests(pairs)
+
+
+def _refsum_cases():
+    import glob
+    return sorted(glob.glob(os.path.join(GOLDEN, "refsum_gpu_*.npz")))
+
+
+@pytest.mark.parametrize("path", _refsum_cases(), ids=lambda p: os.path.basename(p)[11:-4])
+def test_oracle_against_reference_gpu_digest_head(oracle_mod, path):
+    # The reference's own kernels on benchmark configuration 2's shape (100,000 x 384): the fixture keeps the
+    # head of the reference's sorted pair list; the oracle must reproduce those rows exactly.
+    g = np.load(path)
+    pts = _golden_dataset(oracle_mod, g)
+    head = g["first_pairs"]
+    rows = int(head[-1, 0])  # rows [0, rows) are complete in the head
+    assert rows >= 64
+    mine, _ = oracle_mod.join_band_screened(pts, float(g["epsilon"]), 0, rows)
+    assert np.array_equal(mine, head[head[:, 0] < rows])
+
+
 @pytest.mark.parametrize("path", _ref_gpu_cases(), ids=lambda p: os.path.basename(p)[8:-4])
 def test_oracle_against_reference_gpu_output(oracle_mod, path):
     # Pair lists produced by the reference's own kernels (compiled unmodified, run on a B200).
@@ -183,3 +210,24 @@ def test_accumulate_model_known_answers(oracle_mod):
     assert dot([(-1.0, 1.0), (-2.0 ** -11, 1.75 * 2.0 ** -12)]) == -(1 + u)
     assert dot([(1.0, 1.0)] + [(0, 0)] * 15 + [(2.0 ** -13, 2.0 ** -13)] * 16, 32) == 1.0
     assert dot([(2.0 ** -13, 2.0 ** -13)] * 16 + [(0, 0)] * 15 + [(1.0, 1.0)], 32) == 1 + 2 * u
+
+
+@pytest.mark.parametrize("n,d,eps,band", [(1000, 64, 0.2, (0, 1000)), (4096, 128, 0.3136, (1024, 1100)),
+                                          (777, 333, 0.63, (700, 777)), (600, 1024, 1.1, (17, 211)),
+                                          (300, 70, 1e3, (0, 300))])
+def test_screened_band_join_equals_the_full_restatement(oracle_mod, n, d, eps, band):
+    # The band join used on million-point inputs (FP32 screen, accumulate model only near the threshold)
+    # must give exactly what the plain restatement gives: pairs and FP32 distances, bit for bit.
+    pts = oracle_mod.gen_exponential(n, d)
+    want, want_d2 = oracle_mod.join_fp16_fp32(pts, eps, q_begin=band[0], q_end=band[1])
+    got, got_d2 = oracle_mod.join_band_screened(pts, eps, band[0], band[1])
+    assert len(want) > band[1] - band[0] or eps < 0.25, len(want)
+    assert np.array_equal(got, want) and np.array_equal(got_d2.view(np.uint32), want_d2.view(np.uint32))
+    rng = np.random.default_rng(n)
+    x = rng.standard_normal((500, d))
+    x /= np.linalg.norm(x, axis=1, keepdims=True)
+    unit = oracle_mod.double_to_half(x)
+    for e in (0.0, 1.2, 1.45):
+        a, a2 = oracle_mod.join_fp16_fp32(unit, e, q_begin=100, q_end=164)
+        b, b2 = oracle_mod.join_band_screened(unit, e, 100, 164)
+        assert np.array_equal(a, b) and np.array_equal(a2.view(np.uint32), b2.view(np.uint32))

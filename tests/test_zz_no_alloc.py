@@ -74,3 +74,64 @@ def test_static_scratch_overflow_and_limits(gpu_join, oracle_mod):
     # count-only use: no output buffer at all
     found, stored = _lib.join_static_scratch(dev.data_ptr(), 8, 64, 64, 0.0, 0, 0)
     assert found == 64 and stored == 0
+
+
+def test_static_scratch_leaves_free_memory_alone(gpu_join, oracle_mod):
+    """The property in the entry point's name: once the library's module is on the GPU, a call changes
+    nothing about the amount of free device memory (no cudaMalloc / cudaFree hides inside it)."""
+    import torch
+    from fasted_b200 import _lib
+    pts = oracle_mod.gen_exponential(2000, 128)
+    dev = torch.from_numpy(pts.view(np.int16)).cuda()
+    out = torch.zeros((1 << 20,), dtype=torch.int64, device="cuda")
+    torch.cuda.synchronize()
+    first = _lib.join_static_scratch(dev.data_ptr(), 2000, 128, 128, 0.3, out.data_ptr(), 1 << 20)
+    free_before, _ = torch.cuda.mem_get_info()
+    second = _lib.join_static_scratch(dev.data_ptr(), 2000, 128, 128, 0.3, out.data_ptr(), 1 << 20)
+    third = _lib.join_static_scratch(dev.data_ptr(), 1500, 128, 128, 0.25, out.data_ptr(), 1 << 20)
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before
+    assert first == second and third[0] < second[0]
+
+
+_FIRST_CALL = r"""
+import sys
+sys.path.insert(0, {root!r})
+import numpy as np, torch
+import oracle
+from fasted_b200 import _lib, SelfJoin
+pts = oracle.gen_exponential(1500, 96)
+dev = torch.from_numpy(pts.view(np.int16)).cuda()          # the host's pool stands in: torch owns these
+out = torch.zeros((1 << 19,), dtype=torch.int64, device="cuda")
+torch.cuda.synchronize()
+# The very first call into the library in this process: it is the one that makes the CUDA runtime
+# load the library's module (kernels + the built-in scratch area) on this GPU.
+free0, _ = torch.cuda.mem_get_info()
+found1, stored1 = _lib.join_static_scratch(dev.data_ptr(), 1500, 96, 96, 0.3, out.data_ptr(), 1 << 19)
+free1, _ = torch.cuda.mem_get_info()
+k1 = np.sort(out.cpu().numpy().view(np.uint64)[:stored1])
+found2, stored2 = _lib.join_static_scratch(dev.data_ptr(), 1500, 96, 96, 0.3, out.data_ptr(), 1 << 19)
+free2, _ = torch.cuda.mem_get_info()
+k2 = np.sort(out.cpu().numpy().view(np.uint64)[:stored2])
+with SelfJoin(0) as sj:                                      # the allocating entry point, for comparison
+    sj.set_points(pts)
+    st = sj.join(0.3)
+    want = oracle.pair_keys(sj.pairs())
+assert found1 == found2 == st.pairs_found == len(want), (found1, found2, st.pairs_found)
+assert np.array_equal(k1, want) and np.array_equal(k2, want)
+assert free2 == free1, (free1, free2)                        # later calls take nothing
+print("MODULE_LOAD_BYTES", free0 - free1)
+"""
+
+
+def test_static_scratch_as_the_first_call_of_a_process(native_lib, oracle_mod):
+    """In a fresh process the entry point is the first thing asked of the library, so this call is the
+    one during which the CUDA runtime places the library's module on the GPU; it must work, give the
+    allocating entry point's result, and every call after it must leave free memory untouched."""
+    import subprocess
+    import sys
+    from conftest import ROOT
+    r = subprocess.run([sys.executable, "-c", _FIRST_CALL.format(root=ROOT)], capture_output=True, text=True,
+                       timeout=600)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "MODULE_LOAD_BYTES" in r.stdout
