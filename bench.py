@@ -220,6 +220,9 @@ def main() -> None:
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the symmetric-mode and accuracy legs")
     ap.add_argument("--no-refgpu", action="store_true", help="skip the reference's own kernels on this GPU")
+    ap.add_argument("--e2e-mode", default="stream", choices=["stream", "serial"],
+                    help="N = 1: stream = fasted_join_stream (egress pipelined behind the join); serial = fasted_join, "
+                         "then fasted_get_pairs (sort and copy after the join, as the reference orders them)")
     ap.add_argument("--no-balance", action="store_true", help="N > 1: keep equal bands (no sizing by measured rate)")
     ap.add_argument("--option", action="append", default=[], help="name=value for fasted_set_option (tuning runs)")
     args = ap.parse_args()
@@ -428,6 +431,11 @@ def main() -> None:
         def step_e2e():
             if world == 1:
                 sj.set_points_ptr(host_pts.data_ptr(), n, d, ld)
+                if args.e2e_mode == "serial":
+                    st = sj.join(eps, capacity=capacity)
+                    m = min(int(st.pairs_stored), out_cap)
+                    sj.pairs_into(host_out.data_ptr(), m)
+                    return st, m
                 st = sj.join_stream(eps, capacity=capacity, pairs_host=host_out.data_ptr(), host_capacity=out_cap)
                 return st, min(int(st.pairs_stored), out_cap)
             dev_pts[pad_begin:pad_end].copy_(host_pts, non_blocking=True)
@@ -457,6 +465,7 @@ def main() -> None:
         e2e = {"value": flop / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOPS", "ms_per_step": e2e_ms,
                "h2d_bytes_per_step": host_pts.numel() * 2 * world, "d2h_bytes_per_step": d2h,
                "join_kernel_ms": float(np.mean(e2e_join_ms)), "egress_tail_ms": float(np.mean(e2e_tail_ms)),
+               "sort_ms": float(st.sort_ms), "mode": args.e2e_mode if world == 1 else "stream",
                "join_launches_per_step": e2e_chunks,
                "api": "fasted_set_points_host_f16 + fasted_join_stream (pinned host buffers; sort and device-to-host "
                       "copy pipelined behind the join)"

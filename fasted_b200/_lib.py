@@ -60,7 +60,8 @@ DECLARED_SYMBOLS = [
     "fasted_points_info", "fasted_get_points_host_f16", "fasted_get_rows_host_f16", "fasted_row_norms", "fasted_get_norms",
     "fasted_join", "fasted_selftest_wait_timeout", "fasted_join_symmetric_shard", "fasted_tile_schedule", "fasted_estimate_epsilon", "fasted_get_pairs", "fasted_pairs_device", "fasted_brute_force_f64", "fasted_brute_force_f64_pairs", "fasted_set_option",
     "fasted_dataset_exponential_f16", "fasted_dataset_csv_shape", "fasted_dataset_csv_f16",
-    "fasted_join_static_scratch", "fasted_join_stream",
+    "fasted_join_static_scratch", "fasted_join_stream", "fasted_tile_schedule_stationary",
+    "fasted_broadcast_points",
 ]
 
 CHUNK_FN = ctypes.CFUNCTYPE(ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_uint64,
@@ -88,6 +89,7 @@ def load() -> ctypes.CDLL:
     L.fasted_set_points_device_f16.argtypes = [_vp, _vp, _i64, _i64, _i64]
     L.fasted_generate_exponential.argtypes = [_vp, _i64, _i64, ctypes.c_double, ctypes.c_double, _u64]
     L.fasted_copy_points_from.argtypes = [_vp, _vp]
+    L.fasted_broadcast_points.argtypes = [ctypes.POINTER(_vp), ctypes.c_int, ctypes.POINTER(ctypes.c_double)]
     L.fasted_fill_exponential_device.argtypes = [_vp, _vp, _i64, _i64, _i64, ctypes.c_double, ctypes.c_double, _u64]
     L.fasted_points_info.argtypes = [_vp, ctypes.POINTER(_vp), ctypes.POINTER(_i64), ctypes.POINTER(_i64),
                                      ctypes.POINTER(_i64)]
@@ -100,6 +102,8 @@ def load() -> ctypes.CDLL:
                                      _vp, ctypes.POINTER(JoinStats)]
     L.fasted_tile_schedule.argtypes = [_i64, _i64, _i64, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
                                        ctypes.c_int, ctypes.c_int, ctypes.c_int, _vp, _i64, ctypes.POINTER(_i64)]
+    L.fasted_tile_schedule_stationary.argtypes = [_i64, _i64, _i64, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                                  _vp, _i64, ctypes.POINTER(_i64)]
     L.fasted_join_symmetric_shard.argtypes = [_vp, ctypes.c_double, ctypes.c_int, ctypes.c_int, _u64, ctypes.c_uint,
                                               ctypes.POINTER(JoinStats)]
     L.fasted_selftest_wait_timeout.argtypes = [_vp, ctypes.c_double, ctypes.POINTER(ctypes.c_ulonglong),
@@ -162,6 +166,27 @@ def tile_schedule(n: int, q_begin: int, q_end: int, grid: int, cta: int, tile_m:
     _check(load().fasted_tile_schedule(n, q_begin, q_end, tile_m, band_tiles, int(symmetric), shard_rank, shard_world,
                                        grid, cta, out.ctypes.data_as(_vp), count.value, ctypes.byref(count)))
     return out
+
+
+def tile_schedule_stationary(n: int, q_begin: int, q_end: int, grid: int, cta: int, rows_per_band: int,
+                             symmetric: bool = False) -> np.ndarray:
+    """The (tile row, tile column) sequence one CTA of the query-stationary join kernel walks."""
+    count = _i64()
+    _check(load().fasted_tile_schedule_stationary(n, q_begin, q_end, rows_per_band, int(symmetric), grid, cta, None, 0,
+                                                  ctypes.byref(count)))
+    out = np.empty((count.value, 2), dtype=np.int32)
+    _check(load().fasted_tile_schedule_stationary(n, q_begin, q_end, rows_per_band, int(symmetric), grid, cta,
+                                                  out.ctypes.data_as(_vp), count.value, ctypes.byref(count)))
+    return out
+
+
+def broadcast_points(contexts: list["SelfJoin"]) -> float:
+    """fasted_broadcast_points: replicate contexts[0]'s dataset into the other contexts (one GPU each, same
+    process) with one NCCL broadcast; returns the collective's wall time in milliseconds."""
+    arr = (_vp * len(contexts))(*[c._h for c in contexts])
+    ms = ctypes.c_double()
+    _check(load().fasted_broadcast_points(arr, len(contexts), ctypes.byref(ms)))
+    return ms.value
 
 
 class SelfJoin:

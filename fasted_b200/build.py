@@ -38,7 +38,7 @@ def build(verbose: bool = False, force: bool = False) -> str:
     deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)] + [os.path.join(ROOT, "include", "fasted.h"), __file__]
     if force or _stale(lib, deps):
         cmd = [NVCC, *ARCH, *COMMON, "-shared", "-o", lib, *[os.path.join(CSRC, s) for s in LIB_SOURCES],
-               "-Xptxas", "-v" if verbose else "-warn-spills", "-lgomp"]
+               "-Xptxas", "-v" if verbose else "-warn-spills", "-lgomp", "-ldl"]
         if verbose:
             print(" ".join(cmd))
         subprocess.check_call(cmd)

@@ -15,6 +15,9 @@
 #include <string>
 #include <vector>
 
+#include <dlfcn.h>
+#include <nccl.h>  // types and prototypes only: the library is bound at run time (see NcclApi)
+
 #include <cub/device/device_radix_sort.cuh>
 
 #include "kernels.cuh"
@@ -98,12 +101,17 @@ struct fasted_ctx {
 
     // egress pipeline of fasted_join_stream: a chunk's sort and its device-to-host copy run on
     // streams of their own (highest priority) while the next chunks are being joined
-    cudaStream_t sort_stream = nullptr, copy_stream = nullptr;
+    cudaStream_t copy_stream = nullptr;
     std::vector<cudaEvent_t> chunk_ev;            // end of each chunk's join launch
-    cudaEvent_t ev_sorted = nullptr, ev_copied[2] = {nullptr, nullptr};
+    std::vector<cudaEvent_t> sorted_ev;           // end of each chunk's sort + unpack
+    std::vector<cudaEvent_t> copied_ev;           // end of each chunk's device-to-host copy
+    std::vector<cudaEvent_t> sort_t0, sort_t1;    // timing brackets of the sorts
+    cudaEvent_t ev_tail = nullptr, ev_copied[2] = {nullptr, nullptr};
+    int stream_key32 = 1;                          // option: 32-bit records where they fit
     unsigned long long* chunk_end_host = nullptr;  // pinned: the found counter after each chunk
     size_t chunk_end_cap = 0;
     int stream_chunk_bands = 0;                    // option: raster bands per chunk (0 = automatic)
+    int query_stationary = -1;                     // option: -1 automatic, 0 never, 1 whenever the rows are short enough
 
     // pinned staging for transfers from / to pageable host memory
     void* stage_buf[2] = {nullptr, nullptr};
@@ -121,9 +129,22 @@ struct JoinPlan {
     fasted::JoinParams p;
     int grid;
     bool pair;
+    bool astat;      // query-stationary kernel (short rows)
+    int smem_bytes;  // its dynamic shared memory
 };
 
 namespace {
+
+constexpr int kMaxDynamicSmem = 227 * 1024;  // per-block limit of sm_100
+constexpr int kAStatAutoMinStages = 3;       // automatic choice: query-stationary when its ring has at least this depth
+
+// Depth of the query-stationary kernel's candidate ring for rows of k_steps K steps (0: does not fit).
+int astat_stages_for(int k_steps) {
+    if (k_steps > fasted::kAStatMaxK) return 0;
+    int s = fasted::kAStatMaxStages;
+    while (s > 0 && fasted::astat_smem_bytes(k_steps, s) > kMaxDynamicSmem) --s;
+    return s;
+}
 
 int make_map(fasted_ctx* c, CUtensorMap* map, int box_rows) {
     EncodeTiledFn enc = get_encode_fn();
@@ -381,6 +402,7 @@ int fasted_create(int device, fasted_ctx** out) {
                          fasted::kNormSmemBytes);
     cudaFuncSetAttribute(fasted::join_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          fasted::kPairSmemBytes);
+    cudaFuncSetAttribute(fasted::join_astat_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynamicSmem);
     {
         // How many 2-CTA clusters of the pair kernel the device can hold at once.
         cudaLaunchConfig_t cfg = {};
@@ -424,13 +446,13 @@ void fasted_destroy(fasted_ctx* c) {
         if (c->stage_buf[i]) cudaFreeHost(c->stage_buf[i]);
         if (c->stage_ev[i]) cudaEventDestroy(c->stage_ev[i]);
     }
-    for (cudaEvent_t ev : c->chunk_ev)
-        if (ev) cudaEventDestroy(ev);
-    if (c->ev_sorted) cudaEventDestroy(c->ev_sorted);
+    for (auto* list : {&c->chunk_ev, &c->sorted_ev, &c->copied_ev, &c->sort_t0, &c->sort_t1})
+        for (cudaEvent_t ev : *list)
+            if (ev) cudaEventDestroy(ev);
+    if (c->ev_tail) cudaEventDestroy(c->ev_tail);
     for (auto& ev : c->ev_copied)
         if (ev) cudaEventDestroy(ev);
     if (c->chunk_end_host) cudaFreeHost(c->chunk_end_host);
-    if (c->sort_stream) cudaStreamDestroy(c->sort_stream);
     if (c->copy_stream) cudaStreamDestroy(c->copy_stream);
     if (c->owns_stream && c->stream) cudaStreamDestroy(c->stream);
     delete c;
@@ -459,6 +481,12 @@ int fasted_set_option(fasted_ctx* c, const char* name, int64_t value) {
     } else if (!strcmp(name, "cta_pair")) {
         if (value != 0 && value != 1) return fail(FASTED_EINVAL, "cta_pair must be 0 or 1");
         c->cta_pair = static_cast<int>(value);
+    } else if (!strcmp(name, "query_stationary")) {
+        if (value < -1 || value > 1) return fail(FASTED_EINVAL, "query_stationary must be -1, 0 or 1");
+        c->query_stationary = static_cast<int>(value);
+    } else if (!strcmp(name, "stream_key32")) {
+        if (value != 0 && value != 1) return fail(FASTED_EINVAL, "stream_key32 must be 0 or 1");
+        c->stream_key32 = static_cast<int>(value);
     } else if (!strcmp(name, "stream_chunk_bands")) {
         if (value < 0 || value > (1 << 20)) return fail(FASTED_EINVAL, "stream_chunk_bands out of range");
         c->stream_chunk_bands = static_cast<int>(value);
@@ -537,6 +565,141 @@ int fasted_copy_points_from(fasted_ctx* dst, fasted_ctx* src) {
         return fail(FASTED_ECUDA, "peer copy of points failed: %s", cudaGetErrorString(e));
     }
     return adopt_points(dst, dev, true, src->n, src->d, src->ld);
+}
+
+// ---------------------------------------------------------------------------
+// Replication of the dataset over the GPUs of one process: one NCCL broadcast
+// ---------------------------------------------------------------------------
+//
+// The candidate set is the only thing the GPUs share, and it is replicated by one collective: a
+// broadcast from the GPU that holds it (a ring / tree over NVLink moves every byte out of the root
+// once, where G - 1 peer copies that all read the root would queue on its egress links).  NCCL is
+// bound at run time (dlopen of libnccl.so.2) so that the library still loads, and every single-GPU
+// path still works, where NCCL is not installed; a process that already holds an NCCL (the one a
+// Python framework bundles) gets that same copy.  The communicators are created once per set of
+// devices with ncclCommInitAll (one process, several GPUs) and kept for the life of the process.
+namespace {
+struct NcclApi {
+    void* handle = nullptr;
+    decltype(&ncclCommInitAll) CommInitAll = nullptr;
+    decltype(&ncclGroupStart) GroupStart = nullptr;
+    decltype(&ncclGroupEnd) GroupEnd = nullptr;
+    decltype(&ncclBroadcast) Broadcast = nullptr;
+    decltype(&ncclGetErrorString) GetErrorString = nullptr;
+    bool ok = false;
+};
+
+NcclApi& nccl_api() {
+    static NcclApi api;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        api.handle = dlopen("libnccl.so.2", RTLD_NOW | RTLD_LOCAL);
+        if (api.handle) {
+            api.CommInitAll = reinterpret_cast<decltype(api.CommInitAll)>(dlsym(api.handle, "ncclCommInitAll"));
+            api.GroupStart = reinterpret_cast<decltype(api.GroupStart)>(dlsym(api.handle, "ncclGroupStart"));
+            api.GroupEnd = reinterpret_cast<decltype(api.GroupEnd)>(dlsym(api.handle, "ncclGroupEnd"));
+            api.Broadcast = reinterpret_cast<decltype(api.Broadcast)>(dlsym(api.handle, "ncclBroadcast"));
+            api.GetErrorString = reinterpret_cast<decltype(api.GetErrorString)>(dlsym(api.handle, "ncclGetErrorString"));
+            api.ok = api.CommInitAll && api.GroupStart && api.GroupEnd && api.Broadcast && api.GetErrorString;
+        }
+    }
+    return api;
+}
+
+struct NcclGroup {
+    std::vector<int> devices;
+    std::vector<ncclComm_t> comms;
+};
+std::vector<NcclGroup> g_nccl_groups;  // one per distinct device list, never destroyed
+}  // namespace
+
+int fasted_broadcast_points(fasted_ctx* const* ctxs, int count, double* ms_out) {
+    if (!ctxs || count < 1) return fail(FASTED_EINVAL, "bad argument");
+    for (int g = 0; g < count; ++g)
+        if (!ctxs[g]) return fail(FASTED_EINVAL, "context %d is null", g);
+    fasted_ctx* src = ctxs[0];
+    if (!src->points) return fail(FASTED_ESTATE, "the first context has no dataset");
+    if (ms_out) *ms_out = 0.0;
+    if (count == 1) return FASTED_OK;
+    std::vector<int> devices(count);
+    for (int g = 0; g < count; ++g) {
+        devices[g] = ctxs[g]->device;
+        for (int h = 0; h < g; ++h)
+            if (devices[h] == devices[g])
+                return fail(FASTED_EINVAL, "contexts %d and %d share device %d: a broadcast needs one GPU per context", h, g,
+                            devices[g]);
+    }
+    NcclApi& api = nccl_api();
+    if (!api.ok) return fail(FASTED_ENODEV, "NCCL (libnccl.so.2) is not available: %s", api.handle ? "symbols missing" : dlerror());
+    NcclGroup* grp = nullptr;
+    for (auto& g : g_nccl_groups)
+        if (g.devices == devices) grp = &g;
+    if (!grp) {
+        NcclGroup ng;
+        ng.devices = devices;
+        ng.comms.resize(count);
+        ncclResult_t r = api.CommInitAll(ng.comms.data(), count, devices.data());
+        if (r != ncclSuccess) return fail(FASTED_ECUDA, "ncclCommInitAll failed: %s", api.GetErrorString(r));
+        g_nccl_groups.push_back(std::move(ng));
+        grp = &g_nccl_groups.back();
+    }
+    const size_t bytes = static_cast<size_t>(src->n) * src->ld * 2;
+    std::vector<__half*> dst(count, nullptr);
+    dst[0] = src->points;
+    for (int g = 1; g < count; ++g) {
+        CU_TRY(cudaSetDevice(ctxs[g]->device));
+        CU_TRY(cudaStreamSynchronize(ctxs[g]->stream));
+        release_points(ctxs[g]);
+        cudaError_t e = alloc_points(ctxs[g], &dst[g], bytes);
+        if (e != cudaSuccess) {
+            for (int h = 1; h < g; ++h) {
+                cudaSetDevice(ctxs[h]->device);
+                cudaFree(dst[h]);
+            }
+            return fail(FASTED_ECUDA, "allocation of the replica on device %d failed: %s", ctxs[g]->device,
+                        cudaGetErrorString(e));
+        }
+    }
+    CU_TRY(cudaSetDevice(src->device));
+    CU_TRY(cudaStreamSynchronize(src->stream));
+    const double t0 = [] {
+        timespec ts;
+        clock_gettime(CLOCK_MONOTONIC, &ts);
+        return ts.tv_sec * 1e3 + ts.tv_nsec * 1e-6;
+    }();
+    ncclResult_t r = api.GroupStart();
+    for (int g = 0; g < count && r == ncclSuccess; ++g) {
+        cudaSetDevice(ctxs[g]->device);
+        r = api.Broadcast(dst[g], dst[g], bytes, ncclUint8, 0, grp->comms[g], ctxs[g]->stream);
+    }
+    const ncclResult_t r2 = api.GroupEnd();
+    if (r == ncclSuccess) r = r2;
+    cudaError_t e = cudaSuccess;
+    for (int g = 0; g < count; ++g) {
+        cudaSetDevice(ctxs[g]->device);
+        const cudaError_t eg = cudaStreamSynchronize(ctxs[g]->stream);
+        if (e == cudaSuccess) e = eg;
+    }
+    if (r != ncclSuccess || e != cudaSuccess) {
+        for (int g = 1; g < count; ++g) {
+            cudaSetDevice(ctxs[g]->device);
+            cudaFree(dst[g]);
+        }
+        return r != ncclSuccess ? fail(FASTED_ECUDA, "ncclBroadcast failed: %s", api.GetErrorString(r))
+                                : fail(FASTED_ECUDA, "broadcast of the points failed: %s", cudaGetErrorString(e));
+    }
+    if (ms_out) {
+        timespec ts;
+        clock_gettime(CLOCK_MONOTONIC, &ts);
+        *ms_out = ts.tv_sec * 1e3 + ts.tv_nsec * 1e-6 - t0;
+    }
+    for (int g = 1; g < count; ++g) {
+        CU_TRY(cudaSetDevice(ctxs[g]->device));
+        int rc = adopt_points(ctxs[g], dst[g], true, src->n, src->d, src->ld);
+        if (rc) return rc;
+    }
+    return FASTED_OK;
 }
 
 int fasted_generate_exponential(fasted_ctx* c, int64_t n, int64_t d, double lambda, double max_value, uint64_t seed) {
@@ -707,6 +870,7 @@ static int plan_join(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end, 
     p.raw_dot = (flags & FASTED_JOIN_RAW_DOT) && want_dist ? 1 : 0;
     p.key_shift = 32;
     p.key_qbase = 0;
+    p.key32 = 0;
     if (shard_world > 1 && !symmetric) return fail(FASTED_EINVAL, "band snakes are for the symmetric schedule only");
     p.tiles_m = static_cast<int>((q_end - q_begin + tile_m - 1) / tile_m);
     p.tiles_n = static_cast<int>((c->n + fasted::kTileN - 1) / fasted::kTileN);
@@ -716,6 +880,8 @@ static int plan_join(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end, 
     p.band_tiles = std::max(1, std::min(band, std::max(p.tiles_m, 1)));
     p.total_tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
     int grid;
+    out->astat = false;
+    out->smem_bytes = 0;
     if (pair) {
         int clusters = c->grid > 0 ? std::max(1, c->grid / 2) : c->max_pair_clusters;
         if (p.total_tiles < clusters) clusters = static_cast<int>(std::max<long long>(p.total_tiles, 1));
@@ -723,6 +889,18 @@ static int plan_join(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end, 
     } else {
         grid = c->grid > 0 ? c->grid : c->num_sms;
         if (p.total_tiles < grid) grid = static_cast<int>(std::max<long long>(p.total_tiles, 1));
+        // Short rows: keep the query tile in shared memory and stream candidates only (join_astat_kernel).
+        const int stages = astat_stages_for(p.k_steps);
+        const bool want = c->query_stationary == 1 || (c->query_stationary < 0 && stages >= kAStatAutoMinStages);
+        if (want && stages >= 2 && shard_world <= 1) {
+            out->astat = true;
+            out->smem_bytes = fasted::astat_smem_bytes(p.k_steps, stages);
+            p.astat_stages = stages;
+            // rows per band: the largest divisor of the grid up to 40 (37 for 148 CTAs: 37 rows x 4 CTAs each)
+            int r = std::min(grid, 40);
+            while (grid % r != 0) --r;
+            p.astat_rows = r;
+        }
     }
     out->p = p;
     out->grid = grid;
@@ -746,6 +924,9 @@ static int launch_join(fasted_ctx* c, const JoinPlan& pl) {
         cfg.attrs = &attr;
         cfg.numAttrs = 1;
         CU_TRY(cudaLaunchKernelEx(&cfg, fasted::join_pair_kernel, c->map_a, pl.p));
+    } else if (pl.astat) {
+        fasted::join_astat_kernel<<<pl.grid, fasted::kJoinThreads, pl.smem_bytes, c->stream>>>(c->map_a, c->map_b, pl.p);
+        CU_TRY(cudaGetLastError());
     } else {
         fasted::join_kernel<<<pl.grid, fasted::kJoinThreads, fasted::kJoinSmemBytes, c->stream>>>(c->map_a, c->map_b,
                                                                                                  pl.p);
@@ -789,7 +970,10 @@ static void fill_stats(fasted_ctx* c, const JoinPlan& pl, const unsigned long lo
     stats->cta0_tiles = 0;
     stats->chunks = 1;
     stats->tail_ms = 0;
-    if (!pl.pair && pl.p.total_tiles > 0) {
+    if (pl.astat && pl.p.total_tiles > 0) {
+        fasted::AStatIter ti;
+        for (ti.init(pl.p, 0, pl.grid); ti.valid; ti.advance(pl.p)) ++stats->cta0_tiles;
+    } else if (!pl.pair && pl.p.total_tiles > 0) {
         fasted::TileIter ti;
         for (ti.init(pl.p, 0, pl.grid); ti.valid; ti.advance(pl.p)) ++stats->cta0_tiles;
     }
@@ -922,35 +1106,52 @@ int fasted_join_symmetric_shard(fasted_ctx* c, double eps, int shard_rank, int s
 //
 // The reference sorts the whole pair list after its kernel and then copies it to the host
 // (source/findPairs.cuh:699-716, source/pair.cuh:139-158): three serial phases.  Here the query range
-// is cut into chunks of whole raster bands, one join launch per chunk, all enqueued at once.  The
-// launches share one found counter, so chunk k's records occupy the slots between the counter's
-// value after chunk k-1 and after chunk k; and because chunks are contiguous, ascending ranges of
-// query rows, the chunks' sorted lists laid end to end ARE the global row-major order.  While the GPU
-// joins chunk k+1 the host picks up chunk k: its slice is sorted (keys packed relative to the chunk,
-// so the radix sort sees only bits(n) + bits(chunk rows) significant bits), unpacked and copied to
-// the host on two high-priority streams.  When the last launch retires, only the last chunk's sort
-// and copy are still to come.
+// is cut into chunks of whole raster bands, one join launch per chunk.  The launches share one found
+// counter, so chunk k's records occupy the slots between the counter's value after chunk k-1 and
+// after chunk k; and because chunks are contiguous, ascending ranges of query rows, the chunks' sorted
+// lists laid end to end ARE the global row-major order.
+//
+// Stream order on the join stream:  join(0) join(1) sort(0) join(2) sort(1) join(3) ...
+// The host stays two launches ahead: when chunk k's launch retires (an event and a pinned copy of the
+// counter tell it how many records the chunk has) it enqueues sort(k) -- a radix sort over only the
+// slice's significant bits, then the unpacking to (query, candidate) records -- behind join(k+1),
+// which is already running, and then join(k+2).  The sort of a chunk therefore runs on an otherwise
+// idle GPU between two launches (a persistent join CTA fills its SM, nothing fits beside it), costs
+// what a sort of that slice costs and nothing more, and the GPU never waits for the host.  The
+// device-to-host copy of chunk k runs on a copy stream while the GPU joins chunk k+2.  When the last
+// launch retires, only the last chunk's sort and copy are still to come.
+//
+// Records are packed relative to the chunk: ((query - first row of the chunk) << bits(n)) |
+// candidate.  Where that fits 32 bits (n up to a few million points with chunks of a thousand rows
+// and more) the kernel writes 32-bit records: half the bytes to write, sort and read back.
 
 static int ensure_stream_pipeline(fasted_ctx* c, size_t chunks) {
-    if (!c->sort_stream) {
+    if (!c->copy_stream) {
         int lo = 0, hi = 0;
         CU_TRY(cudaDeviceGetStreamPriorityRange(&lo, &hi));
-        CU_TRY(cudaStreamCreateWithPriority(&c->sort_stream, cudaStreamNonBlocking, hi));
         CU_TRY(cudaStreamCreateWithPriority(&c->copy_stream, cudaStreamNonBlocking, hi));
-        CU_TRY(cudaEventCreateWithFlags(&c->ev_sorted, cudaEventDisableTiming));
+        CU_TRY(cudaEventCreate(&c->ev_tail));
         for (auto& ev : c->ev_copied) CU_TRY(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
     }
     while (c->chunk_ev.size() < chunks) {
-        cudaEvent_t ev = nullptr;
+        cudaEvent_t ev = nullptr, sorted = nullptr, copied = nullptr, t0 = nullptr, t1 = nullptr;
         CU_TRY(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+        CU_TRY(cudaEventCreateWithFlags(&sorted, cudaEventDisableTiming));
+        CU_TRY(cudaEventCreateWithFlags(&copied, cudaEventDisableTiming));
+        c->copied_ev.push_back(copied);
+        CU_TRY(cudaEventCreate(&t0));
+        CU_TRY(cudaEventCreate(&t1));
         c->chunk_ev.push_back(ev);
+        c->sorted_ev.push_back(sorted);
+        c->sort_t0.push_back(t0);
+        c->sort_t1.push_back(t1);
     }
-    if (c->chunk_end_cap < chunks) {
+    if (c->chunk_end_cap < chunks + 8) {
         if (c->chunk_end_host) cudaFreeHost(c->chunk_end_host);
         c->chunk_end_host = nullptr;
         c->chunk_end_cap = 0;
-        CU_TRY(cudaMallocHost(&c->chunk_end_host, chunks * sizeof(unsigned long long)));
-        c->chunk_end_cap = chunks;
+        CU_TRY(cudaMallocHost(&c->chunk_end_host, (chunks + 8) * sizeof(unsigned long long)));
+        c->chunk_end_cap = chunks + 8;
     }
     return FASTED_OK;
 }
@@ -978,37 +1179,55 @@ int fasted_join_stream(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end
     rc = ensure_pair_buffers(c, capacity, want_dist);
     if (rc) return rc;
 
-    // Chunks of whole raster bands: at most 64 of them, each at least about a millisecond of tensor work.
+    // Chunks of whole raster bands: about 64 of them, each at least about a millisecond of tensor
+    // work -- but no more rows than 32-bit records can number, where one band's rows can be.
     JoinPlan whole;
     rc = plan_join(c, eps, q_begin, q_end, capacity, flags, 0, 1, &whole);
     if (rc) return rc;
-    const int64_t band_rows = static_cast<int64_t>(whole.p.band_tiles) * whole.p.tile_m;
+    const int64_t band_rows = whole.astat ? static_cast<int64_t>(whole.p.astat_rows) * whole.p.tile_m
+                                          : static_cast<int64_t>(whole.p.band_tiles) * whole.p.tile_m;
     const int64_t rows = q_end - q_begin;
     const int64_t total_bands = std::max<int64_t>(1, (rows + band_rows - 1) / band_rows);
+    const int key_shift = bits_of(static_cast<uint64_t>(c->n - 1));
+    const int64_t rows32 = key_shift < 32 ? (int64_t(1) << (32 - key_shift)) : 0;  // rows a 32-bit record can number
     int64_t bands_per_chunk = c->stream_chunk_bands;
     if (bands_per_chunk <= 0) {
         const double min_rows = 2e12 / (2.0 * static_cast<double>(c->n) * static_cast<double>(c->ld));
         bands_per_chunk = std::max<int64_t>((total_bands + 63) / 64,
                                             static_cast<int64_t>(std::ceil(min_rows / static_cast<double>(band_rows))));
+        if (rows32 >= band_rows) bands_per_chunk = std::min<int64_t>(bands_per_chunk, rows32 / band_rows);
     }
     bands_per_chunk = std::max<int64_t>(1, std::min<int64_t>(bands_per_chunk, total_bands));
     const int64_t chunk_rows = bands_per_chunk * band_rows;
     const size_t chunks = static_cast<size_t>((rows + chunk_rows - 1) / chunk_rows);
-    rc = ensure_stream_pipeline(c, chunks + 8);
+    const bool key32 = c->stream_key32 != 0 && chunk_rows <= rows32;
+    rc = ensure_stream_pipeline(c, chunks + 1);
     if (rc) return rc;
-    const int key_shift = bits_of(static_cast<uint64_t>(c->n - 1));
-    const int sort_bits = std::min(64, key_shift + bits_of(static_cast<uint64_t>(std::max<int64_t>(chunk_rows - 1, 1))));
+    const int sort_bits = std::min(key32 ? 32 : 64,
+                                   key_shift + bits_of(static_cast<uint64_t>(std::max<int64_t>(chunk_rows - 1, 1))));
+    // 32-bit records: both halves of the sort's double buffer live in `keys` (capacity 64-bit words hold
+    // 2 x capacity 32-bit ones), the unpacked (query, candidate) records go to `keys_alt`.
+    uint32_t* const ping32 = reinterpret_cast<uint32_t*>(c->keys);
+    uint32_t* const pong32 = ping32 + capacity;
 
     // Sort scratch for the largest slice a chunk can have (the library sort's scratch is bounded: it
     // works through long inputs in portions), allocated before anything is enqueued.
     {
-        cub::DoubleBuffer<unsigned long long> kb(c->keys, c->keys_alt);
-        cub::DoubleBuffer<float> vb(c->dist, c->dist_alt);
         size_t need = 0;
-        if (want_dist)
-            CU_TRY(cub::DeviceRadixSort::SortPairs(nullptr, need, kb, vb, capacity, 0, sort_bits, c->sort_stream));
-        else
-            CU_TRY(cub::DeviceRadixSort::SortKeys(nullptr, need, kb, capacity, 0, sort_bits, c->sort_stream));
+        cub::DoubleBuffer<float> vb(c->dist, c->dist_alt);
+        if (key32) {
+            cub::DoubleBuffer<uint32_t> kb(ping32, pong32);
+            if (want_dist)
+                CU_TRY(cub::DeviceRadixSort::SortPairs(nullptr, need, kb, vb, capacity, 0, sort_bits, c->stream));
+            else
+                CU_TRY(cub::DeviceRadixSort::SortKeys(nullptr, need, kb, capacity, 0, sort_bits, c->stream));
+        } else {
+            cub::DoubleBuffer<unsigned long long> kb(c->keys, c->keys_alt);
+            if (want_dist)
+                CU_TRY(cub::DeviceRadixSort::SortPairs(nullptr, need, kb, vb, capacity, 0, sort_bits, c->stream));
+            else
+                CU_TRY(cub::DeviceRadixSort::SortKeys(nullptr, need, kb, capacity, 0, sort_bits, c->stream));
+        }
         if (need > c->sort_tmp_bytes) {
             if (c->sort_tmp) cudaFree(c->sort_tmp);
             c->sort_tmp = nullptr;
@@ -1023,7 +1242,6 @@ int fasted_join_stream(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end
     }
     const bool host_pinned = pairs_host && host_is_pinned(pairs_host) && (!dist2_host || host_is_pinned(dist2_host));
 
-    // ---- enqueue everything the join stream will do ----
     c->stored = 0;
     c->result_pairs = nullptr;
     c->result_dist = nullptr;
@@ -1034,88 +1252,61 @@ int fasted_join_stream(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end
         if (rc) return rc;
     }
     CU_TRY(cudaEventRecord(c->ev[1], c->stream));
-    std::vector<int64_t> chunk_q0(chunks);
-    for (size_t k = 0; k < chunks; ++k) {
-        const int64_t b = q_begin + static_cast<int64_t>(k) * chunk_rows, e = std::min<int64_t>(q_end, b + chunk_rows);
-        chunk_q0[k] = b;
+
+    auto chunk_begin = [&](size_t k) { return q_begin + static_cast<int64_t>(k) * chunk_rows; };
+    auto enqueue_join = [&](size_t k) -> int {
+        const int64_t b = chunk_begin(k), e = std::min<int64_t>(q_end, b + chunk_rows);
         JoinPlan pl;
-        rc = plan_join(c, eps, b, e, capacity, flags, 0, 1, &pl);
-        if (rc) return rc;
+        int r = plan_join(c, eps, b, e, capacity, flags, 0, 1, &pl);
+        if (r) return r;
         pl.p.key_shift = key_shift;
         pl.p.key_qbase = static_cast<int>(b);
-        rc = launch_join(c, pl);
-        if (rc) return rc;
+        pl.p.key32 = key32 ? 1 : 0;
+        r = launch_join(c, pl);
+        if (r) return r;
+        // (pinned destination: a copy into pageable memory would hold the host until the GPU gets here)
         CU_TRY(cudaMemcpyAsync(c->chunk_end_host + k, c->counters, sizeof(unsigned long long), cudaMemcpyDeviceToHost,
                                c->stream));
         CU_TRY(cudaEventRecord(c->chunk_ev[k], c->stream));
-    }
-    CU_TRY(cudaEventRecord(c->ev[2], c->stream));
-    // (pinned destination: a copy into pageable memory would hold the host here until the last chunk)
-    unsigned long long* h = c->chunk_end_host + chunks;
-    CU_TRY(cudaMemcpyAsync(h, c->counters, 5 * sizeof(unsigned long long), cudaMemcpyDeviceToHost, c->stream));
-
-    // ---- pick the chunks up as they retire ----
-    int abort_rc = FASTED_OK;
-    uint64_t prev_end = 0;
-    double tail_start = 0;
-    auto now_ms = [] {
-        timespec ts;
-        clock_gettime(CLOCK_MONOTONIC, &ts);
-        return ts.tv_sec * 1e3 + ts.tv_nsec * 1e-6;
+        return FASTED_OK;
     };
-    for (size_t k = 0; k < chunks && abort_rc == FASTED_OK; ++k) {
-        CU_TRY(cudaEventSynchronize(c->chunk_ev[k]));
-        if (k + 1 == chunks) tail_start = now_ms();
-        const uint64_t end_k = c->chunk_end_host[k];
-        const uint64_t a = std::min<uint64_t>(prev_end, capacity), b = std::min<uint64_t>(end_k, capacity);
-        prev_end = end_k;
-        if (b <= a) continue;
-        const uint64_t m = b - a;
-        // sort the slice (on the sort stream; the join stream is already past it)
-        cub::DoubleBuffer<unsigned long long> kb(c->keys + a, c->keys_alt + a);
-        cub::DoubleBuffer<float> vb(want_dist ? c->dist + a : nullptr, want_dist ? c->dist_alt + a : nullptr);
-        if (m > 1) {
-            size_t need = c->sort_tmp_bytes;
-            if (want_dist)
-                CU_TRY(cub::DeviceRadixSort::SortPairs(c->sort_tmp, need, kb, vb, m, 0, sort_bits, c->sort_stream));
-            else
-                CU_TRY(cub::DeviceRadixSort::SortKeys(c->sort_tmp, need, kb, m, 0, sort_bits, c->sort_stream));
-        }
-        fasted::unpack_pairs_kernel<<<unpack_blocks(c, m), 256, 0, c->sort_stream>>>(
-            kb.Current(), reinterpret_cast<int2*>(c->keys_alt + a), m, nullptr, 0ull, key_shift,
-            static_cast<int>(chunk_q0[k]));
-        CU_TRY(cudaGetLastError());
-        if (want_dist && vb.Current() != c->dist_alt + a)
-            CU_TRY(cudaMemcpyAsync(c->dist_alt + a, vb.Current(), m * sizeof(float), cudaMemcpyDeviceToDevice,
-                                   c->sort_stream));
-        CU_TRY(cudaEventRecord(c->ev_sorted, c->sort_stream));
-        CU_TRY(cudaStreamWaitEvent(c->copy_stream, c->ev_sorted, 0));
+    constexpr size_t kAhead = 2;  // join launches enqueued beyond the chunk the host is waiting for
+    for (size_t k = 0; k < std::min(kAhead, chunks); ++k) {
+        rc = enqueue_join(k);
+        if (rc) return rc;
+    }
 
-        // copy it to the host
+    // Delivery of chunk k's sorted records [a, b) to the host; runs one chunk behind the sorts so that
+    // the host never waits for a copy while it could be feeding the join stream.
+    int abort_rc = FASTED_OK;
+    struct Pending {
+        bool any = false;
+        uint64_t a = 0, b = 0;
+        size_t chunk = 0;
+    } pend;
+    auto deliver = [&](const Pending& pd) -> int {
+        if (!pd.any) return FASTED_OK;
+        const uint64_t a = pd.a, m = pd.b - pd.a;
         const int2* src_pairs = reinterpret_cast<const int2*>(c->keys_alt) + a;
         const float* src_dist = want_dist ? c->dist_alt + a : nullptr;
         if (pairs_host) {
-            const uint64_t hb = std::min<uint64_t>(b, host_capacity);
+            const uint64_t hb = std::min<uint64_t>(pd.b, host_capacity);
             const uint64_t hm = hb > a ? hb - a : 0;
-            if (hm > 0) {
-                if (host_pinned) {
-                    CU_TRY(cudaMemcpyAsync(pairs_host + 2 * a, src_pairs, hm * 8, cudaMemcpyDeviceToHost, c->copy_stream));
-                    if (dist2_host)
-                        CU_TRY(cudaMemcpyAsync(dist2_host + a, src_dist, hm * 4, cudaMemcpyDeviceToHost, c->copy_stream));
-                    CU_TRY(cudaStreamSynchronize(c->copy_stream));
-                } else {
-                    CU_TRY(download_bytes(c, pairs_host + 2 * a, src_pairs, hm * 8, c->copy_stream));
-                    if (dist2_host) CU_TRY(download_bytes(c, dist2_host + a, src_dist, hm * 4, c->copy_stream));
-                }
-                if (on_chunk && on_chunk(user, pairs_host + 2 * a, dist2_host ? dist2_host + a : nullptr, a, hm) != 0)
-                    abort_rc = fail(FASTED_EINVAL, "the chunk callback asked to stop");
+            if (hm == 0) return FASTED_OK;
+            if (host_pinned) {
+                CU_TRY(cudaEventSynchronize(c->copied_ev[pd.chunk]));  // the copies were enqueued when the sort was
+            } else {
+                CU_TRY(download_bytes(c, pairs_host + 2 * a, src_pairs, hm * 8, c->copy_stream));
+                if (dist2_host) CU_TRY(download_bytes(c, dist2_host + a, src_dist, hm * 4, c->copy_stream));
             }
+            if (on_chunk && on_chunk(user, pairs_host + 2 * a, dist2_host ? dist2_host + a : nullptr, a, hm) != 0)
+                return fail(FASTED_EINVAL, "the chunk callback asked to stop");
         } else if (on_chunk) {
             // No destination of the caller's: runs of records pass through the two pinned staging
             // buffers; while the callback reads one, the DMA engine fills the other.
             const uint64_t run = (kStageBytes / (want_dist ? 12 : 8)) & ~uint64_t(1023);
             const uint64_t runs = (m + run - 1) / run;
-            for (uint64_t i = 0; i <= runs && abort_rc == FASTED_OK; ++i) {
+            for (uint64_t i = 0; i <= runs; ++i) {
                 if (i < runs) {
                     const uint64_t off = i * run, cnt = std::min(run, m - off);
                     char* buf = static_cast<char*>(c->stage_buf[i & 1]);
@@ -1131,17 +1322,92 @@ int fasted_join_stream(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end
                     CU_TRY(cudaEventSynchronize(c->ev_copied[(i - 1) & 1]));
                     if (on_chunk(user, reinterpret_cast<const int32_t*>(buf),
                                  want_dist ? reinterpret_cast<const float*>(buf + run * 8) : nullptr, a + off, cnt) != 0)
-                        abort_rc = fail(FASTED_EINVAL, "the chunk callback asked to stop");
+                        return fail(FASTED_EINVAL, "the chunk callback asked to stop");
                 }
             }
-        } else {
-            CU_TRY(cudaStreamSynchronize(c->sort_stream));
         }
+        return FASTED_OK;
+    };
+
+    uint64_t prev_end = 0;
+    size_t sorts = 0;
+    for (size_t k = 0; k < chunks; ++k) {
+        CU_TRY(cudaEventSynchronize(c->chunk_ev[k]));
+        const uint64_t end_k = c->chunk_end_host[k];
+        const uint64_t a = std::min<uint64_t>(prev_end, capacity), b = std::min<uint64_t>(end_k, capacity);
+        prev_end = end_k;
+        Pending now;
+        if (b > a && abort_rc == FASTED_OK) {
+            const uint64_t m = b - a;
+            // sort(k) and its unpacking, on the join stream, behind the launch that is running now
+            CU_TRY(cudaEventRecord(c->sort_t0[sorts], c->stream));
+            cub::DoubleBuffer<float> vb(want_dist ? c->dist + a : nullptr, want_dist ? c->dist_alt + a : nullptr);
+            size_t need = c->sort_tmp_bytes;
+            if (key32) {
+                cub::DoubleBuffer<uint32_t> kb(ping32 + a, pong32 + a);
+                if (m > 1) {
+                    if (want_dist)
+                        CU_TRY(cub::DeviceRadixSort::SortPairs(c->sort_tmp, need, kb, vb, m, 0, sort_bits, c->stream));
+                    else
+                        CU_TRY(cub::DeviceRadixSort::SortKeys(c->sort_tmp, need, kb, m, 0, sort_bits, c->stream));
+                }
+                fasted::unpack_pairs32_kernel<<<unpack_blocks(c, m), 256, 0, c->stream>>>(
+                    kb.Current(), reinterpret_cast<int2*>(c->keys_alt + a), m, key_shift, static_cast<int>(chunk_begin(k)));
+            } else {
+                cub::DoubleBuffer<unsigned long long> kb(c->keys + a, c->keys_alt + a);
+                if (m > 1) {
+                    if (want_dist)
+                        CU_TRY(cub::DeviceRadixSort::SortPairs(c->sort_tmp, need, kb, vb, m, 0, sort_bits, c->stream));
+                    else
+                        CU_TRY(cub::DeviceRadixSort::SortKeys(c->sort_tmp, need, kb, m, 0, sort_bits, c->stream));
+                }
+                fasted::unpack_pairs_kernel<<<unpack_blocks(c, m), 256, 0, c->stream>>>(
+                    kb.Current(), reinterpret_cast<int2*>(c->keys_alt + a), m, nullptr, 0ull, key_shift,
+                    static_cast<int>(chunk_begin(k)));
+            }
+            CU_TRY(cudaGetLastError());
+            if (want_dist && vb.Current() != c->dist_alt + a)
+                CU_TRY(cudaMemcpyAsync(c->dist_alt + a, vb.Current(), m * sizeof(float), cudaMemcpyDeviceToDevice,
+                                       c->stream));
+            CU_TRY(cudaEventRecord(c->sort_t1[sorts], c->stream));
+            CU_TRY(cudaEventRecord(c->sorted_ev[k], c->stream));
+            ++sorts;
+            now.any = true;
+            now.a = a;
+            now.b = b;
+            now.chunk = k;
+        }
+        // keep the join stream fed before anything else
+        if (k + kAhead < chunks && abort_rc == FASTED_OK) {
+            rc = enqueue_join(k + kAhead);
+            if (rc) return rc;
+        }
+        if (now.any) {
+            CU_TRY(cudaStreamWaitEvent(c->copy_stream, c->sorted_ev[k], 0));
+            if (pairs_host && host_pinned) {
+                const uint64_t hb = std::min<uint64_t>(now.b, host_capacity);
+                if (hb > now.a) {
+                    CU_TRY(cudaMemcpyAsync(pairs_host + 2 * now.a, reinterpret_cast<const int2*>(c->keys_alt) + now.a,
+                                           (hb - now.a) * 8, cudaMemcpyDeviceToHost, c->copy_stream));
+                    if (dist2_host)
+                        CU_TRY(cudaMemcpyAsync(dist2_host + now.a, c->dist_alt + now.a, (hb - now.a) * 4,
+                                               cudaMemcpyDeviceToHost, c->copy_stream));
+                }
+                CU_TRY(cudaEventRecord(c->copied_ev[k], c->copy_stream));
+            }
+        }
+        // chunk k-1's records: on the host by now, or nearly
+        if (abort_rc == FASTED_OK) abort_rc = deliver(pend);
+        pend = now;
     }
-    CU_TRY(cudaStreamSynchronize(c->sort_stream));
+    if (chunks > 0) CU_TRY(cudaEventRecord(c->ev[2], c->stream));
+    unsigned long long* h = c->chunk_end_host + chunks;
+    if (chunks == 0) CU_TRY(cudaEventRecord(c->ev[2], c->stream));
+    CU_TRY(cudaMemcpyAsync(h, c->counters, 5 * sizeof(unsigned long long), cudaMemcpyDeviceToHost, c->stream));
+    if (abort_rc == FASTED_OK) abort_rc = deliver(pend);
+    CU_TRY(cudaEventRecord(c->ev_tail, c->copy_stream));
     CU_TRY(cudaStreamSynchronize(c->copy_stream));
     CU_TRY(cudaStreamSynchronize(c->stream));
-    const double tail_ms = tail_start > 0 ? now_ms() - tail_start : 0.0;
     c->norms_valid = (h[2] & fasted::kErrNormWait) == 0;
     if (h[2]) return fail(FASTED_EKERNEL, "a device-side wait ran out (status 0x%llx)", h[2]);
     if (abort_rc != FASTED_OK) return abort_rc;
@@ -1150,14 +1416,27 @@ int fasted_join_stream(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end
     c->result_pairs = c->keys_alt;
     c->result_dist = want_dist ? c->dist_alt : nullptr;
     c->result_sorted = true;
-    // (ev[3], ev[4] bracket nothing here: the sorts overlap the join)
     CU_TRY(cudaEventRecord(c->ev[3], c->stream));
     CU_TRY(cudaEventRecord(c->ev[4], c->stream));
     CU_TRY(cudaStreamSynchronize(c->stream));
     fill_stats(c, whole, h, stored, stats);
     if (stats) {
+        // ev[1] -> ev[2] spans the join launches AND the sorts that ran between them
+        float sort_ms = 0.f, last_sort_ms = 0.f;
+        for (size_t i = 0; i < sorts; ++i) {
+            float t = 0.f;
+            cudaEventElapsedTime(&t, c->sort_t0[i], c->sort_t1[i]);
+            sort_ms += t;
+            if (i + 1 == sorts) last_sort_ms = t;
+        }
+        // (what nothing can hide: the last chunk's sort, then whatever of its copy remains after ev[2])
+        stats->sort_ms = sort_ms;
+        stats->join_ms = std::max(0.0, stats->join_ms - static_cast<double>(sort_ms));
+        stats->kernel_ms = stats->norms_ms + stats->join_ms;
+        float tail = 0.f;
+        if (cudaEventElapsedTime(&tail, c->ev[2], c->ev_tail) != cudaSuccess) tail = 0.f;
+        stats->tail_ms = static_cast<double>(last_sort_ms) + std::max(0.f, tail);
         stats->chunks = static_cast<int>(chunks);
-        stats->tail_ms = tail_ms;
         stats->cta0_cycles = 0;  // the counter holds the last chunk's only
         stats->cta0_tiles = 0;
     }
@@ -1181,11 +1460,39 @@ int fasted_tile_schedule(int64_t n, int64_t q_begin, int64_t q_end, int tile_m, 
     p.raw_dot = 0;
     p.key_shift = 32;
     p.key_qbase = 0;
+    p.key32 = 0;
     if (shard_world > 1 && !symmetric) return fail(FASTED_EINVAL, "band snakes are for the symmetric schedule only");
     p.tiles_m = static_cast<int>((q_end - q_begin + tile_m - 1) / tile_m);
     p.tiles_n = static_cast<int>((n + fasted::kTileN - 1) / fasted::kTileN);
     p.band_tiles = std::max(1, std::min(band_tiles, std::max(p.tiles_m, 1)));
     fasted::TileIter ti;
+    int64_t count = 0;
+    for (ti.init(p, cta, grid); ti.valid; ti.advance(p)) {
+        if (tiles_out && count < max_tiles) {
+            tiles_out[2 * count] = ti.tm;
+            tiles_out[2 * count + 1] = ti.tn;
+        }
+        ++count;
+    }
+    *count_out = count;
+    return FASTED_OK;
+}
+
+int fasted_tile_schedule_stationary(int64_t n, int64_t q_begin, int64_t q_end, int rows_per_band, int symmetric, int grid,
+                                    int cta, int32_t* tiles_out, int64_t max_tiles, int64_t* count_out) {
+    if (n <= 0 || q_begin < 0 || q_end < q_begin || q_end > n || grid <= 0 || cta < 0 || cta >= grid || !count_out ||
+        rows_per_band <= 0 || rows_per_band > grid)
+        return fail(FASTED_EINVAL, "bad argument");
+    fasted::JoinParams p{};
+    p.n = static_cast<int>(n);
+    p.q_begin = static_cast<int>(q_begin);
+    p.q_end = static_cast<int>(q_end);
+    p.tile_m = fasted::kTileM;
+    p.symmetric = symmetric ? 1 : 0;
+    p.tiles_m = static_cast<int>((q_end - q_begin + fasted::kTileM - 1) / fasted::kTileM);
+    p.tiles_n = static_cast<int>((n + fasted::kTileN - 1) / fasted::kTileN);
+    p.astat_rows = rows_per_band;
+    fasted::AStatIter ti;
     int64_t count = 0;
     for (ti.init(p, cta, grid); ti.valid; ti.advance(p)) {
         if (tiles_out && count < max_tiles) {
@@ -1446,6 +1753,7 @@ int fasted_join_static_scratch(const void* points_dev, int64_t n, int64_t d, int
     p.shard_world = 1;
     p.key_shift = 32;
     p.key_qbase = 0;
+    p.key32 = 0;
     const int grid = static_cast<int>(std::min<long long>(p.total_tiles, num_sms));
 
     // The scratch area keeps whatever the previous call left: the counters must start at zero

@@ -68,14 +68,27 @@ struct JoinParams {
     int shard_rank, shard_world;   // symmetric mode over several GPUs: this launch takes the raster bands
                                    // r, 2G-1-r, 2G+r, 4G-1-r, ... (a snake over the G shards, which evens out
                                    // the shrinking band lengths of the triangle); 0, 1 = everything
+    int astat_rows;                // query-stationary kernel: tile rows per band (at most the grid size)
+    int astat_stages;              // query-stationary kernel: depth of its candidate ring
     int key_shift, key_qbase;      // record = ((query - key_qbase) << key_shift) | candidate.  32 and 0 give the
                                    // plain (query << 32) | candidate; a launch over one chunk of query rows can
                                    // pack tighter, so that the chunk's sort has fewer significant bits to look at
+    int key32;                     // 1: the packed record fits 32 bits and `keys` is an array of uint32_t (half the
+                                   // bytes to write, to sort and to read back)
 };
 
 __device__ __forceinline__ unsigned long long pack_record(const JoinParams& p, unsigned long long q,
                                                           unsigned long long c) {
     return ((q - static_cast<unsigned long long>(p.key_qbase)) << p.key_shift) | c;
+}
+
+__device__ __forceinline__ void store_record(const JoinParams& p, unsigned long long slot, unsigned long long q,
+                                             unsigned long long c) {
+    const unsigned long long rec = pack_record(p, q, c);
+    if (p.key32)
+        reinterpret_cast<uint32_t*>(p.keys)[slot] = static_cast<uint32_t>(rec);
+    else
+        p.keys[slot] = rec;
 }
 
 // Persistent static schedule: CTA (or CTA pair) b handles tiles b, b + grid, b + 2*grid, ... of a
@@ -542,7 +555,7 @@ __device__ __forceinline__ void epilogue_emit(const JoinParams& p, EpiHits& h, i
             m &= m - 1;
             const unsigned long long q = qk + ((i & 2) ? 8u : 0u);
             const unsigned long long c = ck + 8u * (i >> 2) + (i & 1);
-            if (slot < p.capacity) p.keys[slot] = pack_record(p, q, c);
+            if (slot < p.capacity) store_record(p, slot, q, c);
             ++slot;
         }
         while (r) {
@@ -550,7 +563,7 @@ __device__ __forceinline__ void epilogue_emit(const JoinParams& p, EpiHits& h, i
             r &= r - 1;
             const unsigned long long q = qk + ((i & 2) ? 8u : 0u);
             const unsigned long long c = ck + 8u * (i >> 2) + (i & 1);
-            if (slot < p.capacity) p.keys[slot] = pack_record(p, c, q);
+            if (slot < p.capacity) store_record(p, slot, c, q);
             ++slot;
         }
     }
@@ -585,14 +598,14 @@ __device__ __forceinline__ void epilogue_emit_dist(const JoinParams& p, const Ep
                 const unsigned long long c = ck + 8u * (i >> 2) + (i & 1);
                 if (m & (1u << i)) {
                     if (slot < p.capacity) {
-                        p.keys[slot] = pack_record(p, q, c);
+                        store_record(p, slot, q, c);
                         p.dist2[slot] = d2;
                     }
                     ++slot;
                 }
                 if (r & (1u << i)) {
                     if (slot < p.capacity) {
-                        p.keys[slot] = pack_record(p, c, q);
+                        store_record(p, slot, c, q);
                         p.dist2[slot] = d2;
                     }
                     ++slot;
@@ -845,6 +858,296 @@ join_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     __syncthreads();
     // SM cycles CTA 0 spent on its share of the tiles: lets the host derive the mean SM clock of the
     // launch (cycles / device time) and the share of those cycles the tensor pipe had work for.
+    if (blockIdx.x == 0 && threadIdx.x == 0) p.counters[4] = static_cast<unsigned long long>(clock64() - clock_start);
+    if (warp == 1) {
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc<1>(tmem_base, kTmemCols);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// The join for short rows: query tile stationary in shared memory
+// ---------------------------------------------------------------------------
+//
+// For d <= 512 (at most 8 K steps) the main loop of join_kernel is bound by the L2 -> SM operand
+// feed, not by the tensor pipe: every K step brings 16 KB of query rows and 32 KB of candidate rows
+// for 512 clocks of MMA work, and every tile fetches its query rows again although a CTA's 128 x d
+// query tile is only 16 KB per K step.  Here a CTA keeps its query tile resident and sweeps along
+// its tile ROW: per K step only the 32 KB candidate box moves (one third less traffic into the SM),
+// and the shared memory the query stages occupied becomes a deeper candidate ring.
+//
+// Schedule (AStatIter): the tile rows are cut into bands of R rows (R = 37 for 148 CTAs).  In a
+// band of `rows` rows, C = grid / rows CTAs share each row: CTA b takes row b % rows and the tile
+// columns (b / rows), (b / rows) + C, ...  CTAs with consecutive indices sit on the two SMs of a TPC
+// and walk neighbouring rows through the SAME columns at the same time, so their candidate boxes
+// are fetched from L2 once per TPC; a band's sweep reads every candidate row from DRAM once.
+// Roles, epilogue, barriers and the bounded waits are those of join_kernel; in addition a_full /
+// a_empty hand the resident query tile between the TMA thread and the MMA thread once per row.
+constexpr int kAStatMaxStages = 6;
+constexpr int kAStatMaxK = 8;
+
+struct AStatIter {
+    int grid, cta;
+    int band_start;  // first tile row of the current band
+    int rows, cper;  // tile rows in the current band, CTAs per row
+    int tm, tn;
+    bool valid;
+    bool new_row;    // the current tile is this CTA's first of a new tile row: load the query tile
+
+    __host__ __device__ __forceinline__ void enter_band(const JoinParams& p) {
+        for (;;) {
+            if (band_start >= p.tiles_m) {
+                valid = false;
+                return;
+            }
+            rows = p.tiles_m - band_start < p.astat_rows ? p.tiles_m - band_start : p.astat_rows;
+            cper = grid / rows;  // >= 1: astat_rows <= grid
+            const int r = cta % rows, c = cta / rows;
+            if (c < cper) {
+                tm = band_start + r;
+                tn = c;
+                if (p.symmetric) {
+                    // tile (tm, tn) lies entirely below the diagonal iff tn * kTileN + kTileN - 1 < first row
+                    const int tn0 = (p.q_begin + tm * kTileM) / kTileN;
+                    if (tn0 > tn) tn += (tn0 - tn + cper - 1) / cper * cper;
+                }
+                if (tn < p.tiles_n) {
+                    valid = true;
+                    new_row = true;
+                    return;
+                }
+            }
+            band_start += p.astat_rows;  // nothing for this CTA in this band
+        }
+    }
+    __host__ __device__ __forceinline__ void init(const JoinParams& p, int cta_, int grid_) {
+        grid = grid_;
+        cta = cta_;
+        band_start = 0;
+        valid = false;
+        new_row = false;
+        enter_band(p);
+    }
+    __host__ __device__ __forceinline__ void advance(const JoinParams& p) {
+        tn += cper;
+        new_row = false;
+        if (tn >= p.tiles_n) {
+            band_start += p.astat_rows;
+            enter_band(p);
+        }
+    }
+};
+
+struct AStatSmemAux {
+    unsigned long long full_bar[kAStatMaxStages];
+    unsigned long long empty_bar[kAStatMaxStages];
+    unsigned long long a_full_bar, a_empty_bar;
+    unsigned long long acc_full_bar[2];
+    unsigned long long acc_empty_bar[2];
+    uint32_t tmem_base;
+    int abort_flag;
+    alignas(16) float warp_cand[kEpiWarps][kEpiCols];
+};
+
+__host__ __device__ constexpr int astat_smem_bytes(int k_steps, int stages) {
+    return 1024 + k_steps * static_cast<int>(kStageBytesA) + stages * static_cast<int>(kStageBytesB) +
+           static_cast<int>(sizeof(AStatSmemAux)) + 64;
+}
+
+__global__ void __launch_bounds__(kJoinThreads, 1)
+join_astat_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                  const JoinParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_u32 = ptx::smem_u32(smem_raw);
+    const uint32_t a_u32 = (raw_u32 + 1023u) & ~1023u;                       // resident query tile: k_steps boxes
+    const uint32_t b_u32 = a_u32 + static_cast<uint32_t>(p.k_steps) * kStageBytesA;  // candidate ring
+    const int stages = p.astat_stages;
+    AStatSmemAux* aux = reinterpret_cast<AStatSmemAux*>(smem_raw + (b_u32 - raw_u32) +
+                                                        static_cast<uint32_t>(stages) * kStageBytesB);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    volatile int* abort_flag = &aux->abort_flag;
+
+    if (threadIdx.x == 0) {
+        aux->abort_flag = 0;
+        for (int s = 0; s < stages; ++s) {
+            ptx::mbar_init(ptx::smem_u32(&aux->full_bar[s]), 1);
+            ptx::mbar_init(ptx::smem_u32(&aux->empty_bar[s]), 1);
+        }
+        ptx::mbar_init(ptx::smem_u32(&aux->a_full_bar), 1);
+        ptx::mbar_init(ptx::smem_u32(&aux->a_empty_bar), 1);
+        for (int b = 0; b < 2; ++b) {
+            ptx::mbar_init(ptx::smem_u32(&aux->acc_full_bar[b]), 1);
+            ptx::mbar_init(ptx::smem_u32(&aux->acc_empty_bar[b]), kEpiWarps);
+        }
+        ptx::fence_mbar_init();
+        ptx::prefetch_tensormap(&map_a);
+        ptx::prefetch_tensormap(&map_b);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc<1>(ptx::smem_u32(&aux->tmem_base), kTmemCols);
+        ptx::tmem_relinquish<1>();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem_base = aux->tmem_base;
+    const long long clock_start = clock64();
+    const int cta = static_cast<int>(blockIdx.x), grid = static_cast<int>(gridDim.x);
+
+    if (warp == 0) {
+        // ------------------------- TMA producer -------------------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0, a_rows_loaded = 0;
+            bool ok = true;
+            long long issued = 0;
+            AStatIter ti;
+            for (ti.init(p, cta, grid); ti.valid && ok; ti.advance(p)) {
+                if (ti.new_row) {
+                    // the MMAs that read the previous row's query tile are complete (first row: a fresh
+                    // barrier counts as released)
+                    ok = ptx::mbar_wait_bounded(ptx::smem_u32(&aux->a_empty_bar), (a_rows_loaded & 1u) ^ 1u, abort_flag,
+                                                kWaitLimitNs);
+                    if (!ok) break;
+                    const uint32_t bar = ptx::smem_u32(&aux->a_full_bar);
+                    ptx::mbar_expect_tx(bar, static_cast<uint32_t>(p.k_steps) * kStageBytesA);
+                    for (int ks = 0; ks < p.k_steps; ++ks)
+                        ptx::tma_load_2d(a_u32 + static_cast<uint32_t>(ks) * kStageBytesA, &map_a, bar, ks * kTileK,
+                                         p.q_begin + ti.tm * kTileM);
+                    ++a_rows_loaded;
+                }
+                const int row_b = ti.tn * kTileN;
+                for (int ks = 0; ks < p.k_steps; ++ks) {
+                    ok = ptx::mbar_wait_bounded(ptx::smem_u32(&aux->empty_bar[stage]), phase ^ 1u, abort_flag,
+                                                kWaitLimitNs);
+                    if (!ok) break;
+                    const uint32_t bar = ptx::smem_u32(&aux->full_bar[stage]);
+                    ptx::mbar_expect_tx(bar, kStageBytesB);
+                    ptx::tma_load_2d(b_u32 + static_cast<uint32_t>(stage) * kStageBytesB, &map_b, bar, ks * kTileK, row_b);
+                    ++issued;
+                    if (++stage == stages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+            if (!ok) {
+                atomicOr(p.counters + 2, kErrProducerWait);
+                // Bounded wait for the loads still in flight (the query tile and at most `stages` boxes).
+                const uint64_t t0 = ptx::globaltimer_ns();
+                if (a_rows_loaded > 0)
+                    while (!ptx::mbar_try_wait(ptx::smem_u32(&aux->a_full_bar), (a_rows_loaded - 1u) & 1u) &&
+                           ptx::globaltimer_ns() - t0 < 20000000ull) {
+                    }
+                const long long pending = issued < stages ? issued : stages;
+                int s = stage;
+                uint32_t ph = phase;
+                for (long long i = 0; i < pending; ++i) {
+                    if (--s < 0) {
+                        s = stages - 1;
+                        ph ^= 1u;
+                    }
+                    while (!ptx::mbar_try_wait(ptx::smem_u32(&aux->full_bar[s]), ph) &&
+                           ptx::globaltimer_ns() - t0 < 20000000ull) {
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------- MMA issuer ---------------------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = ptx::make_f16_idesc(kTileM, kTileN);
+            int stage = 0;
+            uint32_t phase = 0, a_rows_seen = 0;
+            bool ok = true;
+            long long it = 0;
+            AStatIter ti;
+            for (ti.init(p, cta, grid); ti.valid && ok; ti.advance(p), ++it) {
+                if (ti.new_row) {
+                    // everything issued so far read the previous query tile: release it, then wait for the new one
+                    if (a_rows_seen > 0) ptx::umma_commit_1cta(ptx::smem_u32(&aux->a_empty_bar));
+                    ok = ptx::mbar_wait_bounded(ptx::smem_u32(&aux->a_full_bar), a_rows_seen & 1u, abort_flag, kWaitLimitNs);
+                    if (!ok) break;
+                    ++a_rows_seen;
+                    ptx::tc_fence_after_sync();
+                }
+                const int buf = static_cast<int>(it & 1);
+                const uint32_t acc_phase = static_cast<uint32_t>((it >> 1) & 1);
+                ok = ptx::mbar_wait_bounded(ptx::smem_u32(&aux->acc_empty_bar[buf]), acc_phase ^ 1u, abort_flag,
+                                            kWaitLimitNs);
+                if (!ok) break;
+                ptx::tc_fence_after_sync();
+                const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(buf * kTileN);
+                for (int ks = 0; ks < p.k_steps; ++ks) {
+                    ok = ptx::mbar_wait_bounded(ptx::smem_u32(&aux->full_bar[stage]), phase, abort_flag, kWaitLimitNs);
+                    if (!ok) break;
+                    ptx::tc_fence_after_sync();
+                    const uint64_t desc_a = ptx::make_kmajor_sw128_desc(a_u32 + static_cast<uint32_t>(ks) * kStageBytesA);
+                    const uint64_t desc_b =
+                        ptx::make_kmajor_sw128_desc(b_u32 + static_cast<uint32_t>(stage) * kStageBytesB);
+#pragma unroll
+                    for (int k = 0; k < kTileK / kUmmaK; ++k)
+                        ptx::umma_f16_ss<1>(tmem_d, desc_a + 2u * k, desc_b + 2u * k, idesc, (ks > 0 || k > 0) ? 1u : 0u);
+                    ptx::umma_commit_1cta(ptx::smem_u32(&aux->empty_bar[stage]));
+                    if (++stage == stages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (ok) ptx::umma_commit_1cta(ptx::smem_u32(&aux->acc_full_bar[buf]));
+            }
+            if (!ok) atomicOr(p.counters + 2, kErrMmaWait);
+        }
+    } else {
+        // ------------------------- Epilogue -----------------------------
+        const int quarter = warp & 3;
+        const int ewarp = warp - 2;
+        const int col_off = (ewarp >> 2) * kEpiCols;
+        float* wcn = aux->warp_cand[ewarp];
+        bool ok = true;
+        long long it = 0;
+        AStatIter ti;
+        ti.init(p, cta, grid);
+        float4 next_cand;
+        float next_query;
+        EpiHits pend;
+        pend.any = false;
+        if (ti.valid)
+            fetch_warp_norms(p, ti.tn * kTileN + col_off, p.q_begin + ti.tm * kTileM + quarter * 32, lane, next_cand,
+                             next_query);
+        for (; ti.valid; ++it) {
+            const int buf = static_cast<int>(it & 1);
+            const uint32_t acc_phase = static_cast<uint32_t>((it >> 1) & 1);
+            const int q0 = p.q_begin + ti.tm * kTileM + quarter * 32;
+            const int c0 = ti.tn * kTileN + col_off;
+            __syncwarp();
+            reinterpret_cast<float4*>(wcn)[lane] = next_cand;
+            const float sq_lane = next_query;
+            __syncwarp();
+            ti.advance(p);
+            if (ti.valid)
+                fetch_warp_norms(p, ti.tn * kTileN + col_off, p.q_begin + ti.tm * kTileM + quarter * 32, lane,
+                                 next_cand, next_query);
+            if (ok) ok = ptx::mbar_wait_bounded(ptx::smem_u32(&aux->acc_full_bar[buf]), acc_phase, abort_flag,
+                                                kWaitLimitNs);
+            if (!ok) continue;
+            ptx::tc_fence_after_sync();
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                                   static_cast<uint32_t>(buf * kTileN + col_off);
+            epilogue_tile(p, taddr, wcn, sq_lane, q0, c0, lane, pend, [&] {
+                ptx::tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&aux->acc_empty_bar[buf]));
+            });
+        }
+        if (pend.any) epilogue_emit(p, pend, lane);
+        if (!ok && lane == 0) atomicOr(p.counters + 2, kErrEpilogueWait);
+    }
+
+    ptx::tc_fence_before_sync();
+    __syncthreads();
     if (blockIdx.x == 0 && threadIdx.x == 0) p.counters[4] = static_cast<unsigned long long>(clock64() - clock_start);
     if (warp == 1) {
         ptx::tc_fence_after_sync();
@@ -1123,6 +1426,18 @@ __global__ void unpack_pairs_kernel(const unsigned long long* keys, int2* out, u
     for (unsigned long long i = static_cast<unsigned long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < count;
          i += stride) {
         const unsigned long long k = keys[i];
+        out[i] = make_int2(static_cast<int>(k >> shift) + qbase, static_cast<int>(k & mask));
+    }
+}
+
+// The same for 32-bit records (JoinParams::key32); keys and out must not overlap.
+__global__ void unpack_pairs32_kernel(const uint32_t* __restrict__ keys, int2* __restrict__ out, unsigned long long count,
+                                      int shift, int qbase) {
+    const uint32_t mask = shift >= 32 ? ~0u : ((1u << shift) - 1u);
+    const unsigned long long stride = static_cast<unsigned long long>(gridDim.x) * blockDim.x;
+    for (unsigned long long i = static_cast<unsigned long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < count;
+         i += stride) {
+        const uint32_t k = keys[i];
         out[i] = make_int2(static_cast<int>(k >> shift) + qbase, static_cast<int>(k & mask));
     }
 }

@@ -31,6 +31,8 @@ def fill_device(sj, dev_pts, wl: dict) -> None:
     n, d = wl["n"], wl["d"]
     ld = dev_pts.shape[1]
     kind = wl["dist"]
+    # whatever produced dev_pts (its zero fill) ran on a torch stream; the library works on its own
+    torch.cuda.current_stream(dev_pts.device).synchronize()
     if kind == "exp":
         # counter-based generator on the device: the reference's distribution (Exponential(40), rejected
         # to [0, 10], double -> float -> half), not its sequential stream
@@ -64,6 +66,7 @@ def fill_device(sj, dev_pts, wl: dict) -> None:
                 a += m
     else:
         raise ValueError(kind)
+    torch.cuda.current_stream(dev_pts.device).synchronize()
 
 
 def host_sample(wl: dict, rows: int) -> np.ndarray:

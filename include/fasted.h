@@ -163,6 +163,15 @@ int fasted_set_points_device_f16(fasted_ctx* ctx, const void* dev, int64_t n, in
  * GPUs (layer 1 with FASTED_NUM_GPUS); one process per GPU uses an NCCL broadcast instead. */
 int fasted_copy_points_from(fasted_ctx* dst, fasted_ctx* src);
 
+/* Replicate the resident dataset of ctxs[0] into ctxs[1 .. count) -- contexts of this process on
+ * `count` distinct GPUs -- with ONE NCCL broadcast over NVLink (communicators from ncclCommInitAll,
+ * kept for the life of the process).  The reference is single-GPU (cudaSetDevice(0),
+ * source/findPairs.cuh:622) and has no counterpart; one process per GPU uses the broadcast of its
+ * own process group instead (fasted_b200/dist.py).  NCCL is bound at run time: without libnccl.so.2
+ * the call fails with FASTED_ENODEV and fasted_copy_points_from remains.  *ms_out (optional): wall
+ * time of the collective. */
+int fasted_broadcast_points(fasted_ctx* const* ctxs, int count, double* ms_out);
+
 /* Allocate an n x d dataset on the device and fill it with the counter-based
  * Exponential(lambda) generator (values rejected to [0, max_value], rounded
  * double -> float -> half).  For benchmark shapes too large for the reference's
@@ -321,6 +330,12 @@ int fasted_tile_schedule(int64_t n, int64_t q_begin, int64_t q_end, int tile_m, 
                          int shard_rank, int shard_world, int grid, int cta, int32_t* tiles_out, int64_t max_tiles,
                          int64_t* count_out);
 
+/* The same for the query-stationary kernel that joins short rows (d <= 512): bands of rows_per_band
+ * 128-row tile rows (at most `grid`); in a band of r rows CTA b takes row b % r and the tile columns
+ * b / r, b / r + grid / r, ...  (tm, tn) pairs as above. */
+int fasted_tile_schedule_stationary(int64_t n, int64_t q_begin, int64_t q_end, int rows_per_band, int symmetric, int grid,
+                                    int cta, int32_t* tiles_out, int64_t max_tiles, int64_t* count_out);
+
 /* Self-test of the failure path every device-side wait of this library has: a one-block kernel
  * waits, with a limit of limit_ms (at most 1000), on a barrier that nothing completes.  The wait
  * must give up, the kernel must return normally, *status_out must carry the wait's status bits
@@ -334,7 +349,10 @@ int fasted_selftest_wait_timeout(fasted_ctx* ctx, double limit_ms, unsigned long
  * tcgen05 cta_group::2; same results bit for bit; default 0 because it sustains less under the
  * power cap on B200), "exact_norms" (1 = correctly rounded row norms (FP64 sum, one rounding)
  * instead of the reference's round-toward-zero chain: NOT the reference's numerics, but closer to an
- * FP64 join on this hardware, whose tensor-core accumulate does not truncate; default 0). */
+ * FP64 join on this hardware, whose tensor-core accumulate does not truncate; default 0),
+ * "query_stationary" (-1 = automatic: for rows of at most 384 values a CTA keeps its 128 query rows in
+ * shared memory and streams candidate rows only; 0 = never, 1 = whenever d <= 512; same results bit for
+ * bit), "stream_chunk_bands" (raster bands per chunk of fasted_join_stream, 0 = automatic). */
 int fasted_set_option(fasted_ctx* ctx, const char* name, int64_t value);
 
 #ifdef __cplusplus

@@ -256,6 +256,38 @@ def test_join_against_reference_gpu_output(gpu_join, oracle_mod, path):
     assert np.array_equal(got, g["pairs"])
 
 
+@pytest.mark.parametrize("n,d,eps", [(256, 64, 1e3), (300, 100, 1e3), (1000, 256, 0.5), (2000, 512, 0.7), (5000, 448, 0.68),
+                                     (4096, 128, 0.3136), (777, 333, 0.62), (20_000, 384, 0.58), (9000, 64, 0.2),
+                                     (1, 8, 1.0), (130, 512, 1e3)])
+def test_query_stationary_kernel_is_bit_identical(gpu_join, oracle_mod, n, d, eps):
+    # Short rows can be joined by the kernel that keeps a CTA's query tile in shared memory and walks
+    # tile rows instead of raster bands.  Same accumulators, same K order: pairs and distances must
+    # equal the raster kernel's bit for bit, for the full and the symmetric schedule, bands included.
+    rng = np.random.default_rng(7 * n + d)
+    pts = oracle_mod.double_to_half(rng.exponential(1 / 40.0, size=(n, d)))
+    gpu_join.set_points(pts)
+    try:
+        gpu_join.set_option("query_stationary", 0)
+        a = gpu_join.join(eps, capacity=min(n * n, 40_000_000), flags=1)
+        pa, da = gpu_join.pairs(with_dist2=True)
+        gpu_join.set_option("query_stationary", 1)
+        b = gpu_join.join(eps, capacity=min(n * n, 40_000_000), flags=1)
+        pb, db = gpu_join.pairs(with_dist2=True)
+        assert a.status == 0 and b.status == 0 and a.pairs_found == b.pairs_found == len(pa)
+        assert np.array_equal(pa, pb) and np.array_equal(da.view(np.uint32), db.view(np.uint32))
+        c = gpu_join.join(eps, capacity=min(n * n, 40_000_000), flags=1 | 8)
+        pc, dc = gpu_join.pairs(with_dist2=True)
+        assert c.pairs_found == a.pairs_found
+        assert np.array_equal(pa, pc) and np.array_equal(da.view(np.uint32), dc.view(np.uint32))
+        if n > 600:
+            gpu_join.join(eps, q_begin=128, q_end=min(n, 600), capacity=min(n * n, 40_000_000))
+            assert np.array_equal(gpu_join.pairs(), pa[(pa[:, 0] >= 128) & (pa[:, 0] < min(n, 600))])
+            st = gpu_join.join_stream(eps, capacity=min(n * n, 40_000_000))
+            assert st.pairs_found == a.pairs_found and np.array_equal(gpu_join.pairs(), pa)
+    finally:
+        gpu_join.set_option("query_stationary", -1)
+
+
 def _refsum_cases():
     import glob
     return sorted(glob.glob(os.path.join(GOLDEN, "refsum_gpu_*.npz")))

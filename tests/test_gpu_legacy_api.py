@@ -109,6 +109,38 @@ def test_copy_points_between_contexts(gpu_join, oracle_mod):
             other.copy_points_from(other)
 
 
+def test_broadcast_points_over_the_gpus_of_one_process(gpu_join, oracle_mod):
+    """The in-library NCCL broadcast (ncclCommInitAll, one process): every further GPU receives the
+    dataset of GPU 0 bit for bit and joins its band of it.  Two contexts on one GPU are refused."""
+    import torch
+    from fasted_b200 import SelfJoin, _lib
+    pts = oracle_mod.gen_exponential(3000, 96)
+    gpu_join.set_points(pts)
+    with SelfJoin(0) as same:
+        with pytest.raises(_lib.FastedError) as e:
+            _lib.broadcast_points([gpu_join, same])
+        assert e.value.code == _lib.EINVAL and "share device" in str(e.value)
+    assert _lib.broadcast_points([gpu_join]) == 0.0
+    g = min(torch.cuda.device_count(), 4)
+    if g < 2:
+        pytest.skip("needs two GPUs")
+    others = [SelfJoin(i) for i in range(1, g)]
+    try:
+        for _ in range(2):  # the second call reuses the communicators
+            ms = _lib.broadcast_points([gpu_join] + others)
+            assert ms > 0
+        gpu_join.join(0.3, capacity=2_000_000)
+        want = gpu_join.pairs()
+        for i, o in enumerate(others):
+            assert o.points_info()[1:3] == (3000, 96)
+            assert np.array_equal(o.get_points(), pts.view(np.uint16))
+            o.join(0.3, q_begin=1024 * (i % 2), q_end=3000, capacity=2_000_000)
+            assert np.array_equal(o.pairs(), want[want[:, 0] >= 1024 * (i % 2)])
+    finally:
+        for o in others:
+            o.close()
+
+
 _TWO_GPU_DRIVER = r"""
 import sys
 sys.path.insert(0, {root!r})
@@ -148,3 +180,46 @@ def test_more_gpus_than_present_is_an_error(native_lib):
     env = dict(os.environ, FASTED_NUM_GPUS="64")
     r = subprocess.run([exe, "-e", "1000", "64", "0.1"], capture_output=True, text=True, env=env, timeout=600)
     assert r.returncode == 1 and "Error: Failed to run." in r.stdout
+
+
+_REFERENCE_DRIVER = r"""
+import json, os, sys
+sys.path.insert(0, os.path.join({ref!r}, "results", "scripts"))
+from experiment.find_pairs import load_findpairs, RerunnablePairsFinder     # the reference's own modules,
+from experiment.experiments import ExperimentRunner, SearchParameters, find_epsilon_binary, bound_epsilon
+lib = load_findpairs()                      # loads ../../source/main.so relative to the working directory
+runner = ExperimentRunner(lib)
+finder = RerunnablePairsFinder(lambda e, s: lib.runFromExponentialDataset(10000, 64, 40.0, 10.0, e, s), lib.reRun)
+sel = lambda eps: finder(eps, False).get_selectivity()
+lo, hi = bound_epsilon(0.01, 100000, 16.0, sel)
+eps = find_epsilon_binary(16.0, sel, initial_epsilon=0.01)
+trials = runner.run_time_trials(finder, [SearchParameters(16.0, eps, False)], 3)
+lib.releaseResources()
+print("JSON" + json.dumps(dict(lo=lo, hi=hi, eps=eps, sel=[t.results.get_selectivity() for t in trials],
+                               found=[t.results.pairsFound for t in trials], tflops=[t.results.TFLOPS for t in trials])))
+"""
+
+
+def test_the_references_own_driver_runs_against_this_library(native_lib, oracle_mod, tmp_path):
+    """The reference's experiment driver itself (results/scripts/experiment: load_findpairs, bound_epsilon,
+    find_epsilon_binary, run_time_trials), unmodified, with this library in the place of its main.so.
+    Needs the reference checkout (FASTED_REFERENCE_ROOT, default /root/reference); skipped without it."""
+    from fasted_b200 import _lib
+    ref = os.environ.get("FASTED_REFERENCE_ROOT", "/root/reference")
+    if not os.path.isdir(os.path.join(ref, "results", "scripts", "experiment")):
+        pytest.skip("the reference checkout is not present on this machine")
+    (tmp_path / "source").mkdir()
+    os.symlink(_lib.LEGACY_LIB_PATH, tmp_path / "source" / "main.so")
+    cwd = tmp_path / "results" / "scripts"
+    cwd.mkdir(parents=True)
+    r = subprocess.run([sys.executable, "-c", _REFERENCE_DRIVER.format(ref=ref)], capture_output=True, text=True,
+                       cwd=str(cwd), env=dict(os.environ, FASTED_OUTPUT_DIR=str(tmp_path)), timeout=900)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    out = json.loads(r.stdout.split("JSON")[-1])
+    assert out["lo"] < out["eps"] < out["hi"]
+    assert all(abs(s - 16.0) <= 0.16 + 1e-9 for s in out["sel"])  # within a percent of the target, as the driver asks
+    assert len(set(out["found"])) == 1 and all(t > 0 for t in out["tflops"])
+    # the count the driver converged on is the oracle's count at that epsilon
+    pts = oracle_mod.gen_exponential(10000, 64)
+    want, _ = oracle_mod.join_fp16_fp32(pts, out["eps"])
+    assert out["found"][0] == len(want)

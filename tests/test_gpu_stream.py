@@ -15,19 +15,24 @@ def _points(oracle_mod, n, d, seed):
     return oracle_mod.double_to_half(rng.exponential(1 / 40.0, size=(n, d)))
 
 
-@pytest.mark.parametrize("n,d,eps,band_tiles,chunk_bands", [
-    (4096, 128, 0.3136, 0, 0),      # automatic chunking (one or two chunks at this size)
-    (5000, 200, 0.36, 2, 1),        # 20 chunks of 256 rows
-    (3001, 64, 0.25, 1, 3),         # ragged last chunk, d a single K step
-    (9000, 1024, 1.1, 4, 2),
-    (700, 333, 0.5, 1, 1),          # d not a multiple of 64
+@pytest.mark.parametrize("n,d,eps,band_tiles,chunk_bands,qs,key32", [
+    (4096, 128, 0.3136, 0, 0, -1, 1),   # everything automatic (one or two chunks at this size)
+    (5000, 200, 0.36, 2, 1, 0, 1),      # raster kernel, 20 chunks of 256 rows, 32-bit records
+    (5000, 200, 0.36, 2, 1, 0, 0),      # the same with 64-bit records
+    (3001, 64, 0.25, 1, 3, 0, 1),       # ragged last chunk, d a single K step
+    (9000, 1024, 1.1, 4, 2, -1, 1),
+    (700, 333, 0.62, 1, 1, 0, 1),       # d not a multiple of 64
+    (12_000, 200, 0.36, 0, 1, 1, 1),    # query-stationary kernel: chunks of 37 tile rows
+    (12_000, 64, 0.25, 0, 1, 1, 0),
 ])
-def test_stream_equals_join_then_get_pairs(gpu_join, oracle_mod, n, d, eps, band_tiles, chunk_bands):
+def test_stream_equals_join_then_get_pairs(gpu_join, oracle_mod, n, d, eps, band_tiles, chunk_bands, qs, key32):
     import torch
     pts = _points(oracle_mod, n, d, n + d)
     gpu_join.set_points(pts)
     gpu_join.set_option("band_tiles", band_tiles)
     gpu_join.set_option("stream_chunk_bands", chunk_bands)
+    gpu_join.set_option("query_stationary", qs)
+    gpu_join.set_option("stream_key32", key32)
     try:
         st0 = gpu_join.join(eps, flags=1)
         want, want_d2 = gpu_join.pairs(with_dist2=True)
@@ -46,10 +51,12 @@ def test_stream_equals_join_then_get_pairs(gpu_join, oracle_mod, n, d, eps, band
         assert [f for f, *_ in seen] == list(np.cumsum([0] + [c for _, c, *_ in seen[:-1]]))
         assert sum(c for _, c, *_ in seen) == m
         assert all(want[f].tolist() == p0 and want_d2[f] == d0 for f, _, p0, d0 in seen)
-        if chunk_bands:
+        if chunk_bands and qs == 0:
             rows_per_chunk = chunk_bands * (band_tiles or 16) * 128
             assert st.chunks == -(-n // rows_per_chunk)
-            assert len(seen) <= st.chunks
+        if chunk_bands and qs == 1:
+            assert st.chunks == -(-n // (chunk_bands * 37 * 128))
+        assert len(seen) <= st.chunks
         # fasted_get_pairs works afterwards, as after fasted_join
         again, again_d2 = gpu_join.pairs(with_dist2=True)
         assert np.array_equal(again, want) and np.array_equal(again_d2.view(np.uint32), want_d2.view(np.uint32))
@@ -71,6 +78,8 @@ def test_stream_equals_join_then_get_pairs(gpu_join, oracle_mod, n, d, eps, band
     finally:
         gpu_join.set_option("band_tiles", 0)
         gpu_join.set_option("stream_chunk_bands", 0)
+        gpu_join.set_option("query_stationary", -1)
+        gpu_join.set_option("stream_key32", 1)
 
 
 def test_stream_against_the_oracle(gpu_join, oracle_mod):
@@ -79,12 +88,14 @@ def test_stream_against_the_oracle(gpu_join, oracle_mod):
     gpu_join.set_points(pts)
     gpu_join.set_option("band_tiles", 2)
     gpu_join.set_option("stream_chunk_bands", 2)
+    gpu_join.set_option("query_stationary", 0)  # raster bands: six chunks at this size
     try:
         got, got_d2 = [], []
         gpu_join.join_stream(0.36, flags=1, on_chunk=lambda p, d2, first: (got.append(p.copy()), got_d2.append(d2.copy())) and 0)
     finally:
         gpu_join.set_option("band_tiles", 0)
         gpu_join.set_option("stream_chunk_bands", 0)
+        gpu_join.set_option("query_stationary", -1)
     assert_identical_to_oracle(oracle_mod, pts, 192, 0.36, np.concatenate(got), np.concatenate(got_d2))
 
 
@@ -94,6 +105,7 @@ def test_stream_overflow_clip_and_abort(gpu_join, oracle_mod):
     gpu_join.set_points(pts)
     gpu_join.set_option("band_tiles", 2)
     gpu_join.set_option("stream_chunk_bands", 1)
+    gpu_join.set_option("query_stationary", 0)  # raster bands of 2 tile rows: chunks of 256 rows
     try:
         full = gpu_join.join(0.3)
         want = gpu_join.pairs()
@@ -133,3 +145,4 @@ def test_stream_overflow_clip_and_abort(gpu_join, oracle_mod):
     finally:
         gpu_join.set_option("band_tiles", 0)
         gpu_join.set_option("stream_chunk_bands", 0)
+        gpu_join.set_option("query_stationary", -1)

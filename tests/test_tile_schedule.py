@@ -64,3 +64,34 @@ def test_symmetric_shards_partition_the_triangle_evenly(native_lib, n, world, ba
     assert np.array_equal(got, needed)
     if tiles_m >= 8 * world * band:
         assert (max(loads) - min(loads)) / max(loads) < 0.02  # the snake evens out the triangle
+
+
+@pytest.mark.parametrize("n,q_begin,q_end,grid,rows,symmetric", [
+    (1000, 0, 1000, 7, 7, False), (5000, 0, 5000, 148, 37, False), (5000, 1280, 3333, 148, 37, False),
+    (100_000, 0, 100_000, 148, 37, False), (300, 0, 300, 3, 3, False), (1, 0, 1, 1, 1, False),
+    (4096, 0, 4096, 100, 25, False), (5000, 0, 5000, 148, 37, True), (33_333, 0, 33_333, 148, 37, True),
+    (1000, 0, 1000, 8, 8, True), (70_000, 0, 70_000, 148, 4, False),
+])
+def test_stationary_schedule_covers_every_tile_once_row_by_row(native_lib, n, q_begin, q_end, grid, rows, symmetric):
+    # The query-stationary kernel: every needed tile exactly once over all CTAs; a CTA walks one tile
+    # row at a time (so that the row's query tile can stay in shared memory) with ascending columns;
+    # the CTAs that share a row split its columns evenly.
+    from fasted_b200 import _lib
+    per_cta = [_lib.tile_schedule_stationary(n, q_begin, q_end, grid, c, rows, symmetric) for c in range(grid)]
+    tiles_m, tiles_n = -(-(q_end - q_begin) // 128), -(-n // 256)
+    tm, tn = np.meshgrid(np.arange(tiles_m), np.arange(tiles_n), indexing="ij")
+    needed = (tn * 256 + 255 >= q_begin + tm * 128) if symmetric else np.ones((tiles_m, tiles_n), dtype=bool)
+    got = np.zeros((tiles_m, tiles_n), dtype=np.int32)
+    for t in per_cta:
+        np.add.at(got, (t[:, 0], t[:, 1]), 1)
+        if len(t) > 1:
+            same_row = t[1:, 0] == t[:-1, 0]
+            assert (t[1:, 1][same_row] > t[:-1, 1][same_row]).all()      # ascending columns inside a row
+            assert (t[1:, 0][~same_row] > t[:-1, 0][~same_row]).all()    # a row is never revisited
+    assert np.array_equal(got, needed.astype(np.int32))
+    if not symmetric and tiles_m >= rows and tiles_n >= 4 * (grid // rows):
+        full_band = [len(t[t[:, 0] < rows]) for t in per_cta if len(t)]
+        assert max(full_band) - min(full_band) <= 1
+    from fasted_b200 import FastedError
+    with pytest.raises(FastedError):
+        _lib.tile_schedule_stationary(n, q_begin, q_end, grid, 0, grid + 1, symmetric)
