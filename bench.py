@@ -246,8 +246,8 @@ def main() -> None:
     import torch
     import torch.distributed as dist
     from fasted_b200 import SelfJoin, JOIN_NO_SORT
-    from fasted_b200.dist import (GpuBandEngine, SharedPairBuffer, allgather_points, band_bounds, sharded_self_join,
-                                  weighted_band_bounds)
+    from fasted_b200.dist import (GpuBandEngine, SharedChunkTable, SharedPairBuffer, allgather_points, band_bounds,
+                                  dealt_self_join, sharded_self_join)
     from fasted_b200.dist import band_rows as rows_per_band
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -317,35 +317,25 @@ def main() -> None:
             eps = float(t.item())
     per_point = int(wl.get("pairs_per_point", 256))
 
-    # ---- bands: equal to begin with; at N > 1 re-sized by the rate every GPU showed in the warm-up ---
+    # ---- the split over the GPUs --------------------------------------------------------------------
+    # N > 1: the ranks take chunks of whole raster bands from one shared table, each whenever its join
+    # stream has room (dealt_self_join): a GPU that runs faster under its own power cap takes more chunks,
+    # so all ranks finish within one small chunk of each other.  --no-balance: one fixed, equal band per rank.
+    dealt = world > 1 and not args.no_balance
     bounds = [band_bounds(n, world, r) for r in range(world)]
-    cap_rows = int(max(b - a for a, b in bounds) * (1.15 if world > 1 else 1.0)) + 128
+    cap_rows = int(max(b - a for a, b in bounds) * (1.3 if dealt else 1.0)) + 128
+    capacity = max(1, cap_rows) * per_point
+    table = SharedChunkTable.collective(n) if dealt else None
 
     def step_resident():
+        if dealt:
+            return dealt_self_join(sj, n, eps, table, None, capacity=capacity, flags=JOIN_NO_SORT)[2]
         a, b = bounds[rank]
-        return sj.join(eps, q_begin=a, q_end=b, capacity=max(1, cap_rows) * per_point, flags=JOIN_NO_SORT)
-
-    def rebalance():
-        # rows per millisecond of every rank's last join -> bands in proportion (multiples of 128 rows)
-        a, b = bounds[rank]
-        st = step_resident()
-        mine = torch.tensor([(b - a) / max(st.join_ms, 1e-6)], dtype=torch.float64, device="cuda")
-        rates = torch.empty(world, dtype=torch.float64, device="cuda")
-        dist.all_gather_into_tensor(rates, mine)
-        new = weighted_band_bounds(n, rates.tolist())
-        if max(y - x for x, y in new) <= cap_rows:
-            bounds[:] = new
-        return rates.tolist()
+        return sj.join(eps, q_begin=a, q_end=b, capacity=capacity, flags=JOIN_NO_SORT)
 
     for _ in range(args.warmup):
         step_resident()
-    rates = None
-    if world > 1 and not args.no_balance:
-        rates = rebalance()
-        rates = rebalance()  # second round: on the bands the first one chose
     q_begin, q_end = bounds[rank]
-    band_rows = q_end - q_begin
-    capacity = max(1, cap_rows) * per_point
 
     # ---- timed region 1: dataset resident, device-timed -----------------------------------------
     sampler = ClockSampler(local_rank)
@@ -362,9 +352,16 @@ def main() -> None:
         found = int(st.pairs_found)
         cyc.append(int(st.cta0_cycles))
         tiles0 = int(st.cta0_tiles)
+        last_rows = int(st.tiles_m) * 128
     ev1.record()
     barrier()
     clocks = sampler.stop()
+    band_rows = min(last_rows, n) if dealt else q_end - q_begin  # query rows this rank joined in its last step
+    rows_share = None
+    if world > 1:
+        t = torch.empty(world, dtype=torch.float64, device="cuda")
+        dist.all_gather_into_tensor(t, torch.tensor([float(band_rows)], dtype=torch.float64, device="cuda"))
+        rows_share = [int(x) for x in t.tolist()]
     total_ms = allmax(ev0.elapsed_time(ev1))
     found_total = int(allsum(float(found)))
     join_ms_max, norm_ms_max = allmax(float(np.mean(join_ms))), allmax(float(np.mean(norm_ms)))
@@ -441,6 +438,9 @@ def main() -> None:
             dev_pts[pad_begin:pad_end].copy_(host_pts, non_blocking=True)
             allgather_points(dev_pts, rank, world)
             sj.set_points_device(dev_pts.data_ptr(), n, d, ld, keepalive=dev_pts)
+            if dealt:
+                _, _, st = dealt_self_join(sj, n, eps, table, shared, capacity=capacity)
+                return st, int(st.pairs_stored)
             _, _, stored = sharded_self_join(engine, n, eps, gather=False, bounds=bounds, shared=shared)
             return engine.last_stats, stored
 
@@ -469,9 +469,12 @@ def main() -> None:
                "join_launches_per_step": e2e_chunks,
                "api": "fasted_set_points_host_f16 + fasted_join_stream (pinned host buffers; sort and device-to-host "
                       "copy pipelined behind the join)"
-               if world == 1 else "per rank: pinned host band -> its GPU, one NCCL all-gather, fasted_join_stream on the "
-                                    "band, count exchange, fasted_get_pairs into one shared page-locked host buffer at "
-                                    "the exclusive-scan offset; byte counts are sums over the ranks"}
+               if world == 1 else "per rank: pinned host band -> its GPU, one NCCL all-gather, then "
+                                    + ("fasted_join_stream_shared: chunks taken from one shared table, every sorted chunk "
+                                       "copied to its final place in one shared page-locked host buffer while the join runs"
+                                       if dealt else "fasted_join_stream on the rank's band, count exchange, fasted_get_pairs "
+                                       "into one shared page-locked host buffer at the exclusive-scan offset")
+                                    + "; byte counts are sums over the ranks"}
         if shared is not None:
             # the single list on the host: strictly ascending keys == every band in place, nothing missing
             if rank == 0:
@@ -511,10 +514,9 @@ def main() -> None:
                 "workload": f"{name}: self-join of {n} x {d} points, {wl['dist']} (seed {SEED}), FP16, "
                             f"eps for ~{wl['target']} neighbours per point",
                 "n": n, "d": d, "epsilon": eps, "mean_neighbours": (found_total - n) / n,
-                "parallelism": f"query-row bands x{world}" + ("" if args.no_balance else ", sized by the rate each GPU "
-                               "showed in the warm-up") if world > 1 else "single GPU",
-                "bands": bounds if world > 1 else None,
-                "band_rates_rows_per_ms": rates,
+                "parallelism": (f"query rows over {world} GPUs: " + ("chunks of raster bands taken on demand from a shared "
+                                "table" if dealt else "one fixed equal band per rank")) if world > 1 else "single GPU",
+                "rows_per_rank_last_step": rows_share,
                 "l2": "inputs larger than L2 (no flush needed)" if n * ld * 2 > 2 * 126e6 else "inputs fit L2",
                 "baseline_note": "vs_baseline divides by the reference's published A100-PCIe figure for this shape "
                                  "(153.64 TFLOPS at eps=0.001)" if name in PUBLISHED_A100_TFLOPS else None,
@@ -528,7 +530,7 @@ def main() -> None:
             "sm_clock_in_kernel_mhz": float(np.mean(cyc)) / (float(np.mean(join_ms)) * 1e3) if cyc and cyc[0] else None,
             "tensor_busy_share_cta0": (tiles0 * (-(-d // 64)) * 512.0) / float(np.mean(cyc)) if cyc and cyc[0] else None,
             "e2e": e2e,
-            "gpu_launches": 3 * args.steps,  # per step: row_norms_kernel, join_kernel, unpack_pairs_kernel
+            "gpu_launches": 2 * args.steps,  # per step: row_norms_kernel, join_kernel (records stay packed until asked for)
             "roofline": {"bound": "tensor", "kernel": "join_kernel", "achieved": achieved, "peak": peak,
                          "unit": "TFLOP/s", "frac": achieved / peak if peak else None,
                          # DRAM bytes per launch: ncu measured one pass over the candidates per raster band

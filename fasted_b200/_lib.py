@@ -62,6 +62,9 @@ DECLARED_SYMBOLS = [
     "fasted_dataset_exponential_f16", "fasted_dataset_csv_shape", "fasted_dataset_csv_f16",
     "fasted_join_static_scratch", "fasted_join_stream", "fasted_tile_schedule_stationary",
     "fasted_broadcast_points",
+    "fasted_shared_chunks_bytes", "fasted_shared_chunks_init", "fasted_join_stream_shared", "fasted_shared_chunks_totals",
+    "fasted_shared_chunks_init_plan", "fasted_shared_chunks_take", "fasted_shared_chunks_publish",
+    "fasted_shared_chunks_offset", "fasted_shared_chunks_fail",
 ]
 
 CHUNK_FN = ctypes.CFUNCTYPE(ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_uint64,
@@ -100,6 +103,21 @@ def load() -> ctypes.CDLL:
     L.fasted_join.argtypes = [_vp, ctypes.c_double, _i64, _i64, _u64, ctypes.c_uint, ctypes.POINTER(JoinStats)]
     L.fasted_join_stream.argtypes = [_vp, ctypes.c_double, _i64, _i64, _u64, ctypes.c_uint, _vp, _vp, _u64, CHUNK_FN,
                                      _vp, ctypes.POINTER(JoinStats)]
+    L.fasted_shared_chunks_bytes.argtypes = [_u64]
+    L.fasted_shared_chunks_bytes.restype = ctypes.c_size_t
+    L.fasted_shared_chunks_init.argtypes = [_vp, _vp, ctypes.c_size_t, ctypes.c_double, _i64, _i64, ctypes.c_int,
+                                            ctypes.POINTER(_u64)]
+    L.fasted_join_stream_shared.argtypes = [_vp, ctypes.c_double, _u64, ctypes.c_uint, _vp, _vp, _u64,
+                                            ctypes.POINTER(JoinStats)]
+    L.fasted_shared_chunks_totals.argtypes = [_vp, ctypes.POINTER(ctypes.c_ulonglong), ctypes.POINTER(ctypes.c_ulonglong),
+                                              ctypes.POINTER(ctypes.c_ulonglong)]
+    L.fasted_shared_chunks_init_plan.argtypes = [_vp, ctypes.c_size_t, _i64, _i64, _i64, ctypes.POINTER(_u64)]
+    L.fasted_shared_chunks_take.argtypes = [_vp]
+    L.fasted_shared_chunks_take.restype = _i64
+    L.fasted_shared_chunks_publish.argtypes = [_vp, _u64, _u64, _u64]
+    L.fasted_shared_chunks_offset.argtypes = [_vp, _u64, ctypes.c_double, ctypes.POINTER(_u64)]
+    L.fasted_shared_chunks_fail.argtypes = [_vp]
+    L.fasted_shared_chunks_fail.restype = None
     L.fasted_tile_schedule.argtypes = [_i64, _i64, _i64, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
                                        ctypes.c_int, ctypes.c_int, ctypes.c_int, _vp, _i64, ctypes.POINTER(_i64)]
     L.fasted_tile_schedule_stationary.argtypes = [_i64, _i64, _i64, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
@@ -324,6 +342,18 @@ class SelfJoin:
         _check(rc)
         self._last = st
         self._last_dist = want_dist
+        return st
+
+    def join_stream_shared(self, eps: float, table_address: int, capacity: int = 0, flags: int = 0,
+                           pairs_host: int = 0, host_capacity: int = 0) -> JoinStats:
+        """fasted_join_stream_shared: this rank's part of a join whose chunks all ranks of the node take from
+        one shared table (fasted_b200.dist.SharedChunkTable); records go to their final place in the host
+        buffer all ranks share.  Returns this rank's statistics."""
+        st = JoinStats()
+        _check(self._L.fasted_join_stream_shared(self._h, float(eps), capacity, flags, _vp(table_address),
+                                                 _vp(pairs_host or None), host_capacity, ctypes.byref(st)))
+        self._last = st
+        self._last_dist = False
         return st
 
     def estimate_epsilon(self, target_mean_neighbours: float, sample_rows: int = 0, rel_tol: float = 0.01):

@@ -6,7 +6,10 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <sched.h>
+
 #include <algorithm>
+#include <atomic>
 #include <cfloat>
 #include <cstdarg>
 #include <cstdio>
@@ -94,6 +97,9 @@ struct fasted_ctx {
     size_t sort_tmp_bytes = 0;
     uint64_t stored = 0;
     void* result_pairs = nullptr;  // int2 records of the last join
+    bool unpack_pending = false;   // the last join left packed records in `keys` (device order); they are
+                                   // turned into int2 records when somebody asks for them
+    unsigned long long* counters_host = nullptr;  // pinned mirror of the counter block
     float* result_dist = nullptr;
     bool result_sorted = false;
 
@@ -108,6 +114,8 @@ struct fasted_ctx {
     std::vector<cudaEvent_t> sort_t0, sort_t1;    // timing brackets of the sorts
     cudaEvent_t ev_tail = nullptr, ev_copied[2] = {nullptr, nullptr};
     int stream_key32 = 1;                          // option: 32-bit records where they fit
+    double density_hint = 0.0;                     // records per query row of the last join ...
+    int64_t hint_n = 0, hint_d = 0;                // ... on a dataset of this shape (a re-upload of the same shape keeps it)
     unsigned long long* chunk_end_host = nullptr;  // pinned: the found counter after each chunk
     size_t chunk_end_cap = 0;
     int stream_chunk_bands = 0;                    // option: raster bands per chunk (0 = automatic)
@@ -177,6 +185,7 @@ int adopt_points(fasted_ctx* c, __half* dev, bool owns, int64_t n, int64_t d, in
     c->norms_valid = false;
     c->stored = 0;
     c->result_pairs = nullptr;
+    c->unpack_pending = false;
     if (c->norms_cap < n) {
         if (c->norms) cudaFree(c->norms);
         c->norms = nullptr;
@@ -224,6 +233,7 @@ void free_pair_buffers(fasted_ctx* c) {
     c->stored = 0;
     c->result_pairs = nullptr;
     c->result_dist = nullptr;
+    c->unpack_pending = false;
 }
 
 // ---- transfers through pinned staging ---------------------------------------------------------
@@ -391,9 +401,10 @@ int fasted_create(int device, fasted_ctx** out) {
             return fail(FASTED_ECUDA, "cudaEventCreate failed");
         }
     }
-    if (cudaMalloc(&c->counters, 8 * sizeof(unsigned long long)) != cudaSuccess) {
+    if (cudaMalloc(&c->counters, 8 * sizeof(unsigned long long)) != cudaSuccess ||
+        cudaMallocHost(&c->counters_host, 8 * sizeof(unsigned long long)) != cudaSuccess) {
         fasted_destroy(c);
-        return fail(FASTED_ECUDA, "cudaMalloc of counters failed");
+        return fail(FASTED_ECUDA, "allocation of the counters failed");
     }
     cudaFuncSetAttribute(fasted::join_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, fasted::kJoinSmemBytes);
     cudaFuncSetAttribute(fasted::row_norms_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -440,6 +451,7 @@ void fasted_destroy(fasted_ctx* c) {
     free_pair_buffers(c);
     if (c->norms) cudaFree(c->norms);
     if (c->counters) cudaFree(c->counters);
+    if (c->counters_host) cudaFreeHost(c->counters_host);
     for (auto& ev : c->ev)
         if (ev) cudaEventDestroy(ev);
     for (int i = 0; i < 2; ++i) {
@@ -979,6 +991,14 @@ static void fill_stats(fasted_ctx* c, const JoinPlan& pl, const unsigned long lo
     }
 }
 
+static bool symmetric_flag(unsigned flags) { return (flags & FASTED_JOIN_SYMMETRIC) != 0; }
+
+static void set_density_hint(fasted_ctx* c, double records_per_row) {
+    c->density_hint = records_per_row;
+    c->hint_n = c->n;
+    c->hint_d = c->d;
+}
+
 static int unpack_blocks(fasted_ctx* c, uint64_t count) {
     return static_cast<int>(std::min<uint64_t>((count + 255) / 256, static_cast<uint64_t>(c->num_sms) * 16));
 }
@@ -1013,31 +1033,33 @@ static int join_impl(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end, 
     c->stored = 0;
     c->result_pairs = nullptr;
     c->result_dist = nullptr;
+    c->unpack_pending = false;
 
     if (flags & FASTED_JOIN_NO_SORT) {
-        // Device order is the result: the records are unpacked by a kernel that reads the count on the
-        // device, so the call needs the host only once, at its end (what a sweep of small joins pays
-        // per call is launch and synchronisation latency, not kernel time).
+        // Device order is the result.  The call needs the host once, at its end: the counters come back
+        // through a pinned mirror, and the packed records are turned into (query, candidate) records
+        // only when somebody asks for them (what a sweep of small joins pays per call is launch and
+        // synchronisation latency, not kernel time).
         CU_TRY(cudaEventRecord(c->ev[3], c->stream));
-        fasted::unpack_pairs_kernel<<<unpack_blocks(c, capacity), 256, 0, c->stream>>>(
-            c->keys, reinterpret_cast<int2*>(c->keys_alt), capacity, c->counters, 0ull, 32, 0);
-        CU_TRY(cudaGetLastError());
         CU_TRY(cudaEventRecord(c->ev[4], c->stream));
-        CU_TRY(cudaMemcpyAsync(h, c->counters, sizeof(h), cudaMemcpyDeviceToHost, c->stream));
+        CU_TRY(cudaMemcpyAsync(c->counters_host, c->counters, sizeof(h), cudaMemcpyDeviceToHost, c->stream));
         CU_TRY(cudaStreamSynchronize(c->stream));
+        std::memcpy(h, c->counters_host, sizeof(h));
         c->norms_valid = (h[2] & fasted::kErrNormWait) == 0;
         if (h[2]) return fail(FASTED_EKERNEL, "a device-side wait ran out (status 0x%llx)", h[2]);
         const uint64_t stored = std::min<uint64_t>(h[0], capacity);
         c->stored = stored;
-        c->result_pairs = c->keys_alt;
+        if (q_end > q_begin && !symmetric_flag(flags)) set_density_hint(c, static_cast<double>(h[0]) / static_cast<double>(q_end - q_begin));
+        c->unpack_pending = true;
         c->result_dist = want_dist ? c->dist : nullptr;
         c->result_sorted = false;
         fill_stats(c, pl, h, stored, stats);
         return FASTED_OK;
     }
 
-    CU_TRY(cudaMemcpyAsync(h, c->counters, sizeof(h), cudaMemcpyDeviceToHost, c->stream));
+    CU_TRY(cudaMemcpyAsync(c->counters_host, c->counters, sizeof(h), cudaMemcpyDeviceToHost, c->stream));
     CU_TRY(cudaStreamSynchronize(c->stream));
+    std::memcpy(h, c->counters_host, sizeof(h));
     c->norms_valid = (h[2] & fasted::kErrNormWait) == 0;
     if (h[2]) return fail(FASTED_EKERNEL, "a device-side wait ran out (status 0x%llx)", h[2]);
     // Every record with a slot below the capacity is written, the others are dropped.
@@ -1076,12 +1098,13 @@ static int join_impl(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end, 
     }
     if (stored > 0) {
         fasted::unpack_pairs_kernel<<<unpack_blocks(c, stored), 256, 0, c->stream>>>(
-            sorted_keys, reinterpret_cast<int2*>(c->keys_alt), stored, nullptr, 0ull, 32, 0);
+            sorted_keys, reinterpret_cast<int2*>(c->keys_alt), stored, 32, 0);
         CU_TRY(cudaGetLastError());
     }
     CU_TRY(cudaEventRecord(c->ev[4], c->stream));
     CU_TRY(cudaStreamSynchronize(c->stream));
     c->stored = stored;
+    if (q_end > q_begin && !symmetric_flag(flags)) set_density_hint(c, static_cast<double>(h[0]) / static_cast<double>(q_end - q_begin));
     c->result_pairs = c->keys_alt;
     c->result_dist = want_dist ? sorted_dist : nullptr;
     c->result_sorted = true;
@@ -1162,13 +1185,86 @@ static int bits_of(uint64_t v) {  // number of bits needed to write v (at least 
     return b;
 }
 
-int fasted_join_stream(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end, uint64_t capacity, unsigned flags,
-                       int32_t* pairs_host, float* dist2_host, uint64_t host_capacity, fasted_chunk_fn on_chunk,
-                       void* user, fasted_join_stats* stats) {
+// The chunk plan of a streamed join over query rows [q_begin, q_end): chunks of whole raster bands.
+// min_chunks = 0: about 64 chunks, each at least about a millisecond of tensor work (one GPU).  A
+// larger min_chunks (ranks that share the chunks want many small ones, so that the last chunk a rank
+// takes is a small part of its work) is honoured down to one band per chunk.  Never more rows than
+// 32-bit records can number, where one band's rows can be.
+struct ChunkPlan {
+    int64_t band_rows, chunk_rows;
+    uint64_t chunks;
+    int key_shift;
+    bool fits32;  // a chunk's rows can be numbered by a 32-bit record
+};
+
+static int plan_chunks(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end, uint64_t min_chunks, ChunkPlan* out) {
+    JoinPlan whole;
+    int rc = plan_join(c, eps, q_begin, q_end, 1, 0, 0, 1, &whole);
+    if (rc) return rc;
+    const int64_t band_rows = whole.astat ? static_cast<int64_t>(whole.p.astat_rows) * whole.p.tile_m
+                                          : static_cast<int64_t>(whole.p.band_tiles) * whole.p.tile_m;
+    const int64_t rows = q_end - q_begin;
+    const int64_t total_bands = std::max<int64_t>(1, (rows + band_rows - 1) / band_rows);
+    const int key_shift = bits_of(static_cast<uint64_t>(std::max<int64_t>(c->n - 1, 1)));
+    const int64_t rows32 = key_shift < 32 ? (int64_t(1) << (32 - key_shift)) : 0;
+    int64_t bands_per_chunk = c->stream_chunk_bands;
+    if (bands_per_chunk <= 0) {
+        const double min_rows = 2e12 / (2.0 * static_cast<double>(c->n) * static_cast<double>(c->ld));
+        const int64_t want_chunks = std::max<int64_t>(64, static_cast<int64_t>(min_chunks));
+        bands_per_chunk = (total_bands + want_chunks - 1) / want_chunks;
+        if (min_chunks == 0)
+            bands_per_chunk = std::max<int64_t>(bands_per_chunk,
+                                                static_cast<int64_t>(std::ceil(min_rows / static_cast<double>(band_rows))));
+        // Dense outputs (the last join on this dataset stored 128 records per row or more): chunks small
+        // enough for 32-bit records, which halve the sort's traffic.  Sparse outputs: fewer, larger chunks,
+        // because a sort of a small slice is all launch overhead.
+        if (rows32 >= band_rows && c->density_hint >= 128.0 && c->hint_n == c->n && c->hint_d == c->d)
+            bands_per_chunk = std::min<int64_t>(bands_per_chunk, rows32 / band_rows);
+    }
+    bands_per_chunk = std::max<int64_t>(1, std::min<int64_t>(bands_per_chunk, total_bands));
+    out->band_rows = band_rows;
+    out->chunk_rows = bands_per_chunk * band_rows;
+    out->chunks = static_cast<uint64_t>((rows + out->chunk_rows - 1) / out->chunk_rows);
+    out->key_shift = key_shift;
+    out->fits32 = out->chunk_rows <= rows32;
+    return FASTED_OK;
+}
+
+// ---- chunks shared by the ranks of one node ----------------------------------------------------
+//
+// One process per GPU, all holding the same dataset: instead of giving every rank one fixed band of
+// query rows, the ranks take CHUNKS from a common counter, each whenever its join stream has room for
+// another launch.  A GPU that runs faster (each sits under its own power cap) simply takes more
+// chunks, so all ranks finish within one chunk of each other; and since chunk k's place in the global
+// list is the sum of the record counts of chunks 0 .. k-1 -- which other ranks publish at about the
+// time chunk k itself retires -- every rank can copy its chunks straight to their final position in
+// one shared host buffer while the join is still running.  The table lives in memory that all ranks
+// map (a shared file mapping); it is the only thing the ranks exchange during the join: no collective.
+struct SharedChunks {
+    uint64_t magic;
+    int64_t q_begin, q_end, chunk_rows;
+    uint64_t chunks;
+    std::atomic<uint64_t> next;    // next chunk to hand out
+    std::atomic<uint64_t> failed;  // a rank gave up: everybody stops waiting
+    std::atomic<uint64_t> found_total, stored_total;
+    std::atomic<uint64_t> count[1];  // records stored for chunk k; kUnknownCount until its rank publishes it
+};
+constexpr uint64_t kSharedMagic = 0x46615354454463ull;
+constexpr uint64_t kUnknownCount = ~0ull;
+static_assert(sizeof(std::atomic<uint64_t>) == sizeof(uint64_t), "lock-free 64-bit atomics expected");
+
+int64_t fasted_shared_chunks_take(void* mem);
+int fasted_shared_chunks_publish(void* mem, uint64_t chunk, uint64_t stored, uint64_t found);
+
+static int join_stream_core(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end, uint64_t capacity, unsigned flags,
+                            int32_t* pairs_host, float* dist2_host, uint64_t host_capacity, fasted_chunk_fn on_chunk,
+                            void* user, SharedChunks* shared, fasted_join_stats* stats) {
     int rc = check_join_args(c, eps, q_begin, &q_end);
     if (rc) return rc;
-    if (flags & (FASTED_JOIN_SYMMETRIC | FASTED_JOIN_NO_SORT | FASTED_JOIN_RAW_DOT))
-        return fail(FASTED_EINVAL, "fasted_join_stream takes FASTED_JOIN_DIST2 and FASTED_JOIN_KEEP_NORMS only");
+    const bool count_only = shared != nullptr && (flags & FASTED_JOIN_NO_SORT) != 0;
+    if (flags & (FASTED_JOIN_SYMMETRIC | FASTED_JOIN_RAW_DOT | (shared ? FASTED_JOIN_DIST2 : FASTED_JOIN_NO_SORT)))
+        return fail(FASTED_EINVAL, shared ? "the shared-chunk join takes FASTED_JOIN_NO_SORT and FASTED_JOIN_KEEP_NORMS only"
+                                          : "fasted_join_stream takes FASTED_JOIN_DIST2 and FASTED_JOIN_KEEP_NORMS only");
     const bool want_dist = (flags & FASTED_JOIN_DIST2) != 0;
     if (dist2_host && !want_dist) return fail(FASTED_EINVAL, "dist2_host given without FASTED_JOIN_DIST2");
     CU_TRY(cudaSetDevice(c->device));
@@ -1179,28 +1275,26 @@ int fasted_join_stream(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end
     rc = ensure_pair_buffers(c, capacity, want_dist);
     if (rc) return rc;
 
-    // Chunks of whole raster bands: about 64 of them, each at least about a millisecond of tensor
-    // work -- but no more rows than 32-bit records can number, where one band's rows can be.
     JoinPlan whole;
-    rc = plan_join(c, eps, q_begin, q_end, capacity, flags, 0, 1, &whole);
+    rc = plan_join(c, eps, q_begin, q_end, capacity, flags & ~FASTED_JOIN_NO_SORT, 0, 1, &whole);
     if (rc) return rc;
-    const int64_t band_rows = whole.astat ? static_cast<int64_t>(whole.p.astat_rows) * whole.p.tile_m
-                                          : static_cast<int64_t>(whole.p.band_tiles) * whole.p.tile_m;
-    const int64_t rows = q_end - q_begin;
-    const int64_t total_bands = std::max<int64_t>(1, (rows + band_rows - 1) / band_rows);
-    const int key_shift = bits_of(static_cast<uint64_t>(c->n - 1));
-    const int64_t rows32 = key_shift < 32 ? (int64_t(1) << (32 - key_shift)) : 0;  // rows a 32-bit record can number
-    int64_t bands_per_chunk = c->stream_chunk_bands;
-    if (bands_per_chunk <= 0) {
-        const double min_rows = 2e12 / (2.0 * static_cast<double>(c->n) * static_cast<double>(c->ld));
-        bands_per_chunk = std::max<int64_t>((total_bands + 63) / 64,
-                                            static_cast<int64_t>(std::ceil(min_rows / static_cast<double>(band_rows))));
-        if (rows32 >= band_rows) bands_per_chunk = std::min<int64_t>(bands_per_chunk, rows32 / band_rows);
+    ChunkPlan cp;
+    rc = plan_chunks(c, eps, q_begin, q_end, 0, &cp);
+    if (rc) return rc;
+    if (shared) {
+        // the plan every rank follows is the one in the table (made by fasted_shared_chunks_init)
+        if (shared->magic != kSharedMagic || shared->q_begin != q_begin || shared->q_end != q_end ||
+            shared->chunk_rows <= 0 || shared->chunk_rows % cp.band_rows != 0)
+            return fail(FASTED_EINVAL, "the shared chunk table does not belong to this join");
+        cp.chunk_rows = shared->chunk_rows;
+        cp.chunks = shared->chunks;
+        const int64_t rows32 = cp.key_shift < 32 ? (int64_t(1) << (32 - cp.key_shift)) : 0;
+        cp.fits32 = cp.chunk_rows <= rows32;
     }
-    bands_per_chunk = std::max<int64_t>(1, std::min<int64_t>(bands_per_chunk, total_bands));
-    const int64_t chunk_rows = bands_per_chunk * band_rows;
-    const size_t chunks = static_cast<size_t>((rows + chunk_rows - 1) / chunk_rows);
-    const bool key32 = c->stream_key32 != 0 && chunk_rows <= rows32;
+    const int key_shift = cp.key_shift;
+    const int64_t chunk_rows = cp.chunk_rows;
+    const size_t chunks = static_cast<size_t>(cp.chunks);  // chunks of the whole join (all ranks')
+    const bool key32 = c->stream_key32 != 0 && cp.fits32;
     rc = ensure_stream_pipeline(c, chunks + 1);
     if (rc) return rc;
     const int sort_bits = std::min(key32 ? 32 : 64,
@@ -1212,7 +1306,7 @@ int fasted_join_stream(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end
 
     // Sort scratch for the largest slice a chunk can have (the library sort's scratch is bounded: it
     // works through long inputs in portions), allocated before anything is enqueued.
-    {
+    if (!count_only) {
         size_t need = 0;
         cub::DoubleBuffer<float> vb(c->dist, c->dist_alt);
         if (key32) {
@@ -1245,6 +1339,7 @@ int fasted_join_stream(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end
     c->stored = 0;
     c->result_pairs = nullptr;
     c->result_dist = nullptr;
+    c->unpack_pending = false;
     CU_TRY(cudaMemsetAsync(c->counters, 0, 8 * sizeof(unsigned long long), c->stream));
     CU_TRY(cudaEventRecord(c->ev[0], c->stream));
     if (!(flags & FASTED_JOIN_KEEP_NORMS) || !c->norms_valid) {
@@ -1253,11 +1348,22 @@ int fasted_join_stream(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end
     }
     CU_TRY(cudaEventRecord(c->ev[1], c->stream));
 
-    auto chunk_begin = [&](size_t k) { return q_begin + static_cast<int64_t>(k) * chunk_rows; };
-    auto enqueue_join = [&](size_t k) -> int {
-        const int64_t b = chunk_begin(k), e = std::min<int64_t>(q_end, b + chunk_rows);
+    // Launch j of this rank joins chunk ids[j]: the next in order (one GPU), or the next one nobody
+    // has taken yet (chunks shared by several ranks).
+    std::vector<size_t> ids;
+    auto chunk_begin = [&](size_t id) { return q_begin + static_cast<int64_t>(id) * chunk_rows; };
+    auto enqueue_next_join = [&]() -> int {
+        size_t id = ids.size();
+        if (shared) {
+            const int64_t taken = fasted_shared_chunks_take(shared);
+            if (taken < 0) return FASTED_OK;
+            id = static_cast<size_t>(taken);
+        }
+        if (id >= chunks) return FASTED_OK;
+        const size_t j = ids.size();
+        const int64_t b = chunk_begin(id), e = std::min<int64_t>(q_end, b + chunk_rows);
         JoinPlan pl;
-        int r = plan_join(c, eps, b, e, capacity, flags, 0, 1, &pl);
+        int r = plan_join(c, eps, b, e, capacity, flags & ~FASTED_JOIN_NO_SORT, 0, 1, &pl);
         if (r) return r;
         pl.p.key_shift = key_shift;
         pl.p.key_qbase = static_cast<int>(b);
@@ -1265,41 +1371,82 @@ int fasted_join_stream(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end
         r = launch_join(c, pl);
         if (r) return r;
         // (pinned destination: a copy into pageable memory would hold the host until the GPU gets here)
-        CU_TRY(cudaMemcpyAsync(c->chunk_end_host + k, c->counters, sizeof(unsigned long long), cudaMemcpyDeviceToHost,
+        CU_TRY(cudaMemcpyAsync(c->chunk_end_host + j, c->counters, sizeof(unsigned long long), cudaMemcpyDeviceToHost,
                                c->stream));
-        CU_TRY(cudaEventRecord(c->chunk_ev[k], c->stream));
+        CU_TRY(cudaEventRecord(c->chunk_ev[j], c->stream));
+        ids.push_back(id);
         return FASTED_OK;
     };
     constexpr size_t kAhead = 2;  // join launches enqueued beyond the chunk the host is waiting for
-    for (size_t k = 0; k < std::min(kAhead, chunks); ++k) {
-        rc = enqueue_join(k);
+    for (size_t k = 0; k < kAhead; ++k) {
+        rc = enqueue_next_join();
         if (rc) return rc;
     }
 
-    // Delivery of chunk k's sorted records [a, b) to the host; runs one chunk behind the sorts so that
-    // the host never waits for a copy while it could be feeding the join stream.
+    // Place of a chunk's first record in the list the host receives.  One GPU: the chunk's first slot.
+    // Shared chunks: the sum of the counts of all chunks before it, as soon as their ranks have
+    // published them (they retire at about the same time as this one; the wait is bounded).
+    uint64_t known_upto = 0, prefix = 0;  // prefix = records of chunks [0, known_upto)
+    auto global_offset = [&](size_t id, uint64_t* off) -> int {
+        timespec t0;
+        clock_gettime(CLOCK_MONOTONIC, &t0);
+        for (unsigned spin = 0; known_upto < id; ++spin) {
+            const uint64_t v = shared->count[known_upto].load(std::memory_order_acquire);
+            if (v != kUnknownCount) {
+                prefix += v;
+                ++known_upto;
+                continue;
+            }
+            if (shared->failed.load(std::memory_order_acquire)) return fail(FASTED_ESTATE, "another rank gave up its join");
+            if ((spin & 1023u) == 1023u) {
+                timespec t1;
+                clock_gettime(CLOCK_MONOTONIC, &t1);
+                if (t1.tv_sec - t0.tv_sec > 120)
+                    return fail(FASTED_ESTATE, "chunk %llu was not published within 120 s by the rank that took it",
+                                (unsigned long long)known_upto);
+                sched_yield();
+            }
+        }
+        *off = prefix;
+        return FASTED_OK;
+    };
+
+    // Delivery of a chunk's sorted records (device slots [a, b)) to the host; runs one chunk behind the
+    // sorts so that the host never waits for a copy while it could be feeding the join stream.
     int abort_rc = FASTED_OK;
     struct Pending {
         bool any = false;
         uint64_t a = 0, b = 0;
-        size_t chunk = 0;
+        size_t j = 0;
+        bool copy_enqueued = false;
     } pend;
     auto deliver = [&](const Pending& pd) -> int {
         if (!pd.any) return FASTED_OK;
         const uint64_t a = pd.a, m = pd.b - pd.a;
         const int2* src_pairs = reinterpret_cast<const int2*>(c->keys_alt) + a;
         const float* src_dist = want_dist ? c->dist_alt + a : nullptr;
+        uint64_t at = a;  // index of the chunk's first record in the host list
+        if (shared) {
+            const int r = global_offset(ids[pd.j], &at);
+            if (r) return r;
+        }
         if (pairs_host) {
-            const uint64_t hb = std::min<uint64_t>(pd.b, host_capacity);
-            const uint64_t hm = hb > a ? hb - a : 0;
+            const uint64_t hm = at < host_capacity ? std::min<uint64_t>(m, host_capacity - at) : 0;
             if (hm == 0) return FASTED_OK;
             if (host_pinned) {
-                CU_TRY(cudaEventSynchronize(c->copied_ev[pd.chunk]));  // the copies were enqueued when the sort was
+                if (!pd.copy_enqueued) {
+                    CU_TRY(cudaMemcpyAsync(pairs_host + 2 * at, src_pairs, hm * 8, cudaMemcpyDeviceToHost, c->copy_stream));
+                    if (dist2_host)
+                        CU_TRY(cudaMemcpyAsync(dist2_host + at, src_dist, hm * 4, cudaMemcpyDeviceToHost, c->copy_stream));
+                    CU_TRY(cudaEventRecord(c->copied_ev[pd.j], c->copy_stream));
+                }
+                // with nobody to tell, the copy may finish on its own (the end of the call waits for it)
+                if (on_chunk) CU_TRY(cudaEventSynchronize(c->copied_ev[pd.j]));
             } else {
-                CU_TRY(download_bytes(c, pairs_host + 2 * a, src_pairs, hm * 8, c->copy_stream));
-                if (dist2_host) CU_TRY(download_bytes(c, dist2_host + a, src_dist, hm * 4, c->copy_stream));
+                CU_TRY(download_bytes(c, pairs_host + 2 * at, src_pairs, hm * 8, c->copy_stream));
+                if (dist2_host) CU_TRY(download_bytes(c, dist2_host + at, src_dist, hm * 4, c->copy_stream));
             }
-            if (on_chunk && on_chunk(user, pairs_host + 2 * a, dist2_host ? dist2_host + a : nullptr, a, hm) != 0)
+            if (on_chunk && on_chunk(user, pairs_host + 2 * at, dist2_host ? dist2_host + at : nullptr, at, hm) != 0)
                 return fail(FASTED_EINVAL, "the chunk callback asked to stop");
         } else if (on_chunk) {
             // No destination of the caller's: runs of records pass through the two pinned staging
@@ -1321,25 +1468,30 @@ int fasted_join_stream(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end
                     const char* buf = static_cast<const char*>(c->stage_buf[(i - 1) & 1]);
                     CU_TRY(cudaEventSynchronize(c->ev_copied[(i - 1) & 1]));
                     if (on_chunk(user, reinterpret_cast<const int32_t*>(buf),
-                                 want_dist ? reinterpret_cast<const float*>(buf + run * 8) : nullptr, a + off, cnt) != 0)
+                                 want_dist ? reinterpret_cast<const float*>(buf + run * 8) : nullptr, at + off, cnt) != 0)
                         return fail(FASTED_EINVAL, "the chunk callback asked to stop");
                 }
             }
         }
         return FASTED_OK;
     };
+    auto give_up = [&](int code) {
+        if (shared) shared->failed.store(1, std::memory_order_release);
+        return code;
+    };
 
     uint64_t prev_end = 0;
     size_t sorts = 0;
-    for (size_t k = 0; k < chunks; ++k) {
-        CU_TRY(cudaEventSynchronize(c->chunk_ev[k]));
-        const uint64_t end_k = c->chunk_end_host[k];
-        const uint64_t a = std::min<uint64_t>(prev_end, capacity), b = std::min<uint64_t>(end_k, capacity);
-        prev_end = end_k;
+    for (size_t j = 0; j < ids.size(); ++j) {
+        CU_TRY(cudaEventSynchronize(c->chunk_ev[j]));
+        const uint64_t end_j = c->chunk_end_host[j];
+        const uint64_t a = std::min<uint64_t>(prev_end, capacity), b = std::min<uint64_t>(end_j, capacity);
+        if (shared) fasted_shared_chunks_publish(shared, ids[j], b - a, end_j - prev_end);  // later chunks can be placed
+        prev_end = end_j;
         Pending now;
-        if (b > a && abort_rc == FASTED_OK) {
+        if (b > a && abort_rc == FASTED_OK && !count_only) {
             const uint64_t m = b - a;
-            // sort(k) and its unpacking, on the join stream, behind the launch that is running now
+            // sort(j) and its unpacking, on the join stream, behind the launch that is running now
             CU_TRY(cudaEventRecord(c->sort_t0[sorts], c->stream));
             cub::DoubleBuffer<float> vb(want_dist ? c->dist + a : nullptr, want_dist ? c->dist_alt + a : nullptr);
             size_t need = c->sort_tmp_bytes;
@@ -1352,7 +1504,7 @@ int fasted_join_stream(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end
                         CU_TRY(cub::DeviceRadixSort::SortKeys(c->sort_tmp, need, kb, m, 0, sort_bits, c->stream));
                 }
                 fasted::unpack_pairs32_kernel<<<unpack_blocks(c, m), 256, 0, c->stream>>>(
-                    kb.Current(), reinterpret_cast<int2*>(c->keys_alt + a), m, key_shift, static_cast<int>(chunk_begin(k)));
+                    kb.Current(), reinterpret_cast<int2*>(c->keys_alt + a), m, key_shift, static_cast<int>(chunk_begin(ids[j])));
             } else {
                 cub::DoubleBuffer<unsigned long long> kb(c->keys + a, c->keys_alt + a);
                 if (m > 1) {
@@ -1362,29 +1514,29 @@ int fasted_join_stream(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end
                         CU_TRY(cub::DeviceRadixSort::SortKeys(c->sort_tmp, need, kb, m, 0, sort_bits, c->stream));
                 }
                 fasted::unpack_pairs_kernel<<<unpack_blocks(c, m), 256, 0, c->stream>>>(
-                    kb.Current(), reinterpret_cast<int2*>(c->keys_alt + a), m, nullptr, 0ull, key_shift,
-                    static_cast<int>(chunk_begin(k)));
+                    kb.Current(), reinterpret_cast<int2*>(c->keys_alt + a), m, key_shift, static_cast<int>(chunk_begin(ids[j])));
             }
             CU_TRY(cudaGetLastError());
             if (want_dist && vb.Current() != c->dist_alt + a)
                 CU_TRY(cudaMemcpyAsync(c->dist_alt + a, vb.Current(), m * sizeof(float), cudaMemcpyDeviceToDevice,
                                        c->stream));
             CU_TRY(cudaEventRecord(c->sort_t1[sorts], c->stream));
-            CU_TRY(cudaEventRecord(c->sorted_ev[k], c->stream));
+            CU_TRY(cudaEventRecord(c->sorted_ev[j], c->stream));
             ++sorts;
             now.any = true;
             now.a = a;
             now.b = b;
-            now.chunk = k;
+            now.j = j;
         }
         // keep the join stream fed before anything else
-        if (k + kAhead < chunks && abort_rc == FASTED_OK) {
-            rc = enqueue_join(k + kAhead);
-            if (rc) return rc;
+        if (abort_rc == FASTED_OK) {
+            rc = enqueue_next_join();
+            if (rc) return give_up(rc);
         }
         if (now.any) {
-            CU_TRY(cudaStreamWaitEvent(c->copy_stream, c->sorted_ev[k], 0));
-            if (pairs_host && host_pinned) {
+            CU_TRY(cudaStreamWaitEvent(c->copy_stream, c->sorted_ev[j], 0));
+            if (!shared && pairs_host && host_pinned) {
+                // one GPU: the chunk's place on the host is its first slot, known already
                 const uint64_t hb = std::min<uint64_t>(now.b, host_capacity);
                 if (hb > now.a) {
                     CU_TRY(cudaMemcpyAsync(pairs_host + 2 * now.a, reinterpret_cast<const int2*>(c->keys_alt) + now.a,
@@ -1393,29 +1545,46 @@ int fasted_join_stream(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end
                         CU_TRY(cudaMemcpyAsync(dist2_host + now.a, c->dist_alt + now.a, (hb - now.a) * 4,
                                                cudaMemcpyDeviceToHost, c->copy_stream));
                 }
-                CU_TRY(cudaEventRecord(c->copied_ev[k], c->copy_stream));
+                CU_TRY(cudaEventRecord(c->copied_ev[j], c->copy_stream));
+                now.copy_enqueued = true;
             }
         }
-        // chunk k-1's records: on the host by now, or nearly
-        if (abort_rc == FASTED_OK) abort_rc = deliver(pend);
+        // the previous chunk's records: on the host by now, or nearly
+        if (abort_rc == FASTED_OK) {
+            abort_rc = deliver(pend);
+            if (abort_rc != FASTED_OK) give_up(abort_rc);
+        }
         pend = now;
     }
-    if (chunks > 0) CU_TRY(cudaEventRecord(c->ev[2], c->stream));
+    const size_t mine = ids.size();
+    CU_TRY(cudaEventRecord(c->ev[2], c->stream));
     unsigned long long* h = c->chunk_end_host + chunks;
-    if (chunks == 0) CU_TRY(cudaEventRecord(c->ev[2], c->stream));
     CU_TRY(cudaMemcpyAsync(h, c->counters, 5 * sizeof(unsigned long long), cudaMemcpyDeviceToHost, c->stream));
-    if (abort_rc == FASTED_OK) abort_rc = deliver(pend);
+    if (abort_rc == FASTED_OK) {
+        abort_rc = deliver(pend);
+        if (abort_rc != FASTED_OK) give_up(abort_rc);
+    }
     CU_TRY(cudaEventRecord(c->ev_tail, c->copy_stream));
     CU_TRY(cudaStreamSynchronize(c->copy_stream));
     CU_TRY(cudaStreamSynchronize(c->stream));
     c->norms_valid = (h[2] & fasted::kErrNormWait) == 0;
-    if (h[2]) return fail(FASTED_EKERNEL, "a device-side wait ran out (status 0x%llx)", h[2]);
+    if (h[2]) return give_up(fail(FASTED_EKERNEL, "a device-side wait ran out (status 0x%llx)", h[2]));
     if (abort_rc != FASTED_OK) return abort_rc;
     const uint64_t stored = std::min<uint64_t>(h[0], capacity);
     c->stored = stored;
-    c->result_pairs = c->keys_alt;
-    c->result_dist = want_dist ? c->dist_alt : nullptr;
-    c->result_sorted = true;
+    {
+        int64_t my_rows = 0;
+        for (size_t id : ids) my_rows += std::min<int64_t>(q_end, chunk_begin(id) + chunk_rows) - chunk_begin(id);
+        if (my_rows > 0) set_density_hint(c, static_cast<double>(h[0]) / static_cast<double>(my_rows));
+    }
+    if (count_only) {
+        c->stored = 0;  // a counting run: the (chunk-relative, unsorted) records are not offered afterwards
+        c->result_sorted = false;
+    } else {
+        c->result_pairs = c->keys_alt;  // one GPU: the whole list; shared chunks: this rank's chunks in the order it took them
+        c->result_dist = want_dist ? c->dist_alt : nullptr;
+        c->result_sorted = shared == nullptr;
+    }
     CU_TRY(cudaEventRecord(c->ev[3], c->stream));
     CU_TRY(cudaEventRecord(c->ev[4], c->stream));
     CU_TRY(cudaStreamSynchronize(c->stream));
@@ -1436,11 +1605,126 @@ int fasted_join_stream(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end
         float tail = 0.f;
         if (cudaEventElapsedTime(&tail, c->ev[2], c->ev_tail) != cudaSuccess) tail = 0.f;
         stats->tail_ms = static_cast<double>(last_sort_ms) + std::max(0.f, tail);
-        stats->chunks = static_cast<int>(chunks);
-        stats->cta0_cycles = 0;  // the counter holds the last chunk's only
+        stats->chunks = static_cast<int>(mine);
+        if (shared) {  // this rank's share of the tile rows
+            int64_t my_rows = 0;
+            for (size_t id : ids) my_rows += std::min<int64_t>(q_end, chunk_begin(id) + chunk_rows) - chunk_begin(id);
+            stats->tiles_m = static_cast<int>((my_rows + whole.p.tile_m - 1) / whole.p.tile_m);
+        }
+        stats->cta0_cycles = 0;  // the counter holds the last launch's only
         stats->cta0_tiles = 0;
     }
     return FASTED_OK;
+}
+
+int fasted_join_stream(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end, uint64_t capacity, unsigned flags,
+                       int32_t* pairs_host, float* dist2_host, uint64_t host_capacity, fasted_chunk_fn on_chunk,
+                       void* user, fasted_join_stats* stats) {
+    return join_stream_core(c, eps, q_begin, q_end, capacity, flags, pairs_host, dist2_host, host_capacity, on_chunk, user,
+                            nullptr, stats);
+}
+
+size_t fasted_shared_chunks_bytes(uint64_t max_chunks) {
+    return sizeof(SharedChunks) + static_cast<size_t>(max_chunks) * sizeof(uint64_t);
+}
+
+int fasted_shared_chunks_init(fasted_ctx* c, void* mem, size_t bytes, double eps, int64_t q_begin, int64_t q_end,
+                              int ranks, uint64_t* chunks_out) {
+    if (!mem || ranks < 1) return fail(FASTED_EINVAL, "bad argument");
+    int rc = check_join_args(c, eps, q_begin, &q_end);
+    if (rc) return rc;
+    ChunkPlan cp;
+    // many small chunks: the last chunk a rank takes should be a small part (about 2 %) of its share
+    rc = plan_chunks(c, eps, q_begin, q_end, static_cast<uint64_t>(ranks) * 48, &cp);
+    if (rc) return rc;
+    if (fasted_shared_chunks_bytes(cp.chunks) > bytes)
+        return fail(FASTED_EINVAL, "the table needs %zu bytes for %llu chunks, %zu were given", fasted_shared_chunks_bytes(cp.chunks),
+                    (unsigned long long)cp.chunks, bytes);
+    return fasted_shared_chunks_init_plan(mem, bytes, q_begin, q_end, cp.chunk_rows, chunks_out);
+}
+
+int fasted_shared_chunks_init_plan(void* mem, size_t bytes, int64_t q_begin, int64_t q_end, int64_t chunk_rows,
+                                   uint64_t* chunks_out) {
+    if (!mem || q_begin < 0 || q_end < q_begin || chunk_rows <= 0) return fail(FASTED_EINVAL, "bad argument");
+    const uint64_t chunks = static_cast<uint64_t>((q_end - q_begin + chunk_rows - 1) / chunk_rows);
+    if (fasted_shared_chunks_bytes(chunks) > bytes) return fail(FASTED_EINVAL, "the table is too small for %llu chunks", (unsigned long long)chunks);
+    SharedChunks* t = static_cast<SharedChunks*>(mem);
+    t->q_begin = q_begin;
+    t->q_end = q_end;
+    t->chunk_rows = chunk_rows;
+    t->chunks = chunks;
+    t->next.store(0, std::memory_order_relaxed);
+    t->failed.store(0, std::memory_order_relaxed);
+    t->found_total.store(0, std::memory_order_relaxed);
+    t->stored_total.store(0, std::memory_order_relaxed);
+    for (uint64_t k = 0; k < chunks; ++k) t->count[k].store(kUnknownCount, std::memory_order_relaxed);
+    std::atomic_thread_fence(std::memory_order_release);
+    t->magic = kSharedMagic;
+    if (chunks_out) *chunks_out = chunks;
+    return FASTED_OK;
+}
+
+int64_t fasted_shared_chunks_take(void* mem) {
+    SharedChunks* t = static_cast<SharedChunks*>(mem);
+    if (!t || t->magic != kSharedMagic || t->failed.load(std::memory_order_acquire)) return -1;
+    const uint64_t id = t->next.fetch_add(1, std::memory_order_acq_rel);
+    return id < t->chunks ? static_cast<int64_t>(id) : -1;
+}
+
+int fasted_shared_chunks_publish(void* mem, uint64_t chunk, uint64_t stored, uint64_t found) {
+    SharedChunks* t = static_cast<SharedChunks*>(mem);
+    if (!t || t->magic != kSharedMagic || chunk >= t->chunks) return fail(FASTED_EINVAL, "bad chunk");
+    t->found_total.fetch_add(found, std::memory_order_relaxed);
+    t->stored_total.fetch_add(stored, std::memory_order_relaxed);
+    t->count[chunk].store(stored, std::memory_order_release);
+    return FASTED_OK;
+}
+
+int fasted_shared_chunks_offset(void* mem, uint64_t chunk, double timeout_ms, uint64_t* offset_out) {
+    SharedChunks* t = static_cast<SharedChunks*>(mem);
+    if (!t || t->magic != kSharedMagic || chunk > t->chunks || !offset_out) return fail(FASTED_EINVAL, "bad argument");
+    timespec t0;
+    clock_gettime(CLOCK_MONOTONIC, &t0);
+    uint64_t sum = 0;
+    for (uint64_t k = 0; k < chunk;) {
+        const uint64_t v = t->count[k].load(std::memory_order_acquire);
+        if (v != kUnknownCount) {
+            sum += v;
+            ++k;
+            continue;
+        }
+        if (t->failed.load(std::memory_order_acquire)) return fail(FASTED_ESTATE, "another rank gave up its join");
+        timespec t1;
+        clock_gettime(CLOCK_MONOTONIC, &t1);
+        if ((t1.tv_sec - t0.tv_sec) * 1e3 + (t1.tv_nsec - t0.tv_nsec) * 1e-6 > timeout_ms)
+            return fail(FASTED_ESTATE, "chunk %llu was not published in time", (unsigned long long)k);
+        sched_yield();
+    }
+    *offset_out = sum;
+    return FASTED_OK;
+}
+
+void fasted_shared_chunks_fail(void* mem) {
+    SharedChunks* t = static_cast<SharedChunks*>(mem);
+    if (t && t->magic == kSharedMagic) t->failed.store(1, std::memory_order_release);
+}
+
+int fasted_shared_chunks_totals(const void* mem, unsigned long long* found_total, unsigned long long* stored_total,
+                                unsigned long long* failed) {
+    const SharedChunks* t = static_cast<const SharedChunks*>(mem);
+    if (!t || t->magic != kSharedMagic) return fail(FASTED_EINVAL, "not a shared chunk table");
+    if (found_total) *found_total = t->found_total.load(std::memory_order_acquire);
+    if (stored_total) *stored_total = t->stored_total.load(std::memory_order_acquire);
+    if (failed) *failed = t->failed.load(std::memory_order_acquire);
+    return FASTED_OK;
+}
+
+int fasted_join_stream_shared(fasted_ctx* c, double eps, uint64_t capacity, unsigned flags, void* shared_mem,
+                              int32_t* pairs_host, uint64_t host_capacity, fasted_join_stats* stats) {
+    SharedChunks* t = static_cast<SharedChunks*>(shared_mem);
+    if (!t || t->magic != kSharedMagic) return fail(FASTED_EINVAL, "not a shared chunk table");
+    return join_stream_core(c, eps, t->q_begin, t->q_end, capacity, flags, pairs_host, nullptr, host_capacity, nullptr,
+                            nullptr, t, stats);
 }
 
 int fasted_tile_schedule(int64_t n, int64_t q_begin, int64_t q_end, int tile_m, int band_tiles, int symmetric,
@@ -1573,8 +1857,27 @@ int fasted_estimate_epsilon(fasted_ctx* c, double target_mean_neighbours, int64_
     return FASTED_OK;
 }
 
+// Records of a FASTED_JOIN_NO_SORT join are kept packed until they are asked for.
+static int ensure_unpacked(fasted_ctx* c) {
+    if (!c->unpack_pending) return FASTED_OK;
+    CU_TRY(cudaSetDevice(c->device));
+    if (c->stored > 0) {
+        fasted::unpack_pairs_kernel<<<unpack_blocks(c, c->stored), 256, 0, c->stream>>>(
+            c->keys, reinterpret_cast<int2*>(c->keys_alt), c->stored, 32, 0);
+        CU_TRY(cudaGetLastError());
+        CU_TRY(cudaStreamSynchronize(c->stream));
+    }
+    c->result_pairs = c->keys_alt;
+    c->unpack_pending = false;
+    return FASTED_OK;
+}
+
 int fasted_get_pairs(fasted_ctx* c, uint64_t first, uint64_t count, int32_t* pairs_out, float* dist2_out) {
     if (!c) return fail(FASTED_EINVAL, "ctx is null");
+    {
+        const int urc = ensure_unpacked(c);
+        if (urc) return urc;
+    }
     if (first + count > c->stored)
         return fail(FASTED_EINVAL, "range [%llu, %llu) exceeds the %llu stored pairs", (unsigned long long)first,
                     (unsigned long long)(first + count), (unsigned long long)c->stored);
@@ -1588,6 +1891,10 @@ int fasted_get_pairs(fasted_ctx* c, uint64_t first, uint64_t count, int32_t* pai
 
 int fasted_pairs_device(fasted_ctx* c, void** pairs_dev, void** dist2_dev) {
     if (!c) return fail(FASTED_EINVAL, "ctx is null");
+    {
+        const int urc = ensure_unpacked(c);
+        if (urc) return urc;
+    }
     if (pairs_dev) *pairs_dev = c->result_pairs;
     if (dist2_dev) *dist2_dev = c->result_dist;
     return FASTED_OK;

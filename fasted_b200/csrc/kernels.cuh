@@ -1410,17 +1410,10 @@ __global__ void wait_timeout_selftest_kernel(unsigned long long limit_ns, unsign
 // ---------------------------------------------------------------------------
 
 // Packed records -> {int query; int candidate}, the reference's Pair layout (source/pair.cuh:27-30).
-// Record = ((query - qbase) << shift) | candidate (see JoinParams::key_shift).  The number of records is
-// `count`, or, when found_dev is given, min(*found_dev - first_slot, count) read on the device, so
-// that the host need not know it before the launch.  keys and out may be the same buffer.
-__global__ void unpack_pairs_kernel(const unsigned long long* keys, int2* out, unsigned long long count,
-                                    const unsigned long long* __restrict__ found_dev, unsigned long long first_slot,
-                                    int shift, int qbase) {
-    if (found_dev != nullptr) {
-        const unsigned long long f = *found_dev;
-        const unsigned long long avail = f > first_slot ? f - first_slot : 0ull;
-        if (avail < count) count = avail;
-    }
+// Record = ((query - qbase) << shift) | candidate (see JoinParams::key_shift).  keys and out may be the
+// same buffer (every thread reads its record before it writes it).
+__global__ void unpack_pairs_kernel(const unsigned long long* keys, int2* out, unsigned long long count, int shift,
+                                    int qbase) {
     const unsigned long long mask = shift >= 64 ? ~0ull : ((1ull << shift) - 1ull);
     const unsigned long long stride = static_cast<unsigned long long>(gridDim.x) * blockDim.x;
     for (unsigned long long i = static_cast<unsigned long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < count;

@@ -11,6 +11,7 @@ meet in one shared host buffer (SharedPairBuffer), each at the offset its predec
 """
 from __future__ import annotations
 
+import ctypes
 import mmap
 import os
 import tempfile
@@ -55,20 +56,13 @@ def weighted_band_bounds(n: int, weights: Sequence[float], align: int = BAND_ALI
     return [(min(n, a * align), min(n, b * align)) for a, b in zip(cuts, cuts[1:])]
 
 
-class SharedPairBuffer:
-    """ONE host buffer for the whole job's pair list, mapped by every rank of the node.
+class SharedMapping:
+    """A block of host memory that every rank of the node maps: a file under /dev/shm (or under the
+    temporary directory when /dev/shm is too small).  Rank 0 creates the file and removes its name as
+    soon as every rank has mapped it, so nothing is left behind if a rank dies later."""
 
-    The reference's caller receives one row-major list (source/pair.cuh:39-45, 139-146 of the
-    reference).  With one process per GPU the list is assembled without any copy between processes:
-    the buffer is a shared mapping (a file under /dev/shm, or under the temporary directory when
-    /dev/shm is too small), every rank maps it, page-locks its view with cudaHostRegister so that
-    its GPU writes into it by DMA, and copies its band's sorted records to the offset that the
-    exclusive scan of the per-rank counts gives.  Rank 0 creates the file and removes its name as soon
-    as every rank has mapped it, so nothing is left behind if a rank dies later."""
-
-    def __init__(self, capacity_pairs: int, path: str | None = None, register_cuda: bool = False):
-        self.capacity = max(int(capacity_pairs), 1)
-        self.nbytes = self.capacity * 8
+    def __init__(self, nbytes: int, path: str | None = None):
+        self.nbytes = max(int(nbytes), 8)
         self.created = path is None
         if path is None:
             root = "/dev/shm"
@@ -78,7 +72,7 @@ class SharedPairBuffer:
                     root = tempfile.gettempdir()
             except OSError:
                 root = tempfile.gettempdir()
-            path = os.path.join(root, f"fasted_pairs_{os.getpid()}_{uuid.uuid4().hex}")
+            path = os.path.join(root, f"fasted_{os.getpid()}_{uuid.uuid4().hex}")
             fd = os.open(path, os.O_CREAT | os.O_EXCL | os.O_RDWR, 0o600)
             os.ftruncate(fd, self.nbytes)
         else:
@@ -88,17 +82,63 @@ class SharedPairBuffer:
             self._mm = mmap.mmap(fd, self.nbytes)  # MAP_SHARED
         finally:
             os.close(fd)
-        self.array = np.frombuffer(self._mm, dtype=np.int32).reshape(-1, 2)
-        self.address = self.array.ctypes.data
+        self.bytes = np.frombuffer(self._mm, dtype=np.uint8)
+        self.address = self.bytes.ctypes.data
+
+    def unlink(self) -> None:
+        if self.path and os.path.exists(self.path):
+            os.unlink(self.path)
+
+    def close(self) -> None:
+        if getattr(self, "_mm", None) is None:
+            return
+        self.bytes = None
+        try:
+            self._mm.close()
+        except BufferError:
+            pass  # a caller still holds a view; the mapping goes when the view does
+        self._mm = None
+
+    @classmethod
+    def _collective(cls, make, attach):
+        """Called by every rank: rank 0 creates the mapping (make()), the others map it (attach(path, nbytes))."""
+        import torch.distributed as dist
+        if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size() == 1:
+            obj = make()
+            obj.unlink()
+            return obj
+        rank = dist.get_rank()
+        box = [None]
+        obj = None
+        if rank == 0:
+            obj = make()
+            box = [(obj.path, obj.nbytes)]
+        dist.broadcast_object_list(box, src=0)
+        if rank != 0:
+            obj = attach(box[0][0], box[0][1])
+        dist.barrier()
+        if rank == 0:
+            obj.unlink()
+        return obj
+
+
+class SharedPairBuffer(SharedMapping):
+    """ONE host buffer for the whole job's pair list, mapped by every rank of the node.
+
+    The reference's caller receives one row-major list (source/pair.cuh:39-45, 139-146 of the
+    reference).  With one process per GPU the list is assembled without any copy between processes:
+    every rank maps the buffer, page-locks its view with cudaHostRegister so that its GPU writes into
+    it by DMA, and copies its sorted records to the place the counts of the records before them give."""
+
+    def __init__(self, capacity_pairs: int, path: str | None = None, register_cuda: bool = False):
+        self.capacity = max(int(capacity_pairs), 1)
+        super().__init__(self.capacity * 8, path)
+        self.array = self.bytes.view(np.int32).reshape(-1, 2)
         self.registered = False
         if register_cuda:
             import torch
             rc = torch.cuda.cudart().cudaHostRegister(self.address, self.nbytes, 0)
             self.registered = int(rc) == 0  # not registered: copies go through the library's pinned staging
-
-    def unlink(self) -> None:
-        if self.path and os.path.exists(self.path):
-            os.unlink(self.path)
 
     def close(self) -> None:
         if getattr(self, "_mm", None) is None:
@@ -108,33 +148,103 @@ class SharedPairBuffer:
             torch.cuda.cudart().cudaHostUnregister(self.address)
             self.registered = False
         self.array = None
-        try:
-            self._mm.close()
-        except BufferError:
-            pass  # a caller still holds a view; the mapping goes when the view does
-        self._mm = None
+        super().close()
 
     @classmethod
     def collective(cls, capacity_pairs: int, register_cuda: bool = False) -> "SharedPairBuffer":
         """Called by every rank: rank 0 creates the buffer, the others map it."""
-        import torch.distributed as dist
-        if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size() == 1:
-            buf = cls(capacity_pairs, register_cuda=register_cuda)
-            buf.unlink()
-            return buf
-        rank = dist.get_rank()
-        box = [None]
-        buf = None
-        if rank == 0:
-            buf = cls(capacity_pairs, register_cuda=register_cuda)
-            box = [(buf.path, buf.capacity)]
-        dist.broadcast_object_list(box, src=0)
-        if rank != 0:
-            buf = cls(box[0][1], path=box[0][0], register_cuda=register_cuda)
-        dist.barrier()
-        if rank == 0:
-            buf.unlink()
-        return buf
+        return cls._collective(lambda: cls(capacity_pairs, register_cuda=register_cuda),
+                               lambda path, nbytes: cls(nbytes // 8, path=path, register_cuda=register_cuda))
+
+
+class SharedChunkTable(SharedMapping):
+    """The table from which the ranks of a node take their chunks of a streamed join
+    (fasted_shared_chunks_* of the native library): a counter of chunks handed out and, per chunk, the
+    number of records its rank stored, which gives every later chunk its place in the shared list."""
+
+    def __init__(self, max_chunks: int, path: str | None = None, nbytes: int | None = None):
+        from . import _lib
+        self._L = _lib.load()
+        super().__init__(nbytes if nbytes is not None else self._L.fasted_shared_chunks_bytes(max(int(max_chunks), 1)), path)
+
+    @classmethod
+    def collective(cls, n_rows: int) -> "SharedChunkTable":
+        """Room for any chunking of n_rows query rows (a chunk is at least one 128-row tile row)."""
+        max_chunks = -(-n_rows // BAND_ALIGN) + 1
+        return cls._collective(lambda: cls(max_chunks), lambda path, nbytes: cls(0, path=path, nbytes=nbytes))
+
+    def init(self, self_join, eps: float, q_begin: int, q_end: int, ranks: int) -> int:
+        """By ONE rank, before the others are let in: plan the chunks (from that rank's context) and reset the table."""
+        from . import _lib
+        chunks = ctypes.c_uint64()
+        _lib._check(self._L.fasted_shared_chunks_init(self_join._h, ctypes.c_void_p(self.address), self.nbytes, float(eps),
+                                                      q_begin, q_end, ranks, ctypes.byref(chunks)))
+        return int(chunks.value)
+
+    def init_plan(self, q_begin: int, q_end: int, chunk_rows: int) -> int:
+        from . import _lib
+        chunks = ctypes.c_uint64()
+        _lib._check(self._L.fasted_shared_chunks_init_plan(ctypes.c_void_p(self.address), self.nbytes, q_begin, q_end,
+                                                           chunk_rows, ctypes.byref(chunks)))
+        return int(chunks.value)
+
+    def take(self) -> int:
+        return int(self._L.fasted_shared_chunks_take(ctypes.c_void_p(self.address)))
+
+    def publish(self, chunk: int, stored: int, found: int) -> None:
+        from . import _lib
+        _lib._check(self._L.fasted_shared_chunks_publish(ctypes.c_void_p(self.address), chunk, stored, found))
+
+    def offset(self, chunk: int, timeout_ms: float = 60_000.0) -> int:
+        from . import _lib
+        off = ctypes.c_uint64()
+        _lib._check(self._L.fasted_shared_chunks_offset(ctypes.c_void_p(self.address), chunk, float(timeout_ms),
+                                                        ctypes.byref(off)))
+        return int(off.value)
+
+    def fail(self) -> None:
+        self._L.fasted_shared_chunks_fail(ctypes.c_void_p(self.address))
+
+    def totals(self) -> tuple[int, int, int]:
+        """(pairs found, pairs stored, failed flag) over all ranks, once every rank is done."""
+        from . import _lib
+        f, s_, bad = ctypes.c_ulonglong(), ctypes.c_ulonglong(), ctypes.c_ulonglong()
+        _lib._check(self._L.fasted_shared_chunks_totals(ctypes.c_void_p(self.address), ctypes.byref(f), ctypes.byref(s_),
+                                                        ctypes.byref(bad)))
+        return int(f.value), int(s_.value), int(bad.value)
+
+
+def dealt_self_join(self_join, n: int, eps: float, table: SharedChunkTable, pairs: SharedPairBuffer | None = None,
+                    capacity: int = 0, flags: int = 0):
+    """The self-join over the ranks of one node with chunks dealt out on demand (see SharedChunkTable):
+    faster GPUs take more chunks, and every rank copies its sorted chunks to their final place in the ONE
+    shared host list `pairs` while the join runs.  Collective: every rank calls it.  With
+    flags & JOIN_NO_SORT nothing is sorted or copied (a counting / timing run with the same balance).
+    Returns (found_total, stored_total, this rank's JoinStats); raises BandJoinError on every rank when
+    any rank failed."""
+    import torch.distributed as dist
+    multi = dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1
+    world = dist.get_world_size() if multi else 1
+    rank = dist.get_rank() if multi else 0
+    if rank == 0:
+        table.init(self_join, eps, 0, n, world)
+    if multi:
+        dist.barrier()  # the table is ready
+    error, st = None, None
+    try:
+        st = self_join.join_stream_shared(eps, table.address, capacity=capacity, flags=flags,
+                                          pairs_host=pairs.address if pairs is not None else 0,
+                                          host_capacity=pairs.capacity if pairs is not None else 0)
+    except Exception as exc:  # noqa: BLE001 - the table is marked; every rank learns of it below
+        error = exc
+        table.fail()
+    if multi:
+        dist.barrier()  # every rank's chunks are in place
+    found, stored, failed = table.totals()
+    if failed or error is not None:
+        raise BandJoinError(f"the join failed on at least one of {world} ranks"
+                            + (f"; this rank ({rank}): {error}" if error is not None else "")) from error
+    return found, stored, st
 
 
 class BandJoinError(RuntimeError):

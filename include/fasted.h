@@ -230,6 +230,43 @@ int fasted_join_stream(fasted_ctx* ctx, double eps, int64_t q_begin, int64_t q_e
                        int32_t* pairs_host, float* dist2_host, uint64_t host_capacity, fasted_chunk_fn on_chunk,
                        void* user, fasted_join_stats* stats);
 
+/* The streamed join over the GPUs of one node, one process (or context) per GPU, all holding the same
+ * dataset: the ranks do not own fixed bands of query rows but TAKE chunks of whole raster bands from a
+ * common counter, each whenever its join stream has room for another launch.  A GPU that runs faster
+ * (every GPU sits under its own power cap) takes more chunks, so all ranks finish within one small chunk
+ * of each other; and because chunk k's place in the global list is the sum of the record counts of the
+ * chunks before it -- published by their ranks at about the time chunk k retires -- every rank copies
+ * its sorted chunks straight to their FINAL position in one host buffer that all ranks share, while
+ * the join is still running.  The result in that buffer is the reference's single row-major list
+ * (source/pair.cuh:39-45); the reference itself is single-GPU (source/findPairs.cuh:622).
+ *
+ * The table lives in memory that every rank maps (e.g. a shared file mapping) and is the only thing
+ * the ranks exchange during the join: no collective.  One rank sizes it with
+ * fasted_shared_chunks_bytes(max_chunks) -- q rows / 128 is always enough for max_chunks -- and fills
+ * it with fasted_shared_chunks_init (plan from that rank's context: identical on all ranks, which hold
+ * the same dataset and options) BEFORE the others are let in (a barrier); then every rank calls
+ * fasted_join_stream_shared with its own context and the SAME host buffer (pairs_host = the buffer's
+ * first record in this process's mapping; page-locked memory is written by DMA).  flags:
+ * FASTED_JOIN_KEEP_NORMS, FASTED_JOIN_NO_SORT (count only: no sort, no copy -- a timing or counting
+ * run with the same load balance).  A rank that fails marks the table; the others stop waiting and
+ * fail with FASTED_ESTATE.  After a barrier, fasted_shared_chunks_totals gives the job's totals.
+ * stats: this rank's share (its launches, its records).
+ * The lower-level calls (init_plan / take / publish / offset / fail) are the table's primitives, for
+ * schedulers of the caller's own and for tests; none of them touches a GPU. */
+size_t fasted_shared_chunks_bytes(uint64_t max_chunks);
+int fasted_shared_chunks_init(fasted_ctx* ctx, void* mem, size_t bytes, double eps, int64_t q_begin, int64_t q_end,
+                              int ranks, uint64_t* chunks_out);
+int fasted_join_stream_shared(fasted_ctx* ctx, double eps, uint64_t capacity, unsigned flags, void* shared_mem,
+                              int32_t* pairs_host, uint64_t host_capacity, fasted_join_stats* stats);
+int fasted_shared_chunks_totals(const void* mem, unsigned long long* found_total, unsigned long long* stored_total,
+                                unsigned long long* failed);
+int fasted_shared_chunks_init_plan(void* mem, size_t bytes, int64_t q_begin, int64_t q_end, int64_t chunk_rows,
+                                   uint64_t* chunks_out);
+int64_t fasted_shared_chunks_take(void* mem);                /* next chunk nobody has taken, -1 when none is left */
+int fasted_shared_chunks_publish(void* mem, uint64_t chunk, uint64_t stored, uint64_t found);
+int fasted_shared_chunks_offset(void* mem, uint64_t chunk, double timeout_ms, uint64_t* offset_out);
+void fasted_shared_chunks_fail(void* mem);
+
 /* One shard of the symmetric schedule for a self-join split over shard_world GPUs that all hold the
  * dataset: shard r computes the raster bands r, 2G-1-r, 2G+r, ... (G = shard_world) of the upper
  * triangle and emits both orientations of every hit, so the union of the shards' outputs is the

@@ -223,3 +223,72 @@ def test_a_failing_rank_is_reported_on_every_rank(tmp_path):
             assert "failed on 1 of 3 ranks" in msg
             assert ("this rank (1)" in msg) == (r == 1)
     assert "device-side wait ran out" in eval((tmp_path / "seen1.txt").read_text())[0]
+
+
+def _dealer(rank, world, port, out_dir):
+    # Ranks take chunks from the shared table, "join" them (a deterministic number of records per chunk,
+    # some of them none), publish the counts and write their records to the place the table gives.
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import time
+    from fasted_b200.dist import SharedChunkTable, SharedPairBuffer
+    n_rows, chunk_rows = 100_000, 256
+    table = SharedChunkTable.collective(n_rows)
+    pairs = SharedPairBuffer.collective(400_000)
+    if rank == 0:
+        assert table.init_plan(0, n_rows, chunk_rows) == -(-n_rows // chunk_rows)
+    dist.barrier()
+    count_of = lambda k: (k * 7919) % 11 if k % 5 else 0
+    taken = []
+    while True:
+        k = table.take()
+        if k < 0:
+            break
+        taken.append(k)
+        if rank == 1 and len(taken) % 7 == 0:
+            time.sleep(0.002)  # an uneven rank: the others simply take more chunks
+        table.publish(k, count_of(k), count_of(k) + 1)
+        off = table.offset(k)
+        pairs.array[off:off + count_of(k)] = np.stack([np.full(count_of(k), k), np.arange(count_of(k))], 1)
+    dist.barrier()
+    found, stored, failed = table.totals()
+    chunks = -(-n_rows // chunk_rows)
+    want = np.concatenate([np.stack([np.full(count_of(k), k), np.arange(count_of(k))], 1) for k in range(chunks)])
+    ok = (stored == len(want) and found == stored + chunks and failed == 0
+          and np.array_equal(pairs.array[:stored], want) and table.offset(chunks) == stored)
+    np.save(os.path.join(out_dir, f"dealt{rank}.npy"), np.array([int(ok), len(taken)]))
+    # a rank that gives up: nobody waits for the counts it never published
+    dist.barrier()
+    if rank == 0:
+        table.init_plan(0, n_rows, chunk_rows)
+    dist.barrier()
+    k = table.take()
+    dist.barrier()  # everybody holds a chunk before rank 1 gives up
+    seen = "none"
+    if rank == 1:
+        table.fail()
+    else:
+        table.publish(k, 1, 1)
+        try:
+            table.offset(chunks - 1, timeout_ms=20_000.0)
+        except Exception as exc:  # noqa: BLE001
+            seen = str(exc)
+    with open(os.path.join(out_dir, f"dealt_fail{rank}.txt"), "w") as f:
+        f.write(seen)
+    dist.barrier()
+    assert table.take() == -1  # a failed table hands out nothing
+    pairs.close()
+    table.close()
+    dist.destroy_process_group()
+
+
+def test_chunks_dealt_from_a_shared_table_land_in_order(native_lib, tmp_path):
+    world = 3
+    mp.spawn(_dealer, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    res = [np.load(tmp_path / f"dealt{r}.npy") for r in range(world)]
+    assert all(int(r[0]) == 1 for r in res)
+    assert sum(int(r[1]) for r in res) == -(-100_000 // 256) and min(int(r[1]) for r in res) > 0
+    for r in (0, 2):
+        assert "gave up" in (tmp_path / f"dealt_fail{r}.txt").read_text()

@@ -17,13 +17,13 @@ def _points(oracle_mod, n, d, seed):
 
 @pytest.mark.parametrize("n,d,eps,band_tiles,chunk_bands,qs,key32", [
     (4096, 128, 0.3136, 0, 0, -1, 1),   # everything automatic (one or two chunks at this size)
-    (5000, 200, 0.36, 2, 1, 0, 1),      # raster kernel, 20 chunks of 256 rows, 32-bit records
-    (5000, 200, 0.36, 2, 1, 0, 0),      # the same with 64-bit records
-    (3001, 64, 0.25, 1, 3, 0, 1),       # ragged last chunk, d a single K step
-    (9000, 1024, 1.1, 4, 2, -1, 1),
+    (5000, 200, 0.42, 2, 1, 0, 1),      # raster kernel, 20 chunks of 256 rows, 32-bit records
+    (5000, 200, 0.42, 2, 1, 0, 0),      # the same with 64-bit records
+    (3001, 64, 0.2, 1, 3, 0, 1),        # ragged last chunk, d a single K step
+    (9000, 1024, 1.04, 4, 2, -1, 1),
     (700, 333, 0.62, 1, 1, 0, 1),       # d not a multiple of 64
-    (12_000, 200, 0.36, 0, 1, 1, 1),    # query-stationary kernel: chunks of 37 tile rows
-    (12_000, 64, 0.25, 0, 1, 1, 0),
+    (12_000, 200, 0.41, 0, 1, 1, 1),    # query-stationary kernel: chunks of 37 tile rows
+    (12_000, 64, 0.2, 0, 1, 1, 0),
 ])
 def test_stream_equals_join_then_get_pairs(gpu_join, oracle_mod, n, d, eps, band_tiles, chunk_bands, qs, key32):
     import torch
@@ -107,7 +107,7 @@ def test_stream_overflow_clip_and_abort(gpu_join, oracle_mod):
     gpu_join.set_option("stream_chunk_bands", 1)
     gpu_join.set_option("query_stationary", 0)  # raster bands of 2 tile rows: chunks of 256 rows
     try:
-        full = gpu_join.join(0.3)
+        full = gpu_join.join(0.26)
         want = gpu_join.pairs()
         m = len(want)
         allk = oracle_mod.pair_keys(want)
@@ -115,7 +115,7 @@ def test_stream_overflow_clip_and_abort(gpu_join, oracle_mod):
         # is sorted chunk by chunk, free of duplicates, and part of the full result
         cap = m // 3
         out = np.full((m, 2), -1, dtype=np.int32)
-        st = gpu_join.join_stream(0.3, capacity=cap, pairs_host=out.ctypes.data, host_capacity=m)
+        st = gpu_join.join_stream(0.26, capacity=cap, pairs_host=out.ctypes.data, host_capacity=m)
         assert st.pairs_found == m and st.pairs_stored == cap
         k = oracle_mod.pair_keys(out[:cap])
         assert len(np.unique(k)) == cap and np.isin(k, allk).all() and (out[cap:] == -1).all()
@@ -125,24 +125,83 @@ def test_stream_overflow_clip_and_abort(gpu_join, oracle_mod):
         assert np.array_equal(out[:len(head)], head)
         # host buffer smaller than the result: the head of the list is copied, nothing beyond it
         small = np.full((1000 + 5, 2), -1, dtype=np.int32)
-        st = gpu_join.join_stream(0.3, pairs_host=small.ctypes.data, host_capacity=1000)
+        st = gpu_join.join_stream(0.26, pairs_host=small.ctypes.data, host_capacity=1000)
         assert st.pairs_stored == m and np.array_equal(small[:1000], want[:1000]) and (small[1000:] == -1).all()
         # a callback that asks to stop: the call fails after the GPU work has drained, the context stays usable
         calls = []
         with pytest.raises(FastedError):
-            gpu_join.join_stream(0.3, on_chunk=lambda p, d2, first: calls.append(first) or 1)
+            gpu_join.join_stream(0.26, on_chunk=lambda p, d2, first: calls.append(first) or 1)
         assert calls == [0]
         with pytest.raises(ZeroDivisionError):
-            gpu_join.join_stream(0.3, on_chunk=lambda p, d2, first: 1 // 0)
-        assert gpu_join.join(0.3).pairs_found == full.pairs_found
+            gpu_join.join_stream(0.26, on_chunk=lambda p, d2, first: 1 // 0)
+        assert gpu_join.join(0.26).pairs_found == full.pairs_found
         # flags that make no sense here are refused
         for bad in (2, 8, 16):
             with pytest.raises(FastedError):
-                gpu_join.join_stream(0.3, flags=bad)
+                gpu_join.join_stream(0.26, flags=bad)
         # empty query range
-        st = gpu_join.join_stream(0.3, q_begin=128, q_end=128, on_chunk=lambda *a: 1)
+        st = gpu_join.join_stream(0.26, q_begin=128, q_end=128, on_chunk=lambda *a: 1)
         assert st.pairs_found == 0
     finally:
         gpu_join.set_option("band_tiles", 0)
         gpu_join.set_option("stream_chunk_bands", 0)
         gpu_join.set_option("query_stationary", -1)
+
+
+@pytest.mark.parametrize("n,d,eps,ranks", [(20_000, 128, 0.33, 2), (9000, 1024, 1.04, 3), (30_000, 64, 0.18, 4)])
+def test_chunks_shared_by_several_contexts_give_the_single_list(gpu_join, oracle_mod, n, d, eps, ranks):
+    # The multi-GPU form of the streamed join, here with `ranks` contexts on the GPUs that are present
+    # (all on one GPU if there is only one: the kernels never wait for each other, only the host
+    # threads wait for published counts): every context takes chunks from the shared table and copies
+    # its sorted chunks to their final place in ONE host buffer, which must equal the one-GPU list.
+    import threading
+    import torch
+    from fasted_b200 import SelfJoin, JOIN_NO_SORT
+    from fasted_b200.dist import SharedChunkTable, SharedPairBuffer
+    pts = _points(oracle_mod, n, d, 3 * n + d)
+    gpu_join.set_points(pts)
+    st0 = gpu_join.join(eps)
+    want = gpu_join.pairs()
+    assert st0.pairs_found == st0.pairs_stored == len(want) > n
+    devs = torch.cuda.device_count()
+    ctxs = [SelfJoin(i % devs) for i in range(ranks)]
+    table = SharedChunkTable(-(-n // 128) + 1)
+    pairs = SharedPairBuffer(len(want) + 64, register_cuda=True)
+    try:
+        for c in ctxs:
+            c.set_points(pts)
+            c.set_option("band_tiles", 2)           # many chunks even at this size
+            c.set_option("query_stationary", 0)
+        for flags in (0, JOIN_NO_SORT):
+            pairs.array[:] = -1
+            chunks = table.init(ctxs[0], eps, 0, n, ranks)
+            assert chunks >= 4 * ranks
+            stats, errors = [None] * ranks, []
+
+            def work(i):
+                try:
+                    stats[i] = ctxs[i].join_stream_shared(eps, table.address, capacity=len(want) + 1000, flags=flags,
+                                                          pairs_host=pairs.address, host_capacity=pairs.capacity)
+                except Exception as exc:  # noqa: BLE001
+                    errors.append(exc)
+
+            threads = [threading.Thread(target=work, args=(i,)) for i in range(ranks)]
+            for t in threads:
+                t.start()
+            for t in threads:
+                t.join()
+            assert not errors, errors
+            found, stored, failed = table.totals()
+            assert (found, stored, failed) == (len(want), len(want), 0)
+            assert sum(s.chunks for s in stats) == chunks and sum(s.pairs_found for s in stats) == len(want)
+            if flags == 0:
+                assert np.array_equal(pairs.array[:len(want)], want) and (pairs.array[len(want):] == -1).all()
+            else:
+                assert (pairs.array == -1).all()  # a counting run copies nothing
+    finally:
+        for c in ctxs:
+            c.close()
+        pairs.close()
+        table.close()
+        pairs.unlink()
+        table.unlink()
