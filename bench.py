@@ -223,6 +223,9 @@ def main() -> None:
     ap.add_argument("--e2e-mode", default="stream", choices=["stream", "serial"],
                     help="N = 1: stream = fasted_join_stream (egress pipelined behind the join); serial = fasted_join, "
                          "then fasted_get_pairs (sort and copy after the join, as the reference orders them)")
+    ap.add_argument("--loader-pieces", type=int, default=4,
+                    help="N > 1, end-to-end leg: pieces in which a rank's band is uploaded and all-gathered (1 = upload, "
+                         "then one all-gather)")
     ap.add_argument("--no-balance", action="store_true", help="N > 1: keep equal bands (no sizing by measured rate)")
     ap.add_argument("--option", action="append", default=[], help="name=value for fasted_set_option (tuning runs)")
     args = ap.parse_args()
@@ -247,7 +250,7 @@ def main() -> None:
     import torch.distributed as dist
     from fasted_b200 import SelfJoin, JOIN_NO_SORT
     from fasted_b200.dist import (GpuBandEngine, SharedChunkTable, SharedPairBuffer, allgather_points, band_bounds,
-                                  dealt_self_join, sharded_self_join)
+                                  dealt_self_join, sharded_self_join, upload_and_allgather)
     from fasted_b200.dist import band_rows as rows_per_band
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -435,8 +438,11 @@ def main() -> None:
                     return st, m
                 st = sj.join_stream(eps, capacity=capacity, pairs_host=host_out.data_ptr(), host_capacity=out_cap)
                 return st, min(int(st.pairs_stored), out_cap)
-            dev_pts[pad_begin:pad_end].copy_(host_pts, non_blocking=True)
-            allgather_points(dev_pts, rank, world)
+            if args.loader_pieces > 1:
+                upload_and_allgather(dev_pts, host_pts, rank, world, pieces=args.loader_pieces)
+            else:
+                dev_pts[pad_begin:pad_end].copy_(host_pts, non_blocking=True)
+                allgather_points(dev_pts, rank, world)
             sj.set_points_device(dev_pts.data_ptr(), n, d, ld, keepalive=dev_pts)
             if dealt:
                 _, _, st = dealt_self_join(sj, n, eps, table, shared, capacity=capacity)

@@ -488,8 +488,8 @@ int fasted_set_option(fasted_ctx* c, const char* name, int64_t value) {
         c->band_tiles = static_cast<int>(value);
     } else if (!strcmp(name, "exact_norms")) {
         if (value != 0 && value != 1) return fail(FASTED_EINVAL, "exact_norms must be 0 or 1");
+        if (c->exact_norms != static_cast<int>(value)) c->norms_valid = false;
         c->exact_norms = static_cast<int>(value);
-        c->norms_valid = false;
     } else if (!strcmp(name, "cta_pair")) {
         if (value != 0 && value != 1) return fail(FASTED_EINVAL, "cta_pair must be 0 or 1");
         c->cta_pair = static_cast<int>(value);
@@ -1634,8 +1634,10 @@ int fasted_shared_chunks_init(fasted_ctx* c, void* mem, size_t bytes, double eps
     int rc = check_join_args(c, eps, q_begin, &q_end);
     if (rc) return rc;
     ChunkPlan cp;
-    // many small chunks: the last chunk a rank takes should be a small part (about 2 %) of its share
-    rc = plan_chunks(c, eps, q_begin, q_end, static_cast<uint64_t>(ranks) * 48, &cp);
+    // Many small chunks: the ranks finish within one chunk of each other, so a chunk should be a small
+    // part of a rank's share (1/256 where there are bands enough; never less than one raster band, whose
+    // sweep over all candidates is what keeps the DRAM traffic low).
+    rc = plan_chunks(c, eps, q_begin, q_end, static_cast<uint64_t>(ranks) * 256, &cp);
     if (rc) return rc;
     if (fasted_shared_chunks_bytes(cp.chunks) > bytes)
         return fail(FASTED_EINVAL, "the table needs %zu bytes for %llu chunks, %zu were given", fasted_shared_chunks_bytes(cp.chunks),

@@ -946,24 +946,36 @@ struct AStatSmemAux {
     unsigned long long acc_empty_bar[2];
     uint32_t tmem_base;
     int abort_flag;
-    alignas(16) float warp_cand[kEpiWarps][kEpiCols];
+    // Candidate norms of the tile, one row per half of its columns, double-buffered by tile parity.  The
+    // four epilogue warps of a column half all write the same values (harmless) after the tile's
+    // accumulator is ready: by then every warp has released the tile two back, the last reader of this buffer.
+    alignas(16) float cand[2][kEpiWarps / 4][kEpiCols];
 };
 
+// The shared-memory budget is what decides the depth of the candidate ring (six K steps of query tile plus
+// four 32 KB candidate stages are 224 of the 227 KB a block may have), so nothing is spent on alignment
+// slack: the dynamic shared memory of this kernel is declared 1024-byte aligned (the 128-byte swizzle's
+// requirement), and the kernel checks that before it touches anything.
 __host__ __device__ constexpr int astat_smem_bytes(int k_steps, int stages) {
-    return 1024 + k_steps * static_cast<int>(kStageBytesA) + stages * static_cast<int>(kStageBytesB) +
-           static_cast<int>(sizeof(AStatSmemAux)) + 64;
+    return k_steps * static_cast<int>(kStageBytesA) + stages * static_cast<int>(kStageBytesB) +
+           static_cast<int>(sizeof(AStatSmemAux)) + 16;
 }
+
+constexpr unsigned long long kErrSmemAlign = 16ull;  // status bit: dynamic shared memory was not 1024-byte aligned
 
 __global__ void __launch_bounds__(kJoinThreads, 1)
 join_astat_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                   const JoinParams p) {
-    extern __shared__ uint8_t smem_raw[];
-    const uint32_t raw_u32 = ptx::smem_u32(smem_raw);
-    const uint32_t a_u32 = (raw_u32 + 1023u) & ~1023u;                       // resident query tile: k_steps boxes
+    extern __shared__ __align__(1024) uint8_t smem_astat[];
+    const uint32_t a_u32 = ptx::smem_u32(smem_astat);                        // resident query tile: k_steps boxes
     const uint32_t b_u32 = a_u32 + static_cast<uint32_t>(p.k_steps) * kStageBytesA;  // candidate ring
     const int stages = p.astat_stages;
-    AStatSmemAux* aux = reinterpret_cast<AStatSmemAux*>(smem_raw + (b_u32 - raw_u32) +
+    AStatSmemAux* aux = reinterpret_cast<AStatSmemAux*>(smem_astat + static_cast<uint32_t>(p.k_steps) * kStageBytesA +
                                                         static_cast<uint32_t>(stages) * kStageBytesB);
+    if ((a_u32 & 1023u) != 0) {  // would corrupt every swizzled tile: report and leave (uniform over the CTA)
+        if (threadIdx.x == 0) atomicOr(p.counters + 2, kErrSmemAlign);
+        return;
+    }
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -1105,7 +1117,6 @@ join_astat_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         const int quarter = warp & 3;
         const int ewarp = warp - 2;
         const int col_off = (ewarp >> 2) * kEpiCols;
-        float* wcn = aux->warp_cand[ewarp];
         bool ok = true;
         long long it = 0;
         AStatIter ti;
@@ -1122,10 +1133,8 @@ join_astat_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             const uint32_t acc_phase = static_cast<uint32_t>((it >> 1) & 1);
             const int q0 = p.q_begin + ti.tm * kTileM + quarter * 32;
             const int c0 = ti.tn * kTileN + col_off;
-            __syncwarp();
-            reinterpret_cast<float4*>(wcn)[lane] = next_cand;
+            const float4 cand_now = next_cand;
             const float sq_lane = next_query;
-            __syncwarp();
             ti.advance(p);
             if (ti.valid)
                 fetch_warp_norms(p, ti.tn * kTileN + col_off, p.q_begin + ti.tm * kTileM + quarter * 32, lane,
@@ -1134,6 +1143,9 @@ join_astat_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                                                 kWaitLimitNs);
             if (!ok) continue;
             ptx::tc_fence_after_sync();
+            float* wcn = aux->cand[buf][ewarp >> 2];
+            reinterpret_cast<float4*>(wcn)[lane] = cand_now;
+            __syncwarp();
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                                    static_cast<uint32_t>(buf * kTileN + col_off);
             epilogue_tile(p, taddr, wcn, sq_lane, q0, c0, lane, pend, [&] {

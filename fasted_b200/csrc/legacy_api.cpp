@@ -242,6 +242,12 @@ Results join_resident(double epsilon, bool save_pairs, const std::string& datase
               << std::endl;
     fasted_join_stats st{};
     std::vector<fasted_ctx*> gpus = all_contexts();
+    // FASTED_EXACT_NORMS=1: correctly rounded row norms instead of the reference's round-toward-zero chain
+    // (not the reference's numerics; closer to an FP64 join on this GPU, see fasted_set_option).
+    const char* exact_env = std::getenv("FASTED_EXACT_NORMS");
+    const bool exact_norms = exact_env && std::strcmp(exact_env, "1") == 0;
+    for (fasted_ctx* g : gpus) check(fasted_set_option(g, "exact_norms", exact_norms ? 1 : 0));
+    if (exact_norms) std::cout << "Row norms: correctly rounded (FASTED_EXACT_NORMS=1)" << std::endl;
     std::vector<fasted_join_stats> per_gpu(gpus.size());
     const std::string pairs_path = output_path + ".pairs";
     double sort_start = now_s();

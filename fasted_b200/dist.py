@@ -337,6 +337,48 @@ def allgather_points(points, rank: int, world: int):
     return points
 
 
+def upload_and_allgather(points, host_band, rank: int, world: int, pieces: int = 4):
+    """Loader for ranks that each hold their own band of the matrix in (pinned) HOST memory: the band is
+    uploaded piece by piece on a side stream, and each piece is all-gathered (NCCL over NVLink) as soon
+    as it has landed, so the host link and NVLink work at the same time instead of one after the
+    other.  `points`: world * band_rows rows on the device, `host_band`: this rank's band_rows rows.
+    Equivalent to copying the band into place and calling allgather_points."""
+    import torch
+    import torch.distributed as dist
+    if points.shape[0] % world:
+        raise ValueError("points must hold world * band_rows rows")
+    per = points.shape[0] // world
+    if host_band.shape[0] != per:
+        raise ValueError("host_band must hold band_rows rows")
+    mine = points[rank * per:(rank + 1) * per]
+    if not (dist.is_available() and dist.is_initialized()) or world == 1:
+        mine.copy_(host_band, non_blocking=True)
+        return points
+    pieces = max(1, min(pieces, per // BAND_ALIGN if per >= BAND_ALIGN else 1))
+    cuts = [per * i // pieces // BAND_ALIGN * BAND_ALIGN for i in range(pieces)] + [per]
+    on_gpu = points.is_cuda
+    side = torch.cuda.Stream(device=points.device) if on_gpu else None
+    events = []
+    for a, b in zip(cuts, cuts[1:]):
+        if on_gpu:
+            with torch.cuda.stream(side):
+                mine[a:b].copy_(host_band[a:b], non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(side)
+            events.append(ev)
+        else:
+            mine[a:b].copy_(host_band[a:b])
+    for i, (a, b) in enumerate(zip(cuts, cuts[1:])):
+        if b <= a:
+            continue
+        if on_gpu:
+            torch.cuda.current_stream(points.device).wait_event(events[i])
+        outs = [points[r * per + a:r * per + b].view(torch.uint8).reshape(-1) for r in range(world)]
+        src = mine[a:b].view(torch.uint8).reshape(-1)
+        dist.all_gather(outs, src.clone() if not on_gpu else src)
+    return points
+
+
 def _exchange_counts(dist, torch, values: list[int]) -> list[list[int]]:
     """All-gather of a few integers per rank (the only collective after the join)."""
     world = dist.get_world_size()

@@ -82,13 +82,16 @@ void releaseResources(void);
  *                       hard-wired at source/main.cu:214-215)
  *   FASTED_DEVICE       CUDA device ordinal (default 0, source/findPairs.cuh:622)
  *   FASTED_NUM_GPUS     number of GPUs this one process drives (default 1; "all" = every visible
- *                       device): the dataset is uploaded once and replicated device to device, GPU g
- *                       joins the g-th band of query rows against all candidates, the sorted band
- *                       lists are concatenated on the host in band order
+ *                       device): the dataset is uploaded once and replicated by one NCCL broadcast
+ *                       (peer copies where NCCL is absent), GPU g joins the g-th band of query rows
+ *                       against all candidates, the sorted band lists are concatenated on the host
+ *                       in band order
  *   FASTED_WRITE_DIST   "1": third text column sqrt(d2) in the .pairs file
- *   FASTED_SYMMETRIC    "0": compute all N x N entries like the reference; default: each unordered
- *                       pair is computed once and both orientations are emitted (identical output,
- *                       about twice the reported TFLOPS)
+ *   FASTED_SYMMETRIC    "1": each unordered pair is computed once and both orientations are emitted
+ *                       (identical output in about half the time; "Estimated TFLOPS" still divides
+ *                       2*N*N*D by the time, and a "Schedule:" line on stdout says which one ran).
+ *                       Default: all N x N entries are computed, like the reference.
+ *   FASTED_EXACT_NORMS  "1": correctly rounded row norms (option "exact_norms" of the context API)
  */
 
 /* ------------------------------------------------------------------------

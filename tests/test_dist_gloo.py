@@ -120,8 +120,14 @@ def _worker(rank, world, port, n, d, eps, out_dir):
     a, b = band_bounds(n, world, rank)
     full[a:b] = t[a:b]
     allgather_points(full, rank, world)
+    # the pipelined loader (upload piece by piece, gather each piece as it lands) gives the same matrix
+    from fasted_b200.dist import upload_and_allgather
+    full2 = torch.zeros((world * per, d), dtype=torch.int16)
+    band = torch.zeros((per, d), dtype=torch.int16)
+    band[:b - a] = t[a:b]
+    upload_and_allgather(full2, band, rank, world, pieces=3)
     np.save(os.path.join(out_dir, f"gathered_ok{rank}.npy"),
-            np.array([torch.equal(full[:n], t), bool((full[n:] == 0).all())]))
+            np.array([torch.equal(full[:n], t), bool((full[n:] == 0).all()), torch.equal(full2, full)]))
     pairs, found, stored = sharded_self_join(OracleEngine(pts), n, eps)
     # the same with bands sized by (made-up) measured rates and a shared buffer that the caller owns
     from fasted_b200.dist import SharedPairBuffer, weighted_band_bounds

@@ -148,7 +148,7 @@ def test_stream_overflow_clip_and_abort(gpu_join, oracle_mod):
         gpu_join.set_option("query_stationary", -1)
 
 
-@pytest.mark.parametrize("n,d,eps,ranks", [(20_000, 128, 0.33, 2), (9000, 1024, 1.04, 3), (30_000, 64, 0.18, 4)])
+@pytest.mark.parametrize("n,d,eps,ranks", [(20_000, 128, 0.30, 2), (9000, 1024, 1.04, 3), (30_000, 64, 0.18, 4)])
 def test_chunks_shared_by_several_contexts_give_the_single_list(gpu_join, oracle_mod, n, d, eps, ranks):
     # The multi-GPU form of the streamed join, here with `ranks` contexts on the GPUs that are present
     # (all on one GPU if there is only one: the kernels never wait for each other, only the host
