@@ -4,6 +4,8 @@
 #include <atomic>
 #include <cerrno>
 #include <cstdlib>
+#include <charconv>
+#include <cstdio>
 #include <cstring>
 #include <fstream>
 #include <ios>
@@ -176,7 +178,7 @@ namespace {
 
 // Converts one token like std::stod: leading white space skipped, trailing
 // characters ignored, no digits -> invalid_argument, overflow -> out_of_range.
-double parse_token(const char* begin, const char* end) {
+double parse_token_strtod(const char* begin, const char* end) {
     char buf[64];
     const size_t len = static_cast<size_t>(end - begin);
     std::string big;
@@ -197,6 +199,31 @@ double parse_token(const char* begin, const char* end) {
     return v;
 }
 
+// The same result, several times faster for ordinary decimal tokens: std::from_chars (correctly
+// rounded, like strtod).  Everything it treats differently from strtod -- a leading '+', hexadecimal
+// floats, values that overflow or underflow (where strtod reports ERANGE), empty tokens -- goes to the
+// strtod path above, so the outcome, errors included, is always std::stod's.
+double parse_token(const char* begin, const char* end) {
+    const char* p = begin;
+    while (p < end && (*p == ' ' || (*p >= '\t' && *p <= '\r'))) ++p;
+    if (p < end && *p != '+') {
+        double v = 0.0;
+        const std::from_chars_result r = std::from_chars(p, end, v, std::chars_format::general);
+        const bool hex_prefix = r.ptr < end && (*r.ptr == 'x' || *r.ptr == 'X');
+        if (r.ec == std::errc() && r.ptr != p && !hex_prefix) {
+            const double a = v < 0 ? -v : v;
+            if (a >= 2.2250738585072014e-308 || a == 0.0) {
+                if (a != 0.0) return v;
+                // a true zero, or an underflow that strtod would report: look for a non-zero digit
+                bool nonzero = false;
+                for (const char* q = p; q < r.ptr && *q != 'e' && *q != 'E'; ++q) nonzero |= (*q >= '1' && *q <= '9');
+                if (!nonzero) return v;
+            }
+        }
+    }
+    return parse_token_strtod(begin, end);
+}
+
 // Number of ','-separated tokens std::getline would deliver for this line.
 int64_t count_tokens(const char* b, const char* e) {
     if (b == e) return 0;
@@ -211,9 +238,24 @@ int64_t count_tokens(const char* b, const char* e) {
 
 HostDataset read_csv_dataset(const std::string& path) {
     if (path.empty()) throw std::invalid_argument("filepath must be set.");
-    std::ifstream f(path, std::ios::binary);
-    if (!f.is_open()) throw std::ios_base::failure("Failed to open file: " + path);
-    std::string text((std::istreambuf_iterator<char>(f)), std::istreambuf_iterator<char>());
+    std::string text;
+    {
+        FILE* f = std::fopen(path.c_str(), "rb");
+        if (!f) throw std::ios_base::failure("Failed to open file: " + path);
+        std::fseek(f, 0, SEEK_END);
+        const long size = std::ftell(f);
+        std::fseek(f, 0, SEEK_SET);
+        if (size > 0) {
+            text.resize(static_cast<size_t>(size));
+            const size_t got = std::fread(&text[0], 1, text.size(), f);
+            text.resize(got);
+        } else {  // not seekable: read what comes
+            char buf[1 << 16];
+            size_t got;
+            while ((got = std::fread(buf, 1, sizeof(buf), f)) > 0) text.append(buf, got);
+        }
+        std::fclose(f);
+    }
 
     // Line table (a final line without '\n' counts; an empty tail after the last '\n' does not).
     std::vector<std::pair<size_t, size_t>> lines;

@@ -120,6 +120,7 @@ struct fasted_ctx {
     size_t chunk_end_cap = 0;
     int stream_chunk_bands = 0;                    // option: raster bands per chunk (0 = automatic)
     int query_stationary = -1;                     // option: -1 automatic, 0 never, 1 whenever the rows are short enough
+    int use_pdl = 1;                               // option: let the join start while the norm kernel still runs
 
     // pinned staging for transfers from / to pageable host memory
     void* stage_buf[2] = {nullptr, nullptr};
@@ -493,6 +494,9 @@ int fasted_set_option(fasted_ctx* c, const char* name, int64_t value) {
     } else if (!strcmp(name, "cta_pair")) {
         if (value != 0 && value != 1) return fail(FASTED_EINVAL, "cta_pair must be 0 or 1");
         c->cta_pair = static_cast<int>(value);
+    } else if (!strcmp(name, "dependent_launch")) {
+        if (value != 0 && value != 1) return fail(FASTED_EINVAL, "dependent_launch must be 0 or 1");
+        c->use_pdl = static_cast<int>(value);
     } else if (!strcmp(name, "query_stationary")) {
         if (value < -1 || value > 1) return fail(FASTED_EINVAL, "query_stationary must be -1, 0 or 1");
         c->query_stationary = static_cast<int>(value);
@@ -920,8 +924,27 @@ static int plan_join(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end, 
     return FASTED_OK;
 }
 
-static int launch_join(fasted_ctx* c, const JoinPlan& pl) {
+// after_norms: the launch directly follows the row-norm kernel in the stream; it is then allowed to start
+// while that kernel is still running (programmatic dependent launch), its epilogue waits for the norms.
+static int launch_join(fasted_ctx* c, const JoinPlan& pl, bool after_norms = false) {
     if (pl.p.total_tiles <= 0) return FASTED_OK;
+    if (!pl.pair && after_norms && c->use_pdl) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(pl.grid);
+        cfg.blockDim = dim3(fasted::kJoinThreads);
+        cfg.dynamicSmemBytes = pl.astat ? pl.smem_bytes : fasted::kJoinSmemBytes;
+        cfg.stream = c->stream;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr.val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        if (pl.astat)
+            CU_TRY(cudaLaunchKernelEx(&cfg, fasted::join_astat_kernel, c->map_a, c->map_b, pl.p));
+        else
+            CU_TRY(cudaLaunchKernelEx(&cfg, fasted::join_kernel, c->map_a, c->map_b, pl.p));
+        return FASTED_OK;
+    }
     if (pl.pair) {
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(pl.grid);
@@ -1021,12 +1044,20 @@ static int join_impl(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end, 
 
     CU_TRY(cudaMemsetAsync(c->counters, 0, 8 * sizeof(unsigned long long), c->stream));
     CU_TRY(cudaEventRecord(c->ev[0], c->stream));
-    if (!(flags & FASTED_JOIN_KEEP_NORMS) || !c->norms_valid) {
+    // Small joins (a few tiles per CTA) are launch-bound: the join is then launched as a programmatic
+    // dependent of the norm kernel, with nothing between the two in the stream, so that its prologue and
+    // first tiles overlap the norm kernel.  The two kernels' times can then not be told apart: norms_ms is
+    // reported as 0 and join_ms covers both.
+    const bool need_norms = !(flags & FASTED_JOIN_KEEP_NORMS) || !c->norms_valid;
+    const bool overlap = need_norms && c->use_pdl && !pl.pair && pl.p.total_tiles > 0 &&
+                         pl.p.total_tiles <= 8LL * pl.grid;
+    if (overlap) CU_TRY(cudaEventRecord(c->ev[1], c->stream));
+    if (need_norms) {
         rc = launch_norms(c);
         if (rc) return rc;
     }
-    CU_TRY(cudaEventRecord(c->ev[1], c->stream));
-    rc = launch_join(c, pl);
+    if (!overlap) CU_TRY(cudaEventRecord(c->ev[1], c->stream));
+    rc = launch_join(c, pl, overlap);
     if (rc) return rc;
     CU_TRY(cudaEventRecord(c->ev[2], c->stream));
     unsigned long long h[5] = {0, 0, 0, 0, 0};

@@ -243,6 +243,9 @@ row_norms_kernel(const __grid_constant__ CUtensorMap map, float* __restrict__ no
         ptx::prefetch_tensormap(&map);
     }
     __syncthreads();
+    // The join that follows may be scheduled now: its prologue and its first tiles' loads and MMAs need
+    // nothing of this kernel's; its epilogue waits for the norms (grid_dependency_wait).
+    ptx::launch_dependents();
 
     const int steps_per_block = (k_boxes + kNormBoxesPerStage - 1) / kNormBoxesPerStage;
     // Work items of this CTA: (row block, k step) pairs in order.
@@ -656,16 +659,18 @@ __device__ __forceinline__ void fetch_warp_norms(const JoinParams& p, int c_firs
     static_assert(kEpiCols == 128, "four candidate norms per lane");
     const float inf = __int_as_float(0x7f800000);
     const int c = c_first + 4 * lane;
+    // (plain loads, not the read-only path: when the join overlaps the norm kernel -- dependent launch --
+    // the norms are written during this kernel's lifetime, before grid_dependency_wait() returns)
     if (c + 3 < p.n && p.norms_vec4) {
-        cand = __ldg(reinterpret_cast<const float4*>(p.norms + c));
+        cand = *reinterpret_cast<const float4*>(p.norms + c);
     } else {
-        cand.x = (c + 0 < p.n) ? __ldg(p.norms + c + 0) : inf;
-        cand.y = (c + 1 < p.n) ? __ldg(p.norms + c + 1) : inf;
-        cand.z = (c + 2 < p.n) ? __ldg(p.norms + c + 2) : inf;
-        cand.w = (c + 3 < p.n) ? __ldg(p.norms + c + 3) : inf;
+        cand.x = (c + 0 < p.n) ? p.norms[c + 0] : inf;
+        cand.y = (c + 1 < p.n) ? p.norms[c + 1] : inf;
+        cand.z = (c + 2 < p.n) ? p.norms[c + 2] : inf;
+        cand.w = (c + 3 < p.n) ? p.norms[c + 3] : inf;
     }
     const int q = q_first + lane;
-    query = (q < p.q_end) ? __ldg(p.norms + q) : inf;
+    query = (q < p.q_end) ? p.norms[q] : inf;
 }
 
 struct JoinSmemAux {
@@ -820,6 +825,7 @@ join_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         float next_query;
         EpiHits pend;
         pend.any = false;
+        ptx::grid_dependency_wait();  // the row norms come from the kernel before this one
         if (ti.valid)
             fetch_warp_norms(p, ti.tn * kTileN + col_off, p.q_begin + ti.tm * kTileM + quarter * 32, lane, next_cand,
                              next_query);
@@ -1125,6 +1131,7 @@ join_astat_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         float next_query;
         EpiHits pend;
         pend.any = false;
+        ptx::grid_dependency_wait();  // the row norms come from the kernel before this one
         if (ti.valid)
             fetch_warp_norms(p, ti.tn * kTileN + col_off, p.q_begin + ti.tm * kTileM + quarter * 32, lane, next_cand,
                              next_query);
@@ -1344,6 +1351,7 @@ join_pair_kernel(const __grid_constant__ CUtensorMap map, const JoinParams p) {
         float next_query;
         EpiHits pend;
         pend.any = false;
+        ptx::grid_dependency_wait();  // the row norms come from the kernel before this one
         if (ti.valid)
             fetch_warp_norms(p, ti.tn * kTileN + col_off, p.q_begin + ti.tm * kPairTileM + row_off, lane, next_cand,
                              next_query);

@@ -163,6 +163,15 @@ __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
+// ---- programmatic dependent launch -----------------------------------------
+//
+// A kernel launched with the programmatic-stream-serialization attribute may start while the kernel
+// before it in the stream is still running: it must call grid_dependency_wait() before it touches
+// anything that kernel writes.  The earlier kernel says with launch_dependents() that the next one may
+// be scheduled.  Both are no-ops in a launch without the attribute.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---- tcgen05 ---------------------------------------------------------------
 
 __device__ __forceinline__ void tc_fence_before_sync() {

@@ -124,7 +124,7 @@ enum {
 typedef struct fasted_join_stats {
     unsigned long long pairs_found;
     unsigned long long pairs_stored;
-    double norms_ms;   /* row-norm kernel, device time */
+    double norms_ms;   /* row-norm kernel, device time (0 where a small join overlapped it: join_ms then covers both) */
     double join_ms;    /* join kernel, device time */
     double kernel_ms;  /* start of norms to end of join (the reference's TFLOPS interval) */
     double sort_ms;    /* sort + unpack, device time */
@@ -392,7 +392,9 @@ int fasted_selftest_wait_timeout(fasted_ctx* ctx, double limit_ms, unsigned long
  * FP64 join on this hardware, whose tensor-core accumulate does not truncate; default 0),
  * "query_stationary" (-1 = automatic: for rows of at most 384 values a CTA keeps its 128 query rows in
  * shared memory and streams candidate rows only; 0 = never, 1 = whenever d <= 512; same results bit for
- * bit), "stream_chunk_bands" (raster bands per chunk of fasted_join_stream, 0 = automatic). */
+ * bit), "stream_chunk_bands" (raster bands per chunk of fasted_join_stream, 0 = automatic), "stream_key32" (1 = default:
+ * 32-bit chunk-relative records in fasted_join_stream where they fit), "dependent_launch" (1 = default: a small join is
+ * launched as a programmatic dependent of the row-norm kernel and overlaps it). */
 int fasted_set_option(fasted_ctx* ctx, const char* name, int64_t value);
 
 #ifdef __cplusplus
