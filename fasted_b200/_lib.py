@@ -381,6 +381,12 @@ class SelfJoin:
                                         d2.ctypes.data_as(_vp) if with_dist2 else None))
         return (pairs, d2) if with_dist2 else pairs
 
+    def pairs_device(self) -> tuple[int, int]:
+        """Device addresses of the last join's results: (int2 (query, candidate) records, float distances or 0)."""
+        p, d2 = _vp(), _vp()
+        _check(self._L.fasted_pairs_device(self._h, ctypes.byref(p), ctypes.byref(d2)))
+        return int(p.value or 0), int(d2.value or 0)
+
     def pairs_into(self, host_ptr: int, count: int) -> None:
         _check(self._L.fasted_get_pairs(self._h, 0, count, _vp(host_ptr), None))
 

@@ -5,6 +5,11 @@
 #include <stdexcept>
 
 #include "dataset.hpp"
+
+#include <sys/stat.h>
+
+#include <mutex>
+#include <string>
 #include "error.hpp"
 #include "fasted.h"
 
@@ -45,12 +50,37 @@ int fasted_dataset_exponential_f16(int64_t n, int64_t d, double lambda, double m
     });
 }
 
+// A caller asks for the shape, allocates, then asks for the values: the file parsed for the first call
+// is kept for the second (one entry, dropped when it has been handed out or when another file is asked for).
+namespace {
+struct ParsedCsv {
+    std::string path;
+    long long size = -1, mtime_ns = -1;
+    fasted::HostDataset ds;
+    bool valid = false;
+};
+ParsedCsv g_parsed;
+std::mutex g_parsed_mutex;
+
+bool file_stamp(const char* path, long long* size, long long* mtime_ns) {
+    struct stat st;
+    if (::stat(path, &st) != 0) return false;
+    *size = static_cast<long long>(st.st_size);
+    *mtime_ns = static_cast<long long>(st.st_mtim.tv_sec) * 1000000000LL + st.st_mtim.tv_nsec;
+    return true;
+}
+}  // namespace
+
 int fasted_dataset_csv_shape(const char* path, int64_t* n, int64_t* d) {
     if (!path || !n || !d) return fasted::fail(FASTED_EINVAL, "null argument");
     return guarded([&] {
-        const fasted::HostDataset ds = fasted::read_csv_dataset(path);
+        fasted::HostDataset ds = fasted::read_csv_dataset(path);
         *n = ds.n;
         *d = ds.d;
+        std::lock_guard<std::mutex> lock(g_parsed_mutex);
+        g_parsed.valid = file_stamp(path, &g_parsed.size, &g_parsed.mtime_ns);
+        g_parsed.path = path;
+        g_parsed.ds = std::move(ds);
         return (int)FASTED_OK;
     });
 }
@@ -58,6 +88,17 @@ int fasted_dataset_csv_shape(const char* path, int64_t* n, int64_t* d) {
 int fasted_dataset_csv_f16(const char* path, uint16_t* out, int64_t n, int64_t d, int64_t ld_out) {
     if (!path || !out || ld_out < d) return fasted::fail(FASTED_EINVAL, "bad argument");
     return guarded([&] {
+        {
+            std::lock_guard<std::mutex> lock(g_parsed_mutex);
+            long long size = -1, mtime_ns = -1;
+            if (g_parsed.valid && g_parsed.path == path && file_stamp(path, &size, &mtime_ns) && size == g_parsed.size &&
+                mtime_ns == g_parsed.mtime_ns) {
+                const fasted::HostDataset ds = std::move(g_parsed.ds);
+                g_parsed = ParsedCsv{};
+                return copy_out(ds, out, n, d, ld_out);
+            }
+            g_parsed = ParsedCsv{};
+        }
         const fasted::HostDataset ds = fasted::read_csv_dataset(path);
         return copy_out(ds, out, n, d, ld_out);
     });

@@ -415,6 +415,22 @@ int fasted_create(int device, fasted_ctx** out) {
     cudaFuncSetAttribute(fasted::join_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          fasted::kPairSmemBytes);
     cudaFuncSetAttribute(fasted::join_astat_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynamicSmem);
+    // All kernels of a join ask for the same split of the SM's L1 / shared memory (all of it shared): a
+    // kernel that needs another split than its predecessor makes every SM drain and reconfigure first,
+    // which a 30-microsecond join cannot afford between its norm kernel, its join kernel and the next call.
+    cudaFuncSetAttribute(fasted::join_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    cudaFuncSetAttribute(fasted::join_astat_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                         cudaSharedmemCarveoutMaxShared);
+    cudaFuncSetAttribute(fasted::join_pair_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                         cudaSharedmemCarveoutMaxShared);
+    cudaFuncSetAttribute(fasted::row_norms_kernel<0>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                         cudaSharedmemCarveoutMaxShared);
+    cudaFuncSetAttribute(fasted::row_norms_kernel<1>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                         cudaSharedmemCarveoutMaxShared);
+    cudaFuncSetAttribute(fasted::unpack_pairs_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                         cudaSharedmemCarveoutMaxShared);
+    cudaFuncSetAttribute(fasted::unpack_pairs32_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                         cudaSharedmemCarveoutMaxShared);
     {
         // How many 2-CTA clusters of the pair kernel the device can hold at once.
         cudaLaunchConfig_t cfg = {};

@@ -295,6 +295,22 @@ class GpuBandEngine:
         self.last_stats = st
         return self.sj.pairs(), int(st.pairs_found)
 
+    def join_symmetric_shard_device(self, eps: float, rank: int, world: int):
+        """The same, with the shard's sorted records left on the device: returns (an (m, 2) int32 CUDA tensor
+        that aliases the library's result buffer -- valid until the next join --, pairs found)."""
+        import torch
+        st = self.sj.join_symmetric_shard(eps, rank, world, flags=self.flags)
+        self.last_stats = st
+        m = int(st.pairs_stored)
+        ptr = self.sj.pairs_device()[0]
+
+        class _View:  # the CUDA array interface lets torch wrap foreign device memory without a copy
+            __cuda_array_interface__ = {"shape": (m, 2), "typestr": "<i4", "data": (ptr, False), "version": 2}
+
+        dev = torch.device("cuda", self.sj.device)
+        t = torch.as_tensor(_View(), device=dev) if m else torch.empty((0, 2), dtype=torch.int32, device=dev)
+        return t, int(st.pairs_found)
+
 
 def broadcast_points(points, src: int = 0):
     """The one collective of the path: replicate the FP16 matrix (a torch tensor, in place)."""
@@ -472,11 +488,15 @@ def sharded_self_join_symmetric(engine: BandEngine, n: int, eps: float, gather: 
         return pairs, found, len(pairs)
     world, rank = dist.get_world_size(), dist.get_rank()
     error = None
-    try:
-        pairs, found = engine.join_symmetric_shard(eps, rank, world)
-    except Exception as exc:  # noqa: BLE001 - reported to all ranks before the exchange
-        error, pairs, found = exc, np.empty((0, 2), dtype=np.int32), 0
     backend = dist.get_backend()
+    on_device = backend == "nccl" and hasattr(engine, "join_symmetric_shard_device")
+    try:
+        if on_device:
+            pairs, found = engine.join_symmetric_shard_device(eps, rank, world)
+        else:
+            pairs, found = engine.join_symmetric_shard(eps, rank, world)
+    except Exception as exc:  # noqa: BLE001 - reported to all ranks before the exchange
+        error, pairs, found, on_device = exc, np.empty((0, 2), dtype=np.int32), 0, False
     dev = torch.device("cuda", torch.cuda.current_device()) if backend == "nccl" else torch.device("cpu")
     t = torch.tensor([found, 1 if error is not None else 0], dtype=torch.int64, device=dev)
     dist.all_reduce(t)
@@ -487,13 +507,20 @@ def sharded_self_join_symmetric(engine: BandEngine, n: int, eps: float, gather: 
 
     # records are sorted by (query, candidate): the destination ranges are contiguous slices
     bounds = [band_bounds(n, world, r) for r in range(world)]
-    cuts = np.searchsorted(pairs[:, 0], [b for b, _ in bounds] + [n], side="left")
+    starts = [b for b, _ in bounds] + [n]
+    if on_device:
+        # everything stays on the GPU: cuts, the all-to-all over NVLink, and the merge of what arrives
+        q = pairs[:, 0].contiguous()
+        cuts = torch.searchsorted(q, torch.tensor(starts, dtype=torch.int32, device=q.device)).tolist()
+        send = pairs.reshape(-1)
+    else:
+        cuts = np.searchsorted(pairs[:, 0], starts, side="left")
+        send = torch.from_numpy(np.ascontiguousarray(pairs).reshape(-1)).to(dev)
     send_counts = [int(cuts[r + 1] - cuts[r]) for r in range(world)]
     sc = torch.tensor(send_counts, dtype=torch.int64, device=dev)
     rc = torch.empty(world, dtype=torch.int64, device=dev)
     dist.all_to_all_single(rc, sc)
     recv_counts = [int(x) for x in rc.tolist()]
-    send = torch.from_numpy(np.ascontiguousarray(pairs).reshape(-1)).to(dev)
     recv = torch.empty(2 * sum(recv_counts), dtype=torch.int32, device=dev)
     dist.all_to_all_single(recv, send, output_split_sizes=[2 * c for c in recv_counts],
                            input_split_sizes=[2 * c for c in send_counts])

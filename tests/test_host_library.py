@@ -125,3 +125,29 @@ def test_host_generator_parallel_path_is_the_same_stream(native_lib, oracle_mod)
     from fasted_b200 import _lib
     for n, d, lam, mx in [(1100, 1000, 40.0, 10.0), (3001, 999, 40.0, 10.0), (1500, 800, 1.0, 0.5)]:
         assert np.array_equal(_lib.dataset_exponential(n, d, lam, mx), oracle_mod.gen_exponential(n, d, lam, mx))
+
+
+def test_csv_tokens_are_read_like_the_reference_reads_them(native_lib, oracle_mod, tmp_path):
+    # The loader's fast number parser must agree with the std::stod the reference's loader uses
+    # (source/DataLoader/FilePointGenerator.hpp of the reference), oddities and failures included;
+    # the oracle's reader is the sequential restatement of that loader.
+    from fasted_b200 import _lib
+    p = tmp_path / "odd.csv"
+    p.write_text("1e-30, +2.5,0x1p3, inf\n-0.0,1e-5 ,  3.25abc,-INF\n 4e+2,1E1,0.000000,.5\n\t7.,-.25e1,0e99,65504.9\n")
+    got = _lib.dataset_csv(str(p))
+    want, d = oracle_mod.read_csv(str(p))
+    assert got.shape == (4, 4) and np.array_equal(got, want[:, :d])
+    assert got.view(np.float16)[0].tolist() == [0.0, 2.5, 8.0, float("inf")]
+    for bad in ["1,2\n3,1e-320\n", "1,2\n3,\n", "1,2\n3,abc\n", "1,2\n3,1e999\n", "1,2\n3\n"]:
+        p.write_text(bad)
+        with pytest.raises(_lib.FastedError):
+            _lib.dataset_csv(str(p))
+        with pytest.raises(RuntimeError):
+            oracle_mod.read_csv(str(p))
+    # a large file: same values as the sequential reader (the parallel parse splits it by lines)
+    rng = np.random.default_rng(5)
+    x = rng.exponential(1 / 40.0, size=(3000, 50))
+    p.write_text("\n".join(",".join(f"{v:.7g}" for v in row) for row in x) + "\n")
+    got = _lib.dataset_csv(str(p))
+    want, d = oracle_mod.read_csv(str(p))
+    assert np.array_equal(got, want[:, :d])
