@@ -43,6 +43,8 @@ class JoinStats(ctypes.Structure):
         ("grid", ctypes.c_int),
         ("cta0_cycles", ctypes.c_ulonglong),
         ("cta0_tiles", ctypes.c_ulonglong),
+        ("cta0_setup_cycles", ctypes.c_ulonglong),
+        ("cta0_release_cycles", ctypes.c_ulonglong),
         ("chunks", ctypes.c_int),
         ("tail_ms", ctypes.c_double),
     ]

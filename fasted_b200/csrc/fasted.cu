@@ -1018,6 +1018,8 @@ static void fill_stats(fasted_ctx* c, const JoinPlan& pl, const unsigned long lo
     stats->tiles_n = pl.p.tiles_n;
     stats->grid = pl.grid;
     stats->cta0_cycles = pl.pair ? 0 : h[4];
+    stats->cta0_setup_cycles = pl.pair ? 0 : h[5];
+    stats->cta0_release_cycles = pl.pair ? 0 : h[6];
     stats->cta0_tiles = 0;
     stats->chunks = 1;
     stats->tail_ms = 0;
@@ -1076,7 +1078,7 @@ static int join_impl(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end, 
     rc = launch_join(c, pl, overlap);
     if (rc) return rc;
     CU_TRY(cudaEventRecord(c->ev[2], c->stream));
-    unsigned long long h[5] = {0, 0, 0, 0, 0};
+    unsigned long long h[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     c->stored = 0;
     c->result_pairs = nullptr;
     c->result_dist = nullptr;
@@ -1606,7 +1608,7 @@ static int join_stream_core(fasted_ctx* c, double eps, int64_t q_begin, int64_t 
     const size_t mine = ids.size();
     CU_TRY(cudaEventRecord(c->ev[2], c->stream));
     unsigned long long* h = c->chunk_end_host + chunks;
-    CU_TRY(cudaMemcpyAsync(h, c->counters, 5 * sizeof(unsigned long long), cudaMemcpyDeviceToHost, c->stream));
+    CU_TRY(cudaMemcpyAsync(h, c->counters, 8 * sizeof(unsigned long long), cudaMemcpyDeviceToHost, c->stream));
     if (abort_rc == FASTED_OK) {
         abort_rc = deliver(pend);
         if (abort_rc != FASTED_OK) give_up(abort_rc);

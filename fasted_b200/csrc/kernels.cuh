@@ -688,6 +688,7 @@ constexpr int kJoinSmemBytes = kStages * kStageBytes + 1024 + static_cast<int>(s
 __global__ void __launch_bounds__(kJoinThreads, 1)
 join_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
             const JoinParams p) {
+    const long long clock_entry = clock64();
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_u32 = ptx::smem_u32(smem_raw);
     const uint32_t tiles_u32 = (raw_u32 + 1023u) & ~1023u;
@@ -864,10 +865,15 @@ join_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     __syncthreads();
     // SM cycles CTA 0 spent on its share of the tiles: lets the host derive the mean SM clock of the
     // launch (cycles / device time) and the share of those cycles the tensor pipe had work for.
-    if (blockIdx.x == 0 && threadIdx.x == 0) p.counters[4] = static_cast<unsigned long long>(clock64() - clock_start);
+    const long long clock_end = clock64();
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        p.counters[4] = static_cast<unsigned long long>(clock_end - clock_start);
+        p.counters[5] = static_cast<unsigned long long>(clock_start - clock_entry);  // set-up: barriers, TMEM allocation
+    }
     if (warp == 1) {
         ptx::tc_fence_after_sync();
         ptx::tmem_dealloc<1>(tmem_base, kTmemCols);
+        if (blockIdx.x == 0 && lane == 0) p.counters[6] = static_cast<unsigned long long>(clock64() - clock_end);  // TMEM release
     }
 }
 
@@ -972,6 +978,7 @@ constexpr unsigned long long kErrSmemAlign = 16ull;  // status bit: dynamic shar
 __global__ void __launch_bounds__(kJoinThreads, 1)
 join_astat_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                   const JoinParams p) {
+    const long long clock_entry = clock64();
     extern __shared__ __align__(1024) uint8_t smem_astat[];
     const uint32_t a_u32 = ptx::smem_u32(smem_astat);                        // resident query tile: k_steps boxes
     const uint32_t b_u32 = a_u32 + static_cast<uint32_t>(p.k_steps) * kStageBytesA;  // candidate ring
@@ -1167,10 +1174,15 @@ join_astat_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
 
     ptx::tc_fence_before_sync();
     __syncthreads();
-    if (blockIdx.x == 0 && threadIdx.x == 0) p.counters[4] = static_cast<unsigned long long>(clock64() - clock_start);
+    const long long clock_end = clock64();
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        p.counters[4] = static_cast<unsigned long long>(clock_end - clock_start);
+        p.counters[5] = static_cast<unsigned long long>(clock_start - clock_entry);  // set-up: barriers, TMEM allocation
+    }
     if (warp == 1) {
         ptx::tc_fence_after_sync();
         ptx::tmem_dealloc<1>(tmem_base, kTmemCols);
+        if (blockIdx.x == 0 && lane == 0) p.counters[6] = static_cast<unsigned long long>(clock64() - clock_end);  // TMEM release
     }
 }
 
