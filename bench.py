@@ -356,6 +356,7 @@ def main() -> None:
         cyc.append(int(st.cta0_cycles))
         tiles0 = int(st.cta0_tiles)
         setup_cyc, release_cyc = int(st.cta0_setup_cycles), int(st.cta0_release_cycles)
+        feed_cyc, acc_cyc = int(st.cta0_feed_wait_cycles), int(st.cta0_acc_wait_cycles)
         last_rows = int(st.tiles_m) * 128
     ev1.record()
     barrier()
@@ -536,7 +537,8 @@ def main() -> None:
             # CTA 0's cycles that its tiles' tensor work needs at full rate (k_steps x 4 MMAs x 128 clocks a tile)
             "sm_clock_in_kernel_mhz": float(np.mean(cyc)) / (float(np.mean(join_ms)) * 1e3) if cyc and cyc[0] else None,
             "tensor_busy_share_cta0": (tiles0 * (-(-d // 64)) * 512.0) / float(np.mean(cyc)) if cyc and cyc[0] else None,
-            "cta0_cycles": {"tiles": float(np.mean(cyc)) if cyc else None, "setup": setup_cyc, "tmem_release": release_cyc},
+            "cta0_cycles": {"tiles": float(np.mean(cyc)) if cyc else None, "setup": setup_cyc, "tmem_release": release_cyc,
+                            "mma_thread_waited_for_operands": feed_cyc, "mma_thread_waited_for_accumulator": acc_cyc},
             "e2e": e2e,
             "gpu_launches": 2 * args.steps,  # per step: row_norms_kernel, join_kernel (records stay packed until asked for)
             "roofline": {"bound": "tensor", "kernel": "join_kernel", "achieved": achieved, "peak": peak,

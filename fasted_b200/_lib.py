@@ -45,6 +45,8 @@ class JoinStats(ctypes.Structure):
         ("cta0_tiles", ctypes.c_ulonglong),
         ("cta0_setup_cycles", ctypes.c_ulonglong),
         ("cta0_release_cycles", ctypes.c_ulonglong),
+        ("cta0_feed_wait_cycles", ctypes.c_ulonglong),
+        ("cta0_acc_wait_cycles", ctypes.c_ulonglong),
         ("chunks", ctypes.c_int),
         ("tail_ms", ctypes.c_double),
     ]

@@ -134,6 +134,8 @@ struct fasted_ctx {
     int max_pair_clusters = 0;
 };
 
+constexpr int kCounterWords = 16;  // found, -, status, self-test, and CTA 0's cycle counters (see JoinParams::counters)
+
 struct JoinPlan {
     fasted::JoinParams p;
     int grid;
@@ -402,8 +404,8 @@ int fasted_create(int device, fasted_ctx** out) {
             return fail(FASTED_ECUDA, "cudaEventCreate failed");
         }
     }
-    if (cudaMalloc(&c->counters, 8 * sizeof(unsigned long long)) != cudaSuccess ||
-        cudaMallocHost(&c->counters_host, 8 * sizeof(unsigned long long)) != cudaSuccess) {
+    if (cudaMalloc(&c->counters, kCounterWords * sizeof(unsigned long long)) != cudaSuccess ||
+        cudaMallocHost(&c->counters_host, kCounterWords * sizeof(unsigned long long)) != cudaSuccess) {
         fasted_destroy(c);
         return fail(FASTED_ECUDA, "allocation of the counters failed");
     }
@@ -826,7 +828,7 @@ int fasted_row_norms(fasted_ctx* c, double* ms) {
     if (!c) return fail(FASTED_EINVAL, "ctx is null");
     if (!c->points) return fail(FASTED_ESTATE, "no dataset is resident");
     CU_TRY(cudaSetDevice(c->device));
-    CU_TRY(cudaMemsetAsync(c->counters, 0, 8 * sizeof(unsigned long long), c->stream));
+    CU_TRY(cudaMemsetAsync(c->counters, 0, kCounterWords * sizeof(unsigned long long), c->stream));
     CU_TRY(cudaEventRecord(c->ev[0], c->stream));
     int rc = launch_norms(c);
     if (rc) return rc;
@@ -1020,6 +1022,8 @@ static void fill_stats(fasted_ctx* c, const JoinPlan& pl, const unsigned long lo
     stats->cta0_cycles = pl.pair ? 0 : h[4];
     stats->cta0_setup_cycles = pl.pair ? 0 : h[5];
     stats->cta0_release_cycles = pl.pair ? 0 : h[6];
+    stats->cta0_feed_wait_cycles = pl.pair ? 0 : h[7];
+    stats->cta0_acc_wait_cycles = pl.pair ? 0 : h[8];
     stats->cta0_tiles = 0;
     stats->chunks = 1;
     stats->tail_ms = 0;
@@ -1060,7 +1064,7 @@ static int join_impl(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end, 
     rc = plan_join(c, eps, q_begin, q_end, capacity, flags, shard_rank, shard_world, &pl);
     if (rc) return rc;
 
-    CU_TRY(cudaMemsetAsync(c->counters, 0, 8 * sizeof(unsigned long long), c->stream));
+    CU_TRY(cudaMemsetAsync(c->counters, 0, kCounterWords * sizeof(unsigned long long), c->stream));
     CU_TRY(cudaEventRecord(c->ev[0], c->stream));
     // Small joins (a few tiles per CTA) are launch-bound: the join is then launched as a programmatic
     // dependent of the norm kernel, with nothing between the two in the stream, so that its prologue and
@@ -1078,7 +1082,7 @@ static int join_impl(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end, 
     rc = launch_join(c, pl, overlap);
     if (rc) return rc;
     CU_TRY(cudaEventRecord(c->ev[2], c->stream));
-    unsigned long long h[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    unsigned long long h[kCounterWords] = {};
     c->stored = 0;
     c->result_pairs = nullptr;
     c->result_dist = nullptr;
@@ -1218,12 +1222,12 @@ static int ensure_stream_pipeline(fasted_ctx* c, size_t chunks) {
         c->sort_t0.push_back(t0);
         c->sort_t1.push_back(t1);
     }
-    if (c->chunk_end_cap < chunks + 8) {
+    if (c->chunk_end_cap < chunks + kCounterWords) {
         if (c->chunk_end_host) cudaFreeHost(c->chunk_end_host);
         c->chunk_end_host = nullptr;
         c->chunk_end_cap = 0;
-        CU_TRY(cudaMallocHost(&c->chunk_end_host, (chunks + 8) * sizeof(unsigned long long)));
-        c->chunk_end_cap = chunks + 8;
+        CU_TRY(cudaMallocHost(&c->chunk_end_host, (chunks + kCounterWords) * sizeof(unsigned long long)));
+        c->chunk_end_cap = chunks + kCounterWords;
     }
     return FASTED_OK;
 }
@@ -1389,7 +1393,7 @@ static int join_stream_core(fasted_ctx* c, double eps, int64_t q_begin, int64_t 
     c->result_pairs = nullptr;
     c->result_dist = nullptr;
     c->unpack_pending = false;
-    CU_TRY(cudaMemsetAsync(c->counters, 0, 8 * sizeof(unsigned long long), c->stream));
+    CU_TRY(cudaMemsetAsync(c->counters, 0, kCounterWords * sizeof(unsigned long long), c->stream));
     CU_TRY(cudaEventRecord(c->ev[0], c->stream));
     if (!(flags & FASTED_JOIN_KEEP_NORMS) || !c->norms_valid) {
         rc = launch_norms(c);
@@ -1608,7 +1612,7 @@ static int join_stream_core(fasted_ctx* c, double eps, int64_t q_begin, int64_t 
     const size_t mine = ids.size();
     CU_TRY(cudaEventRecord(c->ev[2], c->stream));
     unsigned long long* h = c->chunk_end_host + chunks;
-    CU_TRY(cudaMemcpyAsync(h, c->counters, 8 * sizeof(unsigned long long), cudaMemcpyDeviceToHost, c->stream));
+    CU_TRY(cudaMemcpyAsync(h, c->counters, kCounterWords * sizeof(unsigned long long), cudaMemcpyDeviceToHost, c->stream));
     if (abort_rc == FASTED_OK) {
         abort_rc = deliver(pend);
         if (abort_rc != FASTED_OK) give_up(abort_rc);
@@ -1844,7 +1848,7 @@ int fasted_selftest_wait_timeout(fasted_ctx* c, double limit_ms, unsigned long l
     if (!c || !status_out) return fail(FASTED_EINVAL, "null argument");
     if (!(limit_ms > 0) || limit_ms > 1000.0) return fail(FASTED_EINVAL, "limit must be in (0, 1000] ms");
     CU_TRY(cudaSetDevice(c->device));
-    CU_TRY(cudaMemsetAsync(c->counters, 0, 8 * sizeof(unsigned long long), c->stream));
+    CU_TRY(cudaMemsetAsync(c->counters, 0, kCounterWords * sizeof(unsigned long long), c->stream));
     fasted::wait_timeout_selftest_kernel<<<1, 32, 0, c->stream>>>(static_cast<unsigned long long>(limit_ms * 1e6),
                                                                  c->counters + 2, c->counters + 3);
     CU_TRY(cudaGetLastError());

@@ -51,7 +51,9 @@ struct JoinParams {
     const float* norms;            // [n] row norms
     int norms_vec4;                // 1: norms is 16-byte aligned (vector loads allowed)
     unsigned long long* counters;  // [0] pairs found, [1] unused (stored = min(found, capacity)), [2] status bits,
-                                   // [4] SM cycles of CTA 0 (single-CTA kernel)
+                                   // CTA 0 of the single-CTA kernels: [4] SM cycles on its tiles, [5] set-up,
+                                   // [6] TMEM release, [7] cycles its MMA thread waited for operands, [8] ... for a
+                                   // free accumulator
     unsigned long long* keys;      // pair buffer: (query << 32) | candidate
     float* dist2;                  // optional squared distances, parallel to keys (may be null)
     unsigned long long capacity;   // pair buffer capacity
@@ -775,6 +777,7 @@ join_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         // ------------------------- MMA issuer ---------------------------
         if (lane == 0) {
             constexpr uint32_t idesc = ptx::make_f16_idesc(kTileM, kTileN);
+            long long feed_wait = 0, acc_wait = 0;  // cycles this thread waited for operands / for a free accumulator
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
@@ -783,14 +786,18 @@ join_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             for (ti.init(p, first_tile, tile_step); ti.valid && ok; ti.advance(p), ++it) {
                 const int buf = static_cast<int>(it & 1);
                 const uint32_t acc_phase = static_cast<uint32_t>((it >> 1) & 1);
+                const long long w0 = clock64();
                 ok = ptx::mbar_wait_bounded(ptx::smem_u32(&aux->acc_empty_bar[buf]), acc_phase ^ 1u, abort_flag,
                                             kWaitLimitNs);
+                acc_wait += clock64() - w0;
                 if (!ok) break;
                 ptx::tc_fence_after_sync();
                 const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(buf * kTileN);
                 for (int ks = 0; ks < p.k_steps; ++ks) {
+                    const long long f0 = clock64();
                     ok = ptx::mbar_wait_bounded(ptx::smem_u32(&aux->full_bar[stage]), phase, abort_flag,
                                                 kWaitLimitNs);
+                    feed_wait += clock64() - f0;
                     if (!ok) break;
                     ptx::tc_fence_after_sync();
                     const uint32_t a_addr = tiles_u32 + stage * kStageBytes;
@@ -811,6 +818,10 @@ join_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 if (ok) ptx::umma_commit_1cta(ptx::smem_u32(&aux->acc_full_bar[buf]));
             }
             if (!ok) atomicOr(p.counters + 2, kErrMmaWait);
+            if (blockIdx.x == 0) {
+                p.counters[7] = static_cast<unsigned long long>(feed_wait);
+                p.counters[8] = static_cast<unsigned long long>(acc_wait);
+            }
         }
     } else {
         // ------------------------- Epilogue -----------------------------
@@ -1084,6 +1095,7 @@ join_astat_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         // ------------------------- MMA issuer ---------------------------
         if (lane == 0) {
             constexpr uint32_t idesc = ptx::make_f16_idesc(kTileM, kTileN);
+            long long feed_wait = 0, acc_wait = 0;  // cycles this thread waited for operands / for a free accumulator
             int stage = 0;
             uint32_t phase = 0, a_rows_seen = 0;
             bool ok = true;
@@ -1100,13 +1112,17 @@ join_astat_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 }
                 const int buf = static_cast<int>(it & 1);
                 const uint32_t acc_phase = static_cast<uint32_t>((it >> 1) & 1);
+                const long long w0 = clock64();
                 ok = ptx::mbar_wait_bounded(ptx::smem_u32(&aux->acc_empty_bar[buf]), acc_phase ^ 1u, abort_flag,
                                             kWaitLimitNs);
+                acc_wait += clock64() - w0;
                 if (!ok) break;
                 ptx::tc_fence_after_sync();
                 const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(buf * kTileN);
                 for (int ks = 0; ks < p.k_steps; ++ks) {
+                    const long long f0 = clock64();
                     ok = ptx::mbar_wait_bounded(ptx::smem_u32(&aux->full_bar[stage]), phase, abort_flag, kWaitLimitNs);
+                    feed_wait += clock64() - f0;
                     if (!ok) break;
                     ptx::tc_fence_after_sync();
                     const uint64_t desc_a = ptx::make_kmajor_sw128_desc(a_u32 + static_cast<uint32_t>(ks) * kStageBytesA);
@@ -1124,6 +1140,10 @@ join_astat_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 if (ok) ptx::umma_commit_1cta(ptx::smem_u32(&aux->acc_full_bar[buf]));
             }
             if (!ok) atomicOr(p.counters + 2, kErrMmaWait);
+            if (blockIdx.x == 0) {
+                p.counters[7] = static_cast<unsigned long long>(feed_wait);
+                p.counters[8] = static_cast<unsigned long long>(acc_wait);
+            }
         }
     } else {
         // ------------------------- Epilogue -----------------------------
@@ -1309,6 +1329,7 @@ join_pair_kernel(const __grid_constant__ CUtensorMap map, const JoinParams p) {
         // ------------------------- MMA issuer (leader CTA only) ----------------------
         if (lane == 0 && leader) {
             constexpr uint32_t idesc = ptx::make_f16_idesc(kPairTileM, kTileN);
+            long long acc_wait = 0;  // (kept for symmetry with the single-CTA kernels; not reported)
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
@@ -1317,8 +1338,10 @@ join_pair_kernel(const __grid_constant__ CUtensorMap map, const JoinParams p) {
             for (ti.init(p, first_tile, tile_step); ti.valid && ok; ti.advance(p), ++it) {
                 const int buf = static_cast<int>(it & 1);
                 const uint32_t acc_phase = static_cast<uint32_t>((it >> 1) & 1);
+                const long long w0 = clock64();
                 ok = ptx::mbar_wait_bounded(ptx::smem_u32(&aux->acc_empty_bar[buf]), acc_phase ^ 1u, abort_flag,
                                             kWaitLimitNs);
+                acc_wait += clock64() - w0;
                 if (!ok) break;
                 ptx::tc_fence_after_sync();
                 const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(buf * kTileN);

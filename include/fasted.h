@@ -135,6 +135,8 @@ typedef struct fasted_join_stats {
     unsigned long long cta0_tiles;   /* tiles CTA 0 computed */
     unsigned long long cta0_setup_cycles;    /* SM cycles CTA 0 spent before its first tile (barriers, TMEM allocation) */
     unsigned long long cta0_release_cycles;  /* SM cycles CTA 0 spent releasing its TMEM at the end */
+    unsigned long long cta0_feed_wait_cycles;  /* SM cycles CTA 0's MMA thread waited for operand stages (TMA) */
+    unsigned long long cta0_acc_wait_cycles;   /* ... and for a free accumulator (the epilogue two tiles back) */
     int chunks;      /* join launches the query range was cut into (1 except for fasted_join_stream) */
     double tail_ms;  /* fasted_join_stream: host wall time from the end of the last join launch until the
                         last record was delivered (what the egress pipeline could not hide) */
