@@ -39,13 +39,25 @@ def _worker(rank, world, port, n, d, eps, out_dir):
     sj = SelfJoin(rank)
     sj.set_points_device(t.data_ptr(), n, d, d, keepalive=t)
     sj.set_option("band_tiles", 2)
+    sj.set_option("query_stationary", 0)  # raster bands of 2 tile rows: two dozen chunks to deal out
     eng = GpuBandEngine(sj)
     a, fa, _ = sharded_self_join(eng, n, eps)
     b, fb, _ = sharded_self_join_symmetric(eng, n, eps)
+    # chunks taken on demand from the shared table, every chunk copied to its final place in ONE shared host list
+    from fasted_b200.dist import SharedChunkTable, SharedPairBuffer, dealt_self_join
+    table = SharedChunkTable.collective(n)
+    shared = SharedPairBuffer.collective(fa + 100, register_cuda=True)
+    fc, sc, st = dealt_self_join(sj, n, eps, table, shared, capacity=fa + 100)
+    fd, sd, st2 = dealt_self_join(sj, n, eps, table, None, capacity=fa + 100, flags=_lib.JOIN_NO_SORT)
     if rank == 0:
         np.save(os.path.join(out_dir, "bands.npy"), a)
         np.save(os.path.join(out_dir, "sym.npy"), b)
-        np.save(os.path.join(out_dir, "found.npy"), np.array([fa, fb]))
+        np.save(os.path.join(out_dir, "dealt.npy"), shared.array[:sc].copy())
+        np.save(os.path.join(out_dir, "found.npy"), np.array([fa, fb, fc, sc, fd]))
+    np.save(os.path.join(out_dir, f"chunks{rank}.npy"), np.array([st.chunks, st2.chunks]))
+    dist.barrier()
+    shared.close()
+    table.close()
     dist.barrier()
     sj.close()
     dist.destroy_process_group()
@@ -63,4 +75,7 @@ def test_two_gpu_sharding_matches_one_gpu(gpu_join, oracle_mod, tmp_path):
     want = gpu_join.pairs()
     assert np.array_equal(np.load(tmp_path / "bands.npy"), want)
     assert np.array_equal(np.load(tmp_path / "sym.npy"), want)
-    assert list(np.load(tmp_path / "found.npy")) == [len(want), len(want)]
+    assert np.array_equal(np.load(tmp_path / "dealt.npy"), want)
+    assert list(np.load(tmp_path / "found.npy")) == [len(want)] * 5
+    chunks = [np.load(tmp_path / f"chunks{r}.npy") for r in range(2)]
+    assert chunks[0][0] + chunks[1][0] == chunks[0][1] + chunks[1][1] >= 20  # every chunk taken exactly once, both times
