@@ -57,24 +57,36 @@ def weighted_band_bounds(n: int, weights: Sequence[float], align: int = BAND_ALI
 
 
 class SharedMapping:
-    """A block of host memory that every rank of the node maps: a file under /dev/shm (or under the
-    temporary directory when /dev/shm is too small).  Rank 0 creates the file and removes its name as
-    soon as every rank has mapped it, so nothing is left behind if a rank dies later."""
+    """A block of host memory that every rank of the node maps.  Backing, in this order: a file under
+    /dev/shm when it has room; else an anonymous memory file (memfd) that the other ranks open through
+    /proc/<pid>/fd (containers often mount a tiny /dev/shm); else a file under the temporary directory.
+    FASTED_SHARED_BACKING = shm | memfd | tmp forces one.  Rank 0 creates the mapping and removes its name
+    (closes its descriptor) as soon as every rank has mapped it, so nothing is left behind if a rank dies later."""
 
     def __init__(self, nbytes: int, path: str | None = None):
         self.nbytes = max(int(nbytes), 8)
         self.created = path is None
+        self._keep_fd = None
         if path is None:
-            root = "/dev/shm"
-            try:
-                st = os.statvfs(root)
-                if st.f_bavail * st.f_frsize < self.nbytes + (64 << 20):
-                    root = tempfile.gettempdir()
-            except OSError:
-                root = tempfile.gettempdir()
-            path = os.path.join(root, f"fasted_{os.getpid()}_{uuid.uuid4().hex}")
-            fd = os.open(path, os.O_CREAT | os.O_EXCL | os.O_RDWR, 0o600)
-            os.ftruncate(fd, self.nbytes)
+            how = os.environ.get("FASTED_SHARED_BACKING", "")
+            if not how:
+                how = "memfd" if hasattr(os, "memfd_create") else "tmp"
+                try:
+                    st = os.statvfs("/dev/shm")
+                    if st.f_bavail * st.f_frsize >= self.nbytes + (64 << 20):
+                        how = "shm"
+                except OSError:
+                    pass
+            if how == "memfd":
+                fd = os.memfd_create("fasted_shared")
+                os.ftruncate(fd, self.nbytes)
+                self._keep_fd = os.dup(fd)  # the name the other ranks open lives as long as this descriptor
+                path = f"/proc/{os.getpid()}/fd/{self._keep_fd}"
+            else:
+                root = "/dev/shm" if how == "shm" else tempfile.gettempdir()
+                path = os.path.join(root, f"fasted_{os.getpid()}_{uuid.uuid4().hex}")
+                fd = os.open(path, os.O_CREAT | os.O_EXCL | os.O_RDWR, 0o600)
+                os.ftruncate(fd, self.nbytes)
         else:
             fd = os.open(path, os.O_RDWR)
         self.path = path
@@ -86,7 +98,11 @@ class SharedMapping:
         self.address = self.bytes.ctypes.data
 
     def unlink(self) -> None:
-        if self.path and os.path.exists(self.path):
+        """Remove the mapping's name (the memory stays while it is mapped)."""
+        if self._keep_fd is not None:
+            os.close(self._keep_fd)
+            self._keep_fd = None
+        elif self.path and not self.path.startswith("/proc/") and os.path.exists(self.path):
             os.unlink(self.path)
 
     def close(self) -> None:

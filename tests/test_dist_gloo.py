@@ -48,11 +48,14 @@ def test_weighted_band_bounds_follow_the_rates():
         weighted_band_bounds(10, [])
 
 
-def test_shared_pair_buffer_is_one_mapping_for_two_openers():
+@pytest.mark.parametrize("backing", ["shm", "memfd", "tmp"])
+def test_shared_pair_buffer_is_one_mapping_for_two_openers(backing, monkeypatch):
     from fasted_b200.dist import SharedPairBuffer
+    monkeypatch.setenv("FASTED_SHARED_BACKING", backing)
     a = SharedPairBuffer(1000)
     try:
         assert os.path.exists(a.path) and a.array.shape == (1000, 2)
+        assert a.path.startswith({"shm": "/dev/shm/", "memfd": "/proc/", "tmp": "/"}[backing])
         b = SharedPairBuffer(1000, path=a.path)
         a.array[10:20] = np.arange(20, dtype=np.int32).reshape(10, 2)
         assert np.array_equal(b.array[10:20], a.array[10:20]) and b.address != 0
