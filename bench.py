@@ -226,6 +226,7 @@ def main() -> None:
     ap.add_argument("--loader-pieces", type=int, default=4,
                     help="N > 1, end-to-end leg: pieces in which a rank's band is uploaded and all-gathered (1 = upload, "
                          "then one all-gather)")
+    ap.add_argument("--no-numa", action="store_true", help="N > 1: do not pin the rank to its GPU's CPU cores")
     ap.add_argument("--no-balance", action="store_true", help="N > 1: keep equal bands (no sizing by measured rate)")
     ap.add_argument("--option", action="append", default=[], help="name=value for fasted_set_option (tuning runs)")
     args = ap.parse_args()
@@ -259,6 +260,11 @@ def main() -> None:
     if world != args.gpus and world > 1:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
     torch.cuda.set_device(local_rank)
+    numa_cores = None
+    if world > 1 and not args.no_numa:
+        # before any page-locked buffer exists: the rank's host buffers should live next to its GPU
+        from fasted_b200.dist import bind_to_gpu_numa_node
+        numa_cores = bind_to_gpu_numa_node(local_rank)
     if world > 1:
         # Rank 0's stdout is the one JSON line: NCCL's version banner (NCCL_DEBUG=VERSION prints it to
         # stdout) is switched off, anything else NCCL is asked to log goes to stderr.
@@ -525,6 +531,7 @@ def main() -> None:
                 "parallelism": (f"query rows over {world} GPUs: " + ("chunks of raster bands taken on demand from a shared "
                                 "table" if dealt else "one fixed equal band per rank")) if world > 1 else "single GPU",
                 "rows_per_rank_last_step": rows_share,
+                "rank0_cpu_cores": (f"{len(numa_cores)} cores next to its GPU" if numa_cores else None),
                 "l2": "inputs larger than L2 (no flush needed)" if n * ld * 2 > 2 * 126e6 else "inputs fit L2",
                 "baseline_note": "vs_baseline divides by the reference's published A100-PCIe figure for this shape "
                                  "(153.64 TFLOPS at eps=0.001)" if name in PUBLISHED_A100_TFLOPS else None,

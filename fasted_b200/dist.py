@@ -369,6 +369,28 @@ def allgather_points(points, rank: int, world: int):
     return points
 
 
+def bind_to_gpu_numa_node(device_index: int) -> list[int] | None:
+    """Pin this process to the CPU cores that are closest to its GPU (NVML's CPU affinity of the device).
+    With one process per GPU on a two-socket host, page-locked host buffers allocated afterwards land
+    on the GPU's own NUMA node, so the uploads of eight ranks do not all cross the socket interconnect.
+    Returns the cores, or None when NVML or the affinity call is not available (nothing is changed then)."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(device_index)
+        ncpu = os.cpu_count() or 1
+        words = pynvml.nvmlDeviceGetCpuAffinity(h, (ncpu + 63) // 64)
+        cores = [64 * w + b for w, mask in enumerate(words) for b in range(64) if (int(mask) >> b) & 1]
+        allowed = os.sched_getaffinity(0)
+        cores = [c for c in cores if c in allowed]
+        if not cores:
+            return None
+        os.sched_setaffinity(0, cores)
+        return cores
+    except Exception:  # noqa: BLE001 - an optimisation only
+        return None
+
+
 def upload_and_allgather(points, host_band, rank: int, world: int, pieces: int = 4):
     """Loader for ranks that each hold their own band of the matrix in (pinned) HOST memory: the band is
     uploaded piece by piece on a side stream, and each piece is all-gathered (NCCL over NVLink) as soon
