@@ -314,7 +314,7 @@ row_norms_kernel(const __grid_constant__ CUtensorMap map, float* __restrict__ no
                 if (r < n) norms[r] = kExact == 1 ? static_cast<float>(acc64) : acc;
             }
         }
-        // Every thread is done with stage s.  The same barrier carries the verdict of the waits, so
+        // Every thread is done with stage s.  The same barrier carries the outcome of the waits, so
         // that all threads leave the loop together if any of them gave up.
         if (__syncthreads_or(ok ? 0 : 1)) {
             ok = false;

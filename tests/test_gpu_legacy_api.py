@@ -203,7 +203,7 @@ print("JSON" + json.dumps(dict(lo=lo, hi=hi, eps=eps, sel=[t.results.get_selecti
 def test_the_references_own_driver_runs_against_this_library(native_lib, oracle_mod, tmp_path):
     """The reference's experiment driver itself (results/scripts/experiment: load_findpairs, bound_epsilon,
     find_epsilon_binary, run_time_trials), unmodified, with this library in the place of its main.so.
-    Needs the reference checkout (FASTED_REFERENCE_ROOT, default /root/reference); skipped without it."""
+    Needs the reference checkout (environment variable FASTED_REFERENCE_ROOT); skipped without it."""
     from fasted_b200 import _lib
     ref = os.environ.get("FASTED_REFERENCE_ROOT", "/root/reference")
     if not os.path.isdir(os.path.join(ref, "results", "scripts", "experiment")):
