@@ -127,7 +127,7 @@ typedef struct fasted_join_stats {
     double norms_ms;   /* row-norm kernel, device time (0 where a small join overlapped it: join_ms then covers both) */
     double join_ms;    /* join kernel, device time */
     double kernel_ms;  /* start of norms to end of join (the reference's TFLOPS interval) */
-    double sort_ms;    /* sort + unpack, device time */
+    double sort_ms;    /* sort + unpack, device time (fasted_join_stream: the sum over the chunks) */
     unsigned long long status;  /* device status bits, 0 = clean */
     int tiles_m, tiles_n;
     int grid;
@@ -137,9 +137,10 @@ typedef struct fasted_join_stats {
     unsigned long long cta0_release_cycles;  /* SM cycles CTA 0 spent releasing its TMEM at the end */
     unsigned long long cta0_feed_wait_cycles;  /* SM cycles CTA 0's MMA thread waited for operand stages (TMA) */
     unsigned long long cta0_acc_wait_cycles;   /* ... and for a free accumulator (the epilogue two tiles back) */
-    int chunks;      /* join launches the query range was cut into (1 except for fasted_join_stream) */
-    double tail_ms;  /* fasted_join_stream: host wall time from the end of the last join launch until the
-                        last record was delivered (what the egress pipeline could not hide) */
+    int chunks;      /* join launches of this call (1 except for fasted_join_stream / fasted_join_stream_shared, where
+                        join_ms is the device time of those launches without the sorts that ran between them) */
+    double tail_ms;  /* fasted_join_stream: device time of the last chunk's sort plus whatever of its copy to the
+                        host was left after the last join launch (what the egress pipeline could not hide) */
 } fasted_join_stats;
 
 const char* fasted_last_error(void);
@@ -394,9 +395,9 @@ int fasted_selftest_wait_timeout(fasted_ctx* ctx, double limit_ms, unsigned long
  * power cap on B200), "exact_norms" (1 = correctly rounded row norms (FP64 sum, one rounding)
  * instead of the reference's round-toward-zero chain: NOT the reference's numerics, but closer to an
  * FP64 join on this hardware, whose tensor-core accumulate does not truncate; default 0),
- * "query_stationary" (-1 = automatic: for rows of at most 384 values a CTA keeps its 128 query rows in
- * shared memory and streams candidate rows only; 0 = never, 1 = whenever d <= 512; same results bit for
- * bit), "stream_chunk_bands" (raster bands per chunk of fasted_join_stream, 0 = automatic), "stream_key32" (1 = default:
+ * "query_stationary" (-1 = automatic: for rows of at most 512 values a CTA keeps its 128 query rows in
+ * shared memory and streams candidate rows only; 0 = never, 1 = the same rule as automatic; same results
+ * bit for bit), "stream_chunk_bands" (raster bands per chunk of fasted_join_stream, 0 = automatic), "stream_key32" (1 = default:
  * 32-bit chunk-relative records in fasted_join_stream where they fit), "dependent_launch" (1 = default: a small join is
  * launched as a programmatic dependent of the row-norm kernel and overlaps it). */
 int fasted_set_option(fasted_ctx* ctx, const char* name, int64_t value);
