@@ -810,16 +810,20 @@ int fasted_get_rows_host_f16(fasted_ctx* c, const int64_t* rows, int64_t count, 
     return FASTED_OK;
 }
 
-static int launch_norms(fasted_ctx* c) {
-    const int row_blocks = static_cast<int>((c->n + fasted::kNormRows - 1) / fasted::kNormRows);
+// Row norms of rows [row_begin, row_end) (row_begin a multiple of 128; the whole matrix by default).
+static int launch_norms(fasted_ctx* c, int64_t row_begin = 0, int64_t row_end = -1) {
+    if (row_end < 0 || row_end > c->n) row_end = c->n;
+    if (row_begin >= row_end) return FASTED_OK;
+    const int first_block = static_cast<int>(row_begin / fasted::kNormRows);
+    const int row_blocks = static_cast<int>((row_end + fasted::kNormRows - 1) / fasted::kNormRows) - first_block;
     const int k_boxes = static_cast<int>((c->d + fasted::kTileK - 1) / fasted::kTileK);
     const int grid = std::min(row_blocks, c->num_sms * 3);
     if (c->exact_norms)
         fasted::row_norms_kernel<1><<<grid, fasted::kNormRows, fasted::kNormSmemBytes, c->stream>>>(
-            c->map_a, c->norms, static_cast<int>(c->n), k_boxes, row_blocks, c->counters + 2);
+            c->map_a, c->norms, static_cast<int>(c->n), k_boxes, row_blocks, first_block, c->counters + 2);
     else
         fasted::row_norms_kernel<0><<<grid, fasted::kNormRows, fasted::kNormSmemBytes, c->stream>>>(
-            c->map_a, c->norms, static_cast<int>(c->n), k_boxes, row_blocks, c->counters + 2);
+            c->map_a, c->norms, static_cast<int>(c->n), k_boxes, row_blocks, first_block, c->counters + 2);
     CU_TRY(cudaGetLastError());
     return FASTED_OK;
 }
@@ -2123,7 +2127,7 @@ int fasted_join_static_scratch(const void* points_dev, int64_t n, int64_t d, int
     CU_TRY(cudaMemsetAsync(counters, 0, kStaticCounterBytes, st));
     const int row_blocks = static_cast<int>((n + fasted::kNormRows - 1) / fasted::kNormRows);
     fasted::row_norms_kernel<0><<<std::min(row_blocks, num_sms * 3), fasted::kNormRows, fasted::kNormSmemBytes, st>>>(
-        map_a, norms, static_cast<int>(n), p.k_steps, row_blocks, counters + 2);
+        map_a, norms, static_cast<int>(n), p.k_steps, row_blocks, 0, counters + 2);
     CU_TRY(cudaGetLastError());
     fasted::join_kernel<<<grid, fasted::kJoinThreads, fasted::kJoinSmemBytes, st>>>(map_a, map_b, p);
     CU_TRY(cudaGetLastError());

@@ -75,9 +75,21 @@ struct JoinParams {
     int key_shift, key_qbase;      // record = ((query - key_qbase) << key_shift) | candidate.  32 and 0 give the
                                    // plain (query << 32) | candidate; a launch over one chunk of query rows can
                                    // pack tighter, so that the chunk's sort has fewer significant bits to look at
+    int cand_t, cand_group_rows, cand_base;  // candidate subset of this launch.  cand_t = 0: all rows, tile column tn
+                                   // covers candidates [tn * 256, +256).  Else the launch joins against G groups of
+                                   // cand_t tile columns each: tile column tn covers the 256 rows that start at
+                                   // (tn / cand_t) * cand_group_rows + cand_base + (tn % cand_t) * 256 (a piece of the
+                                   // matrix that has arrived from every rank while the rest is still on its way)
     int key32;                     // 1: the packed record fits 32 bits and `keys` is an array of uint32_t (half the
                                    // bytes to write, to sort and to read back)
 };
+
+// First candidate row of tile column tn (see JoinParams::cand_t).
+__device__ __forceinline__ int cand_row0(const JoinParams& p, int tn) {
+    if (p.cand_t == 0) return tn * kTileN;
+    const int g = tn / p.cand_t;
+    return g * p.cand_group_rows + p.cand_base + (tn - g * p.cand_t) * kTileN;
+}
 
 __device__ __forceinline__ unsigned long long pack_record(const JoinParams& p, unsigned long long q,
                                                           unsigned long long c) {
@@ -231,7 +243,9 @@ constexpr int kNormSmemBytes = kNormStages * kNormStageBytes + 1024 + 64;
 template <int kExact>
 __global__ void __launch_bounds__(kNormRows)
 row_norms_kernel(const __grid_constant__ CUtensorMap map, float* __restrict__ norms, int n, int k_boxes,
-                 int row_blocks, unsigned long long* __restrict__ status) {
+                 int row_blocks, int row_block_begin, unsigned long long* __restrict__ status) {
+    // (row blocks [row_block_begin, row_block_begin + row_blocks) of 128 rows each: the whole matrix, or
+    // the rows of a piece that has just arrived)
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t bars = base + kNormStages * kNormStageBytes;  // kNormStages full barriers
@@ -258,7 +272,7 @@ row_norms_kernel(const __grid_constant__ CUtensorMap map, float* __restrict__ no
     auto issue = [&](long long item) {
         const int blk = static_cast<int>(item / steps_per_block);
         const int step = static_cast<int>(item - static_cast<long long>(blk) * steps_per_block);
-        const int row0 = (static_cast<int>(blockIdx.x) + blk * static_cast<int>(gridDim.x)) * kNormRows;
+        const int row0 = (row_block_begin + static_cast<int>(blockIdx.x) + blk * static_cast<int>(gridDim.x)) * kNormRows;
         const int s = static_cast<int>(item % kNormStages);
         const uint32_t bar = bars + 8 * s;
         const int nb = min(kNormBoxesPerStage, k_boxes - step * kNormBoxesPerStage);
@@ -310,7 +324,7 @@ row_norms_kernel(const __grid_constant__ CUtensorMap map, float* __restrict__ no
                 }
             }
             if (step == steps_per_block - 1) {
-                const int r = (static_cast<int>(blockIdx.x) + blk * static_cast<int>(gridDim.x)) * kNormRows + tid;
+                const int r = (row_block_begin + static_cast<int>(blockIdx.x) + blk * static_cast<int>(gridDim.x)) * kNormRows + tid;
                 if (r < n) norms[r] = kExact == 1 ? static_cast<float>(acc64) : acc;
             }
         }
@@ -738,7 +752,7 @@ join_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             for (ti.init(p, first_tile, tile_step); ti.valid && ok; ti.advance(p)) {
                 const int tm = ti.tm, tn = ti.tn;
                 const int row_a = p.q_begin + tm * kTileM;
-                const int row_b = tn * kTileN;
+                const int row_b = cand_row0(p, tn);
                 for (int ks = 0; ks < p.k_steps; ++ks) {
                     ok = ptx::mbar_wait_bounded(ptx::smem_u32(&aux->empty_bar[stage]), phase ^ 1u, abort_flag,
                                                 kWaitLimitNs);
@@ -839,20 +853,20 @@ join_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         pend.any = false;
         ptx::grid_dependency_wait();  // the row norms come from the kernel before this one
         if (ti.valid)
-            fetch_warp_norms(p, ti.tn * kTileN + col_off, p.q_begin + ti.tm * kTileM + quarter * 32, lane, next_cand,
+            fetch_warp_norms(p, cand_row0(p, ti.tn) + col_off, p.q_begin + ti.tm * kTileM + quarter * 32, lane, next_cand,
                              next_query);
         for (; ti.valid; ++it) {
             const int buf = static_cast<int>(it & 1);
             const uint32_t acc_phase = static_cast<uint32_t>((it >> 1) & 1);
             const int q0 = p.q_begin + ti.tm * kTileM + quarter * 32;
-            const int c0 = ti.tn * kTileN + col_off;
+            const int c0 = cand_row0(p, ti.tn) + col_off;
             __syncwarp();  // every lane is done with the previous tile's norms
             reinterpret_cast<float4*>(wcn)[lane] = next_cand;
             const float sq_lane = next_query;
             __syncwarp();
             ti.advance(p);
             if (ti.valid)
-                fetch_warp_norms(p, ti.tn * kTileN + col_off, p.q_begin + ti.tm * kTileM + quarter * 32, lane,
+                fetch_warp_norms(p, cand_row0(p, ti.tn) + col_off, p.q_begin + ti.tm * kTileM + quarter * 32, lane,
                                  next_cand, next_query);
             if (ok) ok = ptx::mbar_wait_bounded(ptx::smem_u32(&aux->acc_full_bar[buf]), acc_phase, abort_flag,
                                                 kWaitLimitNs);
@@ -1054,7 +1068,7 @@ join_astat_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                                          p.q_begin + ti.tm * kTileM);
                     ++a_rows_loaded;
                 }
-                const int row_b = ti.tn * kTileN;
+                const int row_b = cand_row0(p, ti.tn);
                 for (int ks = 0; ks < p.k_steps; ++ks) {
                     ok = ptx::mbar_wait_bounded(ptx::smem_u32(&aux->empty_bar[stage]), phase ^ 1u, abort_flag,
                                                 kWaitLimitNs);
@@ -1160,18 +1174,18 @@ join_astat_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         pend.any = false;
         ptx::grid_dependency_wait();  // the row norms come from the kernel before this one
         if (ti.valid)
-            fetch_warp_norms(p, ti.tn * kTileN + col_off, p.q_begin + ti.tm * kTileM + quarter * 32, lane, next_cand,
+            fetch_warp_norms(p, cand_row0(p, ti.tn) + col_off, p.q_begin + ti.tm * kTileM + quarter * 32, lane, next_cand,
                              next_query);
         for (; ti.valid; ++it) {
             const int buf = static_cast<int>(it & 1);
             const uint32_t acc_phase = static_cast<uint32_t>((it >> 1) & 1);
             const int q0 = p.q_begin + ti.tm * kTileM + quarter * 32;
-            const int c0 = ti.tn * kTileN + col_off;
+            const int c0 = cand_row0(p, ti.tn) + col_off;
             const float4 cand_now = next_cand;
             const float sq_lane = next_query;
             ti.advance(p);
             if (ti.valid)
-                fetch_warp_norms(p, ti.tn * kTileN + col_off, p.q_begin + ti.tm * kTileM + quarter * 32, lane,
+                fetch_warp_norms(p, cand_row0(p, ti.tn) + col_off, p.q_begin + ti.tm * kTileM + quarter * 32, lane,
                                  next_cand, next_query);
             if (ok) ok = ptx::mbar_wait_bounded(ptx::smem_u32(&aux->acc_full_bar[buf]), acc_phase, abort_flag,
                                                 kWaitLimitNs);
@@ -1292,7 +1306,7 @@ join_pair_kernel(const __grid_constant__ CUtensorMap map, const JoinParams p) {
             for (ti.init(p, first_tile, tile_step); ti.valid && ok; ti.advance(p)) {
                 const int tm = ti.tm, tn = ti.tn;
                 const int row_a = p.q_begin + tm * kPairTileM + static_cast<int>(rank) * kTileM;
-                const int row_b = tn * kTileN + static_cast<int>(rank) * (kTileN / 2);
+                const int row_b = cand_row0(p, tn) + static_cast<int>(rank) * (kTileN / 2);
                 for (int ks = 0; ks < p.k_steps; ++ks) {
                     ok = ptx::mbar_wait_bounded(ptx::smem_u32(&aux->empty_bar[stage]), phase ^ 1u, abort_flag,
                                                 kWaitLimitNs);
@@ -1388,20 +1402,20 @@ join_pair_kernel(const __grid_constant__ CUtensorMap map, const JoinParams p) {
         pend.any = false;
         ptx::grid_dependency_wait();  // the row norms come from the kernel before this one
         if (ti.valid)
-            fetch_warp_norms(p, ti.tn * kTileN + col_off, p.q_begin + ti.tm * kPairTileM + row_off, lane, next_cand,
+            fetch_warp_norms(p, cand_row0(p, ti.tn) + col_off, p.q_begin + ti.tm * kPairTileM + row_off, lane, next_cand,
                              next_query);
         for (; ti.valid; ++it) {
             const int buf = static_cast<int>(it & 1);
             const uint32_t acc_phase = static_cast<uint32_t>((it >> 1) & 1);
             const int q0 = p.q_begin + ti.tm * kPairTileM + row_off;
-            const int c0 = ti.tn * kTileN + col_off;
+            const int c0 = cand_row0(p, ti.tn) + col_off;
             __syncwarp();
             reinterpret_cast<float4*>(wcn)[lane] = next_cand;
             const float sq_lane = next_query;
             __syncwarp();
             ti.advance(p);
             if (ti.valid)
-                fetch_warp_norms(p, ti.tn * kTileN + col_off, p.q_begin + ti.tm * kPairTileM + row_off, lane,
+                fetch_warp_norms(p, cand_row0(p, ti.tn) + col_off, p.q_begin + ti.tm * kPairTileM + row_off, lane,
                                  next_cand, next_query);
 
             if (ok) ok = ptx::mbar_wait_bounded(ptx::smem_u32(&aux->acc_full_bar[buf]), acc_phase, abort_flag,
