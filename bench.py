@@ -223,6 +223,12 @@ def main() -> None:
     ap.add_argument("--e2e-mode", default="stream", choices=["stream", "serial"],
                     help="N = 1: stream = fasted_join_stream (egress pipelined behind the join); serial = fasted_join, "
                          "then fasted_get_pairs (sort and copy after the join, as the reference orders them)")
+    ap.add_argument("--join-behind-load", type=int, default=1, choices=[0, 1],
+                    help="N > 1, end-to-end leg: 1 = every rank starts joining the first chunks of its own band while "
+                         "the matrix is still being uploaded and all-gathered (fasted_join_stream_arriving); 0 = the "
+                         "join's first launch waits for the whole load")
+    ap.add_argument("--lead-rows", type=int, default=0,
+                    help="query rows per rank joined while the matrix arrives (0 = the library's choice)")
     ap.add_argument("--loader-pieces", type=int, default=4,
                     help="N > 1, end-to-end leg: pieces in which a rank's band is uploaded and all-gathered (1 = upload, "
                          "then one all-gather)")
@@ -252,7 +258,12 @@ def main() -> None:
     from fasted_b200 import SelfJoin, JOIN_NO_SORT
     from fasted_b200.dist import (GpuBandEngine, SharedChunkTable, SharedPairBuffer, allgather_points, band_bounds,
                                   dealt_self_join, sharded_self_join, upload_and_allgather)
-    from fasted_b200.dist import band_rows as rows_per_band
+    from fasted_b200.dist import band_rows as equal_band_rows
+    from fasted_b200.dist import load_and_join
+
+    def rows_per_band(n_rows: int, ranks: int) -> int:
+        # bands that can be cut into --loader-pieces pieces of whole 256-row candidate tiles
+        return equal_band_rows(n_rows, ranks, 256 * max(1, args.loader_pieces))
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -446,6 +457,10 @@ def main() -> None:
                     return st, m
                 st = sj.join_stream(eps, capacity=capacity, pairs_host=host_out.data_ptr(), host_capacity=out_cap)
                 return st, min(int(st.pairs_stored), out_cap)
+            if dealt and args.join_behind_load:
+                _, _, st = load_and_join(sj, dev_pts, host_pts, n, d, eps, table, shared, capacity=capacity,
+                                         pieces=max(1, args.loader_pieces), lead_rows=args.lead_rows)
+                return st, int(st.pairs_stored)
             if args.loader_pieces > 1:
                 upload_and_allgather(dev_pts, host_pts, rank, world, pieces=args.loader_pieces)
             else:
@@ -481,9 +496,14 @@ def main() -> None:
                "join_kernel_ms": float(np.mean(e2e_join_ms)), "egress_tail_ms": float(np.mean(e2e_tail_ms)),
                "sort_ms": float(st.sort_ms), "mode": args.e2e_mode if world == 1 else "stream",
                "join_launches_per_step": e2e_chunks,
+               "join_behind_load": bool(world > 1 and dealt and args.join_behind_load),
                "api": "fasted_set_points_host_f16 + fasted_join_stream (pinned host buffers; sort and device-to-host "
                       "copy pipelined behind the join)"
-               if world == 1 else "per rank: pinned host band -> its GPU, one NCCL all-gather, then "
+               if world == 1 else ("per rank: pinned host band -> its GPU and NCCL all-gather piece by piece on side "
+                                     "streams while fasted_join_stream_arriving already joins the first chunks of the "
+                                     "rank's own band against the pieces that are there; then "
+                                     if dealt and args.join_behind_load else
+                                     "per rank: pinned host band -> its GPU, one NCCL all-gather, then ")
                                     + ("fasted_join_stream_shared: chunks taken from one shared table, every sorted chunk "
                                        "copied to its final place in one shared page-locked host buffer while the join runs"
                                        if dealt else "fasted_join_stream on the rank's band, count exchange, fasted_get_pairs "

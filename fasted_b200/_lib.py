@@ -68,8 +68,25 @@ DECLARED_SYMBOLS = [
     "fasted_broadcast_points",
     "fasted_shared_chunks_bytes", "fasted_shared_chunks_init", "fasted_join_stream_shared", "fasted_shared_chunks_totals",
     "fasted_shared_chunks_init_plan", "fasted_shared_chunks_take", "fasted_shared_chunks_publish",
-    "fasted_shared_chunks_offset", "fasted_shared_chunks_fail",
+    "fasted_shared_chunks_offset", "fasted_shared_chunks_fail", "fasted_shared_chunks_range",
+    "fasted_shared_chunks_init_arriving", "fasted_join_stream_arriving",
 ]
+
+class Arrival(ctypes.Structure):
+    """fasted_arrival of include/fasted.h: how the dataset reaches the GPUs while the join starts."""
+    _fields_ = [("pieces", ctypes.c_int), ("groups", ctypes.c_int), ("group_rows", ctypes.c_int64),
+                ("own_begin", ctypes.c_int64), ("lead_rows", ctypes.c_int64), ("events", ctypes.POINTER(ctypes.c_void_p))]
+
+    @classmethod
+    def make(cls, pieces: int, groups: int, group_rows: int, own_begin: int, lead_rows: int = 0, events=None) -> "Arrival":
+        a = cls(pieces, groups, group_rows, own_begin, lead_rows, None)
+        if events is not None:
+            if len(events) != pieces:
+                raise ValueError("one event per piece")
+            a._handles = (ctypes.c_void_p * pieces)(*[ctypes.c_void_p(int(e) if e else None) for e in events])
+            a.events = ctypes.cast(a._handles, ctypes.POINTER(ctypes.c_void_p))
+        return a
+
 
 CHUNK_FN = ctypes.CFUNCTYPE(ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_uint64,
                             ctypes.c_uint64)
@@ -115,7 +132,13 @@ def load() -> ctypes.CDLL:
                                             ctypes.POINTER(JoinStats)]
     L.fasted_shared_chunks_totals.argtypes = [_vp, ctypes.POINTER(ctypes.c_ulonglong), ctypes.POINTER(ctypes.c_ulonglong),
                                               ctypes.POINTER(ctypes.c_ulonglong)]
-    L.fasted_shared_chunks_init_plan.argtypes = [_vp, ctypes.c_size_t, _i64, _i64, _i64, ctypes.POINTER(_u64)]
+    L.fasted_shared_chunks_init_plan.argtypes = [_vp, ctypes.c_size_t, _i64, _i64, _i64, _i64, ctypes.c_int,
+                                                 ctypes.POINTER(_u64)]
+    L.fasted_shared_chunks_range.argtypes = [_vp, _u64, ctypes.POINTER(_i64), ctypes.POINTER(_i64)]
+    L.fasted_shared_chunks_init_arriving.argtypes = [_vp, _vp, ctypes.c_size_t, ctypes.c_double, ctypes.c_int,
+                                                     ctypes.POINTER(Arrival), ctypes.POINTER(_u64)]
+    L.fasted_join_stream_arriving.argtypes = [_vp, ctypes.c_double, _u64, ctypes.c_uint, _vp, ctypes.POINTER(Arrival),
+                                              _vp, _u64, ctypes.POINTER(JoinStats)]
     L.fasted_shared_chunks_take.argtypes = [_vp]
     L.fasted_shared_chunks_take.restype = _i64
     L.fasted_shared_chunks_publish.argtypes = [_vp, _u64, _u64, _u64]
@@ -356,6 +379,18 @@ class SelfJoin:
         st = JoinStats()
         _check(self._L.fasted_join_stream_shared(self._h, float(eps), capacity, flags, _vp(table_address),
                                                  _vp(pairs_host or None), host_capacity, ctypes.byref(st)))
+        self._last = st
+        self._last_dist = False
+        return st
+
+    def join_stream_arriving(self, eps: float, table_address: int, arrival: "Arrival", capacity: int = 0, flags: int = 0,
+                             pairs_host: int = 0, host_capacity: int = 0) -> JoinStats:
+        """fasted_join_stream_arriving: like join_stream_shared, started while the dataset is still arriving
+        piece by piece (`arrival` carries one CUDA event per piece)."""
+        st = JoinStats()
+        _check(self._L.fasted_join_stream_arriving(self._h, float(eps), capacity, flags, _vp(table_address),
+                                                   ctypes.byref(arrival), _vp(pairs_host or None), host_capacity,
+                                                   ctypes.byref(st)))
         self._last = st
         self._last_dist = False
         return st

@@ -881,7 +881,9 @@ static int default_capacity(fasted_ctx* c, bool want_dist, uint64_t* out) {
 
 // Kernel parameters and grid of one launch over query rows [q_begin, q_end).
 static int plan_join(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end, uint64_t capacity, unsigned flags,
-                     int shard_rank, int shard_world, JoinPlan* out) {
+                     int shard_rank, int shard_world, JoinPlan* out, int cand_tile_columns = 0) {
+    // cand_tile_columns > 0: the launch joins against that many 256-row candidate tiles (a subset of the rows
+    // that the caller describes with JoinParams::cand_t and its companions) instead of all ceil(n / 256)
     const bool want_dist = (flags & FASTED_JOIN_DIST2) != 0;
     fasted::JoinParams p{};
     p.norms = c->norms;
@@ -911,7 +913,7 @@ static int plan_join(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end, 
     p.key32 = 0;
     if (shard_world > 1 && !symmetric) return fail(FASTED_EINVAL, "band snakes are for the symmetric schedule only");
     p.tiles_m = static_cast<int>((q_end - q_begin + tile_m - 1) / tile_m);
-    p.tiles_n = static_cast<int>((c->n + fasted::kTileN - 1) / fasted::kTileN);
+    p.tiles_n = cand_tile_columns > 0 ? cand_tile_columns : static_cast<int>((c->n + fasted::kTileN - 1) / fasted::kTileN);
     // band_tiles counts 128-row tile rows; a pair tile is two of them.
     const int band_opt = c->band_tiles > 0 ? c->band_tiles : default_band_tiles(c->ld);
     const int band = pair ? std::max(1, band_opt / 2) : band_opt;
@@ -1300,24 +1302,46 @@ static int plan_chunks(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end
 struct SharedChunks {
     uint64_t magic;
     int64_t q_begin, q_end, chunk_rows;
-    uint64_t chunks;
-    std::atomic<uint64_t> next;    // next chunk to hand out
+    // One group: chunk k is rows [q_begin + k * chunk_rows, ...).  Several groups (the bands in which the
+    // matrix reaches the GPUs, one per rank): every group is cut into chunks_per_group chunks from its own
+    // first row, and the first lead_chunks chunks of group g are not handed out: rank g joins them itself,
+    // piece by piece, while the rest of the matrix is still arriving (their rows are the first it holds).
+    int64_t group_rows;
+    uint64_t groups, chunks_per_group, lead_chunks;
+    uint64_t chunks;               // ids: groups * chunks_per_group, ascending with the rows they cover
+    std::atomic<uint64_t> next;    // chunks handed out so far (only those that are handed out count)
     std::atomic<uint64_t> failed;  // a rank gave up: everybody stops waiting
     std::atomic<uint64_t> found_total, stored_total;
     std::atomic<uint64_t> count[1];  // records stored for chunk k; kUnknownCount until its rank publishes it
 };
-constexpr uint64_t kSharedMagic = 0x46615354454463ull;
+constexpr uint64_t kSharedMagic = 0x46615354454464ull;
 constexpr uint64_t kUnknownCount = ~0ull;
 static_assert(sizeof(std::atomic<uint64_t>) == sizeof(uint64_t), "lock-free 64-bit atomics expected");
+
+// Rows of chunk `id` (an empty range, begin == end, lies beyond the data).
+static void shared_chunk_range(const SharedChunks* t, uint64_t id, int64_t* begin, int64_t* end) {
+    const uint64_t g = id / t->chunks_per_group, i = id % t->chunks_per_group;
+    const int64_t base = t->groups > 1 ? static_cast<int64_t>(g) * t->group_rows : t->q_begin;
+    const int64_t group_end = t->groups > 1 ? std::min<int64_t>(t->q_end, base + t->group_rows) : t->q_end;
+    const int64_t b = base + static_cast<int64_t>(i) * t->chunk_rows;
+    *begin = std::min<int64_t>(b, std::max<int64_t>(group_end, std::min<int64_t>(base, t->q_end)));
+    *end = std::max<int64_t>(*begin, std::min<int64_t>(group_end, b + t->chunk_rows));
+}
 
 int64_t fasted_shared_chunks_take(void* mem);
 int fasted_shared_chunks_publish(void* mem, uint64_t chunk, uint64_t stored, uint64_t found);
 
 static int join_stream_core(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end, uint64_t capacity, unsigned flags,
                             int32_t* pairs_host, float* dist2_host, uint64_t host_capacity, fasted_chunk_fn on_chunk,
-                            void* user, SharedChunks* shared, fasted_join_stats* stats) {
+                            void* user, SharedChunks* shared, const fasted_arrival* arr, fasted_join_stats* stats) {
     int rc = check_join_args(c, eps, q_begin, &q_end);
     if (rc) return rc;
+    if (arr && (!shared || arr->pieces < 1 || arr->groups < 1 || arr->group_rows <= 0 ||
+                arr->group_rows % (256 * static_cast<int64_t>(arr->pieces)) != 0 || arr->own_begin < 0 ||
+                arr->own_begin % arr->group_rows != 0 ||
+                static_cast<int64_t>(arr->groups) * arr->group_rows < c->n))
+        return fail(FASTED_EINVAL, "bad arrival description (groups x group_rows must cover the matrix, group_rows a "
+                                   "multiple of 256 x pieces, own_begin the first row of a group)");
     const bool count_only = shared != nullptr && (flags & FASTED_JOIN_NO_SORT) != 0;
     if (flags & (FASTED_JOIN_SYMMETRIC | FASTED_JOIN_RAW_DOT | (shared ? FASTED_JOIN_DIST2 : FASTED_JOIN_NO_SORT)))
         return fail(FASTED_EINVAL, shared ? "the shared-chunk join takes FASTED_JOIN_NO_SORT and FASTED_JOIN_KEEP_NORMS only"
@@ -1347,15 +1371,35 @@ static int join_stream_core(fasted_ctx* c, double eps, int64_t q_begin, int64_t 
         cp.chunks = shared->chunks;
         const int64_t rows32 = cp.key_shift < 32 ? (int64_t(1) << (32 - cp.key_shift)) : 0;
         cp.fits32 = cp.chunk_rows <= rows32;
+        if (arr && shared->groups > 1 && (shared->group_rows != arr->group_rows || shared->groups != static_cast<uint64_t>(arr->groups)))
+            return fail(FASTED_EINVAL, "the shared chunk table was planned for other groups than the arrival describes");
     }
     const int key_shift = cp.key_shift;
     const int64_t chunk_rows = cp.chunk_rows;
     const size_t chunks = static_cast<size_t>(cp.chunks);  // chunks of the whole join (all ranks')
-    const bool key32 = c->stream_key32 != 0 && cp.fits32;
+    // The rows this rank joins while the matrix is still arriving: the first lead chunks of its own group,
+    // as ONE launch sequence (one launch per arriving piece), hence one slice of records.
+    int64_t lead_begin = 0, lead_end = 0;
+    uint64_t lead_id = 0;
+    if (arr && shared->lead_chunks > 0) {
+        lead_id = static_cast<uint64_t>(arr->own_begin / arr->group_rows) * shared->chunks_per_group;
+        int64_t b0, e0, b1, e1;
+        shared_chunk_range(shared, lead_id, &b0, &e0);
+        shared_chunk_range(shared, lead_id + shared->lead_chunks - 1, &b1, &e1);
+        lead_begin = b0;
+        lead_end = e1;
+        if (lead_end - lead_begin > arr->group_rows / arr->pieces)
+            return fail(FASTED_EINVAL, "the lead chunks must lie inside the first piece of the rank's own band");
+    } else if (shared && shared->lead_chunks > 0) {
+        return fail(FASTED_EINVAL, "this chunk table sets lead chunks aside: every rank has to join with its arrival description");
+    }
+    const int64_t max_rows = std::max<int64_t>(chunk_rows, lead_end - lead_begin);
+    const int64_t rows32_all = key_shift < 32 ? (int64_t(1) << (32 - key_shift)) : 0;
+    const bool key32 = c->stream_key32 != 0 && cp.fits32 && max_rows <= rows32_all;  // one record width per call
     rc = ensure_stream_pipeline(c, chunks + 1);
     if (rc) return rc;
     const int sort_bits = std::min(key32 ? 32 : 64,
-                                   key_shift + bits_of(static_cast<uint64_t>(std::max<int64_t>(chunk_rows - 1, 1))));
+                                   key_shift + bits_of(static_cast<uint64_t>(std::max<int64_t>(max_rows - 1, 1))));
     // 32-bit records: both halves of the sort's double buffer live in `keys` (capacity 64-bit words hold
     // 2 x capacity 32-bit ones), the unpacked (query, candidate) records go to `keys_alt`.
     uint32_t* const ping32 = reinterpret_cast<uint32_t*>(c->keys);
@@ -1399,26 +1443,45 @@ static int join_stream_core(fasted_ctx* c, double eps, int64_t q_begin, int64_t 
     c->unpack_pending = false;
     CU_TRY(cudaMemsetAsync(c->counters, 0, kCounterWords * sizeof(unsigned long long), c->stream));
     CU_TRY(cudaEventRecord(c->ev[0], c->stream));
-    if (!(flags & FASTED_JOIN_KEEP_NORMS) || !c->norms_valid) {
+    if (!arr && (!(flags & FASTED_JOIN_KEEP_NORMS) || !c->norms_valid)) {
         rc = launch_norms(c);
         if (rc) return rc;
     }
     CU_TRY(cudaEventRecord(c->ev[1], c->stream));
 
-    // Launch j of this rank joins chunk ids[j]: the next in order (one GPU), or the next one nobody
-    // has taken yet (chunks shared by several ranks).
-    std::vector<size_t> ids;
-    auto chunk_begin = [&](size_t id) { return q_begin + static_cast<int64_t>(id) * chunk_rows; };
+    // Launch sequence j of this rank joins rows [begin, end) = chunk `id`: the next in order (one GPU), or the
+    // next one nobody has taken yet (chunks shared by several ranks), or this rank's lead chunks.
+    struct Entry {
+        size_t id;
+        int64_t begin, end;
+    };
+    std::vector<Entry> ids;
+    bool has_lead = false;  // ids[0] is this rank's lead
+    auto snapshot = [&](size_t j) -> int {
+        // (pinned destination: a copy into pageable memory would hold the host until the GPU gets here)
+        CU_TRY(cudaMemcpyAsync(c->chunk_end_host + j, c->counters, sizeof(unsigned long long), cudaMemcpyDeviceToHost,
+                               c->stream));
+        CU_TRY(cudaEventRecord(c->chunk_ev[j], c->stream));
+        return FASTED_OK;
+    };
     auto enqueue_next_join = [&]() -> int {
         size_t id = ids.size();
-        if (shared) {
-            const int64_t taken = fasted_shared_chunks_take(shared);
-            if (taken < 0) return FASTED_OK;
-            id = static_cast<size_t>(taken);
+        int64_t b = 0, e = 0;
+        for (;;) {
+            if (shared) {
+                const int64_t taken = fasted_shared_chunks_take(shared);
+                if (taken < 0) return FASTED_OK;
+                id = static_cast<size_t>(taken);
+                shared_chunk_range(shared, id, &b, &e);
+                if (b < e) break;
+                fasted_shared_chunks_publish(shared, id, 0, 0);  // a chunk beyond the data: nothing to join
+            } else {
+                if (id >= chunks) return FASTED_OK;
+                b = q_begin + static_cast<int64_t>(id) * chunk_rows;
+                e = std::min<int64_t>(q_end, b + chunk_rows);
+                break;
+            }
         }
-        if (id >= chunks) return FASTED_OK;
-        const size_t j = ids.size();
-        const int64_t b = chunk_begin(id), e = std::min<int64_t>(q_end, b + chunk_rows);
         JoinPlan pl;
         int r = plan_join(c, eps, b, e, capacity, flags & ~FASTED_JOIN_NO_SORT, 0, 1, &pl);
         if (r) return r;
@@ -1427,13 +1490,54 @@ static int join_stream_core(fasted_ctx* c, double eps, int64_t q_begin, int64_t 
         pl.p.key32 = key32 ? 1 : 0;
         r = launch_join(c, pl);
         if (r) return r;
-        // (pinned destination: a copy into pageable memory would hold the host until the GPU gets here)
-        CU_TRY(cudaMemcpyAsync(c->chunk_end_host + j, c->counters, sizeof(unsigned long long), cudaMemcpyDeviceToHost,
-                               c->stream));
-        CU_TRY(cudaEventRecord(c->chunk_ev[j], c->stream));
-        ids.push_back(id);
+        r = snapshot(ids.size());
+        if (r) return r;
+        ids.push_back(Entry{id, b, e});
         return FASTED_OK;
     };
+
+    if (arr && shared->lead_chunks > 0) {
+        // the lead chunks are joined as one sequence: its records are counted under the first id
+        for (uint64_t k = lead_end > lead_begin ? 1 : 0; k < shared->lead_chunks; ++k)
+            fasted_shared_chunks_publish(shared, lead_id + k, 0, 0);
+    }
+    if (arr) {
+        // The matrix arrives in pieces (piece p = rows [g * B + p * B / P, ...) of every group g).  As soon as a
+        // piece is there: its rows' norms, then the lead rows against exactly those candidates.  The launches
+        // of the lead sequence are consecutive on the stream, so its records are one slice like any chunk's.
+        const int64_t piece_rows = arr->group_rows / arr->pieces;
+        for (int pc = 0; pc < arr->pieces; ++pc) {
+            if (arr->events && arr->events[pc])
+                CU_TRY(cudaStreamWaitEvent(c->stream, static_cast<cudaEvent_t>(arr->events[pc]), 0));
+            for (int g = 0; g < arr->groups; ++g) {
+                const int64_t r0 = static_cast<int64_t>(g) * arr->group_rows + static_cast<int64_t>(pc) * piece_rows;
+                rc = launch_norms(c, r0, r0 + piece_rows);
+                if (rc) return rc;
+            }
+            if (lead_end > lead_begin) {
+                JoinPlan pl;
+                const int cand_t = static_cast<int>(piece_rows / fasted::kTileN);
+                rc = plan_join(c, eps, lead_begin, lead_end, capacity, flags & ~FASTED_JOIN_NO_SORT, 0, 1, &pl,
+                               arr->groups * cand_t);
+                if (rc) return rc;
+                pl.p.key_shift = key_shift;
+                pl.p.key_qbase = static_cast<int>(lead_begin);
+                pl.p.key32 = key32 ? 1 : 0;
+                pl.p.cand_t = cand_t;
+                pl.p.cand_group_rows = static_cast<int>(arr->group_rows);
+                pl.p.cand_base = static_cast<int>(static_cast<int64_t>(pc) * piece_rows);
+                rc = launch_join(c, pl);
+                if (rc) return rc;
+            }
+        }
+        if (lead_end > lead_begin) {
+            rc = snapshot(0);
+            if (rc) return rc;
+            ids.push_back(Entry{static_cast<size_t>(lead_id), lead_begin, lead_end});
+            has_lead = true;
+        }
+    }
+
     constexpr size_t kAhead = 2;  // join launches enqueued beyond the chunk the host is waiting for
     for (size_t k = 0; k < kAhead; ++k) {
         rc = enqueue_next_join();
@@ -1443,28 +1547,36 @@ static int join_stream_core(fasted_ctx* c, double eps, int64_t q_begin, int64_t 
     // Place of a chunk's first record in the list the host receives.  One GPU: the chunk's first slot.
     // Shared chunks: the sum of the counts of all chunks before it, as soon as their ranks have
     // published them (they retire at about the same time as this one; the wait is bounded).
-    uint64_t known_upto = 0, prefix = 0;  // prefix = records of chunks [0, known_upto)
-    auto global_offset = [&](size_t id, uint64_t* off) -> int {
+    struct Scan {
+        uint64_t upto = 0, prefix = 0;  // prefix = records of chunks [0, upto)
+    };
+    // (two scans, each moving forward only: the chunks this rank takes come in ascending order, but its lead
+    // chunk -- the first thing it joins -- lies behind every chunk of the bands before its own)
+    Scan scan_dealt, scan_lead;
+    auto advance = [&](Scan& s, size_t id) -> bool {
+        while (s.upto < id) {
+            const uint64_t v = shared->count[s.upto].load(std::memory_order_acquire);
+            if (v == kUnknownCount) return false;
+            s.prefix += v;
+            ++s.upto;
+        }
+        return true;
+    };
+    auto global_offset = [&](Scan& s, size_t id, uint64_t* off) -> int {
         timespec t0;
         clock_gettime(CLOCK_MONOTONIC, &t0);
-        for (unsigned spin = 0; known_upto < id; ++spin) {
-            const uint64_t v = shared->count[known_upto].load(std::memory_order_acquire);
-            if (v != kUnknownCount) {
-                prefix += v;
-                ++known_upto;
-                continue;
-            }
+        for (unsigned spin = 0; !advance(s, id); ++spin) {
             if (shared->failed.load(std::memory_order_acquire)) return fail(FASTED_ESTATE, "another rank gave up its join");
             if ((spin & 1023u) == 1023u) {
                 timespec t1;
                 clock_gettime(CLOCK_MONOTONIC, &t1);
                 if (t1.tv_sec - t0.tv_sec > 120)
                     return fail(FASTED_ESTATE, "chunk %llu was not published within 120 s by the rank that took it",
-                                (unsigned long long)known_upto);
+                                (unsigned long long)s.upto);
                 sched_yield();
             }
         }
-        *off = prefix;
+        *off = s.prefix;
         return FASTED_OK;
     };
 
@@ -1476,7 +1588,8 @@ static int join_stream_core(fasted_ctx* c, double eps, int64_t q_begin, int64_t 
         uint64_t a = 0, b = 0;
         size_t j = 0;
         bool copy_enqueued = false;
-    } pend;
+        bool lead = false;
+    } pend, lead_pend;
     auto deliver = [&](const Pending& pd) -> int {
         if (!pd.any) return FASTED_OK;
         const uint64_t a = pd.a, m = pd.b - pd.a;
@@ -1484,7 +1597,7 @@ static int join_stream_core(fasted_ctx* c, double eps, int64_t q_begin, int64_t 
         const float* src_dist = want_dist ? c->dist_alt + a : nullptr;
         uint64_t at = a;  // index of the chunk's first record in the host list
         if (shared) {
-            const int r = global_offset(ids[pd.j], &at);
+            const int r = global_offset(pd.lead ? scan_lead : scan_dealt, ids[pd.j].id, &at);
             if (r) return r;
         }
         if (pairs_host) {
@@ -1543,7 +1656,7 @@ static int join_stream_core(fasted_ctx* c, double eps, int64_t q_begin, int64_t 
         CU_TRY(cudaEventSynchronize(c->chunk_ev[j]));
         const uint64_t end_j = c->chunk_end_host[j];
         const uint64_t a = std::min<uint64_t>(prev_end, capacity), b = std::min<uint64_t>(end_j, capacity);
-        if (shared) fasted_shared_chunks_publish(shared, ids[j], b - a, end_j - prev_end);  // later chunks can be placed
+        if (shared) fasted_shared_chunks_publish(shared, ids[j].id, b - a, end_j - prev_end);  // later chunks can be placed
         prev_end = end_j;
         Pending now;
         if (b > a && abort_rc == FASTED_OK && !count_only) {
@@ -1561,7 +1674,7 @@ static int join_stream_core(fasted_ctx* c, double eps, int64_t q_begin, int64_t 
                         CU_TRY(cub::DeviceRadixSort::SortKeys(c->sort_tmp, need, kb, m, 0, sort_bits, c->stream));
                 }
                 fasted::unpack_pairs32_kernel<<<unpack_blocks(c, m), 256, 0, c->stream>>>(
-                    kb.Current(), reinterpret_cast<int2*>(c->keys_alt + a), m, key_shift, static_cast<int>(chunk_begin(ids[j])));
+                    kb.Current(), reinterpret_cast<int2*>(c->keys_alt + a), m, key_shift, static_cast<int>(ids[j].begin));
             } else {
                 cub::DoubleBuffer<unsigned long long> kb(c->keys + a, c->keys_alt + a);
                 if (m > 1) {
@@ -1571,7 +1684,7 @@ static int join_stream_core(fasted_ctx* c, double eps, int64_t q_begin, int64_t 
                         CU_TRY(cub::DeviceRadixSort::SortKeys(c->sort_tmp, need, kb, m, 0, sort_bits, c->stream));
                 }
                 fasted::unpack_pairs_kernel<<<unpack_blocks(c, m), 256, 0, c->stream>>>(
-                    kb.Current(), reinterpret_cast<int2*>(c->keys_alt + a), m, key_shift, static_cast<int>(chunk_begin(ids[j])));
+                    kb.Current(), reinterpret_cast<int2*>(c->keys_alt + a), m, key_shift, static_cast<int>(ids[j].begin));
             }
             CU_TRY(cudaGetLastError());
             if (want_dist && vb.Current() != c->dist_alt + a)
@@ -1611,7 +1724,20 @@ static int join_stream_core(fasted_ctx* c, double eps, int64_t q_begin, int64_t 
             abort_rc = deliver(pend);
             if (abort_rc != FASTED_OK) give_up(abort_rc);
         }
+        if (has_lead && j == 0) {
+            // The lead's place in the list is known when every chunk of the bands before this rank's has been
+            // counted, which is late in the join: its records wait on the device until then, and nothing waits
+            // for them (a rank that held back its own later chunks for it would hold up everybody).
+            now.lead = true;
+            lead_pend = now;
+            now = Pending{};
+        }
         pend = now;
+        if (lead_pend.any && abort_rc == FASTED_OK && advance(scan_lead, ids[0].id)) {
+            abort_rc = deliver(lead_pend);
+            if (abort_rc != FASTED_OK) give_up(abort_rc);
+            lead_pend.any = false;
+        }
     }
     const size_t mine = ids.size();
     CU_TRY(cudaEventRecord(c->ev[2], c->stream));
@@ -1619,6 +1745,10 @@ static int join_stream_core(fasted_ctx* c, double eps, int64_t q_begin, int64_t 
     CU_TRY(cudaMemcpyAsync(h, c->counters, kCounterWords * sizeof(unsigned long long), cudaMemcpyDeviceToHost, c->stream));
     if (abort_rc == FASTED_OK) {
         abort_rc = deliver(pend);
+        if (abort_rc != FASTED_OK) give_up(abort_rc);
+    }
+    if (abort_rc == FASTED_OK && lead_pend.any) {  // (every chunk this rank took is published: waiting is safe now)
+        abort_rc = deliver(lead_pend);
         if (abort_rc != FASTED_OK) give_up(abort_rc);
     }
     CU_TRY(cudaEventRecord(c->ev_tail, c->copy_stream));
@@ -1631,7 +1761,7 @@ static int join_stream_core(fasted_ctx* c, double eps, int64_t q_begin, int64_t 
     c->stored = stored;
     {
         int64_t my_rows = 0;
-        for (size_t id : ids) my_rows += std::min<int64_t>(q_end, chunk_begin(id) + chunk_rows) - chunk_begin(id);
+        for (const Entry& en : ids) my_rows += en.end - en.begin;
         if (my_rows > 0) set_density_hint(c, static_cast<double>(h[0]) / static_cast<double>(my_rows));
     }
     if (count_only) {
@@ -1665,7 +1795,7 @@ static int join_stream_core(fasted_ctx* c, double eps, int64_t q_begin, int64_t 
         stats->chunks = static_cast<int>(mine);
         if (shared) {  // this rank's share of the tile rows
             int64_t my_rows = 0;
-            for (size_t id : ids) my_rows += std::min<int64_t>(q_end, chunk_begin(id) + chunk_rows) - chunk_begin(id);
+            for (const Entry& en : ids) my_rows += en.end - en.begin;
             stats->tiles_m = static_cast<int>((my_rows + whole.p.tile_m - 1) / whole.p.tile_m);
         }
         stats->cta0_cycles = 0;  // the counter holds the last launch's only
@@ -1678,7 +1808,7 @@ int fasted_join_stream(fasted_ctx* c, double eps, int64_t q_begin, int64_t q_end
                        int32_t* pairs_host, float* dist2_host, uint64_t host_capacity, fasted_chunk_fn on_chunk,
                        void* user, fasted_join_stats* stats) {
     return join_stream_core(c, eps, q_begin, q_end, capacity, flags, pairs_host, dist2_host, host_capacity, on_chunk, user,
-                            nullptr, stats);
+                            nullptr, nullptr, stats);
 }
 
 size_t fasted_shared_chunks_bytes(uint64_t max_chunks) {
@@ -1699,18 +1829,32 @@ int fasted_shared_chunks_init(fasted_ctx* c, void* mem, size_t bytes, double eps
     if (fasted_shared_chunks_bytes(cp.chunks) > bytes)
         return fail(FASTED_EINVAL, "the table needs %zu bytes for %llu chunks, %zu were given", fasted_shared_chunks_bytes(cp.chunks),
                     (unsigned long long)cp.chunks, bytes);
-    return fasted_shared_chunks_init_plan(mem, bytes, q_begin, q_end, cp.chunk_rows, chunks_out);
+    return fasted_shared_chunks_init_plan(mem, bytes, q_begin, q_end, cp.chunk_rows, 0, 0, chunks_out);
 }
 
 int fasted_shared_chunks_init_plan(void* mem, size_t bytes, int64_t q_begin, int64_t q_end, int64_t chunk_rows,
-                                   uint64_t* chunks_out) {
-    if (!mem || q_begin < 0 || q_end < q_begin || chunk_rows <= 0) return fail(FASTED_EINVAL, "bad argument");
-    const uint64_t chunks = static_cast<uint64_t>((q_end - q_begin + chunk_rows - 1) / chunk_rows);
-    if (fasted_shared_chunks_bytes(chunks) > bytes) return fail(FASTED_EINVAL, "the table is too small for %llu chunks", (unsigned long long)chunks);
+                                   int64_t group_rows, int lead_chunks, uint64_t* chunks_out) {
+    if (!mem || q_begin < 0 || q_end < q_begin || chunk_rows <= 0 || group_rows < 0 || lead_chunks < 0)
+        return fail(FASTED_EINVAL, "bad argument");
+    if (group_rows > 0 && q_begin != 0) return fail(FASTED_EINVAL, "groups need the whole row range [0, n)");
+    const int64_t rows = q_end - q_begin;
+    const uint64_t groups =
+        group_rows > 0 ? static_cast<uint64_t>(std::max<int64_t>(1, (rows + group_rows - 1) / group_rows)) : 1;
+    const int64_t per_group = groups > 1 ? group_rows : rows;
+    const uint64_t cpg = static_cast<uint64_t>(std::max<int64_t>(1, (per_group + chunk_rows - 1) / chunk_rows));
+    if (groups == 1) lead_chunks = 0;
+    if (static_cast<uint64_t>(lead_chunks) > cpg) return fail(FASTED_EINVAL, "more lead chunks than a group has");
+    const uint64_t chunks = groups * cpg;
+    if (fasted_shared_chunks_bytes(chunks) > bytes)
+        return fail(FASTED_EINVAL, "the table is too small for %llu chunks", (unsigned long long)chunks);
     SharedChunks* t = static_cast<SharedChunks*>(mem);
     t->q_begin = q_begin;
     t->q_end = q_end;
     t->chunk_rows = chunk_rows;
+    t->group_rows = groups > 1 ? group_rows : 0;
+    t->groups = groups;
+    t->chunks_per_group = cpg;
+    t->lead_chunks = static_cast<uint64_t>(lead_chunks);
     t->chunks = chunks;
     t->next.store(0, std::memory_order_relaxed);
     t->failed.store(0, std::memory_order_relaxed);
@@ -1726,8 +1870,17 @@ int fasted_shared_chunks_init_plan(void* mem, size_t bytes, int64_t q_begin, int
 int64_t fasted_shared_chunks_take(void* mem) {
     SharedChunks* t = static_cast<SharedChunks*>(mem);
     if (!t || t->magic != kSharedMagic || t->failed.load(std::memory_order_acquire)) return -1;
-    const uint64_t id = t->next.fetch_add(1, std::memory_order_acq_rel);
-    return id < t->chunks ? static_cast<int64_t>(id) : -1;
+    const uint64_t dealt_per_group = t->chunks_per_group - t->lead_chunks;
+    const uint64_t v = t->next.fetch_add(1, std::memory_order_acq_rel);
+    if (dealt_per_group == 0 || v >= t->groups * dealt_per_group) return -1;
+    return static_cast<int64_t>((v / dealt_per_group) * t->chunks_per_group + t->lead_chunks + v % dealt_per_group);
+}
+
+int fasted_shared_chunks_range(const void* mem, uint64_t chunk, int64_t* begin, int64_t* end) {
+    const SharedChunks* t = static_cast<const SharedChunks*>(mem);
+    if (!t || t->magic != kSharedMagic || chunk >= t->chunks || !begin || !end) return fail(FASTED_EINVAL, "bad chunk");
+    shared_chunk_range(t, chunk, begin, end);
+    return FASTED_OK;
 }
 
 int fasted_shared_chunks_publish(void* mem, uint64_t chunk, uint64_t stored, uint64_t found) {
@@ -1783,7 +1936,49 @@ int fasted_join_stream_shared(fasted_ctx* c, double eps, uint64_t capacity, unsi
     SharedChunks* t = static_cast<SharedChunks*>(shared_mem);
     if (!t || t->magic != kSharedMagic) return fail(FASTED_EINVAL, "not a shared chunk table");
     return join_stream_core(c, eps, t->q_begin, t->q_end, capacity, flags, pairs_host, nullptr, host_capacity, nullptr,
-                            nullptr, t, stats);
+                            nullptr, t, nullptr, stats);
+}
+
+int fasted_shared_chunks_init_arriving(fasted_ctx* c, void* mem, size_t bytes, double eps, int ranks,
+                                       const fasted_arrival* arr, uint64_t* chunks_out) {
+    if (!mem || ranks < 1 || !arr || arr->pieces < 1 || arr->groups < 1 || arr->group_rows <= 0 ||
+        arr->group_rows % (256 * static_cast<int64_t>(arr->pieces)) != 0 || arr->lead_rows < 0)
+        return fail(FASTED_EINVAL, "bad argument");
+    int64_t q_end = -1;
+    int rc = check_join_args(c, eps, 0, &q_end);
+    if (rc) return rc;
+    if (static_cast<int64_t>(arr->groups) * arr->group_rows < q_end)
+        return fail(FASTED_EINVAL, "groups x group_rows must cover the matrix");
+    ChunkPlan cp;
+    rc = plan_chunks(c, eps, 0, q_end, static_cast<uint64_t>(ranks) * 256, &cp);
+    if (rc) return rc;
+    // The lead: what a rank joins while the matrix is still on its way.  It has to lie in the first piece of
+    // the rank's band (the rows it holds from the start).  By default one twelfth of the band, which outlasts
+    // a load over PCIe + NVLink for long rows; where the output is dense (the last join on this dataset
+    // stored 128 records per row or more) no more rows than a 32-bit record can number, because wider
+    // records would cost the sorts more than the lead hides.
+    const int64_t piece_rows = arr->group_rows / arr->pieces;
+    int64_t lead_rows = arr->lead_rows > 0 ? arr->lead_rows : arr->group_rows / 12;
+    lead_rows = std::min(lead_rows, piece_rows);
+    const int64_t rows32 = cp.key_shift < 32 ? (int64_t(1) << (32 - cp.key_shift)) : 0;
+    if (cp.fits32 && c->stream_key32 != 0 && c->density_hint >= 128.0 && c->hint_n == c->n && c->hint_d == c->d)
+        lead_rows = std::min(lead_rows, rows32);
+    const int64_t per_group = std::min<int64_t>(arr->group_rows, q_end);
+    const int64_t cpg = std::max<int64_t>(1, (per_group + cp.chunk_rows - 1) / cp.chunk_rows);
+    int64_t lead_chunks = arr->groups > 1 ? std::min<int64_t>(lead_rows / cp.chunk_rows, cpg) : 0;
+    if (arr->lead_rows == 0 && lead_chunks == 0 && arr->groups > 1 && cp.chunk_rows <= piece_rows) lead_chunks = 1;
+    return fasted_shared_chunks_init_plan(mem, bytes, 0, q_end, cp.chunk_rows, arr->groups > 1 ? arr->group_rows : 0,
+                                          static_cast<int>(lead_chunks), chunks_out);
+}
+
+int fasted_join_stream_arriving(fasted_ctx* c, double eps, uint64_t capacity, unsigned flags, void* shared_mem,
+                                const fasted_arrival* arrival, int32_t* pairs_host, uint64_t host_capacity,
+                                fasted_join_stats* stats) {
+    SharedChunks* t = static_cast<SharedChunks*>(shared_mem);
+    if (!t || t->magic != kSharedMagic) return fail(FASTED_EINVAL, "not a shared chunk table");
+    if (!arrival) return fail(FASTED_EINVAL, "no arrival description");
+    return join_stream_core(c, eps, t->q_begin, t->q_end, capacity, flags, pairs_host, nullptr, host_capacity, nullptr,
+                            nullptr, t, arrival, stats);
 }
 
 int fasted_tile_schedule(int64_t n, int64_t q_begin, int64_t q_end, int tile_m, int band_tiles, int symmetric,

@@ -186,7 +186,7 @@ class SharedChunkTable(SharedMapping):
     @classmethod
     def collective(cls, n_rows: int) -> "SharedChunkTable":
         """Room for any chunking of n_rows query rows (a chunk is at least one 128-row tile row)."""
-        max_chunks = -(-n_rows // BAND_ALIGN) + 1
+        max_chunks = -(-n_rows // BAND_ALIGN) + 65  # (+ one partly filled chunk per group of a grouped plan)
         return cls._collective(lambda: cls(max_chunks), lambda path, nbytes: cls(0, path=path, nbytes=nbytes))
 
     def init(self, self_join, eps: float, q_begin: int, q_end: int, ranks: int) -> int:
@@ -197,12 +197,26 @@ class SharedChunkTable(SharedMapping):
                                                       q_begin, q_end, ranks, ctypes.byref(chunks)))
         return int(chunks.value)
 
-    def init_plan(self, q_begin: int, q_end: int, chunk_rows: int) -> int:
+    def init_plan(self, q_begin: int, q_end: int, chunk_rows: int, group_rows: int = 0, lead_chunks: int = 0) -> int:
         from . import _lib
         chunks = ctypes.c_uint64()
         _lib._check(self._L.fasted_shared_chunks_init_plan(ctypes.c_void_p(self.address), self.nbytes, q_begin, q_end,
-                                                           chunk_rows, ctypes.byref(chunks)))
+                                                           chunk_rows, group_rows, lead_chunks, ctypes.byref(chunks)))
         return int(chunks.value)
+
+    def init_arriving(self, self_join, eps: float, ranks: int, arrival) -> int:
+        """By ONE rank: the plan for a join that starts while the dataset is arriving (fasted_join_stream_arriving)."""
+        from . import _lib
+        chunks = ctypes.c_uint64()
+        _lib._check(self._L.fasted_shared_chunks_init_arriving(self_join._h, ctypes.c_void_p(self.address), self.nbytes,
+                                                               float(eps), ranks, ctypes.byref(arrival), ctypes.byref(chunks)))
+        return int(chunks.value)
+
+    def chunk_range(self, chunk: int) -> tuple[int, int]:
+        from . import _lib
+        b, e = ctypes.c_int64(), ctypes.c_int64()
+        _lib._check(self._L.fasted_shared_chunks_range(ctypes.c_void_p(self.address), chunk, ctypes.byref(b), ctypes.byref(e)))
+        return int(b.value), int(e.value)
 
     def take(self) -> int:
         return int(self._L.fasted_shared_chunks_take(ctypes.c_void_p(self.address)))
@@ -431,6 +445,92 @@ def upload_and_allgather(points, host_band, rank: int, world: int, pieces: int =
         src = mine[a:b].view(torch.uint8).reshape(-1)
         dist.all_gather(outs, src.clone() if not on_gpu else src)
     return points
+
+
+_loader_streams: dict = {}
+
+
+def upload_and_allgather_events(points, host_band, rank: int, world: int, pieces: int = 4):
+    """The same loader, entirely on side streams, for a join that starts while the matrix arrives
+    (fasted_join_stream_arriving): returns one CUDA event per piece; event p completes when rows
+    [g * B + p * B / P, g * B + (p + 1) * B / P) of every band g are resident on this GPU (B = band rows, a
+    multiple of 256 * P).  The calling stream is not made to wait: whoever reads `points` waits for the events.
+    Work enqueued on the calling stream before this call (the previous join) is waited for by the side streams."""
+    import torch
+    import torch.distributed as dist
+    per = points.shape[0] // world
+    if points.shape[0] % world or host_band.shape[0] != per:
+        raise ValueError("points must hold world * band_rows rows, host_band band_rows rows")
+    if per % (256 * pieces):
+        raise ValueError("band rows must be a multiple of 256 * pieces")
+    key = (points.device.index, "upload"), (points.device.index, "gather")
+    for k in key:
+        if k not in _loader_streams:
+            _loader_streams[k] = torch.cuda.Stream(device=points.device)
+    up, gather = _loader_streams[key[0]], _loader_streams[key[1]]
+    here = torch.cuda.current_stream(points.device)
+    up.wait_stream(here)
+    gather.wait_stream(here)
+    mine = points[rank * per:(rank + 1) * per]
+    step = per // pieces
+    landed = []
+    with torch.cuda.stream(up):
+        for p in range(pieces):
+            mine[p * step:(p + 1) * step].copy_(host_band[p * step:(p + 1) * step], non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record(up)
+            landed.append(ev)
+    events = []
+    multi = dist.is_available() and dist.is_initialized() and world > 1
+    with torch.cuda.stream(gather):
+        for p in range(pieces):
+            gather.wait_event(landed[p])
+            if multi:
+                outs = [points[r * per + p * step:r * per + (p + 1) * step].view(torch.uint8).reshape(-1) for r in range(world)]
+                dist.all_gather(outs, mine[p * step:(p + 1) * step].view(torch.uint8).reshape(-1))
+            ev = torch.cuda.Event()
+            ev.record(gather)
+            events.append(ev)
+    return events
+
+
+def load_and_join(self_join, points, host_band, n: int, d: int, eps: float, table: "SharedChunkTable",
+                  pairs: "SharedPairBuffer | None" = None, capacity: int = 0, flags: int = 0, pieces: int = 4,
+                  lead_rows: int = 0):
+    """One end-to-end step for ranks that each hold their own band of the matrix on the host: the band is uploaded
+    and all-gathered piece by piece on side streams while every rank already joins the first chunks of its own
+    band against the pieces that have arrived; the rest of the chunks are dealt out as in dealt_self_join.
+    `points`: world * band_rows rows on the device (band_rows a multiple of 256 * pieces), rows beyond n zero.
+    Collective.  Returns (found_total, stored_total, this rank's JoinStats)."""
+    import torch.distributed as dist
+    from . import _lib
+    multi = dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1
+    world = dist.get_world_size() if multi else 1
+    rank = dist.get_rank() if multi else 0
+    per = points.shape[0] // world
+    self_join.set_points_device(points.data_ptr(), n, d, points.shape[1], keepalive=points)  # geometry only: nothing is read
+    plan = _lib.Arrival.make(pieces, world, per, rank * per, lead_rows)
+    if rank == 0:
+        table.init_arriving(self_join, eps, world, plan)
+    if multi:
+        dist.barrier()  # the table is ready (before the loader: a barrier behind it would wait for the whole load)
+    events = upload_and_allgather_events(points, host_band, rank, world, pieces)
+    arrival = _lib.Arrival.make(pieces, world, per, rank * per, lead_rows, [e.cuda_event for e in events])
+    error, st = None, None
+    try:
+        st = self_join.join_stream_arriving(eps, table.address, arrival, capacity=capacity, flags=flags,
+                                            pairs_host=pairs.address if pairs is not None else 0,
+                                            host_capacity=pairs.capacity if pairs is not None else 0)
+    except Exception as exc:  # noqa: BLE001 - the table is marked; every rank learns of it below
+        error = exc
+        table.fail()
+    if multi:
+        dist.barrier()
+    found, stored, failed = table.totals()
+    if failed or error is not None:
+        raise BandJoinError(f"the join failed on at least one of {world} ranks"
+                            + (f"; this rank ({rank}): {error}" if error is not None else "")) from error
+    return found, stored, st
 
 
 def _exchange_counts(dist, torch, values: list[int]) -> list[list[int]]:

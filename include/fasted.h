@@ -268,12 +268,44 @@ int fasted_join_stream_shared(fasted_ctx* ctx, double eps, uint64_t capacity, un
                               int32_t* pairs_host, uint64_t host_capacity, fasted_join_stats* stats);
 int fasted_shared_chunks_totals(const void* mem, unsigned long long* found_total, unsigned long long* stored_total,
                                 unsigned long long* failed);
+/* group_rows = 0: chunk k is rows [q_begin + k * chunk_rows, ...).  group_rows > 0 (needs q_begin = 0): the rows
+ * are cut into groups of group_rows rows, every group into chunks from its own first row, and the first lead_chunks
+ * chunks of every group are not handed out by take (see fasted_join_stream_arriving). */
 int fasted_shared_chunks_init_plan(void* mem, size_t bytes, int64_t q_begin, int64_t q_end, int64_t chunk_rows,
-                                   uint64_t* chunks_out);
+                                   int64_t group_rows, int lead_chunks, uint64_t* chunks_out);
+int fasted_shared_chunks_range(const void* mem, uint64_t chunk, int64_t* begin, int64_t* end); /* rows of a chunk */
 int64_t fasted_shared_chunks_take(void* mem);                /* next chunk nobody has taken, -1 when none is left */
 int fasted_shared_chunks_publish(void* mem, uint64_t chunk, uint64_t stored, uint64_t found);
 int fasted_shared_chunks_offset(void* mem, uint64_t chunk, double timeout_ms, uint64_t* offset_out);
 void fasted_shared_chunks_fail(void* mem);
+
+/* The same join started while the dataset is still ARRIVING on the GPUs.  The loader this is made for: G ranks,
+ * rank g holds rows [g * B, (g + 1) * B) on its host (B = group_rows), uploads them in P pieces and all-gathers
+ * every piece as soon as it has landed, so piece p -- rows [g * B + p * B / P, g * B + (p + 1) * B / P) of EVERY
+ * band g -- is complete on every GPU at about (p + 1) / P of the load.  Without this call the join's first launch
+ * waits for the whole load.  With it, every rank first joins a few chunks of its OWN band (the "lead": rows of its
+ * own first piece, resident from the start) against piece 0, then against piece 1, ... each launch behind the
+ * event that says the piece is complete (a launch takes candidate rows of one piece only; row norms are computed
+ * piece by piece in front of it); when the last piece is in, the remaining chunks are dealt out as in
+ * fasted_join_stream_shared.  The result is the same list in the same shared buffer.
+ *   pieces, groups, group_rows: P, G, B; B a multiple of 256 * P, G * B >= n (rows beyond n do not exist).
+ *   own_begin: first row of the calling rank's band (g * B); every band needs exactly one rank that calls.
+ *   lead_rows: for fasted_shared_chunks_init_arriving only: rows of the lead (rounded down to whole chunks, at
+ *              most one piece); 0 = the library's choice.
+ *   events:    P cudaEvent_t handles; events[p] completes when piece p of every band is resident on THIS GPU.
+ *              The join stream waits for them in order (cudaStreamWaitEvent); NULL, or a NULL entry = resident
+ *              already.  They must have been recorded before the call.
+ * fasted_shared_chunks_init_arriving plans the table for this (one rank, before the others are let in). */
+typedef struct fasted_arrival {
+    int pieces, groups;
+    int64_t group_rows, own_begin, lead_rows;
+    void* const* events;
+} fasted_arrival;
+int fasted_shared_chunks_init_arriving(fasted_ctx* ctx, void* mem, size_t bytes, double eps, int ranks,
+                                       const fasted_arrival* arrival, uint64_t* chunks_out);
+int fasted_join_stream_arriving(fasted_ctx* ctx, double eps, uint64_t capacity, unsigned flags, void* shared_mem,
+                                const fasted_arrival* arrival, int32_t* pairs_host, uint64_t host_capacity,
+                                fasted_join_stats* stats);
 
 /* One shard of the symmetric schedule for a self-join split over shard_world GPUs that all hold the
  * dataset: shard r computes the raster bands r, 2G-1-r, 2G+r, ... (G = shard_world) of the upper

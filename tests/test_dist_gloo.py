@@ -301,3 +301,46 @@ def test_chunks_dealt_from_a_shared_table_land_in_order(native_lib, tmp_path):
     assert sum(int(r[1]) for r in res) == -(-100_000 // 256) and min(int(r[1]) for r in res) > 0
     for r in (0, 2):
         assert "gave up" in (tmp_path / f"dealt_fail{r}.txt").read_text()
+
+
+@pytest.mark.parametrize("n_rows,chunk_rows,group_rows,lead", [
+    (100_000, 256, 25_600, 3),   # four bands, the last partly beyond the data
+    (5000, 256, 2560, 2),        # a band that ends inside a chunk
+    (70_000, 4736, 35_840, 1),   # chunks that do not divide the band: its last chunk is shorter
+    (9000, 512, 2560, 0),        # grouped, nothing set aside
+])
+def test_grouped_chunk_table_covers_every_row_once(native_lib, n_rows, chunk_rows, group_rows, lead):
+    # The plan of a join that starts while the matrix arrives: every band (group) is cut into chunks from its
+    # own first row, the first `lead` chunks of every band are kept for the band's own rank, the others are
+    # handed out; chunk ids ascend with the rows, so the prefix of the published counts is a chunk's place.
+    from fasted_b200.dist import SharedChunkTable
+    table = SharedChunkTable(-(-n_rows // 128) + 65)
+    try:
+        chunks = table.init_plan(0, n_rows, chunk_rows, group_rows, lead)
+        groups = -(-n_rows // group_rows)
+        per_group = -(-group_rows // chunk_rows)
+        assert chunks == groups * per_group
+        ranges = [table.chunk_range(k) for k in range(chunks)]
+        covered, prev_end = 0, 0
+        for k, (b, e) in enumerate(ranges):
+            assert prev_end <= b <= e <= n_rows
+            if e > b:
+                assert b == prev_end and b == (k // per_group) * group_rows + (k % per_group) * chunk_rows
+                prev_end = e
+            covered += e - b
+        assert covered == n_rows and prev_end == n_rows
+        handed = []
+        while (k := table.take()) >= 0:
+            handed.append(k)
+        kept = [k for k in range(chunks) if k % per_group < lead]
+        assert sorted(handed + kept) == list(range(chunks)) and handed == sorted(handed)
+        assert table.take() == -1
+        with pytest.raises(Exception):
+            table.chunk_range(chunks)
+        with pytest.raises(Exception):
+            table.init_plan(0, n_rows, chunk_rows, group_rows, per_group + 1)
+        with pytest.raises(Exception):
+            table.init_plan(256, n_rows, chunk_rows, group_rows, 0)   # groups need the whole row range
+    finally:
+        table.close()
+        table.unlink()

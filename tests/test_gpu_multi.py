@@ -48,11 +48,28 @@ def _worker(rank, world, port, n, d, eps, out_dir):
     table = SharedChunkTable.collective(n)
     shared = SharedPairBuffer.collective(fa + 100, register_cuda=True)
     fc, sc, st = dealt_self_join(sj, n, eps, table, shared, capacity=fa + 100)
+    dealt_list = shared.array[:sc].copy()
+    shared.array[:] = -1
     fd, sd, st2 = dealt_self_join(sj, n, eps, table, None, capacity=fa + 100, flags=_lib.JOIN_NO_SORT)
+    # the same join started while the matrix is still arriving: every rank holds its band on the host, uploads
+    # and all-gathers it in two pieces on side streams, and joins its first chunks behind the pieces' events
+    from fasted_b200.dist import band_rows, load_and_join
+    pieces = 2
+    per = band_rows(n, world, 256 * pieces)
+    big = torch.zeros((world * per, d), dtype=torch.float16, device="cuda")
+    host_band = torch.zeros((per, d), dtype=torch.float16).pin_memory()
+    mine = t[rank * per:min(n, (rank + 1) * per)]
+    host_band[:mine.shape[0]].copy_(mine)
+    torch.cuda.synchronize()
+    fe, se, st3 = load_and_join(sj, big, host_band, n, d, eps, table, shared, capacity=fa + 100, pieces=pieces)
+    arriving = shared.array[:se].copy()
+    loaded_ok = bool(torch.equal(big[:n], t))
     if rank == 0:
+        np.save(os.path.join(out_dir, "arriving.npy"), arriving)
+        np.save(os.path.join(out_dir, "arriving_counts.npy"), np.array([fe, se, int(loaded_ok)]))
         np.save(os.path.join(out_dir, "bands.npy"), a)
         np.save(os.path.join(out_dir, "sym.npy"), b)
-        np.save(os.path.join(out_dir, "dealt.npy"), shared.array[:sc].copy())
+        np.save(os.path.join(out_dir, "dealt.npy"), dealt_list)
         np.save(os.path.join(out_dir, "found.npy"), np.array([fa, fb, fc, sc, fd]))
     np.save(os.path.join(out_dir, f"chunks{rank}.npy"), np.array([st.chunks, st2.chunks]))
     dist.barrier()
@@ -77,5 +94,7 @@ def test_two_gpu_sharding_matches_one_gpu(gpu_join, oracle_mod, tmp_path):
     assert np.array_equal(np.load(tmp_path / "sym.npy"), want)
     assert np.array_equal(np.load(tmp_path / "dealt.npy"), want)
     assert list(np.load(tmp_path / "found.npy")) == [len(want)] * 5
+    assert np.array_equal(np.load(tmp_path / "arriving.npy"), want)
+    assert list(np.load(tmp_path / "arriving_counts.npy")) == [len(want), len(want), 1]
     chunks = [np.load(tmp_path / f"chunks{r}.npy") for r in range(2)]
     assert chunks[0][0] + chunks[1][0] == chunks[0][1] + chunks[1][1] >= 20  # every chunk taken exactly once, both times

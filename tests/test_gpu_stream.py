@@ -205,3 +205,104 @@ def test_chunks_shared_by_several_contexts_give_the_single_list(gpu_join, oracle
         table.close()
         pairs.unlink()
         table.unlink()
+
+
+@pytest.mark.parametrize("n,d,eps,ranks,pieces,band_rows,stationary,staged", [
+    (20_000, 128, 0.30, 2, 2, 10_240, 0, True),    # two bands, two pieces, the data lands behind events
+    (20_000, 128, 0.30, 2, 2, 10_240, 1, True),    # query-stationary kernel (chunks of 37 tile rows: one lead chunk or none)
+    (9000, 1024, 1.04, 4, 2, 2560, 0, False),      # last band partly beyond n; dataset resident already (no events)
+    (30_000, 64, 0.18, 3, 1, 10_240, 0, True),     # one piece: the lead runs once, against everything
+])
+def test_join_started_while_the_matrix_arrives(gpu_join, oracle_mod, n, d, eps, ranks, pieces, band_rows, stationary, staged):
+    # fasted_join_stream_arriving with `ranks` contexts on the GPUs present.  The matrix is zero when the calls
+    # start and is filled piece by piece on a side stream (piece p = rows [g*B + p*B/P, ...) of every band g),
+    # one event per piece: a launch that read candidates before their event would see zeros, i.e. other pairs.
+    import threading
+    import torch
+    from fasted_b200 import SelfJoin, _lib
+    from fasted_b200.dist import SharedChunkTable, SharedPairBuffer
+    pts = _points(oracle_mod, n, d, 5 * n + d)
+    gpu_join.set_points(pts)
+    st0 = gpu_join.join(eps)
+    want = gpu_join.pairs()
+    assert st0.pairs_found == st0.pairs_stored == len(want) > n
+    assert ranks * band_rows >= n and band_rows % (256 * pieces) == 0
+    devs = torch.cuda.device_count()
+    host = torch.zeros((ranks * band_rows, d), dtype=torch.float16).pin_memory()
+    host[:n] = torch.from_numpy(pts.view(np.float16))
+    ctxs, bufs, sides = [], [], []
+    table = SharedChunkTable(-(-n // 128) + 65)
+    pairs = SharedPairBuffer(len(want) + 64, register_cuda=True)
+    try:
+        for i in range(ranks):
+            dev = torch.device("cuda", i % devs)
+            c = SelfJoin(i % devs)
+            buf = torch.zeros((ranks * band_rows, d), dtype=torch.float16, device=dev)
+            c.set_points_device(buf.data_ptr(), n, d, d, keepalive=buf)
+            c.set_option("band_tiles", 2)
+            c.set_option("query_stationary", stationary)
+            ctxs.append(c)
+            bufs.append(buf)
+            sides.append(torch.cuda.Stream(device=dev))
+        for lead_rows in (0, 512):
+            pairs.array[:] = -1
+            plan = _lib.Arrival.make(pieces, ranks, band_rows, 0, lead_rows)
+            chunks = table.init_arriving(ctxs[0], eps, ranks, plan)
+            arrivals = []
+            step = band_rows // pieces
+            for i in range(ranks):
+                events = None
+                if staged:
+                    bufs[i].zero_()
+                    torch.cuda.synchronize(bufs[i].device)
+                    events = []
+                    with torch.cuda.stream(sides[i]):
+                        for p in range(pieces):
+                            torch.cuda._sleep(8_000_000)  # a few milliseconds between the pieces
+                            for g in range(ranks):
+                                a = g * band_rows + p * step
+                                bufs[i][a:a + step].copy_(host[a:a + step], non_blocking=True)
+                            ev = torch.cuda.Event()
+                            ev.record(sides[i])
+                            events.append(ev)
+                    arrivals.append((_lib.Arrival.make(pieces, ranks, band_rows, i * band_rows, lead_rows,
+                                                       [e.cuda_event for e in events]), events))
+                else:
+                    bufs[i].copy_(host)
+                    torch.cuda.synchronize(bufs[i].device)
+                    arrivals.append((_lib.Arrival.make(pieces, ranks, band_rows, i * band_rows, lead_rows), None))
+            stats, errors = [None] * ranks, []
+
+            def work(i):
+                try:
+                    stats[i] = ctxs[i].join_stream_arriving(eps, table.address, arrivals[i][0], capacity=len(want) + 1000,
+                                                            pairs_host=pairs.address, host_capacity=pairs.capacity)
+                except Exception as exc:  # noqa: BLE001
+                    errors.append(exc)
+
+            threads = [threading.Thread(target=work, args=(i,)) for i in range(ranks)]
+            for t in threads:
+                t.start()
+            for t in threads:
+                t.join()
+            assert not errors, errors
+            found, stored, failed = table.totals()
+            assert (found, stored, failed) == (len(want), len(want), 0)
+            assert sum(s.pairs_found for s in stats) == len(want)
+            # every band's first chunks were joined by its own rank, as one sequence
+            lead_ids = [k for k in range(chunks) if table.chunk_range(k)[0] % band_rows < 512 and lead_rows == 512]
+            if lead_rows == 512:
+                assert sum(s.chunks for s in stats) <= chunks - len(lead_ids) + ranks
+            assert np.array_equal(pairs.array[:len(want)], want) and (pairs.array[len(want):] == -1).all()
+            # a table with lead chunks cannot be joined without the arrival description
+            if lead_rows == 512 and not stationary:
+                table.init_arriving(ctxs[0], eps, ranks, plan)
+                with pytest.raises(Exception, match="lead chunks"):
+                    ctxs[0].join_stream_shared(eps, table.address, capacity=len(want) + 1000)
+    finally:
+        for c in ctxs:
+            c.close()
+        pairs.close()
+        table.close()
+        pairs.unlink()
+        table.unlink()
