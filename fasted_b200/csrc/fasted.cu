@@ -119,6 +119,7 @@ struct fasted_ctx {
     unsigned long long* chunk_end_host = nullptr;  // pinned: the found counter after each chunk
     size_t chunk_end_cap = 0;
     int stream_chunk_bands = 0;                    // option: raster bands per chunk (0 = automatic)
+    int stream_sort_batch = 16;                    // option: chunks whose records one sort may take together
     int query_stationary = -1;                     // option: -1 automatic, 0 never, 1 whenever the rows are short enough
     int use_pdl = 1;                               // option: let the join start while the norm kernel still runs
 
@@ -521,6 +522,9 @@ int fasted_set_option(fasted_ctx* c, const char* name, int64_t value) {
     } else if (!strcmp(name, "stream_key32")) {
         if (value != 0 && value != 1) return fail(FASTED_EINVAL, "stream_key32 must be 0 or 1");
         c->stream_key32 = static_cast<int>(value);
+    } else if (!strcmp(name, "stream_sort_batch")) {
+        if (value < 1 || value > 1024) return fail(FASTED_EINVAL, "stream_sort_batch must be 1..1024");
+        c->stream_sort_batch = static_cast<int>(value);
     } else if (!strcmp(name, "stream_chunk_bands")) {
         if (value < 0 || value > (1 << 20)) return fail(FASTED_EINVAL, "stream_chunk_bands out of range");
         c->stream_chunk_bands = static_cast<int>(value);
@@ -1395,11 +1399,21 @@ static int join_stream_core(fasted_ctx* c, double eps, int64_t q_begin, int64_t 
     }
     const int64_t max_rows = std::max<int64_t>(chunk_rows, lead_end - lead_begin);
     const int64_t rows32_all = key_shift < 32 ? (int64_t(1) << (32 - key_shift)) : 0;
-    const bool key32 = c->stream_key32 != 0 && cp.fits32 && max_rows <= rows32_all;  // one record width per call
+    // Two ways to keep the sorts cheap.  Dense output (the last join on this dataset stored 128 records per row
+    // or more): one sort per chunk over 32-bit chunk-relative records, half the bytes.  Otherwise a chunk holds so
+    // few records that its sort is all launch overhead (and each sort drains the join stream once): records
+    // carry absolute rows, and one sort takes the records of up to stream_sort_batch consecutive chunks of this
+    // rank, which ascend with the rows, so every chunk's sorted run comes out where its unsorted records were.
+    const bool fits_key32 = c->stream_key32 != 0 && cp.fits32 && max_rows <= rows32_all;
+    const bool dense = c->density_hint >= 128.0 && c->hint_n == c->n && c->hint_d == c->d;
+    const size_t batch_max = (c->stream_sort_batch > 1 && !(dense && fits_key32)) ? static_cast<size_t>(c->stream_sort_batch) : 1;
+    const bool key32 = fits_key32 && batch_max == 1;  // one record width per call
+    constexpr uint64_t kBatchRecords = 2u << 20;      // a batch is closed early once it holds this many records
     rc = ensure_stream_pipeline(c, chunks + 1);
     if (rc) return rc;
     const int sort_bits = std::min(key32 ? 32 : 64,
-                                   key_shift + bits_of(static_cast<uint64_t>(std::max<int64_t>(max_rows - 1, 1))));
+                                   key_shift + bits_of(static_cast<uint64_t>(std::max<int64_t>(
+                                                   (batch_max > 1 ? static_cast<int64_t>(c->n) : max_rows) - 1, 1))));
     // 32-bit records: both halves of the sort's double buffer live in `keys` (capacity 64-bit words hold
     // 2 x capacity 32-bit ones), the unpacked (query, candidate) records go to `keys_alt`.
     uint32_t* const ping32 = reinterpret_cast<uint32_t*>(c->keys);
@@ -1454,6 +1468,7 @@ static int join_stream_core(fasted_ctx* c, double eps, int64_t q_begin, int64_t 
     struct Entry {
         size_t id;
         int64_t begin, end;
+        int64_t qbase;  // the row its records count from
     };
     std::vector<Entry> ids;
     bool has_lead = false;  // ids[0] is this rank's lead
@@ -1485,14 +1500,15 @@ static int join_stream_core(fasted_ctx* c, double eps, int64_t q_begin, int64_t 
         JoinPlan pl;
         int r = plan_join(c, eps, b, e, capacity, flags & ~FASTED_JOIN_NO_SORT, 0, 1, &pl);
         if (r) return r;
+        const int64_t qbase = batch_max > 1 ? 0 : b;
         pl.p.key_shift = key_shift;
-        pl.p.key_qbase = static_cast<int>(b);
+        pl.p.key_qbase = static_cast<int>(qbase);
         pl.p.key32 = key32 ? 1 : 0;
         r = launch_join(c, pl);
         if (r) return r;
         r = snapshot(ids.size());
         if (r) return r;
-        ids.push_back(Entry{id, b, e});
+        ids.push_back(Entry{id, b, e, qbase});
         return FASTED_OK;
     };
 
@@ -1533,7 +1549,7 @@ static int join_stream_core(fasted_ctx* c, double eps, int64_t q_begin, int64_t 
         if (lead_end > lead_begin) {
             rc = snapshot(0);
             if (rc) return rc;
-            ids.push_back(Entry{static_cast<size_t>(lead_id), lead_begin, lead_end});
+            ids.push_back(Entry{static_cast<size_t>(lead_id), lead_begin, lead_end, lead_begin});
             has_lead = true;
         }
     }
@@ -1589,7 +1605,8 @@ static int join_stream_core(fasted_ctx* c, double eps, int64_t q_begin, int64_t 
         size_t j = 0;
         bool copy_enqueued = false;
         bool lead = false;
-    } pend, lead_pend;
+    } lead_pend;
+    std::vector<Pending> pend, now;  // sorted runs to deliver: of the batch before, of the batch closed just now
     auto deliver = [&](const Pending& pd) -> int {
         if (!pd.any) return FASTED_OK;
         const uint64_t a = pd.a, m = pd.b - pd.a;
@@ -1652,87 +1669,122 @@ static int join_stream_core(fasted_ctx* c, double eps, int64_t q_begin, int64_t 
 
     uint64_t prev_end = 0;
     size_t sorts = 0;
+    size_t batch_first = 0;  // first entry of the open batch
     for (size_t j = 0; j < ids.size(); ++j) {
         CU_TRY(cudaEventSynchronize(c->chunk_ev[j]));
         const uint64_t end_j = c->chunk_end_host[j];
         const uint64_t a = std::min<uint64_t>(prev_end, capacity), b = std::min<uint64_t>(end_j, capacity);
         if (shared) fasted_shared_chunks_publish(shared, ids[j].id, b - a, end_j - prev_end);  // later chunks can be placed
         prev_end = end_j;
-        Pending now;
-        if (b > a && abort_rc == FASTED_OK && !count_only) {
-            const uint64_t m = b - a;
-            // sort(j) and its unpacking, on the join stream, behind the launch that is running now
-            CU_TRY(cudaEventRecord(c->sort_t0[sorts], c->stream));
-            cub::DoubleBuffer<float> vb(want_dist ? c->dist + a : nullptr, want_dist ? c->dist_alt + a : nullptr);
-            size_t need = c->sort_tmp_bytes;
-            if (key32) {
-                cub::DoubleBuffer<uint32_t> kb(ping32 + a, pong32 + a);
-                if (m > 1) {
-                    if (want_dist)
-                        CU_TRY(cub::DeviceRadixSort::SortPairs(c->sort_tmp, need, kb, vb, m, 0, sort_bits, c->stream));
-                    else
-                        CU_TRY(cub::DeviceRadixSort::SortKeys(c->sort_tmp, need, kb, m, 0, sort_bits, c->stream));
+        c->chunk_end_host[j] = b;  // (from here on: the entry's last slot, clipped)
+        now.clear();
+        // The batch [batch_first, j] is closed by its size, by the lead (a batch of its own: its rows do not
+        // ascend with the chunks that follow) or by the end of this rank's entries.
+        const uint64_t batch_a = batch_first == 0 ? 0 : c->chunk_end_host[batch_first - 1];
+        const bool close = j + 1 - batch_first >= batch_max || b - batch_a >= kBatchRecords || (has_lead && j == 0) ||
+                           j + 1 == ids.size();
+        if (close) {
+            if (b > batch_a && abort_rc == FASTED_OK && !count_only) {
+                const uint64_t m = b - batch_a;
+                const int qbase = static_cast<int>(ids[batch_first].qbase);  // (the same for every entry of a batch)
+                // the sort and its unpacking, on the join stream, behind the launch that is running now
+                CU_TRY(cudaEventRecord(c->sort_t0[sorts], c->stream));
+                cub::DoubleBuffer<float> vb(want_dist ? c->dist + batch_a : nullptr, want_dist ? c->dist_alt + batch_a : nullptr);
+                size_t need = c->sort_tmp_bytes;
+                if (key32) {
+                    cub::DoubleBuffer<uint32_t> kb(ping32 + batch_a, pong32 + batch_a);
+                    if (m > 1) {
+                        if (want_dist)
+                            CU_TRY(cub::DeviceRadixSort::SortPairs(c->sort_tmp, need, kb, vb, m, 0, sort_bits, c->stream));
+                        else
+                            CU_TRY(cub::DeviceRadixSort::SortKeys(c->sort_tmp, need, kb, m, 0, sort_bits, c->stream));
+                    }
+                    fasted::unpack_pairs32_kernel<<<unpack_blocks(c, m), 256, 0, c->stream>>>(
+                        kb.Current(), reinterpret_cast<int2*>(c->keys_alt + batch_a), m, key_shift, qbase);
+                } else {
+                    cub::DoubleBuffer<unsigned long long> kb(c->keys + batch_a, c->keys_alt + batch_a);
+                    if (m > 1) {
+                        if (want_dist)
+                            CU_TRY(cub::DeviceRadixSort::SortPairs(c->sort_tmp, need, kb, vb, m, 0, sort_bits, c->stream));
+                        else
+                            CU_TRY(cub::DeviceRadixSort::SortKeys(c->sort_tmp, need, kb, m, 0, sort_bits, c->stream));
+                    }
+                    fasted::unpack_pairs_kernel<<<unpack_blocks(c, m), 256, 0, c->stream>>>(
+                        kb.Current(), reinterpret_cast<int2*>(c->keys_alt + batch_a), m, key_shift, qbase);
                 }
-                fasted::unpack_pairs32_kernel<<<unpack_blocks(c, m), 256, 0, c->stream>>>(
-                    kb.Current(), reinterpret_cast<int2*>(c->keys_alt + a), m, key_shift, static_cast<int>(ids[j].begin));
-            } else {
-                cub::DoubleBuffer<unsigned long long> kb(c->keys + a, c->keys_alt + a);
-                if (m > 1) {
-                    if (want_dist)
-                        CU_TRY(cub::DeviceRadixSort::SortPairs(c->sort_tmp, need, kb, vb, m, 0, sort_bits, c->stream));
-                    else
-                        CU_TRY(cub::DeviceRadixSort::SortKeys(c->sort_tmp, need, kb, m, 0, sort_bits, c->stream));
+                CU_TRY(cudaGetLastError());
+                if (want_dist && vb.Current() != c->dist_alt + batch_a)
+                    CU_TRY(cudaMemcpyAsync(c->dist_alt + batch_a, vb.Current(), m * sizeof(float), cudaMemcpyDeviceToDevice,
+                                           c->stream));
+                CU_TRY(cudaEventRecord(c->sort_t1[sorts], c->stream));
+                CU_TRY(cudaEventRecord(c->sorted_ev[j], c->stream));
+                ++sorts;
+                if (shared) {
+                    // every chunk has its own place in the shared list
+                    uint64_t ea = batch_a;
+                    for (size_t i = batch_first; i <= j; ++i) {
+                        const uint64_t eb = c->chunk_end_host[i];
+                        if (eb > ea) {
+                            Pending pd;
+                            pd.any = true;
+                            pd.a = ea;
+                            pd.b = eb;
+                            pd.j = i;
+                            now.push_back(pd);
+                        }
+                        ea = eb;
+                    }
+                } else {
+                    Pending pd;  // one GPU: the batch is one run of the list
+                    pd.any = true;
+                    pd.a = batch_a;
+                    pd.b = b;
+                    pd.j = j;
+                    now.push_back(pd);
                 }
-                fasted::unpack_pairs_kernel<<<unpack_blocks(c, m), 256, 0, c->stream>>>(
-                    kb.Current(), reinterpret_cast<int2*>(c->keys_alt + a), m, key_shift, static_cast<int>(ids[j].begin));
             }
-            CU_TRY(cudaGetLastError());
-            if (want_dist && vb.Current() != c->dist_alt + a)
-                CU_TRY(cudaMemcpyAsync(c->dist_alt + a, vb.Current(), m * sizeof(float), cudaMemcpyDeviceToDevice,
-                                       c->stream));
-            CU_TRY(cudaEventRecord(c->sort_t1[sorts], c->stream));
-            CU_TRY(cudaEventRecord(c->sorted_ev[j], c->stream));
-            ++sorts;
-            now.any = true;
-            now.a = a;
-            now.b = b;
-            now.j = j;
+            batch_first = j + 1;
         }
         // keep the join stream fed before anything else
         if (abort_rc == FASTED_OK) {
             rc = enqueue_next_join();
             if (rc) return give_up(rc);
         }
-        if (now.any) {
+        if (!now.empty()) {
             CU_TRY(cudaStreamWaitEvent(c->copy_stream, c->sorted_ev[j], 0));
             if (!shared && pairs_host && host_pinned) {
-                // one GPU: the chunk's place on the host is its first slot, known already
-                const uint64_t hb = std::min<uint64_t>(now.b, host_capacity);
-                if (hb > now.a) {
-                    CU_TRY(cudaMemcpyAsync(pairs_host + 2 * now.a, reinterpret_cast<const int2*>(c->keys_alt) + now.a,
-                                           (hb - now.a) * 8, cudaMemcpyDeviceToHost, c->copy_stream));
+                // one GPU: the run's place on the host is its first slot, known already
+                Pending& run = now[0];
+                const uint64_t hb = std::min<uint64_t>(run.b, host_capacity);
+                if (hb > run.a) {
+                    CU_TRY(cudaMemcpyAsync(pairs_host + 2 * run.a, reinterpret_cast<const int2*>(c->keys_alt) + run.a,
+                                           (hb - run.a) * 8, cudaMemcpyDeviceToHost, c->copy_stream));
                     if (dist2_host)
-                        CU_TRY(cudaMemcpyAsync(dist2_host + now.a, c->dist_alt + now.a, (hb - now.a) * 4,
+                        CU_TRY(cudaMemcpyAsync(dist2_host + run.a, c->dist_alt + run.a, (hb - run.a) * 4,
                                                cudaMemcpyDeviceToHost, c->copy_stream));
                 }
                 CU_TRY(cudaEventRecord(c->copied_ev[j], c->copy_stream));
-                now.copy_enqueued = true;
+                run.copy_enqueued = true;
             }
         }
-        // the previous chunk's records: on the host by now, or nearly
-        if (abort_rc == FASTED_OK) {
-            abort_rc = deliver(pend);
+        // the records of the batch before: on the host by now, or nearly
+        for (const Pending& pd : pend) {
+            if (abort_rc != FASTED_OK) break;
+            abort_rc = deliver(pd);
             if (abort_rc != FASTED_OK) give_up(abort_rc);
         }
+        pend.clear();
         if (has_lead && j == 0) {
             // The lead's place in the list is known when every chunk of the bands before this rank's has been
             // counted, which is late in the join: its records wait on the device until then, and nothing waits
             // for them (a rank that held back its own later chunks for it would hold up everybody).
-            now.lead = true;
-            lead_pend = now;
-            now = Pending{};
+            if (!now.empty()) {
+                lead_pend = now[0];
+                lead_pend.lead = true;
+            }
+            now.clear();
         }
-        pend = now;
+        pend.swap(now);
         if (lead_pend.any && abort_rc == FASTED_OK && advance(scan_lead, ids[0].id)) {
             abort_rc = deliver(lead_pend);
             if (abort_rc != FASTED_OK) give_up(abort_rc);
@@ -1743,8 +1795,9 @@ static int join_stream_core(fasted_ctx* c, double eps, int64_t q_begin, int64_t 
     CU_TRY(cudaEventRecord(c->ev[2], c->stream));
     unsigned long long* h = c->chunk_end_host + chunks;
     CU_TRY(cudaMemcpyAsync(h, c->counters, kCounterWords * sizeof(unsigned long long), cudaMemcpyDeviceToHost, c->stream));
-    if (abort_rc == FASTED_OK) {
-        abort_rc = deliver(pend);
+    for (const Pending& pd : pend) {
+        if (abort_rc != FASTED_OK) break;
+        abort_rc = deliver(pd);
         if (abort_rc != FASTED_OK) give_up(abort_rc);
     }
     if (abort_rc == FASTED_OK && lead_pend.any) {  // (every chunk this rank took is published: waiting is safe now)

@@ -430,7 +430,9 @@ int fasted_selftest_wait_timeout(fasted_ctx* ctx, double limit_ms, unsigned long
  * "query_stationary" (-1 = automatic: for rows of at most 512 values a CTA keeps its 128 query rows in
  * shared memory and streams candidate rows only; 0 = never, 1 = the same rule as automatic; same results
  * bit for bit), "stream_chunk_bands" (raster bands per chunk of fasted_join_stream, 0 = automatic), "stream_key32" (1 = default:
- * 32-bit chunk-relative records in fasted_join_stream where they fit), "dependent_launch" (1 = default: a small join is
+ * 32-bit chunk-relative records in fasted_join_stream where they fit and the output is dense), "stream_sort_batch" (16 =
+ * default: where the output is sparse, one sort takes the records of up to this many consecutive chunks; 1 = one sort
+ * per chunk), "dependent_launch" (1 = default: a small join is
  * launched as a programmatic dependent of the row-norm kernel and overlaps it). */
 int fasted_set_option(fasted_ctx* ctx, const char* name, int64_t value);
 
