@@ -229,7 +229,7 @@ def main() -> None:
                          "join's first launch waits for the whole load")
     ap.add_argument("--lead-rows", type=int, default=0,
                     help="query rows per rank joined while the matrix arrives (0 = the library's choice)")
-    ap.add_argument("--loader-pieces", type=int, default=4,
+    ap.add_argument("--loader-pieces", type=int, default=16,
                     help="N > 1, end-to-end leg: pieces in which a rank's band is uploaded and all-gathered (1 = upload, "
                          "then one all-gather)")
     ap.add_argument("--no-numa", action="store_true", help="N > 1: do not pin the rank to its GPU's CPU cores")

@@ -212,6 +212,8 @@ def test_chunks_shared_by_several_contexts_give_the_single_list(gpu_join, oracle
     (20_000, 128, 0.30, 2, 2, 10_240, 1, True),    # query-stationary kernel (chunks of 37 tile rows: one lead chunk or none)
     (9000, 1024, 1.04, 4, 2, 2560, 0, False),      # last band partly beyond n; dataset resident already (no events)
     (30_000, 64, 0.18, 3, 1, 10_240, 0, True),     # one piece: the lead runs once, against everything
+    (20_000, 128, 0.32, 2, 2, 10_240, 0, True),    # ~350 neighbours per point: the second call knows that the output
+                                                   # is dense and keeps 32-bit records and one sort per chunk
 ])
 def test_join_started_while_the_matrix_arrives(gpu_join, oracle_mod, n, d, eps, ranks, pieces, band_rows, stationary, staged):
     # fasted_join_stream_arriving with `ranks` contexts on the GPUs present.  The matrix is zero when the calls
@@ -223,7 +225,7 @@ def test_join_started_while_the_matrix_arrives(gpu_join, oracle_mod, n, d, eps, 
     from fasted_b200.dist import SharedChunkTable, SharedPairBuffer
     pts = _points(oracle_mod, n, d, 5 * n + d)
     gpu_join.set_points(pts)
-    st0 = gpu_join.join(eps)
+    st0 = gpu_join.join(eps, capacity=n * 512)
     want = gpu_join.pairs()
     assert st0.pairs_found == st0.pairs_stored == len(want) > n
     assert ranks * band_rows >= n and band_rows % (256 * pieces) == 0
