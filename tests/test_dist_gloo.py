@@ -344,3 +344,62 @@ def test_grouped_chunk_table_covers_every_row_once(native_lib, n_rows, chunk_row
     finally:
         table.close()
         table.unlink()
+
+
+def _dealer_with_leads(rank, world, port, out_dir):
+    # The protocol of the join that starts while the matrix arrives, on the table's primitives: every rank first
+    # "joins" the lead chunks of its own band (counted under the band's first id), then takes chunks like any
+    # dealer.  A chunk's place is the sum of the counts before it -- and the lead of band r lies behind every
+    # chunk of the bands before it, which are joined later: its records must wait for their place without
+    # holding up the rank's own later chunks (a rank that asked for the lead's place first would wait for itself).
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from fasted_b200.dist import SharedChunkTable, SharedPairBuffer
+    group_rows, chunk_rows, lead = 10_240, 256, 3
+    n_rows = world * group_rows - 1000
+    per_group = group_rows // chunk_rows
+    table = SharedChunkTable.collective(n_rows)
+    pairs = SharedPairBuffer.collective(600_000)
+    if rank == 0:
+        assert table.init_plan(0, n_rows, chunk_rows, group_rows, lead) == world * per_group
+    dist.barrier()
+    rows_of = lambda k: (lambda b, e: e - b)(*table.chunk_range(k))
+    count_of = lambda k: rows_of(k) // 64 + (k * 7919) % 5 if rows_of(k) else 0
+    records = lambda k, m: np.stack([np.full(m, k), np.arange(m)], 1)
+    lead_id = rank * per_group
+    lead_count = sum(count_of(lead_id + i) for i in range(lead))
+    for i in range(1, lead):
+        table.publish(lead_id + i, 0, 0)
+    table.publish(lead_id, lead_count, lead_count)
+    taken = []
+    while True:
+        k = table.take()
+        if k < 0:
+            break
+        assert k % per_group >= lead
+        taken.append(k)
+        table.publish(k, count_of(k), count_of(k))
+        off = table.offset(k)                         # needs the chunks before k only: never this rank's lead
+        pairs.array[off:off + count_of(k)] = records(k, count_of(k))
+    off = table.offset(lead_id)                       # everything this rank took is published: waiting is safe
+    pairs.array[off:off + lead_count] = np.concatenate([records(lead_id + i, count_of(lead_id + i)) for i in range(lead)])
+    dist.barrier()
+    found, stored, failed = table.totals()
+    chunks = world * per_group
+    want = np.concatenate([records(k, count_of(k)) for k in range(chunks)])
+    ok = stored == found == len(want) and failed == 0 and np.array_equal(pairs.array[:stored], want)
+    np.save(os.path.join(out_dir, f"lead{rank}.npy"), np.array([int(ok), len(taken)]))
+    dist.barrier()
+    pairs.close()
+    table.close()
+    dist.destroy_process_group()
+
+
+def test_lead_chunks_find_their_place_without_holding_up_the_dealing(native_lib, tmp_path):
+    world = 3
+    mp.spawn(_dealer_with_leads, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    res = [np.load(tmp_path / f"lead{r}.npy") for r in range(world)]
+    assert all(int(r[0]) == 1 for r in res)
+    assert sum(int(r[1]) for r in res) == world * (10_240 // 256 - 3)
