@@ -229,9 +229,11 @@ def main() -> None:
                          "join's first launch waits for the whole load")
     ap.add_argument("--lead-rows", type=int, default=0,
                     help="query rows per rank joined while the matrix arrives (0 = the library's choice)")
-    ap.add_argument("--loader-pieces", type=int, default=16,
+    ap.add_argument("--loader-pieces", type=int, default=0,
                     help="N > 1, end-to-end leg: pieces in which a rank's band is uploaded and all-gathered (1 = upload, "
-                         "then one all-gather)")
+                         "then one all-gather; 0 = 16 up to 4 GPUs, 8 beyond: the rows a rank joins while the matrix "
+                         "arrives lie in the first piece of its band, and with more GPUs the load is a larger part of "
+                         "the band's work, so the first piece has to be a larger part of the band)")
     ap.add_argument("--no-numa", action="store_true", help="N > 1: do not pin the rank to its GPU's CPU cores")
     ap.add_argument("--no-balance", action="store_true", help="N > 1: keep equal bands (no sizing by measured rate)")
     ap.add_argument("--option", action="append", default=[], help="name=value for fasted_set_option (tuning runs)")
@@ -266,6 +268,8 @@ def main() -> None:
         return equal_band_rows(n_rows, ranks, 256 * max(1, args.loader_pieces))
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.loader_pieces <= 0:
+        args.loader_pieces = 16 if world <= 4 else 8
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if world != args.gpus and world > 1:
@@ -497,6 +501,7 @@ def main() -> None:
                "sort_ms": float(st.sort_ms), "mode": args.e2e_mode if world == 1 else "stream",
                "join_launches_per_step": e2e_chunks,
                "join_behind_load": bool(world > 1 and dealt and args.join_behind_load),
+               "loader_pieces": args.loader_pieces if world > 1 else None,
                "api": "fasted_set_points_host_f16 + fasted_join_stream (pinned host buffers; sort and device-to-host "
                       "copy pipelined behind the join)"
                if world == 1 else ("per rank: pinned host band -> its GPU and NCCL all-gather piece by piece on side "
