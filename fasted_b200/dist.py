@@ -8,6 +8,10 @@ in rank order gives the global row-major order the reference produces on one GPU
 (source/pair.cuh:39-45 of the reference).  No other collective is on the data path; the
 per-rank pair counts are exchanged with one all-gather of three integers, and the bands' lists
 meet in one shared host buffer (SharedPairBuffer), each at the offset its predecessors' counts give.
+
+Three ways to split the rows: fixed bands (sharded_self_join), chunks of raster bands taken on demand from
+a table in shared host memory so that a faster GPU takes more (dealt_self_join), and the same with the join
+started while the matrix is still being uploaded and all-gathered piece by piece (load_and_join).
 """
 from __future__ import annotations
 

@@ -250,7 +250,8 @@ int fasted_join_stream(fasted_ctx* ctx, double eps, int64_t q_begin, int64_t q_e
  *
  * The table lives in memory that every rank maps (e.g. a shared file mapping) and is the only thing
  * the ranks exchange during the join: no collective.  One rank sizes it with
- * fasted_shared_chunks_bytes(max_chunks) -- q rows / 128 is always enough for max_chunks -- and fills
+ * fasted_shared_chunks_bytes(max_chunks) -- q rows / 128 + 1, plus one per band for a plan by bands (below), is
+ * always enough for max_chunks -- and fills
  * it with fasted_shared_chunks_init (plan from that rank's context: identical on all ranks, which hold
  * the same dataset and options) BEFORE the others are let in (a barrier); then every rank calls
  * fasted_join_stream_shared with its own context and the SAME host buffer (pairs_host = the buffer's
